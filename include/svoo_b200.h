@@ -1,0 +1,127 @@
+/*
+ * svoo_b200 -- C ABI of the B200 (sm_100a) implementation of SVOO's online
+ * sparse-attention path: QK co-clustering, cluster-order permute / inverse
+ * permute, cluster-block map, block-sparse attention.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name ends in `_host`.
+ *   - Token tensors are bf16, row-major [BH, N, 128] (BH = batch*heads flattened,
+ *     head dim D must be 128).  Labels, indices, sizes, offsets are int32.
+ *   - The library allocates nothing: outputs and the workspace are caller-owned.
+ *     `stream` is a cudaStream_t passed as void*; all work is enqueued on it and
+ *     no entry point synchronises with the host.
+ *   - Return value: 0 on success; < 0 an SVOO_ERR_* argument error detected on the
+ *     host before anything is launched; > 0 a cudaError_t from a launch.
+ *
+ * Each entry point names the reference interface it replaces (paths inside the
+ * SVOO project).
+ */
+#ifndef SVOO_B200_H
+#define SVOO_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SVOO_B200_VERSION 100
+
+enum {
+  SVOO_OK = 0,
+  SVOO_ERR_NULL = -1,        /* a required pointer is null                       */
+  SVOO_ERR_SHAPE = -2,       /* a size is out of the supported range             */
+  SVOO_ERR_HEAD_DIM = -3,    /* D != 128                                         */
+  SVOO_ERR_WORKSPACE = -4,   /* workspace too small (see *_workspace_bytes)      */
+  SVOO_ERR_ALIGN = -5,       /* a tensor pointer is not 16-byte aligned          */
+  SVOO_ERR_CLUSTERS = -6     /* cluster count above SVOO_MAX_CLUSTERS            */
+};
+
+#define SVOO_MAX_CLUSTERS 1024   /* per side; the reference ships QC=256, KC=1024 */
+#define SVOO_MAX_HEADS 256       /* BH limit of svoo_b200_block_map              */
+
+int svoo_b200_version(void);
+const char* svoo_b200_error_string(int code);
+
+/* Bytes of scratch that svoo_b200_cocluster / svoo_b200_sort_labels /
+ * svoo_b200_sparse_attn need for these sizes (one value covers all three). */
+int svoo_b200_workspace_bytes(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* bytes_out);
+
+/* Replaces co_cluster_tokens (svoo/co_clustering.py:2402-2451) together with the
+ * kernels it drives (profile norm :2088-2144, fused assign :2148-2255, centroid
+ * update :181-303, l2norm svoo/kernels/triton/l2norm.py:9-80).  The random initial
+ * centroid token indices, which the reference draws inside the call, are inputs.
+ * Also returns the stable cluster-order permutation of each side (sorted_idx,
+ * offsets[BH,K+1]), which the reference recomputes with torch.argsort in
+ * svoo/kernels/triton/permute.py:90.  Centroids are bf16 [BH,K,128]. */
+int svoo_b200_cocluster(const void* q, const void* k,
+                        const int32_t* q_init_idx, const int32_t* k_init_idx,
+                        int64_t BH, int64_t N, int64_t D, int64_t QC, int64_t KC, int32_t iters,
+                        int32_t* qlabels, int32_t* klabels,
+                        void* qcentroids, void* kcentroids,
+                        int32_t* qsizes, int32_t* ksizes,
+                        int32_t* q_sorted_idx, int32_t* q_offsets,
+                        int32_t* k_sorted_idx, int32_t* k_offsets,
+                        void* workspace, int64_t workspace_bytes, void* stream);
+
+/* One assignment step of the co-clustering: labels[n] = argmax_j <profile(x_n), P_j>
+ * for tokens x against the profile-forming centroids `form` [BH,K,128] and the
+ * centroids being assigned `own` [BH,J,128] (svoo/co_clustering.py:2427-2433). */
+int svoo_b200_cocluster_assign(const void* x, const void* form_centroids, const void* own_centroids,
+                               int64_t BH, int64_t N, int64_t D, int64_t K, int64_t J,
+                               int32_t* labels, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Stable counting sort of labels in [0,K): sorted_idx[BH,N] and offsets[BH,K+1]
+ * (replaces torch.argsort in svoo/kernels/triton/permute.py:90 and torch.sort in
+ * svoo/co_clustering.py:274). */
+int svoo_b200_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int64_t K,
+                          int32_t* sorted_idx, int32_t* offsets,
+                          void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Mean of the tokens of each cluster (fp32 sums in a fixed order, bf16 result),
+ * empty clusters keep `old_centroids` (svoo/co_clustering.py:253-303).  In place
+ * update is allowed (new_centroids == old_centroids). */
+int svoo_b200_centroid_update(const void* x, const int32_t* sorted_idx, const int32_t* offsets,
+                              const void* old_centroids, int64_t BH, int64_t N, int64_t D, int64_t K,
+                              void* new_centroids, int32_t* sizes,
+                              void* workspace, int64_t workspace_bytes, void* stream);
+
+/* y[bh,s,:] = x[bh,idx[bh,s],:]  (svoo/kernels/triton/permute.py:10-35,68-102). */
+int svoo_b200_permute(const void* x, const int32_t* sorted_idx, int64_t BH, int64_t N, int64_t D,
+                      void* y, void* stream);
+
+/* y[bh,idx[bh,s],:] = x[bh,s,:]  (svoo/kernels/triton/permute.py:39-65,105-130). */
+int svoo_b200_inverse_permute(const void* x, const int32_t* sorted_idx, int64_t BH, int64_t N, int64_t D,
+                              void* y, void* stream);
+
+/* Cluster-block map (identify_dynamic_map, svoo/co_clustering.py:556-633, with
+ * weighted_softmax :544-553) for bf16 centroids.  preserve_host[h] / cap_host[h]
+ * are the per-head floor and cap in numbers of key clusters (cap = KC: no cap);
+ * both are HOST arrays of length BH.  map_out is uint8 [BH,QC,KC], 1 = keep. */
+int svoo_b200_block_map(const void* qcentroids, const void* kcentroids, const int32_t* ksizes,
+                        int64_t BH, int64_t QC, int64_t KC, int64_t D, float top_p,
+                        const int32_t* preserve_host, const int32_t* cap_host,
+                        uint8_t* map_out, void* stream);
+
+/* Block-sparse attention over cluster-ordered q,k,v [BH,S,128]
+ * (dynamic_block_sparse_fwd_flashinfer, svoo/co_clustering.py:1231-1311, whose
+ * semantics are those of _dynamic_block_sparse_fwd_kernel :949-1108): query
+ * cluster i of head bh attends the key clusters j with map[bh,i,j] != 0; rows
+ * without a selected key give 0.  q_offsets [BH,QC+1], k_offsets [BH,KC+1] are
+ * the cluster row offsets.  If out_row_idx is not null the result row s is
+ * written to row out_row_idx[bh,s] (the inverse permutation fused into the
+ * store); otherwise to row s. */
+int svoo_b200_sparse_attn(const void* q, const void* k, const void* v, const uint8_t* map,
+                          const int32_t* q_offsets, const int32_t* k_offsets,
+                          int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, float sm_scale,
+                          void* out, const int32_t* out_row_idx,
+                          void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Exclusive prefix of cluster sizes [BH,K] -> offsets [BH,K+1]
+ * (the torch.cumsum of svoo/co_clustering.py:1147-1148). */
+int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, int32_t* offsets, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SVOO_B200_H */

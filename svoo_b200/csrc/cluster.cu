@@ -1,0 +1,538 @@
+// QK co-clustering kernels: profile prologue, assignment GEMM with fused argmax,
+// stable counting sort of labels, deterministic centroid update.
+//
+// Algebra used by the assignment.  The reference (svoo/co_clustering.py:2148-2255)
+// computes, for token x and own-centroid j,
+//     score_j = sum_k ((x . c_k) / norm(x)) * Phat[j,k],   label = first argmax_j score_j
+// with c_k the profile-forming centroids and Phat the row-normalised centroid-centroid
+// profile.  norm(x) > 0 does not depend on j and the double sum is linear in x, so
+//     label = first argmax_j  x . W_j,     W_j = sum_k Phat[j,k] c_k      (W is [J,128])
+// One GEMM [N,128] x [128,J] per side and iteration replaces the two chained GEMMs and
+// the separate norm pass.  W is carried as a bf16 pair (hi, lo = bf16(W - hi)) so the
+// products keep ~16 mantissa bits, more than the TF32 operands of the reference.
+#include "common.cuh"
+
+namespace svoo {
+
+// ---------------------------------------------------------------------------------------
+// centroids[bh,c,:] = x[bh, idx[bh,c], :]     (svoo/co_clustering.py:2417-2421)
+// ---------------------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const bf16* __restrict__ x, const int32_t* __restrict__ idx,
+                                   bf16* __restrict__ out, int N, int K) {
+  const int bh = blockIdx.y;
+  const int c = blockIdx.x * (blockDim.x / 16) + threadIdx.x / 16;
+  if (c >= K) return;
+  const int lane = threadIdx.x % 16;
+  int src = idx[(int64_t)bh * K + c];
+  src = min(max(src, 0), N - 1);
+  const uint4* s = reinterpret_cast<const uint4*>(x + ((int64_t)bh * N + src) * kHeadDim);
+  uint4* d = reinterpret_cast<uint4*>(out + ((int64_t)bh * K + c) * kHeadDim);
+  d[lane] = s[lane];
+}
+
+// ---------------------------------------------------------------------------------------
+// Prologue: P = bf16(own . form^T), Phat = P / sqrt(sum P^2 + 1e-8) (fp32),
+//           W = Phat . form (fp32) -> (hi, lo) bf16.      One CTA = 8 rows j of one head.
+// (svoo/co_clustering.py:2427-2428 and svoo/kernels/triton/l2norm.py:36-41)
+// ---------------------------------------------------------------------------------------
+constexpr int kProR = 8;
+
+__global__ void __launch_bounds__(256) profile_prologue_kernel(
+    const bf16* __restrict__ own, const bf16* __restrict__ form, bf16* __restrict__ w_hi,
+    bf16* __restrict__ w_lo, int J, int K, int Jpad) {
+  extern __shared__ float sm[];
+  float* own_s = sm;                       // [8][128]
+  float* p_s = sm + kProR * kHeadDim;      // [8][K]
+  __shared__ float inv_norm[kProR];
+  const int bh = blockIdx.y;
+  const int j0 = blockIdx.x * kProR;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const bf16* form_b = form + (int64_t)bh * K * kHeadDim;
+
+  for (int i = tid; i < kProR * kHeadDim; i += 256) {
+    int r = i / kHeadDim, d = i % kHeadDim;
+    own_s[i] = (j0 + r < J) ? __bfloat162float(own[((int64_t)bh * J + j0 + r) * kHeadDim + d]) : 0.f;
+  }
+  __syncthreads();
+
+  // P[r][k]: one warp per k, lanes split the 128 dims (4 each).
+  for (int k = warp; k < K; k += 8) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(form_b + (int64_t)k * kHeadDim + lane * 4);
+    const __nv_bfloat162 v01 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 v23 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float f0 = __low2float(v01), f1 = __high2float(v01), f2 = __low2float(v23), f3 = __high2float(v23);
+    float acc[kProR];
+#pragma unroll
+    for (int r = 0; r < kProR; ++r) {
+      const float4 o = *reinterpret_cast<const float4*>(own_s + r * kHeadDim + lane * 4);
+      acc[r] = o.x * f0 + o.y * f1 + o.z * f2 + o.w * f3;
+    }
+#pragma unroll
+    for (int r = 0; r < kProR; ++r) {
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], s);
+    }
+    if (lane < kProR) {
+      float v = acc[0];
+#pragma unroll
+      for (int r = 1; r < kProR; ++r) v = (lane == r) ? acc[r] : v;
+      p_s[lane * K + k] = bf16_round(v);       // torch.matmul of bf16 tensors returns bf16
+    }
+  }
+  __syncthreads();
+
+  // row norms: warp r sums P[r][:]^2
+  {
+    float s = 0.f;
+    for (int k = lane; k < K; k += 32) { float v = p_s[warp * K + k]; s += v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) inv_norm[warp] = sqrtf(s + 1e-8f);
+  }
+  __syncthreads();
+  for (int i = tid; i < kProR * K; i += 256) p_s[i] = p_s[i] / inv_norm[i / K];
+  __syncthreads();
+
+  // W[r][d] = sum_k Phat[r][k] * form[k][d]; thread = (d, half of the rows)
+  {
+    const int d = tid % kHeadDim, r0 = (tid / kHeadDim) * 4;
+    float w[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < K; ++k) {
+      const float f = __bfloat162float(form_b[(int64_t)k * kHeadDim + d]);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) w[r] = fmaf(p_s[(r0 + r) * K + k], f, w[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int j = j0 + r0 + r;
+      if (j < Jpad) {
+        const float val = (j < J) ? w[r] : 0.f;
+        const bf16 hi = __float2bfloat16_rn(val);
+        const bf16 lo = __float2bfloat16_rn(val - __bfloat162float(hi));
+        w_hi[((int64_t)bh * Jpad + j) * kHeadDim + d] = hi;
+        w_lo[((int64_t)bh * Jpad + j) * kHeadDim + d] = lo;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Assignment: labels[n] = first argmax_j x_n . (W_hi[j] + W_lo[j]),  j < J.
+// CTA = 128 tokens (4 warps x 32), W streamed in tiles of 64 rows, double buffered.
+// ---------------------------------------------------------------------------------------
+constexpr int kAsgBM = 128;
+constexpr int kAsgBJ = 64;
+constexpr int kAsgSmem = kAsgBM * kRowBytes + 2 * 2 * kAsgBJ * kRowBytes;   // 32 KB + 64 KB
+
+__device__ __forceinline__ void asg_load_w(uint32_t dst, const bf16* hi, const bf16* lo, int tid) {
+  // 64 rows x 16 chunks for hi, then the same for lo: 2048 chunks, 16 per thread
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int c = tid + i * 128;
+    const int which = c >> 10, rc = c & 1023, row = rc >> 4, chunk = rc & 15;
+    const bf16* src = (which ? lo : hi) + row * kHeadDim + chunk * 8;
+    cp_async16(dst + which * (kAsgBJ * kRowBytes) + swz(row, chunk), src, true);
+  }
+}
+
+__global__ void __launch_bounds__(128) assign_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_hi,
+                                                     const bf16* __restrict__ w_lo, int32_t* __restrict__ labels,
+                                                     int N, int J, int Jpad) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const uint32_t x_s = smem_u32(smem_raw);
+  const uint32_t w_s = x_s + kAsgBM * kRowBytes;
+  const int bh = blockIdx.y, n0 = blockIdx.x * kAsgBM;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const bf16* xb = x + (int64_t)bh * N * kHeadDim;
+  const bf16* hib = w_hi + (int64_t)bh * Jpad * kHeadDim;
+  const bf16* lob = w_lo + (int64_t)bh * Jpad * kHeadDim;
+
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int c = tid + i * 128, row = c >> 4, chunk = c & 15;
+    const bool ok = n0 + row < N;
+    cp_async16(x_s + swz(row, chunk), xb + (int64_t)(ok ? n0 + row : 0) * kHeadDim + chunk * 8, ok);
+  }
+  asg_load_w(w_s, hib, lob, tid);
+  cp_async_commit();
+
+  uint32_t a[2][8][4];
+  float best[4];
+  int best_j[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { best[i] = -3.4e38f; best_j[i] = 0; }
+
+  const int ntiles = Jpad / kAsgBJ;
+  for (int jt = 0; jt < ntiles; ++jt) {
+    if (jt + 1 < ntiles)
+      asg_load_w(w_s + ((jt + 1) & 1) * (2 * kAsgBJ * kRowBytes), hib + (int64_t)(jt + 1) * kAsgBJ * kHeadDim,
+                 lob + (int64_t)(jt + 1) * kAsgBJ * kHeadDim, tid);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (jt == 0) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const int row = warp * 32 + mt * 16 + (lane % 8) + ((lane / 8) % 2) * 8;
+          ldmatrix_x4(a[mt][ks], x_s + swz(row, ks * 2 + lane / 16));
+        }
+    }
+    const uint32_t wt = w_s + (jt & 1) * (2 * kAsgBJ * kRowBytes);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float acc[2][4][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          const int row = half * 32 + np * 16 + (lane % 8) + (lane / 16) * 8;
+          const uint32_t off = swz(row, ks * 2 + ((lane / 8) % 2));
+          uint32_t bh4[4], bl4[4];
+          ldmatrix_x4(bh4, wt + off);
+          ldmatrix_x4(bl4, wt + kAsgBJ * kRowBytes + off);
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma_bf16(acc[mt][np * 2], a[mt][ks], bh4[0], bh4[1]);
+            mma_bf16(acc[mt][np * 2 + 1], a[mt][ks], bh4[2], bh4[3]);
+            mma_bf16(acc[mt][np * 2], a[mt][ks], bl4[0], bl4[1]);
+            mma_bf16(acc[mt][np * 2 + 1], a[mt][ks], bl4[2], bl4[3]);
+          }
+        }
+      }
+      const int jbase = jt * kAsgBJ + half * 32 + 2 * (lane % 4);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int j = jbase + nt * 8 + c;
+          if (j < J) {
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+              const float v0 = acc[mt][nt][c], v1 = acc[mt][nt][2 + c];
+              if (v0 > best[mt * 2]) { best[mt * 2] = v0; best_j[mt * 2] = j; }
+              if (v1 > best[mt * 2 + 1]) { best[mt * 2 + 1] = v1; best_j[mt * 2 + 1] = j; }
+            }
+          }
+        }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int s = 1; s <= 2; s <<= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best[i], s);
+      const int oj = __shfl_xor_sync(0xffffffffu, best_j[i], s);
+      if (ov > best[i] || (ov == best[i] && oj < best_j[i])) { best[i] = ov; best_j[i] = oj; }
+    }
+  }
+  if (lane % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = n0 + warp * 32 + (i / 2) * 16 + (i % 2) * 8 + lane / 4;
+      if (row < N) labels[(int64_t)bh * N + row] = best_j[i];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Stable counting sort of labels (three kernels).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) label_hist_kernel(const int32_t* __restrict__ labels,
+                                                         int32_t* __restrict__ chunk_hist, int N, int K, int nchunks) {
+  __shared__ int hist[SVOO_MAX_CLUSTERS];
+  const int bh = blockIdx.y, chunk = blockIdx.x;
+  for (int k = threadIdx.x; k < K; k += 256) hist[k] = 0;
+  __syncthreads();
+  const int base = chunk * kSortChunk;
+  for (int i = threadIdx.x; i < kSortChunk; i += 256) {
+    const int n = base + i;
+    if (n < N) {
+      const int l = labels[(int64_t)bh * N + n];
+      if (l >= 0 && l < K) atomicAdd(&hist[l], 1);
+    }
+  }
+  __syncthreads();
+  int32_t* out = chunk_hist + ((int64_t)bh * nchunks + chunk) * K;
+  for (int k = threadIdx.x; k < K; k += 256) out[k] = hist[k];
+}
+
+// One CTA per head: per-cluster exclusive prefix over chunks (in place), totals, offsets.
+__global__ void __launch_bounds__(1024) label_scan_kernel(int32_t* __restrict__ chunk_hist, int32_t* __restrict__ offsets,
+                                                          int32_t* __restrict__ sizes, int K, int nchunks) {
+  __shared__ int warp_tot[32];
+  const int bh = blockIdx.x, k = threadIdx.x, lane = k % 32, warp = k / 32;
+  int total = 0;
+  if (k < K) {
+    int32_t* col = chunk_hist + (int64_t)bh * nchunks * K + k;
+    for (int c = 0; c < nchunks; ++c) {
+      const int v = col[(int64_t)c * K];
+      col[(int64_t)c * K] = total;
+      total += v;
+    }
+    if (sizes) sizes[(int64_t)bh * K + k] = total;
+  }
+  int incl = total;
+#pragma unroll
+  for (int s = 1; s < 32; s <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, incl, s);
+    if (lane >= s) incl += o;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int v = warp_tot[lane];
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, v, s);
+      if (lane >= s) v += o;
+    }
+    warp_tot[lane] = v;
+  }
+  __syncthreads();
+  const int excl = incl - total + (warp ? warp_tot[warp - 1] : 0);
+  if (k < K) offsets[(int64_t)bh * (K + 1) + k] = excl;
+  if (k == K - 1) offsets[(int64_t)bh * (K + 1) + K] = excl + total;
+}
+
+__global__ void __launch_bounds__(256) label_scatter_kernel(const int32_t* __restrict__ labels,
+                                                            const int32_t* __restrict__ chunk_base,
+                                                            const int32_t* __restrict__ offsets,
+                                                            int32_t* __restrict__ sorted_idx, int N, int K, int nchunks) {
+  extern __shared__ int wh[];          // [8][K] per-warp histogram, then per-warp running position
+  const int bh = blockIdx.y, chunk = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  for (int i = tid; i < 8 * K; i += 256) wh[i] = 0;
+  __syncthreads();
+  const int wbase = chunk * kSortChunk + warp * (kSortChunk / 8);
+  const int32_t* lb = labels + (int64_t)bh * N;
+  int mine[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    const int n = wbase + s * 32 + lane;
+    int l = (n < N) ? lb[n] : -1;
+    if (l >= K) l = -1;
+    mine[s] = l;
+    if (l >= 0) atomicAdd(&wh[warp * K + l], 1);
+  }
+  __syncthreads();
+  const int32_t* cb = chunk_base + ((int64_t)bh * nchunks + chunk) * K;
+  const int32_t* ob = offsets + (int64_t)bh * (K + 1);
+  for (int k = tid; k < K; k += 256) {
+    int run = ob[k] + cb[k];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int t = wh[w * K + k];
+      wh[w * K + k] = run;
+      run += t;
+    }
+  }
+  __syncthreads();
+  int32_t* out = sorted_idx + (int64_t)bh * N;
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    const int l = mine[s];
+    const unsigned key = (l >= 0) ? (unsigned)l : (unsigned)(SVOO_MAX_CLUSTERS + lane);
+    const unsigned grp = __match_any_sync(0xffffffffu, key);
+    const int rank = __popc(grp & ((1u << lane) - 1u));
+    int base = 0;
+    if (l >= 0) base = wh[warp * K + l];
+    __syncwarp();
+    if (l >= 0 && rank == 0) wh[warp * K + l] = base + __popc(grp);
+    __syncwarp();
+    if (l >= 0) {
+      const int pos = base + rank;
+      if (pos < N) out[pos] = wbase + s * 32 + lane;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Centroid update: fixed-order fp32 sums over the sorted order, then mean / keep-old.
+// ---------------------------------------------------------------------------------------
+constexpr int kSlabMin = 256;
+
+__device__ __forceinline__ void slab_range(int begin, int end, int z, int& s0, int& s1) {
+  const int size = end - begin;
+  int per = (size + kCentroidSlabs - 1) / kCentroidSlabs;
+  per = per < kSlabMin ? kSlabMin : per;
+  s0 = begin + z * per;
+  s1 = s0 + per < end ? s0 + per : end;
+}
+
+__global__ void __launch_bounds__(256) centroid_partial_kernel(const bf16* __restrict__ x,
+                                                               const int32_t* __restrict__ sorted_idx,
+                                                               const int32_t* __restrict__ offsets,
+                                                               float* __restrict__ partial, int N, int K) {
+  __shared__ float red[16][kHeadDim + 4];
+  const int c = blockIdx.x, z = blockIdx.y, bh = blockIdx.z;
+  const int begin = offsets[(int64_t)bh * (K + 1) + c], end = offsets[(int64_t)bh * (K + 1) + c + 1];
+  int s0, s1;
+  slab_range(begin, end, z, s0, s1);
+  if (s0 >= s1) return;
+  const int grp = threadIdx.x / 16, lane = threadIdx.x % 16;
+  const int32_t* idx = sorted_idx + (int64_t)bh * N;
+  const bf16* xb = x + (int64_t)bh * N * kHeadDim;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int s = s0 + grp; s < s1; s += 64) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int ss = s + u * 16;
+      if (ss < s1) {
+        const int row = idx[ss];
+        v[u] = __ldg(reinterpret_cast<const uint4*>(xb + (int64_t)row * kHeadDim) + lane);
+      } else {
+        v[u] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] += __low2float(h[i]);
+        acc[2 * i + 1] += __high2float(h[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[grp][lane * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < kHeadDim) {
+    float s = 0.f;
+#pragma unroll
+    for (int g = 0; g < 16; ++g) s += red[g][threadIdx.x];
+    partial[(((int64_t)bh * K + c) * kCentroidSlabs + z) * kHeadDim + threadIdx.x] = s;
+  }
+}
+
+__global__ void __launch_bounds__(128) centroid_finalize_kernel(const float* __restrict__ partial,
+                                                                const int32_t* __restrict__ offsets,
+                                                                const bf16* __restrict__ old_c, bf16* __restrict__ new_c,
+                                                                int32_t* __restrict__ sizes, int K) {
+  const int c = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
+  const int begin = offsets[(int64_t)bh * (K + 1) + c], end = offsets[(int64_t)bh * (K + 1) + c + 1];
+  const int cnt = end - begin;
+  const int64_t o = ((int64_t)bh * K + c) * kHeadDim + d;
+  float s = 0.f;
+  for (int z = 0; z < kCentroidSlabs; ++z) {
+    int s0, s1;
+    slab_range(begin, end, z, s0, s1);
+    if (s0 < s1) s += partial[(((int64_t)bh * K + c) * kCentroidSlabs + z) * kHeadDim + d];
+  }
+  const bf16 keep = old_c[o];
+  new_c[o] = cnt > 0 ? __float2bfloat16_rn(s / (float)cnt) : keep;
+  if (d == 0 && sizes) sizes[(int64_t)bh * K + c] = cnt;
+}
+
+// sizes [BH,K] -> offsets [BH,K+1]
+__global__ void __launch_bounds__(1024) offsets_from_sizes_kernel(const int32_t* __restrict__ sizes,
+                                                                  int32_t* __restrict__ offsets, int K) {
+  __shared__ int warp_tot[32];
+  const int bh = blockIdx.x, k = threadIdx.x, lane = k % 32, warp = k / 32;
+  const int v = k < K ? sizes[(int64_t)bh * K + k] : 0;
+  int incl = v;
+#pragma unroll
+  for (int s = 1; s < 32; s <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, incl, s);
+    if (lane >= s) incl += o;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int t = warp_tot[lane];
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, t, s);
+      if (lane >= s) t += o;
+    }
+    warp_tot[lane] = t;
+  }
+  __syncthreads();
+  const int excl = incl - v + (warp ? warp_tot[warp - 1] : 0);
+  if (k < K) offsets[(int64_t)bh * (K + 1) + k] = excl;
+  if (k == K - 1) offsets[(int64_t)bh * (K + 1) + K] = excl + v;
+}
+
+// ---------------------------------------------------------------------------------------
+// Host launchers (called from api.cu)
+// ---------------------------------------------------------------------------------------
+cudaError_t launch_gather_rows(const void* x, const int32_t* idx, void* out, int64_t BH, int64_t N, int64_t K,
+                               cudaStream_t st) {
+  dim3 grid((unsigned)ceil_div64(K, 16), (unsigned)BH);
+  gather_rows_kernel<<<grid, 256, 0, st>>>((const bf16*)x, idx, (bf16*)out, (int)N, (int)K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void* w_lo, int64_t BH, int64_t J,
+                            int64_t K, cudaStream_t st) {
+  const int Jpad = pad_clusters(J);
+  const size_t smem = (size_t)(kProR * kHeadDim + kProR * K) * sizeof(float);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    attr_done = true;
+  }
+  dim3 grid((unsigned)(Jpad / kProR), (unsigned)BH);
+  profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo,
+                                                   (int)J, (int)K, Jpad);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_assign(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int64_t BH, int64_t N,
+                          int64_t J, cudaStream_t st) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAsgSmem);
+    attr_done = true;
+  }
+  dim3 grid((unsigned)ceil_div64(N, kAsgBM), (unsigned)BH);
+  assign_kernel<<<grid, 128, kAsgSmem, st>>>((const bf16*)x, (const bf16*)w_hi, (const bf16*)w_lo, labels, (int)N,
+                                             (int)J, pad_clusters(J));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int64_t K, int32_t* sorted_idx,
+                               int32_t* offsets, int32_t* sizes, int32_t* chunk_hist, cudaStream_t st) {
+  const int nchunks = sort_chunks(N);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(label_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         8 * SVOO_MAX_CLUSTERS * 4);
+    attr_done = true;
+  }
+  dim3 grid((unsigned)nchunks, (unsigned)BH);
+  label_hist_kernel<<<grid, 256, 0, st>>>(labels, chunk_hist, (int)N, (int)K, nchunks);
+  label_scan_kernel<<<(unsigned)BH, 1024, 0, st>>>(chunk_hist, offsets, sizes, (int)K, nchunks);
+  label_scatter_kernel<<<grid, 256, 8 * K * 4, st>>>(labels, chunk_hist, offsets, sorted_idx, (int)N, (int)K, nchunks);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_centroid_update(const void* x, const int32_t* sorted_idx, const int32_t* offsets,
+                                   const void* old_c, void* new_c, int32_t* sizes, float* partial, int64_t BH,
+                                   int64_t N, int64_t K, cudaStream_t st) {
+  dim3 grid((unsigned)K, kCentroidSlabs, (unsigned)BH);
+  centroid_partial_kernel<<<grid, 256, 0, st>>>((const bf16*)x, sorted_idx, offsets, partial, (int)N, (int)K);
+  dim3 grid2((unsigned)K, (unsigned)BH);
+  centroid_finalize_kernel<<<grid2, 128, 0, st>>>(partial, offsets, (const bf16*)old_c, (bf16*)new_c, sizes, (int)K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_offsets_from_sizes(const int32_t* sizes, int32_t* offsets, int64_t BH, int64_t K, cudaStream_t st) {
+  offsets_from_sizes_kernel<<<(unsigned)BH, 1024, 0, st>>>(sizes, offsets, (int)K);
+  return cudaGetLastError();
+}
+
+}  // namespace svoo

@@ -1,0 +1,179 @@
+"""Generate the golden fixtures in this directory from the UNMODIFIED reference.
+
+Run once, in a container that has the reference checkout (path in $SVOO_REFERENCE,
+default /root/reference):
+
+    python tests/golden/make_golden.py            # all fixtures (about 4 minutes)
+    python tests/golden/make_golden.py layer_tiny_bf16   # just that one
+
+The reference's hot path is Triton + torch.  Its Triton kernels are executed on
+CPU tensors by the Triton interpreter (TRITON_INTERPRET=1); the wrappers'
+`assert x.is_cuda` checks are satisfied by overriding the `is_cuda` property, so
+every wrapper (co_cluster_tokens, permute_tensor_by_labels_triton,
+apply_inverse_permutation_triton, dynamic_block_sparse_fwd_triton) and the pure
+torch identify_dynamic_map run exactly as written.  Inputs are re-creatable from
+seeds (svoo_b200.synth); a checksum of them is stored so that a drift of the RNG
+is detected instead of silently invalidating the fixture.
+"""
+import os
+import sys
+import time
+
+os.environ["TRITON_INTERPRET"] = "1"
+REF = os.environ.get("SVOO_REFERENCE", "/root/reference")
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REF)
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+import numpy as np
+import torch
+
+torch.Tensor.is_cuda = property(lambda self: True)
+
+import svoo.co_clustering as ref_cc                      # noqa: E402
+from svoo.kernels.triton import permute as ref_pm        # noqa: E402
+from svoo.sparsity.lookup import SparsityLookup as RefLookup   # noqa: E402
+
+from svoo_b200 import synth                              # noqa: E402
+
+
+checksum = synth.tensor_checksum
+
+
+def f32(t):
+    return t.float().numpy()
+
+
+def layer_case(name, cfg, iters, density, rows_kept=8, max_ratio=None):
+    """Whole path through the reference for one small layer config."""
+    t0 = time.time()
+    q, k, v = synth.make_qkv(cfg)
+    H, N, D = cfg.heads, cfg.n_video, 128
+    q_idx, k_idx = synth.init_indices(cfg)
+    torch.manual_seed(7)                                  # the reference draws from the global RNG
+    ql, qc, qs, kl, kc, ks = ref_cc.co_cluster_tokens(q[0], k[0], cfg.num_q, cfg.num_k, max_iters=iters)
+    # the draws above must be the ones synth.init_indices reproduces
+    torch.manual_seed(7)
+    assert torch.equal(torch.randint(0, N, (H, cfg.num_q)), q_idx)
+    assert torch.equal(torch.randint(0, N, (H, cfg.num_k)), k_idx)
+    # one-iteration run from the same init: not yet amplified by later iterations
+    torch.manual_seed(7)
+    ql1, qc1, qs1, kl1, kc1, ks1 = ref_cc.co_cluster_tokens(q[0], k[0], cfg.num_q, cfg.num_k, max_iters=1)
+
+    qp, q_sorted = ref_pm.permute_tensor_by_labels_triton(q, ql, dim=2)
+    kp, k_sorted = ref_pm.permute_tensor_by_labels_triton(k, kl, dim=2)
+    vp, _ = ref_pm.permute_tensor_by_labels_triton(v, kl, dim=2, sorted_indices=k_sorted)
+    args = dict(min_kc_ratio=density)
+    if max_ratio is not None:
+        args["max_kc_ratio"] = max_ratio
+    dmap = ref_cc.identify_dynamic_map(qc.view(1, H, cfg.num_q, D), kc.view(1, H, cfg.num_k, D),
+                                       qs.view(1, H, -1), ks.view(1, H, -1), cfg.top_p, **args)
+    # The interpreter cannot run tl.dot on bf16 operands (numpy has no bf16), and the
+    # attention kernel, unlike the clustering kernels, does not up-cast before its dots:
+    # give it the same values as fp32.
+    up = (lambda t: t.float()) if cfg.dtype == torch.bfloat16 else (lambda t: t)
+    op = ref_cc.dynamic_block_sparse_fwd_triton(up(qp), up(kp), up(vp), dmap, qs.view(1, H, -1), ks.view(1, H, -1))
+    out = ref_pm.apply_inverse_permutation_triton(op, q_sorted, dim=2)
+    np.savez_compressed(
+        os.path.join(HERE, name + ".npz"),
+        input_checksum=checksum(q, k, v),
+        q_init_idx=q_idx.numpy().astype(np.int32), k_init_idx=k_idx.numpy().astype(np.int32),
+        iters=np.array([iters]),
+        qlabels=ql.numpy().astype(np.int16), klabels=kl.numpy().astype(np.int16),
+        qcentroids=f32(qc), kcentroids=f32(kc), qsizes=qs.numpy(), ksizes=ks.numpy(),
+        qlabels_it1=ql1.numpy().astype(np.int16), klabels_it1=kl1.numpy().astype(np.int16),
+        qcentroids_it1=f32(qc1), kcentroids_it1=f32(kc1),
+        q_sorted=q_sorted.numpy().astype(np.int32), k_sorted=k_sorted.numpy().astype(np.int32),
+        min_kc_ratio=np.array(density if isinstance(density, list) else [density], dtype=np.float64),
+        max_kc_ratio=np.array([-1.0] if max_ratio is None else
+                              (max_ratio if isinstance(max_ratio, list) else [max_ratio]), dtype=np.float64),
+        map_bits=np.packbits(dmap.numpy()), map_shape=np.array(dmap.shape),
+        out_rows=f32(out[0, :, ::rows_kept]).astype(np.float32), rows_kept=np.array([rows_kept]),
+        q_perm_rows=f32(qp[0, :, ::rows_kept * 4]),
+    )
+    print(f"{name}: {time.time() - t0:.1f}s  map density {dmap.float().mean():.3f}")
+
+
+def map_case(name, H, QC, KC, dtype, p, min_ratio, max_ratio, seed):
+    """identify_dynamic_map alone at production cluster counts."""
+    g = torch.Generator("cpu").manual_seed(seed)
+    base = torch.randn(H, 1, 128, generator=g)
+    qc = (base + 0.7 * torch.randn(H, QC, 128, generator=g)).to(dtype)[None]
+    kc = (base + 0.7 * torch.randn(H, KC, 128, generator=g)).to(dtype)[None]
+    ks = torch.randint(0, 400, (1, H, KC), generator=g, dtype=torch.int32)
+    ks[0, :, 3] = 0                                        # an empty key cluster
+    qs = torch.randint(1, 900, (1, H, QC), generator=g, dtype=torch.int32)
+    kw = {}
+    if min_ratio is not None:
+        kw["min_kc_ratio"] = min_ratio
+    if max_ratio is not None:
+        kw["max_kc_ratio"] = max_ratio
+    dmap = ref_cc.identify_dynamic_map(qc, kc, qs, ks, p, **kw)
+    def arr(r):
+        if r is None:
+            return np.array([-1.0])
+        return np.array(r if isinstance(r, list) else [r], dtype=np.float64)
+    np.savez_compressed(
+        os.path.join(HERE, name + ".npz"),
+        seed=np.array([seed]), H=np.array([H]), QC=np.array([QC]), KC=np.array([KC]),
+        is_bf16=np.array([dtype == torch.bfloat16]), p=np.array([p], dtype=np.float64),
+        min_kc_ratio=arr(min_ratio), max_kc_ratio=arr(max_ratio),
+        min_is_list=np.array([isinstance(min_ratio, list)]), max_is_list=np.array([isinstance(max_ratio, list)]),
+        input_checksum=checksum(qc, kc, ks, qs),
+        map_bits=np.packbits(dmap.numpy()), map_shape=np.array(dmap.shape),
+    )
+    print(f"{name}: kept per row mean {dmap.sum(-1).float().mean():.1f}")
+
+
+def lookup_case():
+    """SparsityLookup + per-head clipping on a small CSV in the shipped format."""
+    import csv
+    import tempfile
+    g = torch.Generator("cpu").manual_seed(5)
+    rows = []
+    for step in (1, 2):
+        for layer in range(3):
+            for head in range(4):
+                if (step, layer, head) == (2, 1, 3):
+                    continue                               # a hole: that (step, layer) falls back
+                rows.append((step, layer, head, float(torch.rand(1, generator=g)) * 0.6))
+    path = os.path.join(HERE, "density_profile.csv")
+    with open(path, "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["Step", "Layer", "Head", "Sparsity"])
+        for r in rows:
+            w.writerow([r[0], r[1], r[2], f"{r[3]:.6f}"])
+    lk = RefLookup(path)
+    got = np.array([[lk.get_sparsity_batch(s, l, 4) for l in range(3)] for s in (1, 2)])
+    has = np.array([[lk.has_data_for_step_layer(s, l, 4) for l in range(3)] for s in (1, 2)])
+    np.savez_compressed(os.path.join(HERE, "density_profile_expected.npz"), batch=got, has=has)
+    print("lookup fixture written")
+
+
+def main():
+    import dataclasses
+    only = sys.argv[1:]
+    tiny = synth.LayerConfig("tiny-fp32", 90, 2, (4, 16, 16), torch.float32, 8, 16, 3, (0.25, 0.25), 1, False)
+    if only:
+        if "layer_tiny_bf16" in only:
+            tiny_b = dataclasses.replace(tiny, name="tiny-bf16", cfg_id=91, dtype=torch.bfloat16, rope=True,
+                                         num_q=12, num_k=40, grid=(3, 16, 20))
+            layer_case("layer_tiny_bf16", tiny_b, 2, [0.3, 0.15], max_ratio=[0.3, 0.15])
+        return
+    layer_case("layer_tiny_fp32", tiny, 3, 0.25)
+    tiny_b = dataclasses.replace(tiny, name="tiny-bf16", cfg_id=91, dtype=torch.bfloat16, rope=True,
+                                 num_q=12, num_k=40, grid=(3, 16, 20))
+    layer_case("layer_tiny_bf16", tiny_b, 2, [0.3, 0.15], max_ratio=[0.3, 0.15])
+    layer_case("layer_cfg0", synth.CONFIGS["cfg0"], 10, 0.20, rows_kept=32, max_ratio=0.20)
+    map_case("map_bf16_budget", 4, 100, 500, torch.bfloat16, 0.9, [0.07, 0.12, 0.2, 0.25], [0.07, 0.12, 0.2, 0.25], 11)
+    map_case("map_bf16_topp_floor", 4, 100, 500, torch.bfloat16, 0.9, [0.15, 0.2, 0.0, 0.18], None, 12)
+    map_case("map_bf16_scalar", 3, 64, 256, torch.bfloat16, 0.88, 0.1, None, 13)
+    map_case("map_fp32_topp", 2, 32, 128, torch.float32, 0.9, 0, None, 14)
+    map_case("map_fp32_cap_scalar", 2, 32, 128, torch.float32, 0.95, [0.1, 0.3], 0.2, 15)
+    map_case("map_bf16_big", 2, 256, 1024, torch.bfloat16, 0.9, [0.15, 0.2], None, 16)
+    map_case("map_all_ones", 2, 8, 16, torch.bfloat16, 1.0, 0.1, None, 17)
+    lookup_case()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,105 @@
+"""The CPU oracle against outputs of the unmodified reference (tests/golden)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import svoo_oracle as O
+from svoo_b200 import synth
+from tests import golden_util as gu
+
+
+@pytest.mark.parametrize("name", gu.MAP_CASES)
+def test_map_matches_reference(name):
+    z = gu.load(name)
+    qc, kc, qs, ks, p, kw = gu.map_inputs(z)
+    ref = gu.unpack_map(z)
+    got, prob = O.identify_dynamic_map(qc, kc, qs, ks, p, return_probs=True, **kw)
+    if prob is None:
+        assert got.numpy().all() and ref.all()
+        return
+    # torch.sort in the reference is unstable: equal-probability clusters at the cut may swap
+    assert gu.same_up_to_ties(got.numpy(), ref, prob.numpy())
+    if not z["is_bf16"][0]:
+        assert (got.numpy() == ref).all()
+
+
+@pytest.fixture(scope="module", params=list(gu.LAYER_CASES))
+def layer(request):
+    name = request.param
+    cfg = gu.LAYER_CASES[name]
+    z = gu.load(name)
+    q, k, v = synth.make_qkv(cfg)
+    assert synth.tensor_checksum(q, k, v)[0] == z["input_checksum"][0], "RNG drift: regenerate fixtures"
+    qi, ki = synth.init_indices(cfg)
+    assert (qi.numpy() == z["q_init_idx"]).all() and (ki.numpy() == z["k_init_idx"]).all()
+    return name, cfg, z, q, k, v, qi, ki
+
+
+def test_one_iteration_labels(layer):
+    name, cfg, z, q, k, v, qi, ki = layer
+    ql, qc, qs, kl, kc, ks = O.co_cluster_tokens(q[0], k[0], qi, ki, 1)
+    assert (kl.numpy() == z["klabels_it1"]).mean() >= 0.999
+    assert (ql.numpy() == z["qlabels_it1"]).mean() >= 0.999
+    np.testing.assert_allclose(kc.float().numpy(), z["kcentroids_it1"], atol=2e-2)
+    np.testing.assert_allclose(qc.float().numpy(), z["qcentroids_it1"], atol=2e-2)
+
+
+def test_full_path(layer):
+    name, cfg, z, q, k, v, qi, ki = layer
+    iters = int(z["iters"][0])
+    mn = gu.layer_ratio(z["min_kc_ratio"], cfg.heads)
+    mx = gu.layer_ratio(z["max_kc_ratio"], cfg.heads)
+    out, aux = O.sparse_attention_layer(q, k, v, qi, ki, cfg.num_q, cfg.num_k, iters, cfg.top_p,
+                                        mn, 0 if mx is None else mx)
+    q_agree = (aux["qlabels"].numpy() == z["qlabels"]).mean()
+    k_agree = (aux["klabels"].numpy() == z["klabels"]).mean()
+    assert q_agree >= 0.999 and k_agree >= 0.999, (q_agree, k_agree)
+    # integer results given the reference's own labels
+    ql = torch.from_numpy(z["qlabels"].astype(np.int64))
+    kl = torch.from_numpy(z["klabels"].astype(np.int64))
+    q_idx, q_off = O.sort_labels(ql, cfg.num_q)
+    k_idx, k_off = O.sort_labels(kl, cfg.num_k)
+    assert (np.diff(q_off.numpy(), axis=-1) == z["qsizes"]).all()
+    assert (np.diff(k_off.numpy(), axis=-1) == z["ksizes"]).all()
+    # the reference's argsort is unstable: same members per cluster, any order inside
+    for h in range(cfg.heads):
+        for c in range(cfg.num_q):
+            a, b = int(q_off[h, c]), int(q_off[h, c + 1])
+            assert set(q_idx[h, a:b].tolist()) == set(z["q_sorted"][h, a:b].tolist())
+    # if labels agree completely the downstream results must match the reference closely
+    if q_agree == 1.0 and k_agree == 1.0:
+        ref_map = gu.unpack_map(z)
+        m, prob = O.identify_dynamic_map(aux["qcentroids"][None], aux["kcentroids"][None], aux["qsizes"][None],
+                                         aux["ksizes"][None], cfg.top_p, mn, 0 if mx is None else mx,
+                                         return_probs=True)
+        assert gu.same_up_to_ties(m.numpy(), ref_map, prob.numpy())
+        if (m.numpy() == ref_map).all():
+            rk = int(z["rows_kept"][0])
+            got = out[0, :, ::rk].float().numpy()
+            tol = 2e-2 if cfg.dtype == torch.bfloat16 else 1e-4
+            np.testing.assert_allclose(got, z["out_rows"], atol=tol)
+
+
+def test_attention_given_reference_map(layer):
+    """Attention + permutation semantics with the reference's labels, centroids and map."""
+    name, cfg, z, q, k, v, qi, ki = layer
+    ql = torch.from_numpy(z["qlabels"].astype(np.int64))
+    kl = torch.from_numpy(z["klabels"].astype(np.int64))
+    q_idx, q_off = O.sort_labels(ql, cfg.num_q)
+    k_idx, k_off = O.sort_labels(kl, cfg.num_k)
+    qp, kp, vp = O.permute(q[0], q_idx), O.permute(k[0], k_idx), O.permute(v[0], k_idx)
+    m = torch.from_numpy(gu.unpack_map(z))
+    qs = torch.from_numpy(z["qsizes"])[None]
+    ks = torch.from_numpy(z["ksizes"])[None]
+    op = O.block_sparse_attention(qp[None], kp[None], vp[None], m, qs, ks)
+    out = O.inverse_permute(op[0], q_idx)
+    rk = int(z["rows_kept"][0])
+    tol = 2e-2 if cfg.dtype == torch.bfloat16 else 1e-4
+    np.testing.assert_allclose(out[:, ::rk].float().numpy(), z["out_rows"], atol=tol)
+
+
+def test_exp_is_accurate():
+    x = -np.abs(np.random.default_rng(0).normal(size=4096).astype(np.float32)) * 20
+    got = O.exp_f32(x)
+    ref = np.exp(x.astype(np.float64))
+    assert np.max(np.abs(got - ref) / np.maximum(ref, 1e-38)) < 1e-6
