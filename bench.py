@@ -1,0 +1,377 @@
+"""Benchmark of the sparse-attention layer (co-clustering + permute + block map +
+block-sparse attention + inverse permute) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config cfg2] [--impl reference]
+
+N = 1: the Wan-14B 720p layer (40 heads x 75,600 tokens, 100/500 clusters, 5 iterations,
+per-head density U[0.05, 0.25]) on one GPU.  N > 1 (under torch.distributed.run): the same
+layer, heads sharded over the ranks, activations arriving and leaving sharded by sequence
+(one all-to-all each way inside the timed region) -- total work is fixed ("strong" scaling).
+
+`value` is effective TFLOP/s: the reference algorithm's flops for this layer
+    F = iters*H*[2*N*D*(QC+KC) + 4*N*QC*KC]  +  sum_h 4*N^2*D*rho_h
+(rho_h = realised token-pair density of head h) divided by the step time.
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch
+
+from svoo_b200 import synth
+
+D = 128
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+# ------------------------------------------------------------------------------------------
+# work model
+# ------------------------------------------------------------------------------------------
+def cluster_flops_reference(cfg, heads):
+    n = cfg.n_video
+    return cfg.iters * heads * (2.0 * n * D * (cfg.num_q + cfg.num_k) + 4.0 * n * cfg.num_q * cfg.num_k)
+
+
+def cluster_flops_executed(cfg, heads):
+    """Flops the assignment GEMMs of this implementation run: one [N,128]x[128,J] product per
+    side and iteration, twice (W is a bf16 hi/lo pair)."""
+    n = cfg.n_video
+    return cfg.iters * heads * 2.0 * (2.0 * n * D * (cfg.num_q + cfg.num_k))
+
+
+def attention_flops(rho, n_tokens):
+    return float(sum(4.0 * n_tokens * n_tokens * D * r for r in rho))
+
+
+def realised_density(block_map, q_off, k_off):
+    """rho_h = sum_ij map[h,i,j] |Q_i| |K_j| / S^2 for every head (device tensors)."""
+    qs = (q_off[:, 1:] - q_off[:, :-1]).double()
+    ks = (k_off[:, 1:] - k_off[:, :-1]).double()
+    s = qs.sum(-1)
+    return (torch.einsum("hi,hij,hj->h", qs, block_map.double(), ks) / (s * s)).tolist()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS if k in p}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi samples (SM clock, throttle reasons) of one GPU while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=5)
+
+    def summary(self):
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                mhz.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm (the oracle port of the reference's algorithm, on the host cores)
+# ------------------------------------------------------------------------------------------
+def cpu_layer_sample(cfg, head: int):
+    """One head of the workload through the CPU restatement of the reference path.
+    Returns (seconds, reference-algorithm flops of that head)."""
+    from oracle import svoo_oracle as O
+    one = dataclasses.replace(cfg, heads=1)
+    q, k, v = synth.make_qkv(cfg, heads=[head])
+    qi, ki = synth.init_indices(cfg)
+    d = synth.head_densities(cfg)[head]
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    if cfg.text_tokens:
+        raise NotImplementedError("CPU arm covers the Wan layer configs")
+    out, aux = O.sparse_attention_layer(q, k, v, qi[head:head + 1], ki[head:head + 1], cfg.num_q, cfg.num_k, cfg.iters,
+                                        cfg.top_p, [d], [d])
+    dt = time.perf_counter() - t0
+    rho = O.realised_density(aux["map"], aux["qsizes"][None], aux["ksizes"][None])[0].tolist()
+    return dt, cluster_flops_reference(one, 1) + attention_flops(rho, cfg.n_tokens)
+
+
+def run_reference_arm(args, cfg):
+    """--impl reference: the reference algorithm on the host cores (CPU restatement; the
+    reference's own kernels are Triton/CUDA-only), one head of the layer per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_layer_sample(cfg, 0)
+    tot_t, tot_f = 0.0, 0.0
+    for s in range(args.steps):
+        dt, fl = cpu_layer_sample(cfg, s % cfg.heads)
+        tot_t += dt
+        tot_f += fl
+    val = tot_f / tot_t / 1e12
+    sample = f"1 of {cfg.heads} heads of the {cfg.name} layer per step (full {cfg.n_video} tokens)"
+    line = {
+        "impl": "reference", "metric": "sparse_attn_layer_effective_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot_t / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg.name, "heads": cfg.heads, "tokens": cfg.n_tokens, "q_clusters": cfg.num_q,
+                   "k_clusters": cfg.num_k, "kmeans_iters": cfg.iters, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def run_gpu_arm(args, cfg):
+    import torch.distributed as dist
+    from svoo_b200 import _lib, layer, parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    H, N = cfg.heads, cfg.n_tokens
+    if cfg.text_tokens and world > 1:
+        raise SystemExit("multi-GPU bench covers the Wan layer configs")
+    dens = synth.head_densities(cfg)
+    parts = parallel.head_partition(H, world, dens if world > 1 else None)
+    if world > 1 and len({len(p) for p in parts}) != 1:
+        raise SystemExit(f"{H} heads do not split evenly over {world} ranks")
+    mine = parts[rank]
+    qi_all, ki_all = synth.init_indices(cfg)
+    q_h, k_h, v_h = synth.make_qkv(cfg, heads=mine, pin_memory=True)          # [1, H_r, N, 128] pinned host
+    qi, ki = qi_all[mine].to(dev), ki_all[mine].to(dev)
+    d_mine = [dens[h] for h in mine]
+    kw = dict(num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k, kmeans_iters=cfg.iters, top_p=cfg.top_p,
+              context_length=cfg.text_tokens)
+
+    q_d, k_d, v_d = q_h.to(dev), k_h.to(dev), v_h.to(dev)
+    if world > 1:
+        # sequence-sharded activations, as a sequence-parallel DiT block holds them
+        q_s = parallel.head_to_seq_shard(q_d[0], parts)
+        k_s = parallel.head_to_seq_shard(k_d[0], parts)
+        v_s = parallel.head_to_seq_shard(v_d[0], parts)
+        del q_d, k_d, v_d
+        host_in = [t.cpu().pin_memory() for t in (q_s, k_s, v_s)]
+        host_out = torch.empty_like(host_in[0]).pin_memory()
+    else:
+        host_in = [q_h, k_h, v_h]
+        host_out = torch.empty_like(q_h).pin_memory()
+
+    state = {}
+
+    def step(timer=None):
+        if world > 1:
+            q = parallel.seq_to_head_shard(q_s, parts)[None]
+            k = parallel.seq_to_head_shard(k_s, parts)[None]
+            v = parallel.seq_to_head_shard(v_s, parts)[None]
+        else:
+            q, k, v = q_d, k_d, v_d
+        out, st = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine,
+                                               init_indices=(qi, ki), return_state=True, timer=timer, **kw)
+        state["st"] = st
+        if world > 1:
+            return parallel.head_to_seq_shard(out[0], parts)
+        return out
+
+    dev_in = [torch.empty_like(t, device=dev) for t in host_in]
+
+    def step_e2e():
+        for d_t, h_t in zip(dev_in, host_in):
+            d_t.copy_(h_t, non_blocking=True)
+        if world > 1:
+            q, k, v = (parallel.seq_to_head_shard(t, parts)[None] for t in dev_in)
+        else:
+            q, k, v = dev_in
+        out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki), **kw)
+        if world > 1:
+            out = parallel.head_to_seq_shard(out[0], parts)
+        host_out.copy_(out, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, with_timers=False):
+        timers = []
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            t = layer.StageTimer() if with_timers else None
+            fn(t) if with_timers else fn()
+            if t is not None:
+                timers.append(t)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), timers
+
+    for _ in range(args.warmup):
+        step()
+    launches0 = _lib.LIB.svoo_b200_launch_count()
+    with ClockSampler(local) as clocks:
+        total_ms, timers = timed(step, args.steps, with_timers=True)
+    launches = _lib.LIB.svoo_b200_launch_count() - launches0
+    for _ in range(min(args.warmup, 2)):
+        step_e2e()
+    e2e_ms, _ = timed(step_e2e, args.steps)
+
+    st = state["st"]
+    rho = realised_density(st.block_map, st.q_offsets, st.k_offsets)
+    flops = torch.tensor([cluster_flops_reference(cfg, len(mine)) + attention_flops(rho, N),
+                          attention_flops(rho, N)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(flops)
+    flops_total, flops_attn_all = flops.tolist()
+    ms_per_step = total_ms / args.steps
+    stage = {}
+    for t in timers:
+        for name, ms in t.stage_ms().items():
+            stage[name] = stage.get(name, 0.0) + ms / len(timers)
+    peaks, peak_kind = measured_peaks()
+    attn_ms = stage.get("attention", float("nan"))
+    attn_flops_rank = attention_flops(rho, N)
+    achieved = attn_flops_rank / (attn_ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops_sustained"]
+
+    if rank == 0:
+        bytes_in = sum(t.numel() * t.element_size() for t in host_in)
+        bytes_out = host_out.numel() * host_out.element_size()
+        line = {
+            "metric": "sparse_attn_layer_effective_tflops", "value": flops_total / (ms_per_step * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": cfg.name, "heads": H, "tokens": N, "q_clusters": cfg.num_q, "k_clusters": cfg.num_k,
+                       "kmeans_iters": cfg.iters, "density_budget": list(cfg.density),
+                       "realised_density_mean_rank0": sum(rho) / len(rho),
+                       "parallelism": f"heads/{world}" + ("+ulysses-a2a" if world > 1 else ""),
+                       "l2": "inputs (2.3 GB of Q,K,V) are larger than L2; no flush between steps"},
+            "stage_ms_rank0": {k: round(v, 4) for k, v in stage.items()},
+            "roofline": {"kernel": "sparse_attn", "bound": "tensor", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_kind} sustained bf16",
+                         "traffic": ATTN_DRAM_TRAFFIC_BYTES, "algorithmic_flops_per_launch": attn_flops_rank},
+            "roofline_layer": {"time_at_roofline_ms": layer_roofline_ms(cfg, len(mine), rho, N, peaks),
+                               "frac": layer_roofline_ms(cfg, len(mine), rho, N, peaks) / ms_per_step},
+            "e2e": {"value": flops_total / (e2e_ms / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            dt, fl = cpu_layer_sample(cfg, 0)
+            line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
+                                    "kind": "port", "seconds": dt,
+                                    "sample": f"head 0 of {H} of the {cfg.name} layer, full {cfg.n_video} tokens, once"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one sparse_attn launch, from an ncu capture
+# (see profiles/); None until a capture of this kernel version exists.
+ATTN_DRAM_TRAFFIC_BYTES = None
+
+
+def layer_roofline_ms(cfg, heads, rho, n_tokens, peaks):
+    """Time of the whole layer on `heads` heads at the measured peaks: executed GEMM flops of
+    the clustering and the attention flops at the tensor peak, permute / centroid / sort
+    bytes at the HBM peak."""
+    n = cfg.n_video
+    tensor = (cluster_flops_executed(cfg, heads) + attention_flops(rho, n_tokens)) / (peaks["bf16_tflops_sustained"] * 1e12)
+    row = n * D * 2
+    bytes_cent = cfg.iters * heads * 2 * (2 * row + 3 * 4 * n)       # assign read + centroid gather, labels/idx
+    bytes_perm = heads * (3 * 2 * row + 2 * row + 4 * 4 * n)         # Q,K,V gather; attention output scatter
+    return (tensor + (bytes_cent + bytes_perm) / (peaks["hbm_gbs"] * 1e9)) * 1e3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="svoo_b200", choices=["svoo_b200", "reference"])
+    ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--heads", type=int, default=0, help="override the head count (debugging)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = synth.CONFIGS[args.config]
+    if args.heads:
+        cfg = dataclasses.replace(cfg, heads=args.heads)
+    if args.impl == "reference":
+        run_reference_arm(args, cfg)
+    else:
+        run_gpu_arm(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -43,6 +43,10 @@ enum {
 int svoo_b200_version(void);
 const char* svoo_b200_error_string(int code);
 
+/* Number of kernels this library has launched in the calling process so far
+ * (instrumentation for benchmarks; no counterpart in the reference). */
+int64_t svoo_b200_launch_count(void);
+
 /* Bytes of scratch that svoo_b200_cocluster / svoo_b200_sort_labels /
  * svoo_b200_sparse_attn need for these sizes (one value covers all three). */
 int svoo_b200_workspace_bytes(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* bytes_out);
@@ -86,13 +90,16 @@ int svoo_b200_centroid_update(const void* x, const int32_t* sorted_idx, const in
                               void* new_centroids, int32_t* sizes,
                               void* workspace, int64_t workspace_bytes, void* stream);
 
-/* y[bh,s,:] = x[bh,idx[bh,s],:]  (svoo/kernels/triton/permute.py:10-35,68-102). */
+/* y[bh,s,:] = x[bh,idx[bh,s],:] for s < N  (svoo/kernels/triton/permute.py:10-35,68-102).
+ * x_head_rows / y_head_rows are the rows between consecutive heads in x and y (>= N;
+ * N for dense [BH,N,128] tensors), so a [BH,N] block of a longer sequence can be
+ * permuted in place of the copy in svoo/models/hunyuan10/attention.py:995-997. */
 int svoo_b200_permute(const void* x, const int32_t* sorted_idx, int64_t BH, int64_t N, int64_t D,
-                      void* y, void* stream);
+                      int64_t x_head_rows, int64_t y_head_rows, void* y, void* stream);
 
 /* y[bh,idx[bh,s],:] = x[bh,s,:]  (svoo/kernels/triton/permute.py:39-65,105-130). */
 int svoo_b200_inverse_permute(const void* x, const int32_t* sorted_idx, int64_t BH, int64_t N, int64_t D,
-                              void* y, void* stream);
+                              int64_t x_head_rows, int64_t y_head_rows, void* y, void* stream);
 
 /* Cluster-block map (identify_dynamic_map, svoo/co_clustering.py:556-633, with
  * weighted_softmax :544-553) for bf16 centroids.  preserve_host[h] / cap_host[h]

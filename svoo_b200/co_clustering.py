@@ -1,0 +1,141 @@
+"""The reference's operator interface for the sparse-attention path, on the B200 kernels.
+
+Same names, argument meaning and error behaviour as svoo/co_clustering.py of the
+reference: co_cluster_tokens (:2402), identify_dynamic_map (:556),
+dynamic_block_sparse_fwd_flashinfer (:1231) / dynamic_block_sparse_fwd_triton (:1111).
+Inputs other than bf16 are computed in bf16 and returned in the input dtype.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import ops
+
+Ratio = Union[float, int, Sequence[float], torch.Tensor, None]
+
+
+def _as_bf16(x: torch.Tensor) -> torch.Tensor:
+    return x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+
+
+def draw_init_indices(BH: int, N: int, num_q: int, num_k: int, device, generator=None):
+    """Initial centroid token indices in the reference's draw order: q first, then k
+    (svoo/co_clustering.py:2417-2421)."""
+    q_idx = torch.randint(0, N, (BH, num_q), device=device, generator=generator)
+    k_idx = torch.randint(0, N, (BH, num_k), device=device, generator=generator)
+    return q_idx, k_idx
+
+
+def co_cluster(q_flat: torch.Tensor, k_flat: torch.Tensor, num_q_centroids: int, num_k_centroids: int,
+               max_iters: int = 10, *, init_indices=None, generator=None) -> ops.Clustering:
+    """co_cluster_tokens returning the full device-side result (labels, centroids, sizes and
+    the stable cluster-order permutations), everything int32 / bf16."""
+    assert q_flat.is_cuda and k_flat.is_cuda, "tensors must be on CUDA"
+    BH, N, D = q_flat.shape
+    if init_indices is None:
+        init_indices = draw_init_indices(BH, N, num_q_centroids, num_k_centroids, q_flat.device, generator)
+    q_idx, k_idx = init_indices
+    assert q_idx.shape == (BH, num_q_centroids) and k_idx.shape == (BH, num_k_centroids)
+    return ops.cocluster(_as_bf16(q_flat).contiguous(), _as_bf16(k_flat).contiguous(),
+                         q_idx.to(q_flat.device), k_idx.to(q_flat.device), max_iters)
+
+
+def co_cluster_tokens(q_flat, k_flat, num_q_centroids, num_k_centroids, max_iters=10, *, init_indices=None,
+                      generator=None):
+    """Drop-in for the reference's co_cluster_tokens: returns
+    (qlabels int64, qcentroids, q_cluster_sizes int32, klabels int64, kcentroids, k_cluster_sizes int32)."""
+    c = co_cluster(q_flat, k_flat, num_q_centroids, num_k_centroids, max_iters, init_indices=init_indices,
+                   generator=generator)
+    dt = q_flat.dtype
+    return (c.qlabels.long(), c.qcentroids.to(dt), c.qsizes, c.klabels.long(), c.kcentroids.to(dt), c.ksizes)
+
+
+def _ratio_values(r: Ratio, H: int):
+    if r is None:
+        return None, "none"
+    if isinstance(r, (list, tuple)) or (hasattr(r, "__len__") and len(r) == H):
+        # like the reference: through a float32 tensor, then python floats
+        return [float(v) for v in torch.as_tensor(r, dtype=torch.float32).tolist()], "list"
+    if isinstance(r, (int, float)):
+        return float(r), "scalar"
+    return None, "none"
+
+
+def keep_limits(kc_num: int, H: int, min_kc_ratio: Ratio, max_kc_ratio: Ratio):
+    """Per-head (floor, cap) in numbers of key clusters, with the reference's int() truncation
+    and list/scalar dispatch (svoo/co_clustering.py:589-627).  cap == kc_num means no cap."""
+    mn, mn_kind = _ratio_values(min_kc_ratio, H)
+    mx, mx_kind = _ratio_values(max_kc_ratio, H)
+    preserve = [0] * H
+    if mn_kind == "list":
+        preserve = [int(v * kc_num) if v > 0 else 0 for v in mn]
+    elif mn_kind == "scalar" and mn > 0:
+        preserve = [int(mn * kc_num)] * H
+    cap = [kc_num] * H
+    if mx_kind == "list":
+        for h in range(H):
+            if mx[h] > 0:
+                c = max(1, int(mx[h] * kc_num))
+                if mn_kind == "list":
+                    c = max(c, int(mn[h] * kc_num))
+                cap[h] = c
+    elif mx_kind == "scalar" and mx > 0:
+        c0 = max(1, int(mx * kc_num))
+        for h in range(H):
+            c = c0
+            if mn_kind == "list":
+                if mn[h] > 0:
+                    c = max(c, int(mn[h] * kc_num))
+                c = max(1, c)
+            elif mn_kind == "scalar" and mn > 0:
+                c = max(c, int(mn * kc_num))
+            cap[h] = c
+    return [min(p, kc_num) for p in preserve], [min(c, kc_num) for c in cap]
+
+
+def identify_dynamic_map(query_centroids, key_centroids, q_cluster_sizes, k_cluster_sizes, p, min_kc_ratio=0,
+                         max_kc_ratio=0):
+    """Bool map [B, H, QC, KC] of the key clusters each query cluster keeps
+    (svoo/co_clustering.py:556-633).  No host synchronisation."""
+    B, H, qc_num, D = query_centroids.shape
+    kc_num = key_centroids.shape[2]
+    if p >= 1.0:
+        return torch.ones(B, H, qc_num, kc_num, dtype=torch.bool, device=query_centroids.device)
+    preserve, cap = keep_limits(kc_num, H, min_kc_ratio, max_kc_ratio)
+    m = ops.block_map(_as_bf16(query_centroids).reshape(B * H, qc_num, D).contiguous(),
+                      _as_bf16(key_centroids).reshape(B * H, kc_num, D).contiguous(),
+                      k_cluster_sizes.reshape(B * H, kc_num), float(p), preserve * B, cap * B)
+    return m.view(B, H, qc_num, kc_num).view(torch.bool)
+
+
+def dynamic_block_sparse_fwd(q, k, v, block_mask_map, block_row_sz, block_col_sz, sm_scale=None,
+                             out_row_idx=None):
+    """Block-sparse attention over cluster-ordered q,k,v [B,H,S,D]; returns [B,H,S,D]."""
+    B, H, S, D = q.shape
+    qc_num = block_row_sz.shape[-1]
+    kc_num = block_col_sz.shape[-1]
+    assert block_mask_map.shape == (B, H, qc_num, kc_num)
+    assert q.is_cuda and k.is_cuda and v.is_cuda, "Inputs must be CUDA tensors"
+    assert q.dtype == k.dtype == v.dtype, "Input dtypes must match"
+    dev = q.device
+    q_off = ops.offsets_from_sizes(block_row_sz.reshape(B * H, qc_num).to(dev))
+    k_off = ops.offsets_from_sizes(block_col_sz.reshape(B * H, kc_num).to(dev))
+    m = block_mask_map.to(dev).reshape(B * H, qc_num, kc_num).contiguous()
+    m = m.view(torch.uint8) if m.dtype == torch.bool else m.to(torch.uint8)
+    o = ops.sparse_attn(_as_bf16(q).reshape(B * H, S, D).contiguous(), _as_bf16(k).reshape(B * H, S, D).contiguous(),
+                        _as_bf16(v).reshape(B * H, S, D).contiguous(), m, q_off, k_off, sm_scale,
+                        None if out_row_idx is None else out_row_idx.reshape(B * H, S).contiguous())
+    return o.view(B, H, S, D).to(q.dtype)
+
+
+def dynamic_block_sparse_fwd_flashinfer(q, k, v, block_mask_map, block_row_sz, block_col_sz, is_cpu: bool = True):
+    """Name and signature of the reference's default backend (svoo/co_clustering.py:1231-1239).
+    `is_cpu` only says where the map and sizes live; they are moved to the device either way."""
+    return dynamic_block_sparse_fwd(q, k, v, block_mask_map, block_row_sz, block_col_sz)
+
+
+def dynamic_block_sparse_fwd_triton(q, k, v, dynamic_map, qc_size, kc_size):
+    """Name and signature of the reference's alternative backend (svoo/co_clustering.py:1111)."""
+    return dynamic_block_sparse_fwd(q, k, v, dynamic_map, qc_size, kc_size)

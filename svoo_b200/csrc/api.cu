@@ -1,0 +1,230 @@
+// extern "C" entry points of libsvoo_b200.so: argument checks, workspace carving and the
+// launch sequences.  No entry point allocates or synchronises.
+#include "common.cuh"
+
+namespace svoo {
+cudaError_t launch_gather_rows(const void*, const int32_t*, void*, int64_t, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_prologue(const void*, const void*, void*, void*, int64_t, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_assign(const void*, const void*, const void*, int32_t*, int64_t, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_sort_labels(const int32_t*, int64_t, int64_t, int64_t, int32_t*, int32_t*, int32_t*, int32_t*,
+                               cudaStream_t);
+cudaError_t launch_centroid_update(const void*, const int32_t*, const int32_t*, const void*, void*, int32_t*, float*,
+                                   int64_t, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_offsets_from_sizes(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_permute(const void*, const int32_t*, void*, int64_t, int64_t, int64_t, int64_t, bool, cudaStream_t);
+cudaError_t launch_block_map(const void*, const void*, const int32_t*, uint8_t*, int64_t, int64_t, int64_t, float,
+                             const int32_t*, const int32_t*, cudaStream_t);
+cudaError_t launch_build_runs(const uint8_t*, const int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_build_qtiles(const int32_t*, int4*, int32_t*, int64_t, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, void*, const int32_t*, const int4*,
+                                   const int32_t*, const int2*, const int32_t*, int64_t, int64_t, int64_t, int64_t,
+                                   float, cudaStream_t);
+}  // namespace svoo
+
+namespace svoo {
+int64_t& launch_counter() {
+  static int64_t n = 0;
+  return n;
+}
+}  // namespace svoo
+
+using namespace svoo;
+
+namespace {
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_tokens(int64_t BH, int64_t N, int64_t D) {
+  if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
+  if (BH < 1 || BH > 65535 || N < 1 || N > (1 << 24)) return SVOO_ERR_SHAPE;
+  return SVOO_OK;
+}
+int check_clusters(int64_t K) {
+  if (K < 1) return SVOO_ERR_SHAPE;
+  if (K > SVOO_MAX_CLUSTERS) return SVOO_ERR_CLUSTERS;
+  return SVOO_OK;
+}
+#define SVOO_TRY(expr) do { int _rc = (expr); if (_rc != SVOO_OK) return _rc; } while (0)
+#define SVOO_CUDA(expr) do { cudaError_t _e = (expr); if (_e != cudaSuccess) return (int)_e; } while (0)
+
+template <typename T>
+inline T* ws_at(void* ws, int64_t off) { return reinterpret_cast<T*>(static_cast<char*>(ws) + off); }
+}  // namespace
+
+extern "C" {
+
+int svoo_b200_version(void) { return SVOO_B200_VERSION; }
+
+int64_t svoo_b200_launch_count(void) { return __atomic_load_n(&launch_counter(), __ATOMIC_RELAXED); }
+
+const char* svoo_b200_error_string(int code) {
+  switch (code) {
+    case SVOO_OK: return "ok";
+    case SVOO_ERR_NULL: return "a required pointer is null";
+    case SVOO_ERR_SHAPE: return "a size is out of the supported range";
+    case SVOO_ERR_HEAD_DIM: return "head dimension must be 128";
+    case SVOO_ERR_WORKSPACE: return "workspace too small";
+    case SVOO_ERR_ALIGN: return "tensor pointer is not 16-byte aligned";
+    case SVOO_ERR_CLUSTERS: return "cluster count above 1024";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown svoo_b200 error";
+  }
+}
+
+int svoo_b200_workspace_bytes(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* bytes_out) {
+  if (!bytes_out) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, N, kHeadDim));
+  SVOO_TRY(check_clusters(QC));
+  SVOO_TRY(check_clusters(KC));
+  *bytes_out = workspace_layout(BH, N, QC, KC).total;
+  return SVOO_OK;
+}
+
+int svoo_b200_cocluster_assign(const void* x, const void* form_centroids, const void* own_centroids, int64_t BH,
+                               int64_t N, int64_t D, int64_t K, int64_t J, int32_t* labels, void* workspace,
+                               int64_t workspace_bytes, void* stream) {
+  if (!x || !form_centroids || !own_centroids || !labels || !workspace) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, N, D));
+  SVOO_TRY(check_clusters(K));
+  SVOO_TRY(check_clusters(J));
+  if (!aligned16(x) || !aligned16(form_centroids) || !aligned16(own_centroids) || !aligned16(workspace))
+    return SVOO_ERR_ALIGN;
+  const Workspace w = workspace_layout(BH, N, K, J);
+  if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  SVOO_CUDA(launch_prologue(own_centroids, form_centroids, ws_at<void>(workspace, w.w_hi),
+                            ws_at<void>(workspace, w.w_lo), BH, J, K, st));
+  SVOO_CUDA(launch_assign(x, ws_at<void>(workspace, w.w_hi), ws_at<void>(workspace, w.w_lo), labels, BH, N, J, st));
+  return SVOO_OK;
+}
+
+int svoo_b200_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int64_t K, int32_t* sorted_idx,
+                          int32_t* offsets, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!labels || !sorted_idx || !offsets || !workspace) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, N, kHeadDim));
+  SVOO_TRY(check_clusters(K));
+  const Workspace w = workspace_layout(BH, N, K, K);
+  if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  SVOO_CUDA(launch_sort_labels(labels, BH, N, K, sorted_idx, offsets, nullptr, ws_at<int32_t>(workspace, w.chunk_hist),
+                               (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_centroid_update(const void* x, const int32_t* sorted_idx, const int32_t* offsets,
+                              const void* old_centroids, int64_t BH, int64_t N, int64_t D, int64_t K,
+                              void* new_centroids, int32_t* sizes, void* workspace, int64_t workspace_bytes,
+                              void* stream) {
+  if (!x || !sorted_idx || !offsets || !old_centroids || !new_centroids || !workspace) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, N, D));
+  SVOO_TRY(check_clusters(K));
+  if (!aligned16(x)) return SVOO_ERR_ALIGN;
+  const Workspace w = workspace_layout(BH, N, K, K);
+  if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  SVOO_CUDA(launch_centroid_update(x, sorted_idx, offsets, old_centroids, new_centroids, sizes,
+                                   ws_at<float>(workspace, w.partial), BH, N, K, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_cocluster(const void* q, const void* k, const int32_t* q_init_idx, const int32_t* k_init_idx, int64_t BH,
+                        int64_t N, int64_t D, int64_t QC, int64_t KC, int32_t iters, int32_t* qlabels,
+                        int32_t* klabels, void* qcentroids, void* kcentroids, int32_t* qsizes, int32_t* ksizes,
+                        int32_t* q_sorted_idx, int32_t* q_offsets, int32_t* k_sorted_idx, int32_t* k_offsets,
+                        void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!q || !k || !q_init_idx || !k_init_idx || !qlabels || !klabels || !qcentroids || !kcentroids || !qsizes ||
+      !ksizes || !q_sorted_idx || !q_offsets || !k_sorted_idx || !k_offsets || !workspace)
+    return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, N, D));
+  SVOO_TRY(check_clusters(QC));
+  SVOO_TRY(check_clusters(KC));
+  if (iters < 1 || iters > 1000) return SVOO_ERR_SHAPE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(qcentroids) || !aligned16(kcentroids) || !aligned16(workspace))
+    return SVOO_ERR_ALIGN;
+  const Workspace w = workspace_layout(BH, N, QC, KC);
+  if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  void* w_hi = ws_at<void>(workspace, w.w_hi);
+  void* w_lo = ws_at<void>(workspace, w.w_lo);
+  int32_t* hist = ws_at<int32_t>(workspace, w.chunk_hist);
+  float* partial = ws_at<float>(workspace, w.partial);
+
+  SVOO_CUDA(launch_gather_rows(q, q_init_idx, qcentroids, BH, N, QC, st));
+  SVOO_CUDA(launch_gather_rows(k, k_init_idx, kcentroids, BH, N, KC, st));
+  for (int it = 0; it < iters; ++it) {
+    // keys: profile over the query centroids
+    SVOO_CUDA(launch_prologue(kcentroids, qcentroids, w_hi, w_lo, BH, KC, QC, st));
+    SVOO_CUDA(launch_assign(k, w_hi, w_lo, klabels, BH, N, KC, st));
+    SVOO_CUDA(launch_sort_labels(klabels, BH, N, KC, k_sorted_idx, k_offsets, nullptr, hist, st));
+    SVOO_CUDA(launch_centroid_update(k, k_sorted_idx, k_offsets, kcentroids, kcentroids, ksizes, partial, BH, N, KC, st));
+    // queries: profile over the just-updated key centroids
+    SVOO_CUDA(launch_prologue(qcentroids, kcentroids, w_hi, w_lo, BH, QC, KC, st));
+    SVOO_CUDA(launch_assign(q, w_hi, w_lo, qlabels, BH, N, QC, st));
+    SVOO_CUDA(launch_sort_labels(qlabels, BH, N, QC, q_sorted_idx, q_offsets, nullptr, hist, st));
+    SVOO_CUDA(launch_centroid_update(q, q_sorted_idx, q_offsets, qcentroids, qcentroids, qsizes, partial, BH, N, QC, st));
+  }
+  return SVOO_OK;
+}
+
+int svoo_b200_permute(const void* x, const int32_t* sorted_idx, int64_t BH, int64_t N, int64_t D,
+                      int64_t x_head_rows, int64_t y_head_rows, void* y, void* stream) {
+  if (!x || !sorted_idx || !y) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, N, D));
+  if (x_head_rows < N || y_head_rows < N) return SVOO_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(y)) return SVOO_ERR_ALIGN;
+  SVOO_CUDA(launch_permute(x, sorted_idx, y, BH, N, x_head_rows, y_head_rows, false, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_inverse_permute(const void* x, const int32_t* sorted_idx, int64_t BH, int64_t N, int64_t D,
+                              int64_t x_head_rows, int64_t y_head_rows, void* y, void* stream) {
+  if (!x || !sorted_idx || !y) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, N, D));
+  if (x_head_rows < N || y_head_rows < N) return SVOO_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(y)) return SVOO_ERR_ALIGN;
+  SVOO_CUDA(launch_permute(x, sorted_idx, y, BH, N, x_head_rows, y_head_rows, true, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_block_map(const void* qcentroids, const void* kcentroids, const int32_t* ksizes, int64_t BH, int64_t QC,
+                        int64_t KC, int64_t D, float top_p, const int32_t* preserve_host, const int32_t* cap_host,
+                        uint8_t* map_out, void* stream) {
+  if (!qcentroids || !kcentroids || !ksizes || !preserve_host || !cap_host || !map_out) return SVOO_ERR_NULL;
+  if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
+  if (BH < 1 || BH > SVOO_MAX_HEADS) return SVOO_ERR_SHAPE;
+  SVOO_TRY(check_clusters(QC));
+  SVOO_TRY(check_clusters(KC));
+  if (!aligned16(qcentroids) || !aligned16(kcentroids)) return SVOO_ERR_ALIGN;
+  SVOO_CUDA(launch_block_map(qcentroids, kcentroids, ksizes, map_out, BH, QC, KC, top_p, preserve_host, cap_host,
+                             (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, int32_t* offsets, void* stream) {
+  if (!sizes || !offsets) return SVOO_ERR_NULL;
+  if (BH < 1 || BH > 65535) return SVOO_ERR_SHAPE;
+  SVOO_TRY(check_clusters(K));
+  SVOO_CUDA(launch_offsets_from_sizes(sizes, offsets, BH, K, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_sparse_attn(const void* q, const void* k, const void* v, const uint8_t* map, const int32_t* q_offsets,
+                          const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC,
+                          float sm_scale, void* out, const int32_t* out_row_idx, void* workspace,
+                          int64_t workspace_bytes, void* stream) {
+  if (!q || !k || !v || !map || !q_offsets || !k_offsets || !out || !workspace) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, S, D));
+  SVOO_TRY(check_clusters(QC));
+  SVOO_TRY(check_clusters(KC));
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(workspace))
+    return SVOO_ERR_ALIGN;
+  const Workspace w = workspace_layout(BH, S, QC, KC);
+  if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  int2* runs = ws_at<int2>(workspace, w.runs);
+  int32_t* nruns = ws_at<int32_t>(workspace, w.nruns);
+  int4* qtiles = ws_at<int4>(workspace, w.qtiles);
+  int32_t* nqtiles = ws_at<int32_t>(workspace, w.nqtiles);
+  SVOO_CUDA(launch_build_runs(map, k_offsets, runs, nruns, BH, QC, KC, st));
+  SVOO_CUDA(launch_build_qtiles(q_offsets, qtiles, nqtiles, BH, S, QC, st));
+  SVOO_CUDA(launch_sparse_attn_mma(q, k, v, out, out_row_idx, qtiles, nqtiles, runs, nruns, BH, S, QC, KC, sm_scale, st));
+  return SVOO_OK;
+}
+
+}  // extern "C"

@@ -220,6 +220,7 @@ cudaError_t launch_block_map(const void* qc, const void* kc, const int32_t* ksiz
   dim3 grid((unsigned)QC, (unsigned)BH);
   block_map_kernel<<<grid, 256, 0, st>>>((const bf16*)qc, (const bf16*)kc, ksizes, map, (int)QC, (int)KC, KCpad,
                                          (float)sqrt((double)kHeadDim), top_p, lim);
+  count_launches(1);
   return cudaGetLastError();
 }
 
@@ -228,12 +229,14 @@ cudaError_t launch_build_runs(const uint8_t* map, const int32_t* k_offsets, int2
   const int rows = (int)(BH * QC);
   build_runs_kernel<<<(unsigned)ceil_div(rows, 8), 256, 0, st>>>(map, k_offsets, runs, nruns, (int)QC, (int)KC,
                                                                  max_runs(KC), rows);
+  count_launches(1);
   return cudaGetLastError();
 }
 
 cudaError_t launch_build_qtiles(const int32_t* q_offsets, int4* qtiles, int32_t* nqtiles, int64_t BH, int64_t N,
                                 int64_t QC, cudaStream_t st) {
   build_qtiles_kernel<<<(unsigned)BH, 1024, 0, st>>>(q_offsets, qtiles, nqtiles, (int)QC, max_qtiles(N, QC));
+  count_launches(1);
   return cudaGetLastError();
 }
 

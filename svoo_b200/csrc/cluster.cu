@@ -473,6 +473,7 @@ cudaError_t launch_gather_rows(const void* x, const int32_t* idx, void* out, int
                                cudaStream_t st) {
   dim3 grid((unsigned)ceil_div64(K, 16), (unsigned)BH);
   gather_rows_kernel<<<grid, 256, 0, st>>>((const bf16*)x, idx, (bf16*)out, (int)N, (int)K);
+  count_launches(1);
   return cudaGetLastError();
 }
 
@@ -488,6 +489,7 @@ cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void*
   dim3 grid((unsigned)(Jpad / kProR), (unsigned)BH);
   profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo,
                                                    (int)J, (int)K, Jpad);
+  count_launches(1);
   return cudaGetLastError();
 }
 
@@ -501,6 +503,7 @@ cudaError_t launch_assign(const void* x, const void* w_hi, const void* w_lo, int
   dim3 grid((unsigned)ceil_div64(N, kAsgBM), (unsigned)BH);
   assign_kernel<<<grid, 128, kAsgSmem, st>>>((const bf16*)x, (const bf16*)w_hi, (const bf16*)w_lo, labels, (int)N,
                                              (int)J, pad_clusters(J));
+  count_launches(1);
   return cudaGetLastError();
 }
 
@@ -517,6 +520,7 @@ cudaError_t launch_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int
   label_hist_kernel<<<grid, 256, 0, st>>>(labels, chunk_hist, (int)N, (int)K, nchunks);
   label_scan_kernel<<<(unsigned)BH, 1024, 0, st>>>(chunk_hist, offsets, sizes, (int)K, nchunks);
   label_scatter_kernel<<<grid, 256, 8 * K * 4, st>>>(labels, chunk_hist, offsets, sorted_idx, (int)N, (int)K, nchunks);
+  count_launches(3);
   return cudaGetLastError();
 }
 
@@ -527,11 +531,13 @@ cudaError_t launch_centroid_update(const void* x, const int32_t* sorted_idx, con
   centroid_partial_kernel<<<grid, 256, 0, st>>>((const bf16*)x, sorted_idx, offsets, partial, (int)N, (int)K);
   dim3 grid2((unsigned)K, (unsigned)BH);
   centroid_finalize_kernel<<<grid2, 128, 0, st>>>(partial, offsets, (const bf16*)old_c, (bf16*)new_c, sizes, (int)K);
+  count_launches(2);
   return cudaGetLastError();
 }
 
 cudaError_t launch_offsets_from_sizes(const int32_t* sizes, int32_t* offsets, int64_t BH, int64_t K, cudaStream_t st) {
   offsets_from_sizes_kernel<<<(unsigned)BH, 1024, 0, st>>>(sizes, offsets, (int)K);
+  count_launches(1);
   return cudaGetLastError();
 }
 

@@ -57,13 +57,18 @@ __host__ inline Workspace workspace_layout(int64_t BH, int64_t N, int64_t QC, in
   w.labels_tmp = take(BH * N * 4);
   w.idx_tmp = take(BH * N * 4);
   w.off_tmp = take(BH * (Kmax + 1) * 4);
-  w.runs = take(BH * QC * (int64_t)max_runs(KC) * 8);
-  w.nruns = take(BH * QC * 4);
-  w.qtiles = take(BH * (int64_t)max_qtiles(N, QC) * 16);
+  // sized symmetrically in (QC, KC) so that one workspace serves either side
+  w.runs = take(BH * (QC * KC / 2 + QC + KC) * 8);
+  w.nruns = take(BH * Kmax * 4);
+  w.qtiles = take(BH * (int64_t)max_qtiles(N, Kmax) * 16);
   w.nqtiles = take(BH * 4);
   w.total = o;
   return w;
 }
+
+// Process-wide count of kernel launches (read through svoo_b200_launch_count()).
+int64_t& launch_counter();
+inline void count_launches(int n) { __atomic_fetch_add(&launch_counter(), (int64_t)n, __ATOMIC_RELAXED); }
 
 // ---------------------------------------------------------------------------------------
 // Small device utilities

@@ -10,13 +10,13 @@ constexpr int kPermRowsPerCta = 64;     // 256 threads = 16 rows per pass, 4 pas
 
 template <bool kInverse>
 __global__ void __launch_bounds__(256) permute_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
-                                                      uint4* __restrict__ y, int N) {
+                                                      uint4* __restrict__ y, int N, int64_t x_head_rows, int64_t y_head_rows) {
   const int bh = blockIdx.y;
   const int lane = threadIdx.x % 16, sub = threadIdx.x / 16;
   const int s_base = blockIdx.x * kPermRowsPerCta + sub;
   const int32_t* ib = idx + (int64_t)bh * N;
-  const uint4* xb = x + (int64_t)bh * N * 16;
-  uint4* yb = y + (int64_t)bh * N * 16;
+  const uint4* xb = x + (int64_t)bh * x_head_rows * 16;
+  uint4* yb = y + (int64_t)bh * y_head_rows * 16;
   int other[4];
   uint4 v[4];
 #pragma unroll
@@ -42,13 +42,14 @@ __global__ void __launch_bounds__(256) permute_kernel(const uint4* __restrict__ 
   }
 }
 
-cudaError_t launch_permute(const void* x, const int32_t* idx, void* y, int64_t BH, int64_t N, bool inverse,
-                           cudaStream_t st) {
+cudaError_t launch_permute(const void* x, const int32_t* idx, void* y, int64_t BH, int64_t N, int64_t x_head_rows,
+                           int64_t y_head_rows, bool inverse, cudaStream_t st) {
   dim3 grid((unsigned)ceil_div64(N, kPermRowsPerCta), (unsigned)BH);
   if (inverse)
-    permute_kernel<true><<<grid, 256, 0, st>>>((const uint4*)x, idx, (uint4*)y, (int)N);
+    permute_kernel<true><<<grid, 256, 0, st>>>((const uint4*)x, idx, (uint4*)y, (int)N, x_head_rows, y_head_rows);
   else
-    permute_kernel<false><<<grid, 256, 0, st>>>((const uint4*)x, idx, (uint4*)y, (int)N);
+    permute_kernel<false><<<grid, 256, 0, st>>>((const uint4*)x, idx, (uint4*)y, (int)N, x_head_rows, y_head_rows);
+  count_launches(1);
   return cudaGetLastError();
 }
 

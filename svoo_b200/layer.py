@@ -1,0 +1,106 @@
+"""The whole sparse-attention layer as one stream-ordered sequence of kernels:
+co-clustering -> cluster-order permute -> cluster-block map -> block-sparse attention
+with the inverse permutation fused into its store.
+
+Replaces semantic_aware_permutation + the sparse branch of attention_core_logic
+(svoo/models/wan/attention.py:958-1088,1159-1216) and, with text tokens, the
+Hunyuan variant (svoo/models/hunyuan10/attention.py:977-1110).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import co_clustering as cc
+from . import ops
+
+
+class StageTimer:
+    """CUDA-event marks on the launching stream, one per stage boundary of a layer call.
+    After a synchronize, `stage_ms()` gives the device time between consecutive marks."""
+
+    def __init__(self):
+        self.marks = []
+
+    def mark(self, name: str) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream())
+        self.marks.append((name, ev))
+
+    def stage_ms(self):
+        out = {}
+        for (_, a), (name, b) in zip(self.marks[:-1], self.marks[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
+
+
+@dataclasses.dataclass
+class LayerState:
+    """What a layer call leaves behind; `clustering` can be fed back in to reuse it."""
+    clustering: ops.Clustering
+    block_map: torch.Tensor          # uint8 [H, QC(+2), KC(+2)]
+    q_offsets: torch.Tensor
+    k_offsets: torch.Tensor
+
+
+def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *, num_q_centroids: int,
+                           num_k_centroids: int, kmeans_iters: int, top_p: float, min_kc_ratio=0, max_kc_ratio=0,
+                           init_indices=None, clustering: Optional[ops.Clustering] = None,
+                           context_length: int = 0, prompt_length: Optional[int] = None,
+                           return_state: bool = False, timer: Optional[StageTimer] = None):
+    """query/key/value: [1, H, S, 128] bf16 CUDA, S = video tokens + context_length text
+    tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order."""
+    cfg, H, S, D = query.shape
+    assert cfg == 1, "Batch size must be 1 for kmeans block sparse attention"
+    assert query.is_cuda and query.dtype == torch.bfloat16, "bf16 CUDA tensors expected"
+    n_video = S - context_length
+    q, k, v = query[0], key[0], value[0]
+    if context_length:
+        qv, kv = q[:, :n_video].contiguous(), k[:, :n_video].contiguous()
+    else:
+        qv, kv = q.contiguous(), k.contiguous()
+    mark = timer.mark if timer is not None else (lambda name: None)
+    mark("start")
+    c = clustering
+    if c is None:
+        c = cc.co_cluster(qv, kv, num_q_centroids, num_k_centroids, kmeans_iters, init_indices=init_indices)
+    mark("cocluster")
+    preserve, cap = cc.keep_limits(num_k_centroids, H, min_kc_ratio, max_kc_ratio)
+    if top_p >= 1.0:
+        m = torch.ones(H, num_q_centroids, num_k_centroids, dtype=torch.uint8, device=q.device)
+    else:
+        m = ops.block_map(c.qcentroids, c.kcentroids, c.ksizes, top_p, preserve, cap)
+    mark("block_map")
+
+    if context_length == 0:
+        qp = ops.permute(qv, c.q_sorted_idx)
+        kp = ops.permute(kv, c.k_sorted_idx)
+        vp = ops.permute(v.contiguous(), c.k_sorted_idx)
+        q_off, k_off, ridx = c.q_offsets, c.k_offsets, c.q_sorted_idx
+    else:
+        # text tokens stay where they are, as two extra blocks (prompt, unused prompt)
+        prompt = context_length if prompt_length is None else prompt_length
+        qp, kp, vp = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        ops.permute(q, c.q_sorted_idx, out=qp)
+        ops.permute(k, c.k_sorted_idx, out=kp)
+        ops.permute(v, c.k_sorted_idx, out=vp)
+        qp[:, n_video:], kp[:, n_video:], vp[:, n_video:] = q[:, n_video:], k[:, n_video:], v[:, n_video:]
+        m = F.pad(m, (0, 2, 0, 2), value=0)
+        m[:, -2, :-1] = 1
+        m[:, :-1, -2] = 1
+        m[:, -1, -1] = 1
+        tail = torch.tensor([prompt, context_length - prompt], dtype=torch.int32, device=q.device)
+        q_off = ops.offsets_from_sizes(torch.cat([c.qsizes, tail.expand(H, 2)], 1))
+        k_off = ops.offsets_from_sizes(torch.cat([c.ksizes, tail.expand(H, 2)], 1))
+        text_rows = torch.arange(n_video, S, dtype=torch.int32, device=q.device)
+        ridx = torch.cat([c.q_sorted_idx, text_rows.expand(H, context_length)], 1).contiguous()
+    mark("permute")
+    out = ops.sparse_attn(qp, kp, vp, m.contiguous(), q_off, k_off, D ** -0.5, out_row_idx=ridx)
+    mark("attention")
+    out = out.unsqueeze(0)
+    if return_state:
+        return out, LayerState(c, m, q_off, k_off)
+    return out

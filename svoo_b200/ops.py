@@ -1,0 +1,216 @@
+"""Torch-tensor front end of the C ABI: one function per entry point.
+
+Tensors are CUDA, contiguous; token tensors are bf16 [BH, N, 128].  Work is enqueued
+on torch's current stream; nothing here synchronises with the host.
+"""
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+
+from ._lib import LIB, check
+
+HEAD_DIM = 128
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("svoo_b200 ops need CUDA tensors; there is no CPU path")
+        if not t.is_contiguous():
+            raise ValueError("svoo_b200 ops need contiguous tensors")
+
+
+def _tokens(x: torch.Tensor) -> Tuple[int, int, int]:
+    if x.dim() != 3 or x.dtype != torch.bfloat16:
+        raise ValueError(f"expected bf16 [BH, N, {HEAD_DIM}] tokens, got {x.dtype} {tuple(x.shape)}")
+    return x.shape
+
+
+def workspace_bytes(BH: int, N: int, QC: int, KC: int) -> int:
+    out = ctypes.c_int64(0)
+    check(LIB.svoo_b200_workspace_bytes(BH, N, QC, KC, ctypes.byref(out)), "workspace_bytes")
+    return out.value
+
+
+def workspace(device: torch.device, BH: int, N: int, QC: int, KC: int) -> torch.Tensor:
+    """A cached uint8 scratch tensor of at least the needed size, one per device and stream."""
+    need = workspace_bytes(BH, N, QC, KC)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+@dataclasses.dataclass
+class Clustering:
+    """Everything one co-clustering call produces (all on device)."""
+    qlabels: torch.Tensor      # int32 [BH, N]
+    klabels: torch.Tensor
+    qcentroids: torch.Tensor   # bf16 [BH, QC, 128]
+    kcentroids: torch.Tensor
+    qsizes: torch.Tensor       # int32 [BH, QC]
+    ksizes: torch.Tensor
+    q_sorted_idx: torch.Tensor  # int32 [BH, N] stable cluster-order permutation
+    k_sorted_idx: torch.Tensor
+    q_offsets: torch.Tensor     # int32 [BH, QC+1]
+    k_offsets: torch.Tensor
+
+
+def cocluster(q: torch.Tensor, k: torch.Tensor, q_init_idx: torch.Tensor, k_init_idx: torch.Tensor,
+              iters: int) -> Clustering:
+    _need_cuda(q, k, q_init_idx, k_init_idx)
+    BH, N, D = _tokens(q)
+    if k.shape != q.shape or k.dtype != q.dtype:
+        raise ValueError("q and k must have the same shape and dtype")
+    QC, KC = q_init_idx.shape[-1], k_init_idx.shape[-1]
+    dev = q.device
+    qi = q_init_idx.to(torch.int32).contiguous()
+    ki = k_init_idx.to(torch.int32).contiguous()
+    i32 = dict(dtype=torch.int32, device=dev)
+    c = Clustering(
+        torch.empty(BH, N, **i32), torch.empty(BH, N, **i32),
+        torch.empty(BH, QC, D, dtype=q.dtype, device=dev), torch.empty(BH, KC, D, dtype=q.dtype, device=dev),
+        torch.empty(BH, QC, **i32), torch.empty(BH, KC, **i32),
+        torch.empty(BH, N, **i32), torch.empty(BH, N, **i32),
+        torch.empty(BH, QC + 1, **i32), torch.empty(BH, KC + 1, **i32))
+    ws = workspace(dev, BH, N, QC, KC)
+    check(LIB.svoo_b200_cocluster(
+        q.data_ptr(), k.data_ptr(), qi.data_ptr(), ki.data_ptr(), BH, N, D, QC, KC, int(iters),
+        c.qlabels.data_ptr(), c.klabels.data_ptr(), c.qcentroids.data_ptr(), c.kcentroids.data_ptr(),
+        c.qsizes.data_ptr(), c.ksizes.data_ptr(), c.q_sorted_idx.data_ptr(), c.q_offsets.data_ptr(),
+        c.k_sorted_idx.data_ptr(), c.k_offsets.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "cocluster")
+    return c
+
+
+def cocluster_assign(x: torch.Tensor, form_centroids: torch.Tensor, own_centroids: torch.Tensor) -> torch.Tensor:
+    """int32 labels [BH, N] of tokens x among own_centroids, profiles formed over form_centroids."""
+    _need_cuda(x, form_centroids, own_centroids)
+    BH, N, D = _tokens(x)
+    K, J = form_centroids.shape[1], own_centroids.shape[1]
+    labels = torch.empty(BH, N, dtype=torch.int32, device=x.device)
+    ws = workspace(x.device, BH, N, K, J)
+    check(LIB.svoo_b200_cocluster_assign(x.data_ptr(), form_centroids.data_ptr(), own_centroids.data_ptr(), BH, N, D,
+                                         K, J, labels.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+          "cocluster_assign")
+    return labels
+
+
+def sort_labels(labels: torch.Tensor, num_clusters: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Stable cluster-order permutation: (sorted_idx int32 [BH,N], offsets int32 [BH,K+1]).
+    Labels must lie in [0, num_clusters)."""
+    _need_cuda(labels)
+    lab = labels.to(torch.int32).contiguous()
+    BH, N = lab.shape
+    idx = torch.empty_like(lab)
+    off = torch.empty(BH, num_clusters + 1, dtype=torch.int32, device=lab.device)
+    ws = workspace(lab.device, BH, N, num_clusters, num_clusters)
+    check(LIB.svoo_b200_sort_labels(lab.data_ptr(), BH, N, num_clusters, idx.data_ptr(), off.data_ptr(),
+                                    ws.data_ptr(), ws.numel(), _stream()), "sort_labels")
+    return idx, off
+
+
+def centroid_update(x: torch.Tensor, sorted_idx: torch.Tensor, offsets: torch.Tensor,
+                    old_centroids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    _need_cuda(x, sorted_idx, offsets, old_centroids)
+    BH, N, D = _tokens(x)
+    K = old_centroids.shape[1]
+    new = torch.empty_like(old_centroids)
+    sizes = torch.empty(BH, K, dtype=torch.int32, device=x.device)
+    ws = workspace(x.device, BH, N, K, K)
+    check(LIB.svoo_b200_centroid_update(x.data_ptr(), sorted_idx.data_ptr(), offsets.data_ptr(),
+                                        old_centroids.data_ptr(), BH, N, D, K, new.data_ptr(), sizes.data_ptr(),
+                                        ws.data_ptr(), ws.numel(), _stream()), "centroid_update")
+    return new, sizes
+
+
+def _head_rows(t: torch.Tensor, n: int) -> int:
+    """Rows between consecutive heads of a [BH, >=n, 128] tensor whose rows are dense."""
+    if t.dim() != 3 or t.shape[-1] != HEAD_DIM or t.stride(-1) != 1 or t.stride(1) != HEAD_DIM or t.shape[1] < n:
+        raise ValueError("expected [BH, rows, 128] with dense rows")
+    if t.shape[0] > 1 and t.stride(0) % HEAD_DIM:
+        raise ValueError("head stride must be a whole number of rows")
+    return t.stride(0) // HEAD_DIM if t.shape[0] > 1 else max(t.shape[1], n)
+
+
+def permute(x: torch.Tensor, sorted_idx: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[bh, s] = x[bh, idx[bh, s]] for s < N = idx.shape[1]; x and out may be [BH, N, 128]
+    views (leading rows) of longer per-head sequences."""
+    N = sorted_idx.shape[1]
+    BH = sorted_idx.shape[0]
+    if not (x.is_cuda and sorted_idx.is_cuda and sorted_idx.is_contiguous() and x.dtype == torch.bfloat16):
+        raise ValueError("permute needs CUDA bf16 tokens and a contiguous int32 index")
+    y = torch.empty(BH, N, HEAD_DIM, dtype=x.dtype, device=x.device) if out is None else out
+    check(LIB.svoo_b200_permute(x.data_ptr(), sorted_idx.data_ptr(), BH, N, HEAD_DIM, _head_rows(x, N),
+                                _head_rows(y, N), y.data_ptr(), _stream()), "permute")
+    return y
+
+
+def inverse_permute(x: torch.Tensor, sorted_idx: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[bh, idx[bh, s]] = x[bh, s] for s < N = idx.shape[1]."""
+    N = sorted_idx.shape[1]
+    BH = sorted_idx.shape[0]
+    if not (x.is_cuda and sorted_idx.is_cuda and sorted_idx.is_contiguous() and x.dtype == torch.bfloat16):
+        raise ValueError("inverse_permute needs CUDA bf16 tokens and a contiguous int32 index")
+    y = torch.empty(BH, N, HEAD_DIM, dtype=x.dtype, device=x.device) if out is None else out
+    check(LIB.svoo_b200_inverse_permute(x.data_ptr(), sorted_idx.data_ptr(), BH, N, HEAD_DIM, _head_rows(x, N),
+                                        _head_rows(y, N), y.data_ptr(), _stream()), "inverse_permute")
+    return y
+
+
+def block_map(qcentroids: torch.Tensor, kcentroids: torch.Tensor, ksizes: torch.Tensor, top_p: float,
+              preserve: Sequence[int], cap: Sequence[int]) -> torch.Tensor:
+    """uint8 [BH, QC, KC]; preserve / cap are per-head python ints (numbers of key clusters)."""
+    _need_cuda(qcentroids, kcentroids, ksizes)
+    BH, QC, D = qcentroids.shape
+    KC = kcentroids.shape[1]
+    if qcentroids.dtype != torch.bfloat16 or kcentroids.dtype != torch.bfloat16:
+        raise ValueError("block_map needs bf16 centroids")
+    if len(preserve) != BH or len(cap) != BH:
+        raise ValueError("preserve and cap need one entry per head")
+    out = torch.empty(BH, QC, KC, dtype=torch.uint8, device=qcentroids.device)
+    arr = ctypes.c_int32 * BH
+    ks = ksizes.to(torch.int32).contiguous()
+    check(LIB.svoo_b200_block_map(qcentroids.data_ptr(), kcentroids.data_ptr(), ks.data_ptr(), BH, QC, KC, D,
+                                  float(top_p), arr(*[int(v) for v in preserve]), arr(*[int(v) for v in cap]),
+                                  out.data_ptr(), _stream()), "block_map")
+    return out
+
+
+def offsets_from_sizes(sizes: torch.Tensor) -> torch.Tensor:
+    _need_cuda(sizes)
+    s = sizes.to(torch.int32).contiguous()
+    BH, K = s.shape
+    off = torch.empty(BH, K + 1, dtype=torch.int32, device=s.device)
+    check(LIB.svoo_b200_offsets_from_sizes(s.data_ptr(), BH, K, off.data_ptr(), _stream()), "offsets_from_sizes")
+    return off
+
+
+def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_map_u8: torch.Tensor,
+                q_offsets: torch.Tensor, k_offsets: torch.Tensor, sm_scale: Optional[float] = None,
+                out_row_idx: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Block-sparse attention over cluster-ordered q,k,v [BH,S,128].  With out_row_idx the
+    result rows are scattered to their original positions (fused inverse permutation)."""
+    _need_cuda(q, k, v, block_map_u8, q_offsets, k_offsets)
+    BH, S, D = _tokens(q)
+    QC, KC = q_offsets.shape[1] - 1, k_offsets.shape[1] - 1
+    if tuple(block_map_u8.shape) != (BH, QC, KC) or block_map_u8.dtype not in (torch.uint8, torch.bool):
+        raise ValueError("block map must be uint8/bool [BH, QC, KC]")
+    y = torch.empty_like(q) if out is None else out
+    ws = workspace(q.device, BH, S, QC, KC)
+    scale = D ** -0.5 if sm_scale is None else float(sm_scale)
+    ridx = 0 if out_row_idx is None else out_row_idx.data_ptr()
+    check(LIB.svoo_b200_sparse_attn(q.data_ptr(), k.data_ptr(), v.data_ptr(), block_map_u8.data_ptr(),
+                                    q_offsets.data_ptr(), k_offsets.data_ptr(), BH, S, D, QC, KC, scale,
+                                    y.data_ptr(), ridx, ws.data_ptr(), ws.numel(), _stream()), "sparse_attn")
+    return y

@@ -1,0 +1,69 @@
+"""The C-ABI shared library: loads, exports every declared symbol, rejects bad arguments
+on the host (no kernel is launched here, so this runs without a GPU)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from svoo_b200 import build
+    build.build()
+    from svoo_b200 import _lib
+    return _lib
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "svoo_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(svoo_b200_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    names = declared_functions()
+    assert len(names) >= 12
+    raw = ctypes.CDLL(lib._build.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), f"{n} declared in include/svoo_b200.h but not exported"
+        assert n in lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(lib.SIGNATURES) == names
+
+
+def test_version_and_error_strings(lib):
+    assert lib.LIB.svoo_b200_version() == 100
+    assert lib.LIB.svoo_b200_error_string(0) == b"ok"
+    assert b"128" in lib.LIB.svoo_b200_error_string(-3)
+    with pytest.raises(ValueError):
+        lib.check(-1, "x")
+    with pytest.raises(lib.SvooB200Error):
+        lib.check(700, "x")
+
+
+def test_workspace_bytes(lib):
+    out = ctypes.c_int64(0)
+    assert lib.LIB.svoo_b200_workspace_bytes(40, 75600, 100, 500, ctypes.byref(out)) == 0
+    big = out.value
+    assert 50e6 < big < 2e9
+    assert lib.LIB.svoo_b200_workspace_bytes(40, 75600, 500, 100, ctypes.byref(out)) == 0
+    assert out.value == big                                   # symmetric in (QC, KC)
+    assert lib.LIB.svoo_b200_workspace_bytes(40, 75600, 100, 2000, ctypes.byref(out)) == -6
+    assert lib.LIB.svoo_b200_workspace_bytes(0, 75600, 100, 500, ctypes.byref(out)) == -2
+    assert lib.LIB.svoo_b200_workspace_bytes(1, 10, 1, 1, None) == -1
+
+
+def test_host_side_argument_checks(lib):
+    L = lib.LIB
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p = (p + 255) // 256 * 256
+    assert L.svoo_b200_permute(None, p, 1, 4, 128, 4, 4, p, None) == -1
+    assert L.svoo_b200_permute(p, p, 1, 4, 64, 4, 4, p, None) == -3
+    assert L.svoo_b200_permute(p + 2, p, 1, 4, 128, 4, 4, p, None) == -5
+    assert L.svoo_b200_permute(p, p, 1, 4, 128, 2, 4, p, None) == -2
+    assert L.svoo_b200_sort_labels(p, 1, 4, 4, p, p, p, 16, None) == -4
+    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 2, 2000, 0.1, p, None, p, 1 << 30, None) == -6
+    assert L.svoo_b200_cocluster(p, p, p, p, 1, 4, 128, 2, 2, 0, p, p, p, p, p, p, p, p, p, p, p, 1 << 30, None) == -2

@@ -1,0 +1,57 @@
+"""Head sharding and the Ulysses all-to-all layouts, world_size 2 and 4 over gloo on CPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from svoo_b200 import parallel
+
+
+def test_head_partition():
+    assert parallel.head_partition(40, 8) == [list(range(i * 5, i * 5 + 5)) for i in range(8)]
+    parts = parallel.head_partition(12, 8)
+    assert [len(p) for p in parts] == [2, 2, 2, 2, 1, 1, 1, 1]
+    assert sorted(h for p in parts for h in p) == list(range(12))
+    w = [0.25, 0.05, 0.24, 0.06, 0.2, 0.1, 0.15, 0.15]
+    parts = parallel.head_partition(8, 4, w)
+    assert sorted(h for p in parts for h in p) == list(range(8)) and all(len(p) == 2 for p in parts)
+    loads = [sum(w[h] for h in p) for p in parts]
+    assert max(loads) - min(loads) < 0.011                    # contiguous split would give 0.30 vs 0.30 vs ... worse
+    contiguous = [sum(w[2 * r:2 * r + 2]) for r in range(4)]
+    assert max(loads) <= max(contiguous)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, H, N, weights):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        D = 8
+        g = torch.Generator().manual_seed(0)
+        full = torch.randn(N, H, D, generator=g)              # the same on every rank
+        n_loc = N // world
+        mine = full[rank * n_loc:(rank + 1) * n_loc].contiguous()
+        parts = parallel.head_partition(H, world, weights)
+        heads = parallel.seq_to_head_shard(mine, parts)
+        expect = full[:, parts[rank], :].permute(1, 0, 2)
+        assert torch.equal(heads, expect), "sequence -> head shard layout"
+        back = parallel.head_to_seq_shard(heads * 2.0, parts)
+        assert torch.equal(back, mine * 2.0), "head -> sequence shard layout"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,H,weights", [(2, 4, None), (2, 6, [0.3, 0.1, 0.2, 0.05, 0.25, 0.1]), (4, 8, None)])
+def test_ulysses_layout_round_trip(world, H, weights):
+    mp.spawn(_worker, args=(world, _free_port(), H, 24, weights), nprocs=world, join=True)
