@@ -124,6 +124,21 @@ int svoo_b200_sparse_attn(const void* q, const void* k, const void* v, const uin
                           void* out, const int32_t* out_row_idx,
                           void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Same contract as svoo_b200_sparse_attn, computed by the warp-level-MMA (mma.sync)
+ * kernel instead of the tcgen05 one.  Kept as an independent on-device cross-check of
+ * the tensor-core kernel at sizes the CPU oracle cannot reach; not used by the layer. */
+int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, const uint8_t* map,
+                               const int32_t* q_offsets, const int32_t* k_offsets,
+                               int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, float sm_scale,
+                               void* out, const int32_t* out_row_idx,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Byte offset, inside a workspace of these sizes, of a 4-word int32 status block that
+ * svoo_b200_sparse_attn clears when it is enqueued.  Word 0 becomes non-zero if a CTA of
+ * the attention kernel gave up on one of its bounded barrier waits (its output rows are
+ * then not written).  No counterpart in the reference. */
+int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* offset_out);
+
 /* Exclusive prefix of cluster sizes [BH,K] -> offsets [BH,K+1]
  * (the torch.cumsum of svoo/co_clustering.py:1147-1148). */
 int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, int32_t* offsets, void* stream);

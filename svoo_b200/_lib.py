@@ -37,6 +37,10 @@ SIGNATURES = {
     "svoo_b200_sparse_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                       c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
                                       c_void_p]),
+    "svoo_b200_sparse_attn_simt": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                           c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
+                                           c_void_p]),
+    "svoo_b200_status_offset": (c_int, [c_int64, c_int64, c_int64, c_int64, _I64P]),
     "svoo_b200_offsets_from_sizes": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
 }
 

@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(256) build_runs_kernel(const uint8_t* __restri
 // One CTA per head: the 128-row query tiles of every non-empty query cluster.
 __global__ void __launch_bounds__(1024) build_qtiles_kernel(const int32_t* __restrict__ q_offsets,
                                                             int4* __restrict__ qtiles, int32_t* __restrict__ nqtiles,
-                                                            int QC, int max_tiles) {
+                                                            int QC, int max_tiles, int tile_rows) {
   __shared__ int warp_tot[32];
   const int bh = blockIdx.x, i = threadIdx.x, lane = i % 32, warp = i / 32;
   int begin = 0, end = 0;
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(1024) build_qtiles_kernel(const int32_t* __res
     begin = q_offsets[(int64_t)bh * (QC + 1) + i];
     end = q_offsets[(int64_t)bh * (QC + 1) + i + 1];
   }
-  const int nt = (end - begin + kAttnBM - 1) / kAttnBM;
+  const int nt = (end - begin + tile_rows - 1) / tile_rows;
   int incl = nt;
 #pragma unroll
   for (int s = 1; s < 32; s <<= 1) {
@@ -202,8 +202,8 @@ __global__ void __launch_bounds__(1024) build_qtiles_kernel(const int32_t* __res
   __syncthreads();
   int pos = incl - nt + (warp ? warp_tot[warp - 1] : 0);
   int4* out = qtiles + (int64_t)bh * max_tiles;
-  for (int r = begin; r < end; r += kAttnBM, ++pos)
-    if (pos < max_tiles) out[pos] = make_int4(i, r, min(r + kAttnBM, end), 0);
+  for (int r = begin; r < end; r += tile_rows, ++pos)
+    if (pos < max_tiles) out[pos] = make_int4(i, r, min(r + tile_rows, end), 0);
   if (i == 1023) nqtiles[bh] = min(warp_tot[31], max_tiles);
 }
 
@@ -234,8 +234,8 @@ cudaError_t launch_build_runs(const uint8_t* map, const int32_t* k_offsets, int2
 }
 
 cudaError_t launch_build_qtiles(const int32_t* q_offsets, int4* qtiles, int32_t* nqtiles, int64_t BH, int64_t N,
-                                int64_t QC, cudaStream_t st) {
-  build_qtiles_kernel<<<(unsigned)BH, 1024, 0, st>>>(q_offsets, qtiles, nqtiles, (int)QC, max_qtiles(N, QC));
+                                int64_t QC, int tile_rows, cudaStream_t st) {
+  build_qtiles_kernel<<<(unsigned)BH, 1024, 0, st>>>(q_offsets, qtiles, nqtiles, (int)QC, max_qtiles(N, QC), tile_rows);
   count_launches(1);
   return cudaGetLastError();
 }

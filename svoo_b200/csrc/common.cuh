@@ -30,9 +30,7 @@ struct Workspace {
   int64_t partial;       // float [BH, Kmax, slabs, 128] centroid partial sums
   int64_t w_hi;          // bf16  [BH, Jpad, 128]
   int64_t w_lo;          // bf16  [BH, Jpad, 128]
-  int64_t labels_tmp;    // int32 [BH, N]
-  int64_t idx_tmp;       // int32 [BH, N]
-  int64_t off_tmp;       // int32 [BH, Kmax+1]
+  int64_t status;        // int32 [4]: word 0 != 0 after a kernel gave up on a bounded wait
   int64_t runs;          // int2  [BH, QC, max_runs]
   int64_t nruns;         // int32 [BH, QC]
   int64_t qtiles;        // int4  [BH, max_qtiles]
@@ -54,9 +52,7 @@ __host__ inline Workspace workspace_layout(int64_t BH, int64_t N, int64_t QC, in
   w.partial = take(BH * Kmax * kCentroidSlabs * kHeadDim * 4);
   w.w_hi = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
   w.w_lo = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
-  w.labels_tmp = take(BH * N * 4);
-  w.idx_tmp = take(BH * N * 4);
-  w.off_tmp = take(BH * (Kmax + 1) * 4);
+  w.status = take(16);
   // sized symmetrically in (QC, KC) so that one workspace serves either side
   w.runs = take(BH * (QC * KC / 2 + QC + KC) * 8);
   w.nruns = take(BH * Kmax * 4);

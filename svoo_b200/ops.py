@@ -198,19 +198,34 @@ def offsets_from_sizes(sizes: torch.Tensor) -> torch.Tensor:
 
 def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_map_u8: torch.Tensor,
                 q_offsets: torch.Tensor, k_offsets: torch.Tensor, sm_scale: Optional[float] = None,
-                out_row_idx: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out_row_idx: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                kernel: str = "tcgen05") -> torch.Tensor:
     """Block-sparse attention over cluster-ordered q,k,v [BH,S,128].  With out_row_idx the
-    result rows are scattered to their original positions (fused inverse permutation)."""
+    result rows are scattered to their original positions (fused inverse permutation).
+    kernel="simt" selects the mma.sync cross-check kernel."""
     _need_cuda(q, k, v, block_map_u8, q_offsets, k_offsets)
     BH, S, D = _tokens(q)
     QC, KC = q_offsets.shape[1] - 1, k_offsets.shape[1] - 1
     if tuple(block_map_u8.shape) != (BH, QC, KC) or block_map_u8.dtype not in (torch.uint8, torch.bool):
         raise ValueError("block map must be uint8/bool [BH, QC, KC]")
+    if kernel not in ("tcgen05", "simt"):
+        raise ValueError("kernel must be 'tcgen05' or 'simt'")
     y = torch.empty_like(q) if out is None else out
     ws = workspace(q.device, BH, S, QC, KC)
     scale = D ** -0.5 if sm_scale is None else float(sm_scale)
     ridx = 0 if out_row_idx is None else out_row_idx.data_ptr()
-    check(LIB.svoo_b200_sparse_attn(q.data_ptr(), k.data_ptr(), v.data_ptr(), block_map_u8.data_ptr(),
-                                    q_offsets.data_ptr(), k_offsets.data_ptr(), BH, S, D, QC, KC, scale,
-                                    y.data_ptr(), ridx, ws.data_ptr(), ws.numel(), _stream()), "sparse_attn")
+    fn = LIB.svoo_b200_sparse_attn if kernel == "tcgen05" else LIB.svoo_b200_sparse_attn_simt
+    check(fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), block_map_u8.data_ptr(), q_offsets.data_ptr(),
+             k_offsets.data_ptr(), BH, S, D, QC, KC, scale, y.data_ptr(), ridx, ws.data_ptr(), ws.numel(), _stream()),
+          "sparse_attn")
     return y
+
+
+def attention_status(device: torch.device, BH: int, S: int, QC: int, KC: int) -> int:
+    """Status word of the last svoo_b200_sparse_attn call that used this device's cached
+    workspace with these sizes (synchronises).  0 = every CTA completed; non-zero = a CTA gave
+    up on a bounded barrier wait and left its rows unwritten."""
+    off = ctypes.c_int64(0)
+    check(LIB.svoo_b200_status_offset(BH, S, QC, KC, ctypes.byref(off)), "status_offset")
+    ws = workspace(device, BH, S, QC, KC)
+    return int(ws[off.value:off.value + 4].view(torch.int32).item())

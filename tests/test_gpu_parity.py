@@ -308,6 +308,52 @@ def test_sparse_attention_fused_inverse_permutation(dev):
     assert torch.equal(fused, ops.inverse_permute(plain, idx))
 
 
+def test_tensor_core_kernel_against_mma_sync_kernel(dev):
+    """The tcgen05 kernel and the independent mma.sync kernel on a problem too large for the
+    CPU oracle: 2 heads x 32,760 tokens, 100 x 500 clusters of random sizes, density 0.15."""
+    ops = _mods()[0]
+    g = torch.Generator("cpu").manual_seed(11)
+    H, S, QC, KC = 2, 32760, 100, 500
+
+    def sizes(n):
+        cuts = torch.sort(torch.randint(0, S + 1, (H, n - 1), generator=g), -1).values
+        edges = torch.cat([torch.zeros(H, 1, dtype=torch.long), cuts, torch.full((H, 1), S)], 1)
+        return edges.to(torch.int32)
+
+    q_off, k_off = sizes(QC).to(dev), sizes(KC).to(dev)
+    q, k, v = (torch.randn(H, S, 128, generator=g).bfloat16().to(dev) for _ in range(3))
+    m = (torch.rand(H, QC, KC, generator=g) < 0.15).to(torch.uint8).to(dev)
+    m[:, 7] = 0                                              # a query cluster without keys
+    idx = torch.stack([torch.randperm(S, generator=g) for _ in range(H)]).to(torch.int32).to(dev)
+    a = ops.sparse_attn(q, k, v, m, q_off, k_off, out_row_idx=idx)
+    assert ops.attention_status(dev, H, S, QC, KC) == 0
+    b = ops.sparse_attn(q, k, v, m, q_off, k_off, out_row_idx=idx, kernel="simt")
+    assert torch.isfinite(a.float()).all()
+    assert (a.float() - b.float()).abs().max() <= ATTN_ATOL
+    assert cosine(a, b) >= ATTN_COS
+    rows = idx[0, int(q_off[0, 7]):int(q_off[0, 8])].long()
+    assert (a[0, rows] == 0).all()
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "simt"])
+def test_both_attention_kernels_against_oracle(dev, kernel):
+    ops = _mods()[0]
+    g = torch.Generator("cpu").manual_seed(21)
+    q_sizes, k_sizes = [300, 1, 255, 256, 257, 0, 131], [128, 129, 1, 0, 500, 442]
+    S = sum(q_sizes)
+    assert S == sum(k_sizes)
+    H = 2
+    q, k, v = (torch.randn(1, H, S, 128, generator=g).bfloat16() for _ in range(3))
+    m = torch.rand(1, H, len(q_sizes), len(k_sizes), generator=g) < 0.6
+    qs = torch.tensor(q_sizes, dtype=torch.int32).expand(1, H, -1).contiguous()
+    ks = torch.tensor(k_sizes, dtype=torch.int32).expand(1, H, -1).contiguous()
+    ref = O.block_sparse_attention(q, k, v, m, qs, ks)
+    got = ops.sparse_attn(q[0].to(dev), k[0].to(dev), v[0].to(dev), m[0].to(dev).view(torch.uint8),
+                          ops.offsets_from_sizes(qs[0].to(dev)), ops.offsets_from_sizes(ks[0].to(dev)), kernel=kernel)
+    assert (got.cpu().float() - ref[0].float()).abs().max() <= ATTN_ATOL
+    assert cosine(got.cpu(), ref[0]) >= ATTN_COS
+
+
 # ----------------------------------------------------------------------------------------
 # whole layer
 # ----------------------------------------------------------------------------------------
