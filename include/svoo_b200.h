@@ -34,7 +34,8 @@ enum {
   SVOO_ERR_HEAD_DIM = -3,    /* D != 128                                         */
   SVOO_ERR_WORKSPACE = -4,   /* workspace too small (see *_workspace_bytes)      */
   SVOO_ERR_ALIGN = -5,       /* a tensor pointer is not 16-byte aligned          */
-  SVOO_ERR_CLUSTERS = -6     /* cluster count above SVOO_MAX_CLUSTERS            */
+  SVOO_ERR_CLUSTERS = -6,    /* cluster count above SVOO_MAX_CLUSTERS            */
+  SVOO_ERR_STATIC_SCRATCH = -7 /* problem too large for the built-in scratch array */
 };
 
 #define SVOO_MAX_CLUSTERS 1024   /* per side; the reference ships QC=256, KC=1024 */
@@ -81,6 +82,24 @@ int svoo_b200_cocluster_assign(const void* x, const void* form_centroids, const 
 int svoo_b200_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int64_t K,
                           int32_t* sorted_idx, int32_t* offsets,
                           void* workspace, int64_t workspace_bytes, void* stream);
+
+/* svoo_b200_sort_labels without a workspace argument, for callers that are not able to
+ * allocate device memory when they call the library (a process whose GPU memory is
+ * partitioned once at start-up, a plug-in that only gets raw pointers from its host, a
+ * loop that must not hit the synchronisation an allocation implies).  This entry point has
+ * no counterpart in the reference.  Same inputs, outputs and results as
+ * svoo_b200_sort_labels; its scratch is a 4 MiB array built into the library image, which
+ * every GPU that loads the library keeps resident until the process exits.
+ *   - Limit: BH * ceil(N / 2048) * K <= 1,048,576, otherwise SVOO_ERR_STATIC_SCRATCH is
+ *     returned and nothing is launched (40 heads x 75,600 tokens x 500 clusters fits).
+ *   - It calls no allocating routine.  The first call made with a given device current
+ *     looks up the array's device address; make that first call outside any stream capture.
+ *   - All calls on one GPU share the one array.  It holds whatever the previous call left
+ *     (the kernels overwrite every entry they later read, so no clearing is needed), and
+ *     two calls that run concurrently on the same GPU -- different streams, or different
+ *     host threads -- would overwrite each other's histograms: order them. */
+int svoo_b200_sort_labels_static(const int32_t* labels, int64_t BH, int64_t N, int64_t K,
+                                 int32_t* sorted_idx, int32_t* offsets, void* stream);
 
 /* Mean of the tokens of each cluster (fp32 sums in a fixed order, bf16 result),
  * empty clusters keep `old_centroids` (svoo/co_clustering.py:253-303).  In place

@@ -27,6 +27,7 @@ SIGNATURES = {
                                            c_void_p, c_void_p, c_int64, c_void_p]),
     "svoo_b200_sort_labels": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                       c_void_p]),
+    "svoo_b200_sort_labels_static": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "svoo_b200_centroid_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                           c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "svoo_b200_permute": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),

@@ -68,6 +68,7 @@ const char* svoo_b200_error_string(int code) {
     case SVOO_ERR_WORKSPACE: return "workspace too small";
     case SVOO_ERR_ALIGN: return "tensor pointer is not 16-byte aligned";
     case SVOO_ERR_CLUSTERS: return "cluster count above 1024";
+    case SVOO_ERR_STATIC_SCRATCH: return "problem too large for the built-in scratch array (BH*ceil(N/2048)*K > 1048576)";
     default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown svoo_b200 error";
   }
 }

@@ -542,3 +542,52 @@ cudaError_t launch_offsets_from_sizes(const int32_t* sizes, int32_t* offsets, in
 }
 
 }  // namespace svoo
+
+// ---------------------------------------------------------------------------------------
+// svoo_b200_sort_labels_static: the label sort for callers that cannot hand over a workspace.
+//
+// Some hosts of this library are not allowed to allocate device memory at the point where
+// they call it: a serving process whose HBM is carved up once at start-up, a plug-in that
+// only ever receives raw pointers from its host framework and has no allocator of its own,
+// or a latency-critical loop that must not risk the implicit device synchronisation of an
+// allocation.  For them the per-chunk histogram scratch of the sort lives in the array
+// below instead of a caller-provided workspace.  The price is a fixed 4 MiB of device
+// memory on every GPU that loads the library, held until the process exits, and a size
+// limit: BH * ceil(N / 2048) * K must not exceed kStaticSortInts.
+//
+// `g_static_sort_scratch` names the array for device code.  In host code the same name is
+// only a stand-in symbol, not a device address, so the launcher asks the runtime for the
+// real address once per device (cudaGetSymbolAddress, with that device current) and
+// passes that pointer to the kernels.
+// ---------------------------------------------------------------------------------------
+namespace svoo {
+constexpr int64_t kStaticSortInts = 1 << 20;                       // 4 MiB of int32
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) int32_t g_static_sort_scratch[kStaticSortInts];
+}  // namespace svoo
+
+extern "C" int svoo_b200_sort_labels_static(const int32_t* labels, int64_t BH, int64_t N, int64_t K,
+                                            int32_t* sorted_idx, int32_t* offsets, void* stream) {
+  using namespace svoo;
+  if (!labels || !sorted_idx || !offsets) return SVOO_ERR_NULL;
+  if (BH < 1 || BH > 65535 || N < 1 || N > (1 << 24) || K < 1) return SVOO_ERR_SHAPE;
+  if (K > SVOO_MAX_CLUSTERS) return SVOO_ERR_CLUSTERS;
+  if (BH * (int64_t)sort_chunks(N) * K > kStaticSortInts) return SVOO_ERR_STATIC_SCRATCH;
+  // Address of the array on the current device, looked up on the first call made with that
+  // device current.  Two host threads racing here would store the same value.
+  static int32_t* scratch_of_device[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return SVOO_ERR_SHAPE;
+  int32_t* scratch = scratch_of_device[dev];
+  if (!scratch) {
+    e = cudaGetSymbolAddress((void**)&scratch, g_static_sort_scratch);
+    if (e != cudaSuccess) return (int)e;
+    scratch_of_device[dev] = scratch;
+  }
+  // Nothing in the array has to start at zero: label_hist_kernel writes every
+  // [head, chunk, cluster] entry that the scan and scatter kernels read afterwards.
+  e = launch_sort_labels(labels, BH, N, K, sorted_idx, offsets, nullptr, scratch, (cudaStream_t)stream);
+  return e == cudaSuccess ? SVOO_OK : (int)e;
+}
