@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_mma_kernel(
   }
   // key-tile cursor: run index and first row of the tile inside that run
   int r_cur = 0, p_cur = 0, e_cur = 0;
-  if (nr > 0) { const int2 r = rl[0]; p_cur = max(r.x, 0); e_cur = min(r.y, S); }
+  if (nr > 0) { const int2 r = rl[0]; p_cur = max(r.x, 0); e_cur = min(r.x + rl[1].y - r.y, S); }
   if (nr > 0) load_kv_tile(kv_s, kv_s + kBN * kRowBytes, kb, vb, p_cur, e_cur, tid);
   cp_async_commit();
 
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(256, 1) sparse_attn_mma_kernel(
     int r_nxt = r_cur, p_nxt = p_cur + kBN, e_nxt = e_cur;
     if (p_nxt >= e_cur) {
       r_nxt = r_cur + 1;
-      if (r_nxt < nr) { const int2 r = rl[r_nxt]; p_nxt = max(r.x, 0); e_nxt = min(r.y, S); }
+      if (r_nxt < nr) { const int2 r = rl[r_nxt]; p_nxt = max(r.x, 0); e_nxt = min(r.x + rl[r_nxt + 1].y - r.y, S); }
     }
     if (r_nxt < nr) {
       const uint32_t dst = kv_s + (stage ^ 1) * (2 * kBN * kRowBytes);

@@ -1,26 +1,30 @@
-// Block-sparse attention over cluster-ordered Q/K/V on the 5th-generation tensor cores.
+// Block-sparse attention on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
-// One CTA owns up to two 128-row query tiles of one query cluster (they share the key
-// runs the cluster's map row selects) and walks those runs 128 key rows at a time:
+// One CTA owns up to two 128-row query tiles of one query cluster.  The key rows that the
+// cluster's map row selects form a list of runs of the cluster-ordered K/V; the CTA walks
+// their concatenation 128 keys at a time, so key tiles are always full except the last one
+// (tiles are packed across run boundaries by gathering rows, which a TMA box cannot do).
 //
-//   warp 0      TMA producer: Q tiles once, then K and V tiles through two 2-stage rings
-//               (cp.async.bulk.tensor 2-D boxes of 64 columns x 128 rows, 128-byte swizzle)
-//   warp 1      MMA issuer (one elected thread): S_w = Q_w K^T into TMEM (tcgen05.mma, both
+//   warps 0-3   softmax of query tile 0: thread r owns row r (TMEM lane r): running max and
+//   warps 4-7   sum, P written back over S as packed bf16; same for tile 1
+//   warps 8-11  K loader (and Q, once): cp.async 16-byte gathers into the 128-byte-swizzled
+//               K-major layout the MMA descriptors expect, fence.proxy.async, mbarrier arrive
+//   warps 12-15 V loader, same, two-stage rings for K and for V
+//   warp 16     MMA issuer (one elected thread): S_w = Q_w K^T into TMEM (tcgen05.mma, both
 //               operands from shared memory), then O_w += P_w V with P_w read from TMEM
-//   warps 4-7   softmax of query tile 0: thread r owns row r (TMEM lane r): running max and
-//   warps 8-11  sum, P written back over S as packed bf16; same for tile 1
+//
+// Rows can be fetched through index vectors (q_row_idx / kv_row_idx): the cluster-order
+// permutation of Q, K and V is then fused into the loads and no permuted copy exists.
 //
 // The two query tiles ping-pong: while one tile's rows are in the softmax, the tensor
 // core works on the other tile's products.  O stays in TMEM; it is rescaled by the owning
 // softmax thread only when a row maximum grows by more than 2^8 (the running sum uses the
-// same stale maximum, so the final normalisation is exact).  Key tiles never cross a run
-// end: columns past it are masked to -inf.  Every mbarrier wait is bounded; on expiry the
-// CTA raises an abort flag, sets the status word and leaves through the normal teardown.
+// same stale maximum, so the final normalisation is exact).  Every mbarrier wait is bounded;
+// on expiry the CTA raises an abort flag, sets the status word and leaves through the
+// normal teardown.
 //
 // TMEM columns (512 allocated): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).
 // Semantics: svoo/co_clustering.py:949-1108 (scale D^-0.5, zero output without keys).
-#include <cuda.h>
-
 #include "common.cuh"
 
 namespace svoo {
@@ -31,8 +35,11 @@ constexpr int kBN = 128;                 // key rows per step
 constexpr int kTile = 128 * kRowBytes;   // 32 KB: one [128 x 128] bf16 tile = two 16 KB boxes
 constexpr int kBox = 128 * 128;          // 16 KB: 128 rows x 64 columns
 constexpr int kSmemTiles = 6 * kTile;    // Q0 Q1 | K0 K1 | V0 V1
-constexpr int kSmemBytes = kSmemTiles + 256 + 1024;   // + barriers + alignment slack
-constexpr int kThreads = 384;
+constexpr int kMaxRunsSmem = SVOO_MAX_CLUSTERS / 2 + 2;
+constexpr int kRunTableBytes = (kMaxRunsSmem * 8 + 255) / 256 * 256;
+constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 2048 + 1024;   // + barriers, run table, row maps, slack
+constexpr int kThreads = 544;            // 8 softmax + 4 K-loader + 4 V-loader + 1 MMA warps
+constexpr int kLoaderThreads = 128;      // per tensor (K, V): one thread per key row of a tile
 constexpr float kRescaleThreshold = 8.0f;
 constexpr long long kWaitCycles = 2000000000LL;       // ~1 s
 
@@ -71,10 +78,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
   }
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -108,6 +111,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr) : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Issues the load only; the registers are valid after the next tmem_wait_ld().
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -134,6 +150,41 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ void row_max(const uint32_t (&r)[32], float& m) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) m = fmaxf(m, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+}
+// Only the first `valid` of the 32 columns count (valid may be <= 0 or >= 32).
+__device__ __forceinline__ void row_max_masked(const uint32_t (&r)[32], float& m, int valid) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) m = fmaxf(m, i < valid ? __uint_as_float(r[i]) : -INFINITY);
+}
+// p = exp2(s * scale + neg_m) for 32 columns -> 16 packed bf16 pairs; columns >= valid give 0.
+__device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale, float neg_m,
+                                         float& l0, float& l1, int valid) {
+  if (valid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * i]), scale, neg_m));
+      const float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), scale, neg_m));
+      l0 += p0;
+      l1 += p1;
+      pk[i] = pack_bf16x2(p0, p1);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * i]), scale, neg_m));
+      float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), scale, neg_m));
+      p0 = (2 * i < valid) ? p0 : 0.f;
+      p1 = (2 * i + 1 < valid) ? p1 : 0.f;
+      l0 += p0;
+      l1 += p1;
+      pk[i] = pack_bf16x2(p0, p1);
+    }
+  }
+}
+
 // Shared-memory matrix descriptors, 128-byte swizzle, descriptor version 1 (sm_100).
 //   K-major  (Q, K: rows = M/N index, 64 contiguous elements of the reduction dim per 128-byte row):
 //            8-row groups 1024 B apart (SBO); LBO unused.
@@ -151,38 +202,50 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
 
-// Cursor over the 128-row key tiles of a run list.
-struct TileCursor {
-  const int2* runs;
-  int nr, S, r, p, e;
-  __device__ __forceinline__ void load_run() {
-    if (r < nr) { const int2 x = runs[r]; p = max(x.x, 0); e = min(x.y, S); }
+// Byte offset of 16-byte chunk `chunk` (0..15) of row `row` (0..127) inside a [128 x 128] bf16
+// tile stored as two [128 rows x 128 B] halves with the 128-byte swizzle (chunk ^= row % 8).
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  return (uint32_t)((chunk >> 3) * kBox + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+// Gathers the 128 key rows of packed tile j (virtual rows [128 j, 128 j + 128) of the
+// concatenated runs) into one swizzled tile; rows past the end are zero-filled.  Thread tl
+// (0..127) first resolves the source row of virtual row 128 j + tl into `rowmap` (shared
+// memory), then the 128 threads copy the tile with 16 lanes per 256-byte row.
+__device__ __forceinline__ void gather_tile(uint32_t dst, const bf16* __restrict__ base, const int32_t* __restrict__ row_idx,
+                                            const int2* runs_s, int nr, int& r_cur, int* rowmap, int bar_id, int j,
+                                            int L, int tl) {
+  const int v = j * kBN + tl;
+  int p = -1;
+  if (v < L) {
+    while (r_cur + 1 < nr && v >= runs_s[r_cur + 1].y) ++r_cur;
+    p = runs_s[r_cur].x + (v - runs_s[r_cur].y);
+    if (row_idx) p = __ldg(row_idx + p);
   }
-  __device__ __forceinline__ TileCursor(const int2* runs_, int nr_, int S_) : runs(runs_), nr(nr_), S(S_), r(0), p(0), e(0) {
-    load_run();
-    skip_empty();
+  rowmap[tl] = p;
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(kLoaderThreads) : "memory");
+#pragma unroll 4
+  for (int it = 0; it < 16; ++it) {
+    const int row = it * 8 + (tl >> 4), chunk = tl & 15;
+    const int src = rowmap[row];
+    cp_async16(dst + tile_off(row, chunk), base + (int64_t)(src < 0 ? 0 : src) * kHeadDim + chunk * 8, src >= 0);
   }
-  __device__ __forceinline__ void skip_empty() { while (r < nr && p >= e) { ++r; load_run(); } }
-  __device__ __forceinline__ bool done() const { return r >= nr; }
-  __device__ __forceinline__ int valid() const { return min(e - p, kBN); }
-  __device__ __forceinline__ void next() {
-    p += kBN;
-    if (p >= e) { ++r; load_run(); skip_empty(); }
-  }
-};
+}
+
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
-    const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-    const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ out, const int32_t* __restrict__ out_row_idx,
-    const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles, const int2* __restrict__ runs,
-    const int32_t* __restrict__ nruns, int S, int QC, int max_tiles, int max_runs, float scale_log2,
-    int32_t* __restrict__ status) {
+    const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, bf16* __restrict__ out,
+    const int32_t* __restrict__ q_row_idx, const int32_t* __restrict__ kv_row_idx,
+    const int32_t* __restrict__ out_row_idx, const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles,
+    const int2* __restrict__ runs, const int32_t* __restrict__ nruns, int S, int QC, int max_tiles, int max_runs,
+    float scale_log2, int32_t* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
   const int bh = blockIdx.y;
   if ((int)blockIdx.x >= nqtiles[bh]) return;
   const int4 tile = qtiles[(int64_t)bh * max_tiles + blockIdx.x];
   const int qi = tile.x, row0 = tile.y, row1 = tile.z;
-  const int nr = nruns[(int64_t)bh * QC + qi];
+  const int nr = min(nruns[(int64_t)bh * QC + qi], kMaxRunsSmem - 1);
   const int2* rl = runs + ((int64_t)bh * QC + qi) * max_runs;
   const int nq = (row1 - row0 > kBM) ? 2 : 1;
 
@@ -192,15 +255,23 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemTiles + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemTiles + NUM_BARS * 8 + 8);
+  int2* runs_s = reinterpret_cast<int2*>(gen_base + kSmemTiles + 256);
+  int* rowmaps = reinterpret_cast<int*>(gen_base + kSmemTiles + 256 + kRunTableBytes);   // [K,V][stage][128]
   auto bar = [&](int i) { return bars + 8u * i; };
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   if (tid == 0) {
-    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_READY || i == P_READY + 1) ? kBM : 1);
+    for (int i = 0; i < NUM_BARS; ++i) {
+      int count = 1;
+      if (i == P_READY || i == P_READY + 1) count = kBM;
+      if (i == Q_FULL || i == K_FULL || i == K_FULL + 1 || i == V_FULL || i == V_FULL + 1) count = kLoaderThreads;
+      mbar_init(bar(i), count);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  for (int i = tid; i <= nr; i += kThreads) runs_s[i] = rl[i];
+  if (warp == 16) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -208,29 +279,72 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const int L = runs_s[nr].y;                      // selected key rows in total
+  const int T = (L + kBN - 1) / kBN;               // packed key tiles
 
-  if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      mbar_expect_tx(bar(Q_FULL), nq * kTile);
-      for (int w = 0; w < nq; ++w)
-        for (int h = 0; h < 2; ++h)
-          tma_load_2d(q_s + w * kTile + h * kBox, &tm_q, h * 64, bh * S + row0 + w * kBM, bar(Q_FULL));
-      int j = 0;
-      for (TileCursor c(rl, nr, S); !c.done(); c.next(), ++j) {
+  if (warp >= 8 && warp < 12) {
+    // ---------------------------------------------------------------- Q and K loader
+    const int tl = tid - 8 * 32;
+    if (T > 0) {
+      const bf16* qb = q + (int64_t)bh * S * kHeadDim;
+      const int32_t* qidx = q_row_idx ? q_row_idx + (int64_t)bh * S : nullptr;
+      for (int it = 0; it < nq * 16; ++it) {
+        const int row = it * 8 + (tl >> 4), chunk = tl & 15;
+        const int grow = row0 + row;
+        const bool ok = grow < row1;
+        int p = ok ? grow : row0;
+        if (ok && qidx) p = __ldg(qidx + p);
+        cp_async16(q_s + (row >> 7) * kTile + tile_off(row & 127, chunk), qb + (int64_t)p * kHeadDim + chunk * 8, ok);
+      }
+      const bf16* kb = k + (int64_t)bh * S * kHeadDim;
+      const int32_t* kidx = kv_row_idx ? kv_row_idx + (int64_t)bh * S : nullptr;
+      int r_cur = 0;
+      bool ok = true;
+      for (int j = 0; j < T && ok; ++j) {
         const int s = j & 1;
-        const uint32_t ph = ((j >> 1) & 1) ^ 1;
-        if (!mbar_wait(bar(K_EMPTY + s), ph, abort_flag)) break;
-        mbar_expect_tx(bar(K_FULL + s), kTile);
-        for (int h = 0; h < 2; ++h) tma_load_2d(k_s + s * kTile + h * kBox, &tm_k, h * 64, bh * S + c.p, bar(K_FULL + s));
-        if (!mbar_wait(bar(V_EMPTY + s), ph, abort_flag)) break;
-        mbar_expect_tx(bar(V_FULL + s), kTile);
-        for (int h = 0; h < 2; ++h) tma_load_2d(v_s + s * kTile + h * kBox, &tm_v, h * 64, bh * S + c.p, bar(V_FULL + s));
+        ok = mbar_wait(bar(K_EMPTY + s), ((j >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        gather_tile(k_s + s * kTile, kb, kidx, runs_s, nr, r_cur, rowmaps + s * 128, 1, j, L, tl);
+        cp_async_commit();
+        if (j >= 1) {
+          cp_async_wait<1>();
+          fence_async_proxy();
+          if (j == 1) mbar_arrive(bar(Q_FULL));
+          mbar_arrive(bar(K_FULL + (s ^ 1)));
+        }
+      }
+      cp_async_wait<0>();
+      fence_async_proxy();
+      if (ok) {
+        if (T == 1) mbar_arrive(bar(Q_FULL));
+        mbar_arrive(bar(K_FULL + ((T - 1) & 1)));
       }
     }
-  } else if (warp == 1) {
+  } else if (warp >= 12 && warp < 16) {
+    // ---------------------------------------------------------------- V loader
+    const int tl = tid - 12 * 32;
+    const bf16* vb = v + (int64_t)bh * S * kHeadDim;
+    const int32_t* kidx = kv_row_idx ? kv_row_idx + (int64_t)bh * S : nullptr;
+    int r_cur = 0;
+    bool ok = true;
+    for (int j = 0; j < T && ok; ++j) {
+      const int s = j & 1;
+      ok = mbar_wait(bar(V_EMPTY + s), ((j >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) break;
+      gather_tile(v_s + s * kTile, vb, kidx, runs_s, nr, r_cur, rowmaps + 256 + s * 128, 2, j, L, tl);
+      cp_async_commit();
+      if (j >= 1) {
+        cp_async_wait<1>();
+        fence_async_proxy();
+        mbar_arrive(bar(V_FULL + (s ^ 1)));
+      }
+    }
+    cp_async_wait<0>();
+    fence_async_proxy();
+    if (ok && T > 0) mbar_arrive(bar(V_FULL + ((T - 1) & 1)));
+  } else if (warp == 16) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && T > 0) {
       auto issue_qk = [&](int w, int s) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -244,17 +358,15 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
           umma_ts(tmem + 256 + w * 128, tmem + w * 128 + ks * 8, desc_mnmajor(v_s + s * kTile + ks * 2048), kIdescPV,
                   (accumulate || ks > 0) ? 1u : 0u);
       };
-      TileCursor c(rl, nr, S);
-      bool ok = !c.done() && mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
+      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
       if (ok) {
         tc_fence_after();
         for (int w = 0; w < nq; ++w) { issue_qk(w, 0); tc_commit(bar(S_FULL + w)); }
         tc_commit(bar(K_EMPTY));
       }
-      for (int j = 0; ok && !c.done(); ++j) {
+      for (int j = 0; ok && j < T; ++j) {
         const int s = j & 1, sn = s ^ 1;
-        c.next();
-        const bool has_next = !c.done();
+        const bool has_next = j + 1 < T;
         if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) break;
         for (int w = 0; w < nq && ok; ++w) {
           ok = mbar_wait(bar(P_READY + w), j & 1, abort_flag);
@@ -277,9 +389,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         if (has_next) tc_commit(bar(K_EMPTY + sn));
       }
     }
-  } else if (warp >= 4) {
+  } else {
     // ---------------------------------------------------------------- softmax + epilogue
-    const int w = (warp - 4) >> 2;
+    const int w = warp >> 2;
     if (w < nq) {
       const int quad = warp & 3;
       const int r_local = quad * 32 + lane;                       // row of the query tile == TMEM lane
@@ -288,62 +400,78 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       const uint32_t o_t = tmem + lane_addr + 256 + w * 128;      // O columns
       float m_used = -INFINITY, l_sum = 0.f;
       bool ok = true;
-      int j = 0;
-      uint32_t r[32];
-      for (TileCursor c(rl, nr, S); !c.done(); c.next(), ++j) {
-        const int valid = c.valid();
-        ok = mbar_wait(bar(S_FULL + w), j & 1, abort_flag);
+      uint32_t ra[32], rb[32];
+      for (int j = 0; j < T; ++j) {
+        const int valid = min(L - j * kBN, kBN);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + w), j & 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
-        // pass 1: row maximum of the scaled scores
-        float m_tile = -INFINITY;
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(s_t + ch * 32, r);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = __uint_as_float(r[i]) * scale_log2;
-            m_tile = fmaxf(m_tile, (ch * 32 + i < valid) ? v : -INFINITY);
-          }
+        // pass 1: row maximum of the raw scores (the scale is positive), two loads in flight
+        float m_raw = -INFINITY;
+        tmem_ld32_nowait(s_t, ra);
+        tmem_ld32_nowait(s_t + 32, rb);
+        tmem_wait_ld();
+        if (valid >= kBN) {
+          row_max(ra, m_raw);
+          row_max(rb, m_raw);
+          tmem_ld32_nowait(s_t + 64, ra);
+          tmem_ld32_nowait(s_t + 96, rb);
+          tmem_wait_ld();
+          row_max(ra, m_raw);
+          row_max(rb, m_raw);
+        } else {
+          row_max_masked(ra, m_raw, valid);
+          row_max_masked(rb, m_raw, valid - 32);
+          tmem_ld32_nowait(s_t + 64, ra);
+          tmem_ld32_nowait(s_t + 96, rb);
+          tmem_wait_ld();
+          row_max_masked(ra, m_raw, valid - 64);
+          row_max_masked(rb, m_raw, valid - 96);
         }
+        const float m_tile = m_raw * scale_log2;
         if (j == 0) {
           m_used = m_tile;
         } else {
           const bool need = m_tile > m_used + kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
-            ok = mbar_wait(bar(O_DONE + w), (j - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + w), (j - 1) & 1, abort_flag));
             if (!ok) break;
             tc_fence_after();
             const float alpha = need ? fast_exp2(m_used - m_tile) : 1.0f;
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {
-              tmem_ld32(o_t + ch * 32, r);
+              tmem_ld32(o_t + ch * 32, ra);
 #pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st32(o_t + ch * 32, r);
+              for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
+              tmem_st32(o_t + ch * 32, ra);
             }
             tmem_wait_st();
             l_sum *= alpha;
             if (need) m_used = m_tile;
           }
         }
-        // pass 2: P = exp2(s - m), packed bf16 written over the first 64 columns of S
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(s_t + ch * 32, r);
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int c0 = ch * 32 + 2 * i;
-            float p0 = fast_exp2(__uint_as_float(r[2 * i]) * scale_log2 - m_used);
-            float p1 = fast_exp2(__uint_as_float(r[2 * i + 1]) * scale_log2 - m_used);
-            p0 = (c0 < valid) ? p0 : 0.f;
-            p1 = (c0 + 1 < valid) ? p1 : 0.f;
-            l_sum += p0 + p1;
-            pk[i] = pack_bf16x2(p0, p1);
-          }
-          tmem_st16(s_t + ch * 16, pk);
-        }
+        // pass 2: P = exp2(s * scale - m) as packed bf16 over the first 64 columns of S; the
+        // load of the next 32 columns is in flight while the current 32 are processed
+        const float neg_m = -m_used;
+        float l0 = 0.f, l1 = 0.f;
+        uint32_t pk[16];
+        tmem_ld32_nowait(s_t, ra);
+        tmem_wait_ld();
+        tmem_ld32_nowait(s_t + 32, rb);
+        exp_pack(ra, pk, scale_log2, neg_m, l0, l1, valid);
+        tmem_st16(s_t, pk);
+        tmem_wait_ld();
+        tmem_ld32_nowait(s_t + 64, ra);
+        exp_pack(rb, pk, scale_log2, neg_m, l0, l1, valid - 32);
+        tmem_st16(s_t + 16, pk);
+        tmem_wait_ld();
+        tmem_ld32_nowait(s_t + 96, rb);
+        exp_pack(ra, pk, scale_log2, neg_m, l0, l1, valid - 64);
+        tmem_st16(s_t + 32, pk);
+        tmem_wait_ld();
+        exp_pack(rb, pk, scale_log2, neg_m, l0, l1, valid - 96);
+        tmem_st16(s_t + 48, pk);
+        l_sum += l0 + l1;
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(P_READY + w));
@@ -354,26 +482,26 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       int dst = row;
       if (store && out_row_idx) dst = out_row_idx[(int64_t)bh * S + row];
       bf16* orow = out + ((int64_t)bh * S + (store ? min(max(dst, 0), S - 1) : 0)) * kHeadDim;
-      if (j == 0 || !ok) {
-        if (store && ok) {
+      if (T == 0) {
+        if (store) {
 #pragma unroll
           for (int ch = 0; ch < 16; ++ch) reinterpret_cast<uint4*>(orow)[ch] = make_uint4(0, 0, 0, 0);
         }
-      } else if (mbar_wait(bar(O_DONE + w), (j - 1) & 1, abort_flag)) {
+      } else if (ok && __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + w), (T - 1) & 1, abort_flag))) {
         tc_fence_after();
         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
 #pragma unroll 1
         for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(o_t + ch * 32, r);
+          tmem_ld32(o_t + ch * 32, ra);
           if (store) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
-              v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
-              v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
-              v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
-              reinterpret_cast<uint4*>(orow)[ch * 4 + g] = v;
+              uint4 val;
+              val.x = pack_bf16x2(__uint_as_float(ra[8 * g + 0]) * inv, __uint_as_float(ra[8 * g + 1]) * inv);
+              val.y = pack_bf16x2(__uint_as_float(ra[8 * g + 2]) * inv, __uint_as_float(ra[8 * g + 3]) * inv);
+              val.z = pack_bf16x2(__uint_as_float(ra[8 * g + 4]) * inv, __uint_as_float(ra[8 * g + 5]) * inv);
+              val.w = pack_bf16x2(__uint_as_float(ra[8 * g + 6]) * inv, __uint_as_float(ra[8 * g + 7]) * inv);
+              reinterpret_cast<uint4*>(orow)[ch * 4 + g] = val;
             }
           }
         }
@@ -384,57 +512,25 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag) atomicExch(status, 1);
-  if (warp == 1) {
+  if (warp == 16) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// [rows, 128] bf16 row-major tensor, boxes of 64 columns x 128 rows, 128-byte swizzle, zero fill.
-static bool make_row_map(CUtensorMap* map, const void* ptr, int64_t rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)kRowBytes};
-  const cuuint32_t box[2] = {64, 128};
-  const cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 }  // namespace tc
 
-cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, void* out, const int32_t* out_row_idx,
-                                  const int4* qtiles, const int32_t* nqtiles, const int2* runs, const int32_t* nruns,
-                                  int32_t* status, int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale,
-                                  cudaStream_t st) {
-  alignas(64) CUtensorMap mq, mk, mv;
-  if (!tc::make_row_map(&mq, q, BH * S) || !tc::make_row_map(&mk, k, BH * S) || !tc::make_row_map(&mv, v, BH * S))
-    return cudaErrorInvalidValue;
+cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, void* out, const int32_t* q_row_idx,
+                                  const int32_t* kv_row_idx, const int32_t* out_row_idx, const int4* qtiles,
+                                  const int32_t* nqtiles, const int2* runs, const int32_t* nruns, int32_t* status,
+                                  int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(tc::sparse_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        tc::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)max_qtiles(S, QC), (unsigned)BH);
   tc::sparse_attn_tc_kernel<<<grid, tc::kThreads, tc::kSmemBytes, st>>>(
-      mq, mk, mv, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC),
-      max_runs(KC), sm_scale * 1.4426950408889634f, status);
+      (const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)out, q_row_idx, kv_row_idx, out_row_idx, qtiles, nqtiles,
+      runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), max_runs(KC), sm_scale * 1.4426950408889634f, status);
   count_launches(1);
   return cudaGetLastError();
 }

@@ -134,7 +134,10 @@ __global__ void __launch_bounds__(256) block_map_kernel(const bf16* __restrict__
 }
 
 // One warp per (head, query cluster): maximal stretches of consecutive selected, non-empty
-// key clusters become (first_row, end_row) runs of the cluster-ordered K/V.
+// key clusters become runs of the cluster-ordered K/V.  Run r is stored as
+// (first_row, virtual_begin): virtual_begin is the number of selected key rows before it, so
+// the concatenation of all runs is addressed by one "virtual" row index; entry [nruns] is a
+// sentinel (0, total selected rows).
 __global__ void __launch_bounds__(256) build_runs_kernel(const uint8_t* __restrict__ map,
                                                          const int32_t* __restrict__ k_offsets, int2* __restrict__ runs,
                                                          int32_t* __restrict__ nruns, int QC, int KC, int max_runs,
@@ -167,7 +170,18 @@ __global__ void __launch_bounds__(256) build_runs_kernel(const uint8_t* __restri
     n_end += __popc(eb);
     carry = (bal >> 31) & 1u;
   }
-  if (lane == 0) nruns[row] = n_start < max_runs ? n_start : max_runs;
+  const int n = n_start < max_runs - 1 ? n_start : max_runs - 1;
+  __syncwarp();
+  if (lane == 0) {
+    int vbeg = 0;
+    for (int r = 0; r < n; ++r) {
+      const int2 se = out[r];
+      out[r] = make_int2(se.x, vbeg);
+      vbeg += se.y - se.x;
+    }
+    out[n] = make_int2(0, vbeg);
+    nruns[row] = n;
+  }
 }
 
 // One CTA per head: the 128-row query tiles of every non-empty query cluster.

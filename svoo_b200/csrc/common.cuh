@@ -31,7 +31,7 @@ struct Workspace {
   int64_t w_hi;          // bf16  [BH, Jpad, 128]
   int64_t w_lo;          // bf16  [BH, Jpad, 128]
   int64_t status;        // int32 [4]: word 0 != 0 after a kernel gave up on a bounded wait
-  int64_t runs;          // int2  [BH, QC, max_runs]
+  int64_t runs;          // int2  [BH, QC, max_runs]: (first_row, virtual_begin) + sentinel (0, total)
   int64_t nruns;         // int32 [BH, QC]
   int64_t qtiles;        // int4  [BH, max_qtiles]
   int64_t nqtiles;       // int32 [BH]
@@ -40,7 +40,7 @@ struct Workspace {
 
 __host__ inline int sort_chunks(int64_t N) { return (int)ceil_div64(N, kSortChunk); }
 __host__ inline int pad_clusters(int64_t K) { return (int)align_up(K, 64); }
-__host__ inline int max_runs(int64_t KC) { return (int)(KC / 2 + 1); }
+__host__ inline int max_runs(int64_t KC) { return (int)(KC / 2 + 2); }   // + one sentinel entry
 __host__ inline int max_qtiles(int64_t N, int64_t QC) { return (int)(ceil_div64(N, kAttnBM) + QC); }
 
 __host__ inline Workspace workspace_layout(int64_t BH, int64_t N, int64_t QC, int64_t KC) {
@@ -54,7 +54,7 @@ __host__ inline Workspace workspace_layout(int64_t BH, int64_t N, int64_t QC, in
   w.w_lo = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
   w.status = take(16);
   // sized symmetrically in (QC, KC) so that one workspace serves either side
-  w.runs = take(BH * (QC * KC / 2 + QC + KC) * 8);
+  w.runs = take(BH * (QC * KC / 2 + 2 * (QC + KC)) * 8);
   w.nruns = take(BH * Kmax * 4);
   w.qtiles = take(BH * (int64_t)max_qtiles(N, Kmax) * 16);
   w.nqtiles = take(BH * 4);

@@ -1,6 +1,6 @@
 """The whole sparse-attention layer as one stream-ordered sequence of kernels:
-co-clustering -> cluster-order permute -> cluster-block map -> block-sparse attention
-with the inverse permutation fused into its store.
+co-clustering -> cluster-order permute -> cluster-block map -> block-sparse attention with
+the inverse permutation fused into its store.
 
 Replaces semantic_aware_permutation + the sparse branch of attention_core_logic
 (svoo/models/wan/attention.py:958-1088,1159-1216) and, with text tokens, the
@@ -50,9 +50,12 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
                            num_k_centroids: int, kmeans_iters: int, top_p: float, min_kc_ratio=0, max_kc_ratio=0,
                            init_indices=None, clustering: Optional[ops.Clustering] = None,
                            context_length: int = 0, prompt_length: Optional[int] = None,
-                           return_state: bool = False, timer: Optional[StageTimer] = None):
+                           return_state: bool = False, timer: Optional[StageTimer] = None,
+                           fuse_gather: bool = False):
     """query/key/value: [1, H, S, 128] bf16 CUDA, S = video tokens + context_length text
-    tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order."""
+    tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order.
+    fuse_gather=True skips the three permute passes and lets the attention kernel gather Q, K, V
+    rows through the sorted indices instead (less memory, slower loads)."""
     cfg, H, S, D = query.shape
     assert cfg == 1, "Batch size must be 1 for kmeans block sparse attention"
     assert query.is_cuda and query.dtype == torch.bfloat16, "bf16 CUDA tensors expected"
@@ -76,29 +79,31 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
     mark("block_map")
 
     if context_length == 0:
-        qp = ops.permute(qv, c.q_sorted_idx)
-        kp = ops.permute(kv, c.k_sorted_idx)
-        vp = ops.permute(v.contiguous(), c.k_sorted_idx)
-        q_off, k_off, ridx = c.q_offsets, c.k_offsets, c.q_sorted_idx
+        m_full, q_off, k_off = m, c.q_offsets, c.k_offsets
+        q_idx, k_idx = c.q_sorted_idx, c.k_sorted_idx
     else:
         # text tokens stay where they are, as two extra blocks (prompt, unused prompt)
         prompt = context_length if prompt_length is None else prompt_length
-        qp, kp, vp = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        ops.permute(q, c.q_sorted_idx, out=qp)
-        ops.permute(k, c.k_sorted_idx, out=kp)
-        ops.permute(v, c.k_sorted_idx, out=vp)
-        qp[:, n_video:], kp[:, n_video:], vp[:, n_video:] = q[:, n_video:], k[:, n_video:], v[:, n_video:]
-        m = F.pad(m, (0, 2, 0, 2), value=0)
-        m[:, -2, :-1] = 1
-        m[:, :-1, -2] = 1
-        m[:, -1, -1] = 1
+        m_full = F.pad(m, (0, 2, 0, 2), value=0)
+        m_full[:, -2, :-1] = 1
+        m_full[:, :-1, -2] = 1
+        m_full[:, -1, -1] = 1
         tail = torch.tensor([prompt, context_length - prompt], dtype=torch.int32, device=q.device)
         q_off = ops.offsets_from_sizes(torch.cat([c.qsizes, tail.expand(H, 2)], 1))
         k_off = ops.offsets_from_sizes(torch.cat([c.ksizes, tail.expand(H, 2)], 1))
-        text_rows = torch.arange(n_video, S, dtype=torch.int32, device=q.device)
-        ridx = torch.cat([c.q_sorted_idx, text_rows.expand(H, context_length)], 1).contiguous()
-    mark("permute")
-    out = ops.sparse_attn(qp, kp, vp, m.contiguous(), q_off, k_off, D ** -0.5, out_row_idx=ridx)
+        text_rows = torch.arange(n_video, S, dtype=torch.int32, device=q.device).expand(H, context_length)
+        q_idx = torch.cat([c.q_sorted_idx, text_rows], 1).contiguous()
+        k_idx = torch.cat([c.k_sorted_idx, text_rows], 1).contiguous()
+    m = m_full
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if fuse_gather:
+        mark("permute")
+        out = ops.sparse_attn(q, k, v, m.contiguous(), q_off, k_off, D ** -0.5, q_row_idx=q_idx, kv_row_idx=k_idx,
+                              out_row_idx=q_idx)
+    else:
+        qp, kp, vp = ops.permute(q, q_idx), ops.permute(k, k_idx), ops.permute(v, k_idx)
+        mark("permute")
+        out = ops.sparse_attn(qp, kp, vp, m.contiguous(), q_off, k_off, D ** -0.5, out_row_idx=q_idx)
     mark("attention")
     out = out.unsqueeze(0)
     if return_state:

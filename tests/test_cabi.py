@@ -65,5 +65,5 @@ def test_host_side_argument_checks(lib):
     assert L.svoo_b200_permute(p + 2, p, 1, 4, 128, 4, 4, p, None) == -5
     assert L.svoo_b200_permute(p, p, 1, 4, 128, 2, 4, p, None) == -2
     assert L.svoo_b200_sort_labels(p, 1, 4, 4, p, p, p, 16, None) == -4
-    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 2, 2000, 0.1, p, None, p, 1 << 30, None) == -6
+    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 2, 2000, 0.1, p, None, None, None, p, 1 << 30, None) == -6
     assert L.svoo_b200_cocluster(p, p, p, p, 1, 4, 128, 2, 2, 0, p, p, p, p, p, p, p, p, p, p, p, 1 << 30, None) == -2
