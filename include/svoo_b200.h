@@ -158,9 +158,11 @@ int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, cons
                                void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Byte offset, inside a workspace of these sizes, of a 4-word int32 status block that
- * svoo_b200_sparse_attn clears when it is enqueued.  Word 0 becomes non-zero if a CTA of
- * the attention kernel gave up on one of its bounded barrier waits (its output rows are
- * then not written).  No counterpart in the reference. */
+ * the tensor-core kernels report into.  Word 0 is cleared by svoo_b200_sparse_attn and
+ * becomes non-zero if a CTA of the attention kernel gave up on one of its bounded barrier
+ * waits (its output rows are then not written); word 1 is the same for the assignment
+ * kernel of svoo_b200_cocluster / svoo_b200_cocluster_assign.  No counterpart in the
+ * reference. */
 int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* offset_out);
 
 /* Exclusive prefix of cluster sizes [BH,K] -> offsets [BH,K+1]

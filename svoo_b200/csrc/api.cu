@@ -5,7 +5,8 @@
 namespace svoo {
 cudaError_t launch_gather_rows(const void*, const int32_t*, void*, int64_t, int64_t, int64_t, cudaStream_t);
 cudaError_t launch_prologue(const void*, const void*, void*, void*, int64_t, int64_t, int64_t, cudaStream_t);
-cudaError_t launch_assign(const void*, const void*, const void*, int32_t*, int64_t, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_assign_tc(const void*, const void*, const void*, int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t,
+                             cudaStream_t);
 cudaError_t launch_sort_labels(const int32_t*, int64_t, int64_t, int64_t, int32_t*, int32_t*, int32_t*, int32_t*,
                                cudaStream_t);
 cudaError_t launch_centroid_update(const void*, const int32_t*, const int32_t*, const void*, void*, int32_t*, float*,
@@ -96,7 +97,9 @@ int svoo_b200_cocluster_assign(const void* x, const void* form_centroids, const 
   cudaStream_t st = (cudaStream_t)stream;
   SVOO_CUDA(launch_prologue(own_centroids, form_centroids, ws_at<void>(workspace, w.w_hi),
                             ws_at<void>(workspace, w.w_lo), BH, J, K, st));
-  SVOO_CUDA(launch_assign(x, ws_at<void>(workspace, w.w_hi), ws_at<void>(workspace, w.w_lo), labels, BH, N, J, st));
+  SVOO_CUDA(cudaMemsetAsync(ws_at<int32_t>(workspace, w.status) + 1, 0, 4, st));
+  SVOO_CUDA(launch_assign_tc(x, ws_at<void>(workspace, w.w_hi), ws_at<void>(workspace, w.w_lo), labels,
+                             ws_at<int2>(workspace, w.assign_partial), ws_at<int32_t>(workspace, w.status) + 1, BH, N, J, st));
   return SVOO_OK;
 }
 
@@ -148,18 +151,21 @@ int svoo_b200_cocluster(const void* q, const void* k, const int32_t* q_init_idx,
   void* w_lo = ws_at<void>(workspace, w.w_lo);
   int32_t* hist = ws_at<int32_t>(workspace, w.chunk_hist);
   float* partial = ws_at<float>(workspace, w.partial);
+  int2* apart = ws_at<int2>(workspace, w.assign_partial);
+  int32_t* status = ws_at<int32_t>(workspace, w.status) + 1;       // word 1: assignment kernel
 
+  SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));
   SVOO_CUDA(launch_gather_rows(q, q_init_idx, qcentroids, BH, N, QC, st));
   SVOO_CUDA(launch_gather_rows(k, k_init_idx, kcentroids, BH, N, KC, st));
   for (int it = 0; it < iters; ++it) {
     // keys: profile over the query centroids
     SVOO_CUDA(launch_prologue(kcentroids, qcentroids, w_hi, w_lo, BH, KC, QC, st));
-    SVOO_CUDA(launch_assign(k, w_hi, w_lo, klabels, BH, N, KC, st));
+    SVOO_CUDA(launch_assign_tc(k, w_hi, w_lo, klabels, apart, status, BH, N, KC, st));
     SVOO_CUDA(launch_sort_labels(klabels, BH, N, KC, k_sorted_idx, k_offsets, nullptr, hist, st));
     SVOO_CUDA(launch_centroid_update(k, k_sorted_idx, k_offsets, kcentroids, kcentroids, ksizes, partial, BH, N, KC, st));
     // queries: profile over the just-updated key centroids
     SVOO_CUDA(launch_prologue(qcentroids, kcentroids, w_hi, w_lo, BH, QC, KC, st));
-    SVOO_CUDA(launch_assign(q, w_hi, w_lo, qlabels, BH, N, QC, st));
+    SVOO_CUDA(launch_assign_tc(q, w_hi, w_lo, qlabels, apart, status, BH, N, QC, st));
     SVOO_CUDA(launch_sort_labels(qlabels, BH, N, QC, q_sorted_idx, q_offsets, nullptr, hist, st));
     SVOO_CUDA(launch_centroid_update(q, q_sorted_idx, q_offsets, qcentroids, qcentroids, qsizes, partial, BH, N, QC, st));
   }
@@ -230,7 +236,7 @@ static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, cons
   SVOO_CUDA(launch_build_runs(map, k_offsets, runs, nruns, BH, QC, KC, st));
   SVOO_CUDA(launch_build_qtiles(q_offsets, qtiles, nqtiles, BH, S, QC, tensor_core ? 256 : 128, st));
   if (tensor_core) {
-    SVOO_CUDA(cudaMemsetAsync(status, 0, 16, st));
+    SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));                     // word 0: attention kernel
     SVOO_CUDA(launch_sparse_attn_tc(q, k, v, out, q_row_idx, kv_row_idx, out_row_idx, qtiles, nqtiles, runs, nruns,
                                     status, BH, S, QC, KC, sm_scale, st));
   } else {

@@ -1,0 +1,265 @@
+// Co-clustering assignment on the 5th-generation tensor cores:
+//     label[n] = first argmax_j  x_n . (W_hi[j] + W_lo[j]),   j < J
+// (see cluster.cu for how W = Phat . C replaces the reference's two chained GEMMs,
+// svoo/co_clustering.py:2148-2255).
+//
+// W-stationary, persistent.  The job list is (head, block of 256 W rows, tile of 128 tokens),
+// token tile fastest; each CTA (one per SM) takes a contiguous slice of it.  A block of W
+// (hi and lo, 128 KB) stays in shared memory while the token tiles of that head stream
+// through a two-stage ring (32 KB each), so shared memory is filled at 16 B per MMA clock
+// instead of re-reading W for every token tile.
+//
+//   warp 0      TMA producer (cp.async.bulk.tensor 2-D boxes, 128-byte swizzle, no multicast)
+//   warp 1      MMA issuer: D[128 x 256] (+)= X[128 x 16] . W^T[16 x 256], 8 k-steps for hi and
+//               8 for lo into one of two TMEM accumulators (tcgen05.mma kind::f16, M128 N256)
+//   warps 4-7   epilogue: thread r owns token row r (TMEM lane r), running first-argmax over the
+//               256 columns, one (score, j) pair per token and W block written to scratch
+//
+// A small second kernel reduces the per-block pairs to labels (lower block wins ties).
+// Every mbarrier wait is bounded; on expiry the CTA sets the status word and leaves.
+#include "tc_common.cuh"
+
+namespace svoo {
+namespace tc {
+
+constexpr int kAsgXT = 128;                       // tokens per tile
+constexpr int kAsgJB = 256;                       // W rows per block
+constexpr int kAsgXBytes = kAsgXT * kRowBytes;    // 32 KB
+constexpr int kAsgXHalf = kAsgXT * 128;           // 16 KB: 128 rows x 64 columns
+constexpr int kAsgWHalf = kAsgJB * 128;           // 32 KB: 256 rows x 64 columns
+constexpr int kAsgWBytes = 2 * kAsgWHalf;         // 64 KB per hi / lo
+constexpr int kAsgSmemData = 2 * kAsgWBytes + 2 * kAsgXBytes;      // 192 KB
+constexpr int kAsgSmemBytes = kAsgSmemData + 256 + 1024;
+constexpr int kAsgThreads = 256;
+
+enum AsgBar { W_FULL = 0, W_EMPTY = 1, X_FULL = 2, X_EMPTY = 4, ACC_FULL = 6, ACC_EMPTY = 8, ASG_BARS = 10 };
+
+constexpr uint32_t kIdescAssign = idesc_bf16(128, kAsgJB, false);
+
+struct AsgJob {
+  int bh, jb, t;
+};
+__device__ __forceinline__ AsgJob asg_job(int64_t g, int n_jb, int n_xt) {
+  AsgJob j;
+  j.t = (int)(g % n_xt);
+  const int64_t r = g / n_xt;
+  j.jb = (int)(r % n_jb);
+  j.bh = (int)(r / n_jb);
+  return j;
+}
+
+__global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
+    const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_hi,
+    const __grid_constant__ CUtensorMap tm_lo, int2* __restrict__ partial, int BH, int N, int J, int Jpad,
+    int32_t* __restrict__ status) {
+  extern __shared__ unsigned char smem_raw[];
+  const int n_jb = Jpad / kAsgJB, n_xt = (N + kAsgXT - 1) / kAsgXT;
+  const int64_t total = (int64_t)BH * n_jb * n_xt;
+  const int64_t per = (total + gridDim.x - 1) / gridDim.x;
+  const int64_t g0 = (int64_t)blockIdx.x * per;
+  const int64_t g1 = g0 + per < total ? g0 + per : total;
+  if (g0 >= g1) return;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t whi_s = base, wlo_s = base + kAsgWBytes, x_s = base + 2 * kAsgWBytes;
+  const uint32_t bars = base + kAsgSmemData;
+  unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kAsgSmemData + ASG_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kAsgSmemData + ASG_BARS * 8 + 8);
+  auto bar = [&](int i) { return bars + 8u * i; };
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  if (tid == 0) {
+    for (int i = 0; i < ASG_BARS; ++i) mbar_init(bar(i), (i == ACC_EMPTY || i == ACC_EMPTY + 1) ? 128 : 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int wq = 0, prev_block = -1;
+      int i = 0;
+      for (int64_t g = g0; g < g1; ++g, ++i) {
+        const AsgJob job = asg_job(g, n_jb, n_xt);
+        const int block = job.bh * n_jb + job.jb;
+        if (block != prev_block) {
+          if (!mbar_wait(bar(W_EMPTY), (wq & 1) ^ 1, abort_flag)) break;
+          mbar_expect_tx(bar(W_FULL), 2 * kAsgWBytes);
+          const int y = job.bh * Jpad + job.jb * kAsgJB;
+          for (int h = 0; h < 2; ++h) {
+            tma_load_2d(whi_s + h * kAsgWHalf, &tm_hi, h * 64, y, bar(W_FULL));
+            tma_load_2d(wlo_s + h * kAsgWHalf, &tm_lo, h * 64, y, bar(W_FULL));
+          }
+          prev_block = block;
+          ++wq;
+        }
+        const int s = i & 1;
+        if (!mbar_wait(bar(X_EMPTY + s), ((i >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(bar(X_FULL + s), kAsgXBytes);
+        for (int h = 0; h < 2; ++h)
+          tma_load_2d(x_s + s * kAsgXBytes + h * kAsgXHalf, &tm_x, h * 64, job.bh * N + job.t * kAsgXT, bar(X_FULL + s));
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int wq = 0, prev_block = -1;
+      int i = 0;
+      for (int64_t g = g0; g < g1; ++g, ++i) {
+        const AsgJob job = asg_job(g, n_jb, n_xt);
+        const int block = job.bh * n_jb + job.jb;
+        if (block != prev_block) {
+          if (!mbar_wait(bar(W_FULL), wq & 1, abort_flag)) break;
+          prev_block = block;
+          ++wq;
+        }
+        const int s = i & 1;
+        if (!mbar_wait(bar(X_FULL + s), (i >> 1) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(ACC_EMPTY + s), ((i >> 1) & 1) ^ 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d = tmem + s * kAsgJB;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t a = smem_desc_sw128(x_s + s * kAsgXBytes + (ks >> 2) * kAsgXHalf + (ks & 3) * 32, 16, 1024);
+          const uint32_t woff = (ks >> 2) * kAsgWHalf + (ks & 3) * 32;
+          umma_ss(d, a, smem_desc_sw128(whi_s + woff, 16, 1024), kIdescAssign, ks > 0);
+          umma_ss(d, a, smem_desc_sw128(wlo_s + woff, 16, 1024), kIdescAssign, 1);
+        }
+        tc_commit(bar(X_EMPTY + s));
+        tc_commit(bar(ACC_FULL + s));
+        bool last_of_block = g + 1 >= g1;
+        if (!last_of_block) {
+          const AsgJob nxt = asg_job(g + 1, n_jb, n_xt);
+          last_of_block = nxt.bh * n_jb + nxt.jb != block;
+        }
+        if (last_of_block) tc_commit(bar(W_EMPTY));
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- epilogue: running argmax
+    const int quad = warp & 3;
+    const int r_local = quad * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    uint32_t ra[32], rb[32];
+    int i = 0;
+    bool ok = true;
+    for (int64_t g = g0; g < g1 && ok; ++g, ++i) {
+      const AsgJob job = asg_job(g, n_jb, n_xt);
+      const int s = i & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_FULL + s), (i >> 1) & 1, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t acc = tmem + lane_addr + s * kAsgJB;
+      const int jlim = min(J - job.jb * kAsgJB, kAsgJB);       // valid columns of this block
+      float best = -INFINITY;
+      int best_c = 0;
+      tmem_ld32_nowait(acc, ra);
+      tmem_wait_ld();
+#pragma unroll 1
+      for (int ch = 0; ch < 8; ch += 2) {
+        tmem_ld32_nowait(acc + (ch + 1) * 32, rb);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float val = __uint_as_float(ra[c]);
+          if (ch * 32 + c < jlim && val > best) { best = val; best_c = ch * 32 + c; }
+        }
+        tmem_wait_ld();
+        if (ch + 2 < 8) tmem_ld32_nowait(acc + (ch + 2) * 32, ra);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float val = __uint_as_float(rb[c]);
+          if ((ch + 1) * 32 + c < jlim && val > best) { best = val; best_c = (ch + 1) * 32 + c; }
+        }
+        tmem_wait_ld();
+      }
+      tc_fence_before();
+      mbar_arrive(bar(ACC_EMPTY + s));
+      const int n = job.t * kAsgXT + r_local;
+      if (n < N)
+        partial[((int64_t)job.jb * BH + job.bh) * N + n] = make_int2(__float_as_int(best), job.jb * kAsgJB + best_c);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *abort_flag) atomicExch(status, 2);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
+// labels[bh, n] = j of the best (score, j) pair over the W blocks; the lower block wins ties.
+__global__ void __launch_bounds__(256) assign_reduce_kernel(const int2* __restrict__ partial, int32_t* __restrict__ labels,
+                                                            int64_t BHN, int n_jb) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= BHN) return;
+  int2 b = partial[i];
+  for (int jb = 1; jb < n_jb; ++jb) {
+    const int2 c = partial[(int64_t)jb * BHN + i];
+    if (__int_as_float(c.x) > __int_as_float(b.x)) b = c;
+  }
+  labels[i] = b.y;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+bool make_row_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)kRowBytes};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tc
+
+cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int2* partial,
+                             int32_t* status, int64_t BH, int64_t N, int64_t J, cudaStream_t st) {
+  const int Jpad = pad_clusters(J);
+  alignas(64) CUtensorMap mx, mh, ml;
+  if (!tc::make_row_tensor_map(&mx, x, BH * N, tc::kAsgXT) || !tc::make_row_tensor_map(&mh, w_hi, BH * Jpad, tc::kAsgJB) ||
+      !tc::make_row_tensor_map(&ml, w_lo, BH * Jpad, tc::kAsgJB))
+    return cudaErrorInvalidValue;
+  cudaError_t e = cudaFuncSetAttribute(tc::assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kAsgSmemBytes);
+  if (e != cudaSuccess) return e;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_jb = Jpad / tc::kAsgJB;
+  const int64_t total = BH * n_jb * ceil_div64(N, tc::kAsgXT);
+  const unsigned grid = (unsigned)(total < sms ? total : sms);
+  tc::assign_tc_kernel<<<grid, tc::kAsgThreads, tc::kAsgSmemBytes, st>>>(mx, mh, ml, partial, (int)BH, (int)N, (int)J, Jpad,
+                                                                        status);
+  tc::assign_reduce_kernel<<<(unsigned)ceil_div64(BH * N, 256), 256, 0, st>>>(partial, labels, BH * N, n_jb);
+  count_launches(2);
+  return cudaGetLastError();
+}
+
+}  // namespace svoo

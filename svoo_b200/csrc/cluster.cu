@@ -1,5 +1,5 @@
-// QK co-clustering kernels: profile prologue, assignment GEMM with fused argmax,
-// stable counting sort of labels, deterministic centroid update.
+// QK co-clustering kernels: profile prologue (builds the W operand of the assignment GEMM,
+// which lives in assign_tc.cu), stable counting sort of labels, deterministic centroid update.
 //
 // Algebra used by the assignment.  The reference (svoo/co_clustering.py:2148-2255)
 // computes, for token x and own-centroid j,
@@ -112,134 +112,6 @@ __global__ void __launch_bounds__(256) profile_prologue_kernel(
         w_hi[((int64_t)bh * Jpad + j) * kHeadDim + d] = hi;
         w_lo[((int64_t)bh * Jpad + j) * kHeadDim + d] = lo;
       }
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------
-// Assignment: labels[n] = first argmax_j x_n . (W_hi[j] + W_lo[j]),  j < J.
-// CTA = 128 tokens (4 warps x 32), W streamed in tiles of 64 rows, double buffered.
-// ---------------------------------------------------------------------------------------
-constexpr int kAsgBM = 128;
-constexpr int kAsgBJ = 64;
-constexpr int kAsgSmem = kAsgBM * kRowBytes + 2 * 2 * kAsgBJ * kRowBytes;   // 32 KB + 64 KB
-
-__device__ __forceinline__ void asg_load_w(uint32_t dst, const bf16* hi, const bf16* lo, int tid) {
-  // 64 rows x 16 chunks for hi, then the same for lo: 2048 chunks, 16 per thread
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int c = tid + i * 128;
-    const int which = c >> 10, rc = c & 1023, row = rc >> 4, chunk = rc & 15;
-    const bf16* src = (which ? lo : hi) + row * kHeadDim + chunk * 8;
-    cp_async16(dst + which * (kAsgBJ * kRowBytes) + swz(row, chunk), src, true);
-  }
-}
-
-__global__ void __launch_bounds__(128) assign_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_hi,
-                                                     const bf16* __restrict__ w_lo, int32_t* __restrict__ labels,
-                                                     int N, int J, int Jpad) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  const uint32_t x_s = smem_u32(smem_raw);
-  const uint32_t w_s = x_s + kAsgBM * kRowBytes;
-  const int bh = blockIdx.y, n0 = blockIdx.x * kAsgBM;
-  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const bf16* xb = x + (int64_t)bh * N * kHeadDim;
-  const bf16* hib = w_hi + (int64_t)bh * Jpad * kHeadDim;
-  const bf16* lob = w_lo + (int64_t)bh * Jpad * kHeadDim;
-
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int c = tid + i * 128, row = c >> 4, chunk = c & 15;
-    const bool ok = n0 + row < N;
-    cp_async16(x_s + swz(row, chunk), xb + (int64_t)(ok ? n0 + row : 0) * kHeadDim + chunk * 8, ok);
-  }
-  asg_load_w(w_s, hib, lob, tid);
-  cp_async_commit();
-
-  uint32_t a[2][8][4];
-  float best[4];
-  int best_j[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { best[i] = -3.4e38f; best_j[i] = 0; }
-
-  const int ntiles = Jpad / kAsgBJ;
-  for (int jt = 0; jt < ntiles; ++jt) {
-    if (jt + 1 < ntiles)
-      asg_load_w(w_s + ((jt + 1) & 1) * (2 * kAsgBJ * kRowBytes), hib + (int64_t)(jt + 1) * kAsgBJ * kHeadDim,
-                 lob + (int64_t)(jt + 1) * kAsgBJ * kHeadDim, tid);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-    if (jt == 0) {
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const int row = warp * 32 + mt * 16 + (lane % 8) + ((lane / 8) % 2) * 8;
-          ldmatrix_x4(a[mt][ks], x_s + swz(row, ks * 2 + lane / 16));
-        }
-    }
-    const uint32_t wt = w_s + (jt & 1) * (2 * kAsgBJ * kRowBytes);
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      float acc[2][4][4];
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-#pragma unroll
-        for (int np = 0; np < 2; ++np) {
-          const int row = half * 32 + np * 16 + (lane % 8) + (lane / 16) * 8;
-          const uint32_t off = swz(row, ks * 2 + ((lane / 8) % 2));
-          uint32_t bh4[4], bl4[4];
-          ldmatrix_x4(bh4, wt + off);
-          ldmatrix_x4(bl4, wt + kAsgBJ * kRowBytes + off);
-#pragma unroll
-          for (int mt = 0; mt < 2; ++mt) {
-            mma_bf16(acc[mt][np * 2], a[mt][ks], bh4[0], bh4[1]);
-            mma_bf16(acc[mt][np * 2 + 1], a[mt][ks], bh4[2], bh4[3]);
-            mma_bf16(acc[mt][np * 2], a[mt][ks], bl4[0], bl4[1]);
-            mma_bf16(acc[mt][np * 2 + 1], a[mt][ks], bl4[2], bl4[3]);
-          }
-        }
-      }
-      const int jbase = jt * kAsgBJ + half * 32 + 2 * (lane % 4);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int j = jbase + nt * 8 + c;
-          if (j < J) {
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
-              const float v0 = acc[mt][nt][c], v1 = acc[mt][nt][2 + c];
-              if (v0 > best[mt * 2]) { best[mt * 2] = v0; best_j[mt * 2] = j; }
-              if (v1 > best[mt * 2 + 1]) { best[mt * 2 + 1] = v1; best_j[mt * 2 + 1] = j; }
-            }
-          }
-        }
-    }
-    __syncthreads();
-  }
-  cp_async_wait<0>();
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-#pragma unroll
-    for (int s = 1; s <= 2; s <<= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best[i], s);
-      const int oj = __shfl_xor_sync(0xffffffffu, best_j[i], s);
-      if (ov > best[i] || (ov == best[i] && oj < best_j[i])) { best[i] = ov; best_j[i] = oj; }
-    }
-  }
-  if (lane % 4 == 0) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = n0 + warp * 32 + (i / 2) * 16 + (i % 2) * 8 + lane / 4;
-      if (row < N) labels[(int64_t)bh * N + row] = best_j[i];
     }
   }
 }
@@ -489,20 +361,6 @@ cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void*
   dim3 grid((unsigned)(Jpad / kProR), (unsigned)BH);
   profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo,
                                                    (int)J, (int)K, Jpad);
-  count_launches(1);
-  return cudaGetLastError();
-}
-
-cudaError_t launch_assign(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int64_t BH, int64_t N,
-                          int64_t J, cudaStream_t st) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAsgSmem);
-    attr_done = true;
-  }
-  dim3 grid((unsigned)ceil_div64(N, kAsgBM), (unsigned)BH);
-  assign_kernel<<<grid, 128, kAsgSmem, st>>>((const bf16*)x, (const bf16*)w_hi, (const bf16*)w_lo, labels, (int)N,
-                                             (int)J, pad_clusters(J));
   count_launches(1);
   return cudaGetLastError();
 }

@@ -30,6 +30,7 @@ struct Workspace {
   int64_t partial;       // float [BH, Kmax, slabs, 128] centroid partial sums
   int64_t w_hi;          // bf16  [BH, Jpad, 128]
   int64_t w_lo;          // bf16  [BH, Jpad, 128]
+  int64_t assign_partial;  // int2 [Jpad/256, BH, N]: best (score bits, j) per W block
   int64_t status;        // int32 [4]: word 0 != 0 after a kernel gave up on a bounded wait
   int64_t runs;          // int2  [BH, QC, max_runs]: (first_row, virtual_begin) + sentinel (0, total)
   int64_t nruns;         // int32 [BH, QC]
@@ -39,7 +40,7 @@ struct Workspace {
 };
 
 __host__ inline int sort_chunks(int64_t N) { return (int)ceil_div64(N, kSortChunk); }
-__host__ inline int pad_clusters(int64_t K) { return (int)align_up(K, 64); }
+__host__ inline int pad_clusters(int64_t K) { return (int)align_up(K, 256); }   // W rows, whole 256-row blocks
 __host__ inline int max_runs(int64_t KC) { return (int)(KC / 2 + 2); }   // + one sentinel entry
 __host__ inline int max_qtiles(int64_t N, int64_t QC) { return (int)(ceil_div64(N, kAttnBM) + QC); }
 
@@ -52,6 +53,7 @@ __host__ inline Workspace workspace_layout(int64_t BH, int64_t N, int64_t QC, in
   w.partial = take(BH * Kmax * kCentroidSlabs * kHeadDim * 4);
   w.w_hi = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
   w.w_lo = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
+  w.assign_partial = take((int64_t)(pad_clusters(Kmax) / 256) * BH * N * 8);
   w.status = take(16);
   // sized symmetrically in (QC, KC) so that one workspace serves either side
   w.runs = take(BH * (QC * KC / 2 + 2 * (QC + KC)) * 8);

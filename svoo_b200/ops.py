@@ -238,3 +238,12 @@ def attention_status(device: torch.device, BH: int, S: int, QC: int, KC: int) ->
     check(LIB.svoo_b200_status_offset(BH, S, QC, KC, ctypes.byref(off)), "status_offset")
     ws = workspace(device, BH, S, QC, KC)
     return int(ws[off.value:off.value + 4].view(torch.int32).item())
+
+
+def cluster_status(device: torch.device, BH: int, N: int, QC: int, KC: int) -> int:
+    """Same as attention_status for the assignment kernel of the last cocluster /
+    cocluster_assign call (status word 1)."""
+    off = ctypes.c_int64(0)
+    check(LIB.svoo_b200_status_offset(BH, N, QC, KC, ctypes.byref(off)), "status_offset")
+    ws = workspace(device, BH, N, QC, KC)
+    return int(ws[off.value + 4:off.value + 8].view(torch.int32).item())
