@@ -32,86 +32,117 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int32_t* __
 
 // ---------------------------------------------------------------------------------------
 // Prologue: P = bf16(own . form^T), Phat = P / sqrt(sum P^2 + 1e-8) (fp32),
-//           W = Phat . form (fp32) -> (hi, lo) bf16.      One CTA = 8 rows j of one head.
+//           W = Phat . form (fp32) -> (hi, lo) bf16.     One CTA = 32 rows j of one head;
+//           `form` is swept twice through shared memory in chunks of 32 centroids.
 // (svoo/co_clustering.py:2427-2428 and svoo/kernels/triton/l2norm.py:36-41)
 // ---------------------------------------------------------------------------------------
-constexpr int kProR = 8;
+constexpr int kProR = 32;            // own rows per CTA
+constexpr int kProC = 32;            // form rows per chunk
+constexpr int kProLd = kHeadDim + 1; // padded row length (floats) of the staged tiles
+
+__device__ __forceinline__ void stage_form_chunk(float* dst, const bf16* __restrict__ form_b, int k0, int K, int tid) {
+  // 32 rows x 128 dims: 256 threads, 16 elements each (two 16-byte loads)
+  const int row = tid >> 3, d0 = (tid & 7) * 16;
+  if (k0 + row < K) {
+    const uint4* src = reinterpret_cast<const uint4*>(form_b + (int64_t)(k0 + row) * kHeadDim + d0);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 v = __ldg(src + h);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        dst[row * kProLd + d0 + h * 8 + 2 * e] = __low2float(p[e]);
+        dst[row * kProLd + d0 + h * 8 + 2 * e + 1] = __high2float(p[e]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) dst[row * kProLd + d0 + e] = 0.f;
+  }
+}
 
 __global__ void __launch_bounds__(256) profile_prologue_kernel(
     const bf16* __restrict__ own, const bf16* __restrict__ form, bf16* __restrict__ w_hi,
-    bf16* __restrict__ w_lo, int J, int K, int Jpad) {
+    bf16* __restrict__ w_lo, int J, int K, int Jpad, int Kld) {
   extern __shared__ float sm[];
-  float* own_s = sm;                       // [8][128]
-  float* p_s = sm + kProR * kHeadDim;      // [8][K]
-  __shared__ float inv_norm[kProR];
-  const int bh = blockIdx.y;
-  const int j0 = blockIdx.x * kProR;
+  float* own_s = sm;                          // [32][129]
+  float* chunk_s = own_s + kProR * kProLd;    // [32][129]
+  float* p_s = chunk_s + kProC * kProLd;      // [32][Kld]   Kld odd
+  __shared__ float norm_s[kProR];
+  const int bh = blockIdx.y, j0 = blockIdx.x * kProR;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const bf16* form_b = form + (int64_t)bh * K * kHeadDim;
-
-  for (int i = tid; i < kProR * kHeadDim; i += 256) {
-    int r = i / kHeadDim, d = i % kHeadDim;
-    own_s[i] = (j0 + r < J) ? __bfloat162float(own[((int64_t)bh * J + j0 + r) * kHeadDim + d]) : 0.f;
-  }
-  __syncthreads();
-
-  // P[r][k]: one warp per k, lanes split the 128 dims (4 each).
-  for (int k = warp; k < K; k += 8) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(form_b + (int64_t)k * kHeadDim + lane * 4);
-    const __nv_bfloat162 v01 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-    const __nv_bfloat162 v23 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    const float f0 = __low2float(v01), f1 = __high2float(v01), f2 = __low2float(v23), f3 = __high2float(v23);
-    float acc[kProR];
-#pragma unroll
-    for (int r = 0; r < kProR; ++r) {
-      const float4 o = *reinterpret_cast<const float4*>(own_s + r * kHeadDim + lane * 4);
-      acc[r] = o.x * f0 + o.y * f1 + o.z * f2 + o.w * f3;
-    }
-#pragma unroll
-    for (int r = 0; r < kProR; ++r) {
-#pragma unroll
-      for (int s = 16; s > 0; s >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], s);
-    }
-    if (lane < kProR) {
-      float v = acc[0];
-#pragma unroll
-      for (int r = 1; r < kProR; ++r) v = (lane == r) ? acc[r] : v;
-      p_s[lane * K + k] = bf16_round(v);       // torch.matmul of bf16 tensors returns bf16
-    }
-  }
-  __syncthreads();
-
-  // row norms: warp r sums P[r][:]^2
-  {
-    float s = 0.f;
-    for (int k = lane; k < K; k += 32) { float v = p_s[warp * K + k]; s += v * v; }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) inv_norm[warp] = sqrtf(s + 1e-8f);
-  }
-  __syncthreads();
-  for (int i = tid; i < kProR * K; i += 256) p_s[i] = p_s[i] / inv_norm[i / K];
-  __syncthreads();
-
-  // W[r][d] = sum_k Phat[r][k] * form[k][d]; thread = (d, half of the rows)
-  {
-    const int d = tid % kHeadDim, r0 = (tid / kHeadDim) * 4;
-    float w[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int k = 0; k < K; ++k) {
-      const float f = __bfloat162float(form_b[(int64_t)k * kHeadDim + d]);
-#pragma unroll
-      for (int r = 0; r < 4; ++r) w[r] = fmaf(p_s[(r0 + r) * K + k], f, w[r]);
-    }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int j = j0 + r0 + r;
-      if (j < Jpad) {
-        const float val = (j < J) ? w[r] : 0.f;
-        const bf16 hi = __float2bfloat16_rn(val);
-        const bf16 lo = __float2bfloat16_rn(val - __bfloat162float(hi));
-        w_hi[((int64_t)bh * Jpad + j) * kHeadDim + d] = hi;
-        w_lo[((int64_t)bh * Jpad + j) * kHeadDim + d] = lo;
+  const int d = tid % kHeadDim, rg = tid / kHeadDim;        // phase 3: column d, rows rg*16 .. +15
+  if (j0 >= J) {                                            // padding rows of W: zeros
+    for (int r = rg * 16; r < rg * 16 + 16; ++r)
+      if (j0 + r < Jpad) {
+        w_hi[((int64_t)bh * Jpad + j0 + r) * kHeadDim + d] = __float2bfloat16_rn(0.f);
+        w_lo[((int64_t)bh * Jpad + j0 + r) * kHeadDim + d] = __float2bfloat16_rn(0.f);
       }
+    return;
+  }
+  const bf16* form_b = form + (int64_t)bh * K * kHeadDim;
+  for (int i = tid; i < kProR * kHeadDim; i += 256) {
+    const int r = i / kHeadDim, dd = i % kHeadDim;
+    own_s[r * kProLd + dd] = (j0 + r < J) ? __bfloat162float(own[((int64_t)bh * J + j0 + r) * kHeadDim + dd]) : 0.f;
+  }
+  // sweep 1: P[r][k]; thread = (row r, 4 of the 32 centroids of the chunk)
+  {
+    const int r = tid >> 3, kk = tid & 7;
+    for (int k0 = 0; k0 < K; k0 += kProC) {
+      __syncthreads();
+      stage_form_chunk(chunk_s, form_b, k0, K, tid);
+      __syncthreads();
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* o = own_s + r * kProLd;
+#pragma unroll 8
+      for (int dd = 0; dd < kHeadDim; ++dd) {
+        const float x = o[dd];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] = fmaf(x, chunk_s[(kk + 8 * u) * kProLd + dd], acc[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (k0 + kk + 8 * u < K) p_s[r * Kld + k0 + kk + 8 * u] = bf16_round(acc[u]);   // matmul of bf16 tensors returns bf16
+    }
+  }
+  __syncthreads();
+  // row norms, then Phat in place: 8 warps x 4 rows
+  for (int r = warp * 4; r < warp * 4 + 4; ++r) {
+    float ss = 0.f;
+    for (int k = lane; k < K; k += 32) { const float x = p_s[r * Kld + k]; ss += x * x; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) norm_s[r] = sqrtf(ss + 1e-8f);
+  }
+  __syncthreads();
+  for (int i = tid; i < kProR * K; i += 256) {
+    const int r = i / K, k = i % K;
+    p_s[r * Kld + k] = p_s[r * Kld + k] / norm_s[r];
+  }
+  // sweep 2: W[r][d] = sum_k Phat[r][k] * form[k][d]; thread = (column d, 16 rows)
+  float w[16];
+#pragma unroll
+  for (int u = 0; u < 16; ++u) w[u] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += kProC) {
+    __syncthreads();
+    stage_form_chunk(chunk_s, form_b, k0, K, tid);
+    __syncthreads();
+    const int kn = min(kProC, K - k0);
+    for (int k = 0; k < kn; ++k) {
+      const float f = chunk_s[k * kProLd + d];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) w[u] = fmaf(p_s[(rg * 16 + u) * Kld + k0 + k], f, w[u]);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 16; ++u) {
+    const int j = j0 + rg * 16 + u;
+    if (j < Jpad) {
+      const float val = (j < J) ? w[u] : 0.f;
+      const bf16 hi = __float2bfloat16_rn(val);
+      const bf16 lo = __float2bfloat16_rn(val - __bfloat162float(hi));
+      w_hi[((int64_t)bh * Jpad + j) * kHeadDim + d] = hi;
+      w_lo[((int64_t)bh * Jpad + j) * kHeadDim + d] = lo;
     }
   }
 }
@@ -352,15 +383,13 @@ cudaError_t launch_gather_rows(const void* x, const int32_t* idx, void* out, int
 cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void* w_lo, int64_t BH, int64_t J,
                             int64_t K, cudaStream_t st) {
   const int Jpad = pad_clusters(J);
-  const size_t smem = (size_t)(kProR * kHeadDim + kProR * K) * sizeof(float);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    attr_done = true;
-  }
+  const int Kld = (int)K | 1;                                   // odd row length: conflict-free column walks
+  const size_t smem = (size_t)((kProR + kProC) * kProLd + kProR * Kld) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024);
+  if (e != cudaSuccess) return e;
   dim3 grid((unsigned)(Jpad / kProR), (unsigned)BH);
   profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo,
-                                                   (int)J, (int)K, Jpad);
+                                                   (int)J, (int)K, Jpad, Kld);
   count_launches(1);
   return cudaGetLastError();
 }
