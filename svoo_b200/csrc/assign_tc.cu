@@ -6,14 +6,15 @@
 // W-stationary, persistent.  The job list is (head, block of 256 W rows, tile of 128 tokens),
 // token tile fastest; each CTA (one per SM) takes a contiguous slice of it.  A block of W
 // (hi and lo, 128 KB) stays in shared memory while the token tiles of that head stream
-// through a two-stage ring (32 KB each), so shared memory is filled at 16 B per MMA clock
+// through a three-stage ring (32 KB each), so shared memory is filled at 16 B per MMA clock
 // instead of re-reading W for every token tile.
 //
 //   warp 0      TMA producer (cp.async.bulk.tensor 2-D boxes, 128-byte swizzle, no multicast)
 //   warp 1      MMA issuer: D[128 x 256] (+)= X[128 x 16] . W^T[16 x 256], 8 k-steps for hi and
 //               8 for lo into one of two TMEM accumulators (tcgen05.mma kind::f16, M128 N256)
-//   warps 4-7   epilogue: thread r owns token row r (TMEM lane r), running first-argmax over the
-//               256 columns, one (score, j) pair per token and W block written to scratch
+//   warps 4-11  epilogue: thread r of each group of four warps owns token row r (TMEM lane r)
+//               and one half of the accumulator columns: running first-argmax, one (score, j)
+//               pair per token and column group written to scratch
 //
 // A small second kernel reduces the per-block pairs to labels (lower block wins ties).
 // Every mbarrier wait is bounded; on expiry the CTA sets the status word and leaves.
@@ -23,18 +24,22 @@ namespace svoo {
 namespace tc {
 
 constexpr int kAsgXT = 128;                       // tokens per tile
-constexpr int kAsgJB = 256;                       // W rows per block
 constexpr int kAsgXBytes = kAsgXT * kRowBytes;    // 32 KB
 constexpr int kAsgXHalf = kAsgXT * 128;           // 16 KB: 128 rows x 64 columns
-constexpr int kAsgWHalf = kAsgJB * 128;           // 32 KB: 256 rows x 64 columns
-constexpr int kAsgWBytes = 2 * kAsgWHalf;         // 64 KB per hi / lo
-constexpr int kAsgSmemData = 2 * kAsgWBytes + 2 * kAsgXBytes;      // 192 KB
-constexpr int kAsgSmemBytes = kAsgSmemData + 256 + 1024;
-constexpr int kAsgThreads = 256;
+constexpr int kAsgThreads = 384;                  // producer, MMA, 2 idle, 8 epilogue warps
 
-enum AsgBar { W_FULL = 0, W_EMPTY = 1, X_FULL = 2, X_EMPTY = 4, ACC_FULL = 6, ACC_EMPTY = 8, ASG_BARS = 10 };
-
-constexpr uint32_t kIdescAssign = idesc_bf16(128, kAsgJB, false);
+// JB = W rows per block (256, or 128 when there are at most 128 clusters to assign to).
+template <int JB>
+struct AsgCfg {
+  static constexpr int kWHalf = JB * 128;                       // JB rows x 64 columns
+  static constexpr int kWBytes = 2 * kWHalf;                    // per hi / lo
+  static constexpr int kXStages = JB == 256 ? 3 : 4;
+  static constexpr int kSmemData = 2 * kWBytes + kXStages * kAsgXBytes;
+  static constexpr int kSmemBytes = kSmemData + 256 + 1024;
+  // barrier indices
+  static constexpr int W_FULL = 0, W_EMPTY = 1, X_FULL = 2, X_EMPTY = X_FULL + kXStages,
+                       ACC_FULL = X_EMPTY + kXStages, ACC_EMPTY = ACC_FULL + 2, NUM = ACC_EMPTY + 2;
+};
 
 struct AsgJob {
   int bh, jb, t;
@@ -48,12 +53,33 @@ __device__ __forceinline__ AsgJob asg_job(int64_t g, int n_jb, int n_xt) {
   return j;
 }
 
+// Running first-argmax over 32 accumulator columns starting at column c0.
+__device__ __forceinline__ void argmax32(const uint32_t (&r)[32], int c0, int jlim, float& best, int& best_c) {
+  if (c0 + 32 <= jlim) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const float val = __uint_as_float(r[c]);
+      if (val > best) { best = val; best_c = c0 + c; }
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const float val = __uint_as_float(r[c]);
+      if (c0 + c < jlim && val > best) { best = val; best_c = c0 + c; }
+    }
+  }
+}
+
+template <int JB>
 __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
     const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_hi,
     const __grid_constant__ CUtensorMap tm_lo, int2* __restrict__ partial, int BH, int N, int J, int Jpad,
     int32_t* __restrict__ status) {
+  using C = AsgCfg<JB>;
+  constexpr int NS = C::kXStages;
+  constexpr uint32_t kIdesc = idesc_bf16(128, JB, false);
   extern __shared__ unsigned char smem_raw[];
-  const int n_jb = Jpad / kAsgJB, n_xt = (N + kAsgXT - 1) / kAsgXT;
+  const int n_jb = (J + JB - 1) / JB, n_xt = (N + kAsgXT - 1) / kAsgXT;
   const int64_t total = (int64_t)BH * n_jb * n_xt;
   const int64_t per = (total + gridDim.x - 1) / gridDim.x;
   const int64_t g0 = (int64_t)blockIdx.x * per;
@@ -61,16 +87,16 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
   if (g0 >= g1) return;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t whi_s = base, wlo_s = base + kAsgWBytes, x_s = base + 2 * kAsgWBytes;
-  const uint32_t bars = base + kAsgSmemData;
+  const uint32_t whi_s = base, wlo_s = base + C::kWBytes, x_s = base + 2 * C::kWBytes;
+  const uint32_t bars = base + C::kSmemData;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kAsgSmemData + ASG_BARS * 8);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kAsgSmemData + ASG_BARS * 8 + 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + C::kSmemData + C::NUM * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + C::kSmemData + C::NUM * 8 + 8);
   auto bar = [&](int i) { return bars + 8u * i; };
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   if (tid == 0) {
-    for (int i = 0; i < ASG_BARS; ++i) mbar_init(bar(i), (i == ACC_EMPTY || i == ACC_EMPTY + 1) ? 128 : 1);
+    for (int i = 0; i < C::NUM; ++i) mbar_init(bar(i), (i >= C::ACC_EMPTY) ? 256 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -86,106 +112,98 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int wq = 0, prev_block = -1;
-      int i = 0;
+      int wq = 0, prev_block = -1, i = 0;
       for (int64_t g = g0; g < g1; ++g, ++i) {
         const AsgJob job = asg_job(g, n_jb, n_xt);
         const int block = job.bh * n_jb + job.jb;
         if (block != prev_block) {
-          if (!mbar_wait(bar(W_EMPTY), (wq & 1) ^ 1, abort_flag)) break;
-          mbar_expect_tx(bar(W_FULL), 2 * kAsgWBytes);
-          const int y = job.bh * Jpad + job.jb * kAsgJB;
+          if (!mbar_wait(bar(C::W_EMPTY), (wq & 1) ^ 1, abort_flag)) break;
+          mbar_expect_tx(bar(C::W_FULL), 2 * C::kWBytes);
+          const int y = job.bh * Jpad + job.jb * JB;
           for (int h = 0; h < 2; ++h) {
-            tma_load_2d(whi_s + h * kAsgWHalf, &tm_hi, h * 64, y, bar(W_FULL));
-            tma_load_2d(wlo_s + h * kAsgWHalf, &tm_lo, h * 64, y, bar(W_FULL));
+            tma_load_2d(whi_s + h * C::kWHalf, &tm_hi, h * 64, y, bar(C::W_FULL));
+            tma_load_2d(wlo_s + h * C::kWHalf, &tm_lo, h * 64, y, bar(C::W_FULL));
           }
           prev_block = block;
           ++wq;
         }
-        const int s = i & 1;
-        if (!mbar_wait(bar(X_EMPTY + s), ((i >> 1) & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(bar(X_FULL + s), kAsgXBytes);
+        const int s = i % NS;
+        if (!mbar_wait(bar(C::X_EMPTY + s), ((i / NS) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(bar(C::X_FULL + s), kAsgXBytes);
         for (int h = 0; h < 2; ++h)
-          tma_load_2d(x_s + s * kAsgXBytes + h * kAsgXHalf, &tm_x, h * 64, job.bh * N + job.t * kAsgXT, bar(X_FULL + s));
+          tma_load_2d(x_s + s * kAsgXBytes + h * kAsgXHalf, &tm_x, h * 64, job.bh * N + job.t * kAsgXT, bar(C::X_FULL + s));
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      int wq = 0, prev_block = -1;
-      int i = 0;
+      int wq = 0, prev_block = -1, i = 0;
       for (int64_t g = g0; g < g1; ++g, ++i) {
         const AsgJob job = asg_job(g, n_jb, n_xt);
         const int block = job.bh * n_jb + job.jb;
         if (block != prev_block) {
-          if (!mbar_wait(bar(W_FULL), wq & 1, abort_flag)) break;
+          if (!mbar_wait(bar(C::W_FULL), wq & 1, abort_flag)) break;
           prev_block = block;
           ++wq;
         }
-        const int s = i & 1;
-        if (!mbar_wait(bar(X_FULL + s), (i >> 1) & 1, abort_flag)) break;
-        if (!mbar_wait(bar(ACC_EMPTY + s), ((i >> 1) & 1) ^ 1, abort_flag)) break;
+        const int s = i % NS, b = i & 1;
+        if (!mbar_wait(bar(C::X_FULL + s), (i / NS) & 1, abort_flag)) break;
+        if (!mbar_wait(bar(C::ACC_EMPTY + b), ((i >> 1) & 1) ^ 1, abort_flag)) break;
         tc_fence_after();
-        const uint32_t d = tmem + s * kAsgJB;
+        const uint32_t d = tmem + b * 256;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t a = smem_desc_sw128(x_s + s * kAsgXBytes + (ks >> 2) * kAsgXHalf + (ks & 3) * 32, 16, 1024);
-          const uint32_t woff = (ks >> 2) * kAsgWHalf + (ks & 3) * 32;
-          umma_ss(d, a, smem_desc_sw128(whi_s + woff, 16, 1024), kIdescAssign, ks > 0);
-          umma_ss(d, a, smem_desc_sw128(wlo_s + woff, 16, 1024), kIdescAssign, 1);
+          const uint32_t woff = (ks >> 2) * C::kWHalf + (ks & 3) * 32;
+          umma_ss(d, a, smem_desc_sw128(whi_s + woff, 16, 1024), kIdesc, ks > 0);
+          umma_ss(d, a, smem_desc_sw128(wlo_s + woff, 16, 1024), kIdesc, 1);
         }
-        tc_commit(bar(X_EMPTY + s));
-        tc_commit(bar(ACC_FULL + s));
+        tc_commit(bar(C::X_EMPTY + s));
+        tc_commit(bar(C::ACC_FULL + b));
         bool last_of_block = g + 1 >= g1;
         if (!last_of_block) {
           const AsgJob nxt = asg_job(g + 1, n_jb, n_xt);
           last_of_block = nxt.bh * n_jb + nxt.jb != block;
         }
-        if (last_of_block) tc_commit(bar(W_EMPTY));
+        if (last_of_block) tc_commit(bar(C::W_EMPTY));
       }
     }
   } else if (warp >= 4) {
-    // ---------------------------------------------------------------- epilogue: running argmax
-    const int quad = warp & 3;
+    // ------------------------------------------------- epilogue: running argmax, half of the columns per warp
+    const int quad = warp & 3, half = (warp - 4) >> 2;
     const int r_local = quad * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    constexpr int HC = JB / 2;                               // columns per half
     uint32_t ra[32], rb[32];
     int i = 0;
     bool ok = true;
     for (int64_t g = g0; g < g1 && ok; ++g, ++i) {
       const AsgJob job = asg_job(g, n_jb, n_xt);
-      const int s = i & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(ACC_FULL + s), (i >> 1) & 1, abort_flag));
+      const int b = i & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(C::ACC_FULL + b), (i >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t acc = tmem + lane_addr + s * kAsgJB;
-      const int jlim = min(J - job.jb * kAsgJB, kAsgJB);       // valid columns of this block
+      const uint32_t acc = tmem + lane_addr + b * 256 + half * HC;
+      const int jlim = J - job.jb * JB - half * HC;            // valid columns of this half (may be <= 0)
       float best = -INFINITY;
       int best_c = 0;
       tmem_ld32_nowait(acc, ra);
       tmem_wait_ld();
-#pragma unroll 1
-      for (int ch = 0; ch < 8; ch += 2) {
+#pragma unroll
+      for (int ch = 0; ch < HC / 32; ch += 2) {
         tmem_ld32_nowait(acc + (ch + 1) * 32, rb);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float val = __uint_as_float(ra[c]);
-          if (ch * 32 + c < jlim && val > best) { best = val; best_c = ch * 32 + c; }
-        }
+        argmax32(ra, ch * 32, jlim, best, best_c);
         tmem_wait_ld();
-        if (ch + 2 < 8) tmem_ld32_nowait(acc + (ch + 2) * 32, ra);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float val = __uint_as_float(rb[c]);
-          if ((ch + 1) * 32 + c < jlim && val > best) { best = val; best_c = (ch + 1) * 32 + c; }
-        }
+        if (ch + 2 < HC / 32) tmem_ld32_nowait(acc + (ch + 2) * 32, ra);
+        argmax32(rb, (ch + 1) * 32, jlim, best, best_c);
         tmem_wait_ld();
       }
       tc_fence_before();
-      mbar_arrive(bar(ACC_EMPTY + s));
+      mbar_arrive(bar(C::ACC_EMPTY + b));
       const int n = job.t * kAsgXT + r_local;
       if (n < N)
-        partial[((int64_t)job.jb * BH + job.bh) * N + n] = make_int2(__float_as_int(best), job.jb * kAsgJB + best_c);
+        partial[((int64_t)(job.jb * 2 + half) * BH + job.bh) * N + n] =
+            make_int2(__float_as_int(best), job.jb * JB + half * HC + best_c);
     }
   }
   tc_fence_before();
@@ -197,14 +215,14 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
   }
 }
 
-// labels[bh, n] = j of the best (score, j) pair over the W blocks; the lower block wins ties.
+// labels[bh, n] = j of the best (score, j) pair over the column groups; the lower group wins ties.
 __global__ void __launch_bounds__(256) assign_reduce_kernel(const int2* __restrict__ partial, int32_t* __restrict__ labels,
-                                                            int64_t BHN, int n_jb) {
+                                                            int64_t BHN, int groups) {
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= BHN) return;
   int2 b = partial[i];
-  for (int jb = 1; jb < n_jb; ++jb) {
-    const int2 c = partial[(int64_t)jb * BHN + i];
+  for (int g = 1; g < groups; ++g) {
+    const int2 c = partial[(int64_t)g * BHN + i];
     if (__int_as_float(c.x) > __int_as_float(b.x)) b = c;
   }
   labels[i] = b.y;
@@ -240,24 +258,35 @@ bool make_row_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int bo
 
 }  // namespace tc
 
-cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int2* partial,
-                             int32_t* status, int64_t BH, int64_t N, int64_t J, cudaStream_t st) {
-  const int Jpad = pad_clusters(J);
+template <int JB>
+static cudaError_t launch_assign_tc_jb(const void* x, const void* w_hi, const void* w_lo, int2* partial, int32_t* status,
+                                       int64_t BH, int64_t N, int64_t J, int Jpad, cudaStream_t st) {
+  using C = tc::AsgCfg<JB>;
   alignas(64) CUtensorMap mx, mh, ml;
-  if (!tc::make_row_tensor_map(&mx, x, BH * N, tc::kAsgXT) || !tc::make_row_tensor_map(&mh, w_hi, BH * Jpad, tc::kAsgJB) ||
-      !tc::make_row_tensor_map(&ml, w_lo, BH * Jpad, tc::kAsgJB))
+  if (!tc::make_row_tensor_map(&mx, x, BH * N, tc::kAsgXT) || !tc::make_row_tensor_map(&mh, w_hi, BH * Jpad, JB) ||
+      !tc::make_row_tensor_map(&ml, w_lo, BH * Jpad, JB))
     return cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(tc::assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kAsgSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(tc::assign_tc_kernel<JB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int n_jb = Jpad / tc::kAsgJB;
-  const int64_t total = BH * n_jb * ceil_div64(N, tc::kAsgXT);
+  const int64_t total = BH * ceil_div64(J, JB) * ceil_div64(N, tc::kAsgXT);
   const unsigned grid = (unsigned)(total < sms ? total : sms);
-  tc::assign_tc_kernel<<<grid, tc::kAsgThreads, tc::kAsgSmemBytes, st>>>(mx, mh, ml, partial, (int)BH, (int)N, (int)J, Jpad,
-                                                                        status);
-  tc::assign_reduce_kernel<<<(unsigned)ceil_div64(BH * N, 256), 256, 0, st>>>(partial, labels, BH * N, n_jb);
+  tc::assign_tc_kernel<JB><<<grid, tc::kAsgThreads, C::kSmemBytes, st>>>(mx, mh, ml, partial, (int)BH, (int)N, (int)J, Jpad,
+                                                                         status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int2* partial,
+                             int32_t* status, int64_t BH, int64_t N, int64_t J, cudaStream_t st) {
+  const int Jpad = pad_clusters(J);
+  const int jb = J <= 128 ? 128 : 256;
+  cudaError_t e = jb == 128 ? launch_assign_tc_jb<128>(x, w_hi, w_lo, partial, status, BH, N, J, Jpad, st)
+                            : launch_assign_tc_jb<256>(x, w_hi, w_lo, partial, status, BH, N, J, Jpad, st);
+  if (e != cudaSuccess) return e;
+  const int groups = 2 * (int)ceil_div64(J, jb);
+  tc::assign_reduce_kernel<<<(unsigned)ceil_div64(BH * N, 256), 256, 0, st>>>(partial, labels, BH * N, groups);
   count_launches(2);
   return cudaGetLastError();
 }

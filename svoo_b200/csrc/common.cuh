@@ -30,7 +30,7 @@ struct Workspace {
   int64_t partial;       // float [BH, Kmax, slabs, 128] centroid partial sums
   int64_t w_hi;          // bf16  [BH, Jpad, 128]
   int64_t w_lo;          // bf16  [BH, Jpad, 128]
-  int64_t assign_partial;  // int2 [Jpad/256, BH, N]: best (score bits, j) per W block
+  int64_t assign_partial;  // int2 [Jpad/128, BH, N]: best (score bits, j) per column group
   int64_t status;        // int32 [4]: word 0 != 0 after a kernel gave up on a bounded wait
   int64_t runs;          // int2  [BH, QC, max_runs]: (first_row, virtual_begin) + sentinel (0, total)
   int64_t nruns;         // int32 [BH, QC]
@@ -53,7 +53,7 @@ __host__ inline Workspace workspace_layout(int64_t BH, int64_t N, int64_t QC, in
   w.partial = take(BH * Kmax * kCentroidSlabs * kHeadDim * 4);
   w.w_hi = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
   w.w_lo = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
-  w.assign_partial = take((int64_t)(pad_clusters(Kmax) / 256) * BH * N * 8);
+  w.assign_partial = take((int64_t)(pad_clusters(Kmax) / 128) * BH * N * 8);   // two column groups per 256 rows
   w.status = take(16);
   // sized symmetrically in (QC, KC) so that one workspace serves either side
   w.runs = take(BH * (QC * KC / 2 + 2 * (QC + KC)) * 8);
