@@ -209,7 +209,7 @@ def run_gpu_arm(args, cfg):
     qi, ki = qi_all[mine].to(dev), ki_all[mine].to(dev)
     d_mine = [dens[h] for h in mine]
     kw = dict(num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k, kmeans_iters=cfg.iters, top_p=cfg.top_p,
-              context_length=cfg.text_tokens, fuse_gather=args.fuse_gather)
+              context_length=cfg.text_tokens)
 
     q_d, k_d, v_d = q_h.to(dev), k_h.to(dev), v_h.to(dev)
     if world > 1:
@@ -363,8 +363,6 @@ def main():
     ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS))
     ap.add_argument("--heads", type=int, default=0, help="override the head count (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--fuse-gather", action="store_true",
-                    help="gather Q,K,V rows inside the attention kernel instead of permuting them first")
     args = ap.parse_args()
     cfg = synth.CONFIGS[args.config]
     if args.heads:

@@ -134,21 +134,16 @@ int svoo_b200_block_map(const void* qcentroids, const void* kcentroids, const in
  * semantics are those of _dynamic_block_sparse_fwd_kernel :949-1108): query
  * cluster i of head bh attends the key clusters j with map[bh,i,j] != 0; rows
  * without a selected key give 0.  q_offsets [BH,QC+1], k_offsets [BH,KC+1] are
- * the cluster row offsets.  Three optional int32 [BH,S] index vectors fuse the
- * permutations of svoo/kernels/triton/permute.py into the kernel's loads and store:
- *   q_row_idx   not null: cluster-ordered query row s is read from row q_row_idx[bh,s] of q
- *   kv_row_idx  not null: cluster-ordered key row s is read from row kv_row_idx[bh,s] of k and v
- *   out_row_idx not null: result row s is written to row out_row_idx[bh,s] of out
- * (pass the sorted_idx of svoo_b200_cocluster and q, k, v in their original token order);
- * a null pointer means the tensor is already / stays in cluster order. */
+ * the cluster row offsets.  If out_row_idx is not null the result row s is
+ * written to row out_row_idx[bh,s] (the inverse permutation fused into the
+ * store); otherwise to row s. */
 int svoo_b200_sparse_attn(const void* q, const void* k, const void* v, const uint8_t* map,
                           const int32_t* q_offsets, const int32_t* k_offsets,
                           int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, float sm_scale,
-                          void* out, const int32_t* q_row_idx, const int32_t* kv_row_idx,
-                          const int32_t* out_row_idx,
+                          void* out, const int32_t* out_row_idx,
                           void* workspace, int64_t workspace_bytes, void* stream);
 
-/* Same contract as svoo_b200_sparse_attn without q_row_idx / kv_row_idx, computed by the warp-level-MMA (mma.sync)
+/* Same contract as svoo_b200_sparse_attn, computed by the warp-level-MMA (mma.sync)
  * kernel instead of the tcgen05 one.  Kept as an independent on-device cross-check of
  * the tensor-core kernel at sizes the CPU oracle cannot reach; not used by the layer. */
 int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, const uint8_t* map,

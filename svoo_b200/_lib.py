@@ -36,8 +36,8 @@ SIGNATURES = {
     "svoo_b200_block_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,
                                     _I32P, _I32P, c_void_p, c_void_p]),
     "svoo_b200_sparse_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
-                                      c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
-                                      c_void_p, c_int64, c_void_p]),
+                                      c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
+                                      c_void_p]),
     "svoo_b200_sparse_attn_simt": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
                                            c_void_p]),

@@ -17,9 +17,9 @@ cudaError_t launch_block_map(const void*, const void*, const int32_t*, uint8_t*,
                              const int32_t*, const int32_t*, cudaStream_t);
 cudaError_t launch_build_runs(const uint8_t*, const int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t, cudaStream_t);
 cudaError_t launch_build_qtiles(const int32_t*, int4*, int32_t*, int64_t, int64_t, int64_t, int, cudaStream_t);
-cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, void*, const int32_t*, const int32_t*,
-                                  const int32_t*, const int4*, const int32_t*, const int2*, const int32_t*, int32_t*,
-                                  int64_t, int64_t, int64_t, int64_t, float, cudaStream_t);
+cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, void*, const int32_t*, const int4*,
+                                  const int32_t*, const int2*, const int32_t*, int32_t*, int64_t, int64_t, int64_t,
+                                  int64_t, float, cudaStream_t);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, void*, const int32_t*, const int4*,
                                    const int32_t*, const int2*, const int32_t*, int64_t, int64_t, int64_t, int64_t,
                                    float, cudaStream_t);
@@ -216,9 +216,8 @@ int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, in
 
 static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, const void* v, const uint8_t* map,
                             const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
-                            int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* q_row_idx,
-                            const int32_t* kv_row_idx, const int32_t* out_row_idx, void* workspace,
-                            int64_t workspace_bytes, void* stream) {
+                            int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx,
+                            void* workspace, int64_t workspace_bytes, void* stream) {
   if (!q || !k || !v || !map || !q_offsets || !k_offsets || !out || !workspace) return SVOO_ERR_NULL;
   SVOO_TRY(check_tokens(BH, S, D));
   SVOO_TRY(check_clusters(QC));
@@ -237,10 +236,9 @@ static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, cons
   SVOO_CUDA(launch_build_qtiles(q_offsets, qtiles, nqtiles, BH, S, QC, tensor_core ? 256 : 128, st));
   if (tensor_core) {
     SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));                     // word 0: attention kernel
-    SVOO_CUDA(launch_sparse_attn_tc(q, k, v, out, q_row_idx, kv_row_idx, out_row_idx, qtiles, nqtiles, runs, nruns,
-                                    status, BH, S, QC, KC, sm_scale, st));
+    SVOO_CUDA(launch_sparse_attn_tc(q, k, v, out, out_row_idx, qtiles, nqtiles, runs, nruns, status, BH, S, QC, KC,
+                                    sm_scale, st));
   } else {
-    if (q_row_idx || kv_row_idx) return SVOO_ERR_SHAPE;
     SVOO_CUDA(launch_sparse_attn_mma(q, k, v, out, out_row_idx, qtiles, nqtiles, runs, nruns, BH, S, QC, KC, sm_scale,
                                      st));
   }
@@ -249,18 +247,18 @@ static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, cons
 
 int svoo_b200_sparse_attn(const void* q, const void* k, const void* v, const uint8_t* map, const int32_t* q_offsets,
                           const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC,
-                          float sm_scale, void* out, const int32_t* q_row_idx, const int32_t* kv_row_idx,
-                          const int32_t* out_row_idx, void* workspace, int64_t workspace_bytes, void* stream) {
-  return sparse_attn_impl(true, q, k, v, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, out, q_row_idx,
-                          kv_row_idx, out_row_idx, workspace, workspace_bytes, stream);
+                          float sm_scale, void* out, const int32_t* out_row_idx, void* workspace,
+                          int64_t workspace_bytes, void* stream) {
+  return sparse_attn_impl(true, q, k, v, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, out, out_row_idx,
+                          workspace, workspace_bytes, stream);
 }
 
 int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, const uint8_t* map,
                                const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
                                int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx,
                                void* workspace, int64_t workspace_bytes, void* stream) {
-  return sparse_attn_impl(false, q, k, v, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, out, nullptr, nullptr,
-                          out_row_idx, workspace, workspace_bytes, stream);
+  return sparse_attn_impl(false, q, k, v, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, out, out_row_idx,
+                          workspace, workspace_bytes, stream);
 }
 
 int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* offset_out) {

@@ -3,18 +3,14 @@
 // One CTA owns up to two 128-row query tiles of one query cluster.  The key rows that the
 // cluster's map row selects form a list of runs of the cluster-ordered K/V; the CTA walks
 // their concatenation 128 keys at a time, so key tiles are always full except the last one
-// (tiles are packed across run boundaries by gathering rows, which a TMA box cannot do).
+// (a tile is packed across run boundaries from several TMA boxes of power-of-two heights).
 //
 //   warps 0-3   softmax of query tile 0: thread r owns row r (TMEM lane r): running max and
 //   warps 4-7   sum, P written back over S as packed bf16; same for tile 1
-//   warps 8-11  K loader (and Q, once): cp.async 16-byte gathers into the 128-byte-swizzled
-//               K-major layout the MMA descriptors expect, fence.proxy.async, mbarrier arrive
-//   warps 12-15 V loader, same, two-stage rings for K and for V
-//   warp 16     MMA issuer (one elected thread): S_w = Q_w K^T into TMEM (tcgen05.mma, both
+//   warp 8      TMA producer for Q (once) and K, warp 9 for V: cp.async.bulk.tensor 2-D boxes of
+//               64 columns with the 128-byte swizzle, no multicast; two-stage rings for K and V
+//   warp 10     MMA issuer (one elected thread): S_w = Q_w K^T into TMEM (tcgen05.mma, both
 //               operands from shared memory), then O_w += P_w V with P_w read from TMEM
-//
-// Rows can be fetched through index vectors (q_row_idx / kv_row_idx): the cluster-order
-// permutation of Q, K and V is then fused into the loads and no permuted copy exists.
 //
 // The two query tiles ping-pong: while one tile's rows are in the softmax, the tensor
 // core works on the other tile's products.  O stays in TMEM; it is rescaled by the owning
@@ -37,9 +33,22 @@ constexpr int kBox = 128 * 128;          // 16 KB: 128 rows x 64 columns
 constexpr int kSmemTiles = 6 * kTile;    // Q0 Q1 | K0 K1 | V0 V1
 constexpr int kMaxRunsSmem = SVOO_MAX_CLUSTERS / 2 + 2;
 constexpr int kRunTableBytes = (kMaxRunsSmem * 8 + 255) / 256 * 256;
-constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 2048 + 1024;   // + barriers, run table, row maps, slack
-constexpr int kThreads = 544;            // 8 softmax + 4 K-loader + 4 V-loader + 1 MMA warps
-constexpr int kLoaderThreads = 128;      // per tensor (K, V): one thread per key row of a tile
+constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 1024;   // + barriers, run table, slack
+#ifndef SVOO_SINGLE_PASS
+#define SVOO_SINGLE_PASS 0
+#endif
+constexpr int kKWarp = 8, kVWarp = 9, kMmaWarp = 10;     // after the 8 softmax warps
+// 11 warps; registers are allotted to a CTA in groups of four warps: 65536 / (12 * 32) = 170.
+constexpr int kThreads = (kMmaWarp + 1) * 32;
+constexpr int kBoxHeights = 8;                           // TMA boxes of 1, 2, 4, ..., 128 rows
+
+// Tensor maps of one launch: Q with 128-row boxes; K and V with one map per box height, so a
+// run segment of any length is fetched as a few power-of-two pieces.
+struct AttnMaps {
+  CUtensorMap q;
+  CUtensorMap k[kBoxHeights];
+  CUtensorMap v[kBoxHeights];
+};
 constexpr float kRescaleThreshold = 8.0f;
 
 enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_DONE = 13, NUM_BARS = 15 };
@@ -79,6 +88,21 @@ __device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], uint32_t (&pk)
   }
 }
 
+// 16 columns: x = s * scale + neg_m, running max of x, p = exp2(x) -> 8 packed bf16 pairs.
+__device__ __forceinline__ void exp_pack16(const uint32_t (&r)[16], uint32_t* pk, float scale, float neg_m, float& l0,
+                                           float& l1, float& mx) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float x0 = fmaf(__uint_as_float(r[2 * i]), scale, neg_m);
+    const float x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale, neg_m);
+    mx = fmaxf(mx, fmaxf(x0, x1));
+    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    l0 += p0;
+    l1 += p1;
+    pk[i] = pack_bf16x2(p0, p1);
+  }
+}
+
 // Shared-memory matrix descriptors, 128-byte swizzle, descriptor version 1 (sm_100).
 //   K-major  (Q, K: rows = M/N index, 64 contiguous elements of the reduction dim per 128-byte row):
 //            8-row groups 1024 B apart (SBO); LBO unused.
@@ -96,40 +120,47 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
 
-// Byte offset of 16-byte chunk `chunk` (0..15) of row `row` (0..127) inside a [128 x 128] bf16
-// tile stored as two [128 rows x 128 B] halves with the 128-byte swizzle (chunk ^= row % 8).
-__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
-  return (uint32_t)((chunk >> 3) * kBox + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+// Packed key tile j = virtual rows [128 j, 128 j + 128) of the concatenated runs.  Every run
+// segment inside it is contiguous in the cluster-ordered tensor and is fetched by TMA as
+// power-of-two pieces (two boxes of 64 columns each) placed at its row offset of the swizzled
+// tile; rows past the last selected key are fetched from beyond the end of the tensor, which
+// TMA fills with zeros.  Always 32 KB of transactions per tile.
+__device__ __forceinline__ void tma_gather_tile(uint32_t dst, const CUtensorMap* maps, const int2* runs_s, int nr,
+                                                int& r_cur, int j, int L, int head_row0, int rows_total, uint32_t bar) {
+  int row = 0;
+  while (row < kBN) {
+    const int v = j * kBN + row;
+    int len, y;
+    if (v < L) {
+      while (r_cur + 1 < nr && v >= runs_s[r_cur + 1].y) ++r_cur;
+      len = min(runs_s[r_cur + 1].y - v, kBN - row);
+      y = head_row0 + runs_s[r_cur].x + (v - runs_s[r_cur].y);
+    } else {
+      len = kBN - row;
+      y = rows_total;                                   // out of range: zero fill
+    }
+    while (len > 0) {
+      const int lg = 31 - __clz(len);                   // largest power of two <= len (<= 128)
+      const int h = 1 << lg;
+      tma_load_2d(dst + row * 128, maps + lg, 0, y, bar);
+      tma_load_2d(dst + kBox + row * 128, maps + lg, 64, y, bar);
+      row += h;
+      len -= h;
+      if (y < rows_total) y += h;
+    }
+  }
 }
 
-// Gathers the 128 key rows of packed tile j (virtual rows [128 j, 128 j + 128) of the
-// concatenated runs) into one swizzled tile; rows past the end are zero-filled.  Thread tl
-// (0..127) first resolves the source row of virtual row 128 j + tl into `rowmap` (shared
-// memory), then the 128 threads copy the tile with 16 lanes per 256-byte row.
-__device__ __forceinline__ void gather_tile(uint32_t dst, const bf16* __restrict__ base, const int32_t* __restrict__ row_idx,
-                                            const int2* runs_s, int nr, int& r_cur, int* rowmap, int bar_id, int j,
-                                            int L, int tl) {
-  const int v = j * kBN + tl;
-  int p = -1;
-  if (v < L) {
-    while (r_cur + 1 < nr && v >= runs_s[r_cur + 1].y) ++r_cur;
-    p = runs_s[r_cur].x + (v - runs_s[r_cur].y);
-    if (row_idx) p = __ldg(row_idx + p);
-  }
-  rowmap[tl] = p;
-  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(kLoaderThreads) : "memory");
-#pragma unroll 4
-  for (int it = 0; it < 16; ++it) {
-    const int row = it * 8 + (tl >> 4), chunk = tl & 15;
-    const int src = rowmap[row];
-    cp_async16(dst + tile_off(row, chunk), base + (int64_t)(src < 0 ? 0 : src) * kHeadDim + chunk * 8, src >= 0);
-  }
-}
+#ifdef SVOO_TRACE
+// Debug builds only: clock64 stamps of pipeline events of one CTA, [role][tile][slot].
+__device__ long long g_trace[8 * 64 * 4];
+#define TRACE(role, tile, slot) do { if (blockIdx.x == SVOO_TRACE && blockIdx.y == 0 && (tile) < 64) g_trace[((role) * 64 + (tile)) * 4 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(role, tile, slot) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, bf16* __restrict__ out,
-    const int32_t* __restrict__ q_row_idx, const int32_t* __restrict__ kv_row_idx,
-    const int32_t* __restrict__ out_row_idx, const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles,
+    const __grid_constant__ AttnMaps maps, bf16* __restrict__ out, const int32_t* __restrict__ out_row_idx, const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles,
     const int2* __restrict__ runs, const int32_t* __restrict__ nruns, int S, int QC, int max_tiles, int max_runs,
     float scale_log2, int32_t* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
@@ -148,7 +179,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemTiles + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemTiles + NUM_BARS * 8 + 8);
   int2* runs_s = reinterpret_cast<int2*>(gen_base + kSmemTiles + 256);
-  int* rowmaps = reinterpret_cast<int*>(gen_base + kSmemTiles + 256 + kRunTableBytes);   // [K,V][stage][128]
   auto bar = [&](int i) { return bars + 8u * i; };
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -156,14 +186,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     for (int i = 0; i < NUM_BARS; ++i) {
       int count = 1;
       if (i == P_READY || i == P_READY + 1) count = kBM;
-      if (i == Q_FULL || i == K_FULL || i == K_FULL + 1 || i == V_FULL || i == V_FULL + 1) count = kLoaderThreads;
       mbar_init(bar(i), count);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = tid; i <= nr; i += kThreads) runs_s[i] = rl[i];
-  if (warp == 16) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -174,67 +203,31 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   const int L = runs_s[nr].y;                      // selected key rows in total
   const int T = (L + kBN - 1) / kBN;               // packed key tiles
 
-  if (warp >= 8 && warp < 12) {
-    // ---------------------------------------------------------------- Q and K loader
-    const int tl = tid - 8 * 32;
-    if (T > 0) {
-      const bf16* qb = q + (int64_t)bh * S * kHeadDim;
-      const int32_t* qidx = q_row_idx ? q_row_idx + (int64_t)bh * S : nullptr;
-      for (int it = 0; it < nq * 16; ++it) {
-        const int row = it * 8 + (tl >> 4), chunk = tl & 15;
-        const int grow = row0 + row;
-        const bool ok = grow < row1;
-        int p = ok ? grow : row0;
-        if (ok && qidx) p = __ldg(qidx + p);
-        cp_async16(q_s + (row >> 7) * kTile + tile_off(row & 127, chunk), qb + (int64_t)p * kHeadDim + chunk * 8, ok);
+  if (warp == kKWarp || warp == kVWarp) {
+    // ---------------------------------------------------------------- TMA producers (K + Q, V)
+    if (lane == 0 && T > 0) {
+      const int is_v = warp == kVWarp;
+      const int rows_total = (int)gridDim.y * S;
+      if (!is_v) {
+        mbar_expect_tx(bar(Q_FULL), nq * kTile);
+        for (int w = 0; w < nq; ++w)
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(q_s + w * kTile + h * kBox, &maps.q, h * 64, bh * S + row0 + w * kBM, bar(Q_FULL));
       }
-      const bf16* kb = k + (int64_t)bh * S * kHeadDim;
-      const int32_t* kidx = kv_row_idx ? kv_row_idx + (int64_t)bh * S : nullptr;
+      const CUtensorMap* tm = is_v ? maps.v : maps.k;
+      const uint32_t stage0 = is_v ? v_s : k_s;
+      const int full = is_v ? V_FULL : K_FULL, empty = is_v ? V_EMPTY : K_EMPTY;
       int r_cur = 0;
-      bool ok = true;
-      for (int j = 0; j < T && ok; ++j) {
+      for (int j = 0; j < T; ++j) {
         const int s = j & 1;
-        ok = mbar_wait(bar(K_EMPTY + s), ((j >> 1) & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        gather_tile(k_s + s * kTile, kb, kidx, runs_s, nr, r_cur, rowmaps + s * 128, 1, j, L, tl);
-        cp_async_commit();
-        if (j >= 1) {
-          cp_async_wait<1>();
-          fence_async_proxy();
-          if (j == 1) mbar_arrive(bar(Q_FULL));
-          mbar_arrive(bar(K_FULL + (s ^ 1)));
-        }
-      }
-      cp_async_wait<0>();
-      fence_async_proxy();
-      if (ok) {
-        if (T == 1) mbar_arrive(bar(Q_FULL));
-        mbar_arrive(bar(K_FULL + ((T - 1) & 1)));
+        if (!mbar_wait(bar(empty + s), ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        TRACE(3 + is_v, j, 0);
+        mbar_expect_tx(bar(full + s), kTile);
+        tma_gather_tile(stage0 + s * kTile, tm, runs_s, nr, r_cur, j, L, bh * S, rows_total, bar(full + s));
+        TRACE(3 + is_v, j, 1);
       }
     }
-  } else if (warp >= 12 && warp < 16) {
-    // ---------------------------------------------------------------- V loader
-    const int tl = tid - 12 * 32;
-    const bf16* vb = v + (int64_t)bh * S * kHeadDim;
-    const int32_t* kidx = kv_row_idx ? kv_row_idx + (int64_t)bh * S : nullptr;
-    int r_cur = 0;
-    bool ok = true;
-    for (int j = 0; j < T && ok; ++j) {
-      const int s = j & 1;
-      ok = mbar_wait(bar(V_EMPTY + s), ((j >> 1) & 1) ^ 1, abort_flag);
-      if (!ok) break;
-      gather_tile(v_s + s * kTile, vb, kidx, runs_s, nr, r_cur, rowmaps + 256 + s * 128, 2, j, L, tl);
-      cp_async_commit();
-      if (j >= 1) {
-        cp_async_wait<1>();
-        fence_async_proxy();
-        mbar_arrive(bar(V_FULL + (s ^ 1)));
-      }
-    }
-    cp_async_wait<0>();
-    fence_async_proxy();
-    if (ok && T > 0) mbar_arrive(bar(V_FULL + ((T - 1) & 1)));
-  } else if (warp == 16) {
+  } else if (warp == kMmaWarp) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && T > 0) {
       auto issue_qk = [&](int w, int s) {
@@ -262,6 +255,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) break;
         for (int w = 0; w < nq && ok; ++w) {
           ok = mbar_wait(bar(P_READY + w), j & 1, abort_flag);
+          TRACE(2, j, w);
           if (!ok) break;
           tc_fence_after();
           issue_pv(w, s, j > 0);
@@ -274,6 +268,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
             }
             issue_qk(w, sn);
             tc_commit(bar(S_FULL + w));
+            TRACE(2, j, 2 + w);
           }
         }
         if (!ok) break;
@@ -296,8 +291,39 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       for (int j = 0; j < T; ++j) {
         const int valid = min(L - j * kBN, kBN);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + w), j & 1, abort_flag));
+        if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 0);
         if (!ok) break;
         tc_fence_after();
+        if (SVOO_SINGLE_PASS && j > 0 && valid >= kBN) {
+          // Common case, one TMEM pass: exponentials are taken against the running maximum of
+          // the previous tiles and kept in registers; they are stored only if no row of the
+          // warp outgrew that maximum by more than 2^8, otherwise the two-pass path redoes the tile.
+          const float neg_m0 = -m_used;
+          float mx = -INFINITY, la = 0.f, lb = 0.f;
+          uint32_t pk[64];
+          uint32_t xa[16], xb[16];
+          tmem_ld16_nowait(s_t, xa);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 8; c += 2) {
+            tmem_ld16_nowait(s_t + (c + 1) * 16, xb);
+            exp_pack16(xa, &pk[c * 8], scale_log2, neg_m0, la, lb, mx);
+            tmem_wait_ld();
+            if (c + 2 < 8) tmem_ld16_nowait(s_t + (c + 2) * 16, xa);
+            exp_pack16(xb, &pk[(c + 1) * 8], scale_log2, neg_m0, la, lb, mx);
+            tmem_wait_ld();
+          }
+          if (!__any_sync(0xffffffffu, mx > kRescaleThreshold)) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_st16(s_t + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[c * 16]));
+            l_sum += la + lb;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(P_READY + w));
+            if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 1);
+            continue;
+          }
+        }
         // pass 1: row maximum of the raw scores (the scale is positive), two loads in flight
         float m_raw = -INFINITY;
         tmem_ld32_nowait(s_t, ra);
@@ -367,6 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(P_READY + w));
+        if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 2);
       }
       // epilogue: O / l -> bf16 rows
       const int row = row0 + w * kBM + r_local;
@@ -404,7 +431,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag) atomicExch(status, 1);
-  if (warp == 16) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
@@ -412,17 +439,28 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
 
 }  // namespace tc
 
-cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, void* out, const int32_t* q_row_idx,
-                                  const int32_t* kv_row_idx, const int32_t* out_row_idx, const int4* qtiles,
-                                  const int32_t* nqtiles, const int2* runs, const int32_t* nruns, int32_t* status,
-                                  int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale, cudaStream_t st) {
+#ifdef SVOO_TRACE
+extern "C" int svoo_b200_debug_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, tc::g_trace, sizeof(tc::g_trace));
+}
+#endif
+
+cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, void* out, const int32_t* out_row_idx,
+                                  const int4* qtiles, const int32_t* nqtiles, const int2* runs, const int32_t* nruns,
+                                  int32_t* status, int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale,
+                                  cudaStream_t st) {
+  alignas(64) tc::AttnMaps maps;
+  bool ok = tc::make_row_tensor_map(&maps.q, q, BH * S, 128);
+  for (int i = 0; i < tc::kBoxHeights && ok; ++i)
+    ok = tc::make_row_tensor_map(&maps.k[i], k, BH * S, 1 << i) && tc::make_row_tensor_map(&maps.v[i], v, BH * S, 1 << i);
+  if (!ok) return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(tc::sparse_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        tc::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)max_qtiles(S, QC), (unsigned)BH);
   tc::sparse_attn_tc_kernel<<<grid, tc::kThreads, tc::kSmemBytes, st>>>(
-      (const bf16*)q, (const bf16*)k, (const bf16*)v, (bf16*)out, q_row_idx, kv_row_idx, out_row_idx, qtiles, nqtiles,
-      runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), max_runs(KC), sm_scale * 1.4426950408889634f, status);
+      maps, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), max_runs(KC),
+      sm_scale * 1.4426950408889634f, status);
   count_launches(1);
   return cudaGetLastError();
 }

@@ -32,47 +32,28 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int32_t* __
 
 // ---------------------------------------------------------------------------------------
 // Prologue: P = bf16(own . form^T), Phat = P / sqrt(sum P^2 + 1e-8) (fp32),
-//           W = Phat . form (fp32) -> (hi, lo) bf16.     One CTA = 32 rows j of one head;
-//           `form` is swept twice through shared memory in chunks of 32 centroids.
+//           W = Phat . form (fp32) -> (hi, lo) bf16.     One CTA = 32 rows j of one head.
+// `form` is swept twice through shared memory in chunks of 64 centroids; both sweeps are
+// register-tiled (4x2 and 4x4 outputs per thread, operands read as float2 / float4).
 // (svoo/co_clustering.py:2427-2428 and svoo/kernels/triton/l2norm.py:36-41)
 // ---------------------------------------------------------------------------------------
 constexpr int kProR = 32;            // own rows per CTA
-constexpr int kProC = 32;            // form rows per chunk
-constexpr int kProLd = kHeadDim + 1; // padded row length (floats) of the staged tiles
-
-__device__ __forceinline__ void stage_form_chunk(float* dst, const bf16* __restrict__ form_b, int k0, int K, int tid) {
-  // 32 rows x 128 dims: 256 threads, 16 elements each (two 16-byte loads)
-  const int row = tid >> 3, d0 = (tid & 7) * 16;
-  if (k0 + row < K) {
-    const uint4* src = reinterpret_cast<const uint4*>(form_b + (int64_t)(k0 + row) * kHeadDim + d0);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint4 v = __ldg(src + h);
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        dst[row * kProLd + d0 + h * 8 + 2 * e] = __low2float(p[e]);
-        dst[row * kProLd + d0 + h * 8 + 2 * e + 1] = __high2float(p[e]);
-      }
-    }
-  } else {
-#pragma unroll
-    for (int e = 0; e < 16; ++e) dst[row * kProLd + d0 + e] = 0.f;
-  }
-}
+constexpr int kProC = 64;            // form rows per chunk
 
 __global__ void __launch_bounds__(256) profile_prologue_kernel(
     const bf16* __restrict__ own, const bf16* __restrict__ form, bf16* __restrict__ w_hi,
-    bf16* __restrict__ w_lo, int J, int K, int Jpad, int Kld) {
-  extern __shared__ float sm[];
-  float* own_s = sm;                          // [32][129]
-  float* chunk_s = own_s + kProR * kProLd;    // [32][129]
-  float* p_s = chunk_s + kProC * kProLd;      // [32][Kld]   Kld odd
+    bf16* __restrict__ w_lo, int J, int K, int Jpad) {
+  extern __shared__ __align__(16) float sm[];
+  float* own_t = sm;                            // [128 d][32 r]
+  float* chunk = own_t + kHeadDim * kProR;      // sweep 1: [128 d][64 k]; sweep 2: [64 k][128 d]
+  float* p_t = chunk + kHeadDim * kProC;        // [K][32 r]
+  __shared__ float part_s[8][kProR];
   __shared__ float norm_s[kProR];
   const int bh = blockIdx.y, j0 = blockIdx.x * kProR;
-  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int d = tid % kHeadDim, rg = tid / kHeadDim;        // phase 3: column d, rows rg*16 .. +15
-  if (j0 >= J) {                                            // padding rows of W: zeros
+  const int tid = threadIdx.x;
+  const int lane32 = tid & 31, grp8 = tid >> 5;         // grp8: 0..7
+  if (j0 >= J) {                                        // padding rows of W: zeros
+    const int d = tid & 127, rg = tid >> 7;
     for (int r = rg * 16; r < rg * 16 + 16; ++r)
       if (j0 + r < Jpad) {
         w_hi[((int64_t)bh * Jpad + j0 + r) * kHeadDim + d] = __float2bfloat16_rn(0.f);
@@ -82,67 +63,115 @@ __global__ void __launch_bounds__(256) profile_prologue_kernel(
   }
   const bf16* form_b = form + (int64_t)bh * K * kHeadDim;
   for (int i = tid; i < kProR * kHeadDim; i += 256) {
-    const int r = i / kHeadDim, dd = i % kHeadDim;
-    own_s[r * kProLd + dd] = (j0 + r < J) ? __bfloat162float(own[((int64_t)bh * J + j0 + r) * kHeadDim + dd]) : 0.f;
+    const int r = i >> 7, d = i & 127;
+    own_t[d * kProR + r] = (j0 + r < J) ? __bfloat162float(own[((int64_t)bh * J + j0 + r) * kHeadDim + d]) : 0.f;
   }
-  // sweep 1: P[r][k]; thread = (row r, 4 of the 32 centroids of the chunk)
-  {
-    const int r = tid >> 3, kk = tid & 7;
-    for (int k0 = 0; k0 < K; k0 += kProC) {
-      __syncthreads();
-      stage_form_chunk(chunk_s, form_b, k0, K, tid);
-      __syncthreads();
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      const float* o = own_s + r * kProLd;
-#pragma unroll 8
-      for (int dd = 0; dd < kHeadDim; ++dd) {
-        const float x = o[dd];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) acc[u] = fmaf(x, chunk_s[(kk + 8 * u) * kProLd + dd], acc[u]);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (k0 + kk + 8 * u < K) p_s[r * Kld + k0 + kk + 8 * u] = bf16_round(acc[u]);   // matmul of bf16 tensors returns bf16
-    }
-  }
-  __syncthreads();
-  // row norms, then Phat in place: 8 warps x 4 rows
-  for (int r = warp * 4; r < warp * 4 + 4; ++r) {
-    float ss = 0.f;
-    for (int k = lane; k < K; k += 32) { const float x = p_s[r * Kld + k]; ss += x * x; }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (lane == 0) norm_s[r] = sqrtf(ss + 1e-8f);
-  }
-  __syncthreads();
-  for (int i = tid; i < kProR * K; i += 256) {
-    const int r = i / K, k = i % K;
-    p_s[r * Kld + k] = p_s[r * Kld + k] / norm_s[r];
-  }
-  // sweep 2: W[r][d] = sum_k Phat[r][k] * form[k][d]; thread = (column d, 16 rows)
-  float w[16];
-#pragma unroll
-  for (int u = 0; u < 16; ++u) w[u] = 0.f;
+  // ---- sweep 1: P[r][k]; thread = rows 4*grp8 .. +3, centroids 2*lane32, 2*lane32 + 1 of the chunk
   for (int k0 = 0; k0 < K; k0 += kProC) {
     __syncthreads();
-    stage_form_chunk(chunk_s, form_b, k0, K, tid);
+    {  // stage form[k0 .. k0+63][:] transposed: a warp writes 32 consecutive k of one d
+      const int k = tid & 63;
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        const int d0 = ((tid >> 6) + pass * 4) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (k0 + k < K) v = __ldg(reinterpret_cast<const uint4*>(form_b + (int64_t)(k0 + k) * kHeadDim + d0));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          chunk[(d0 + 2 * e) * kProC + k] = __low2float(h[e]);
+          chunk[(d0 + 2 * e + 1) * kProC + k] = __high2float(h[e]);
+        }
+      }
+    }
+    __syncthreads();
+    float acc[4][2];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < kHeadDim; ++d) {
+      const float4 o = *reinterpret_cast<const float4*>(own_t + d * kProR + 4 * grp8);
+      const float2 c = *reinterpret_cast<const float2*>(chunk + d * kProC + 2 * lane32);
+      acc[0][0] = fmaf(o.x, c.x, acc[0][0]); acc[0][1] = fmaf(o.x, c.y, acc[0][1]);
+      acc[1][0] = fmaf(o.y, c.x, acc[1][0]); acc[1][1] = fmaf(o.y, c.y, acc[1][1]);
+      acc[2][0] = fmaf(o.z, c.x, acc[2][0]); acc[2][1] = fmaf(o.z, c.y, acc[2][1]);
+      acc[3][0] = fmaf(o.w, c.x, acc[3][0]); acc[3][1] = fmaf(o.w, c.y, acc[3][1]);
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int k = k0 + 2 * lane32 + u;
+      if (k < K)       // torch.matmul of bf16 tensors returns bf16
+        *reinterpret_cast<float4*>(p_t + k * kProR + 4 * grp8) =
+            make_float4(bf16_round(acc[0][u]), bf16_round(acc[1][u]), bf16_round(acc[2][u]), bf16_round(acc[3][u]));
+    }
+  }
+  __syncthreads();
+  // ---- row norms and Phat in place: thread = (row lane32, every 8th centroid starting at grp8)
+  {
+    float ss = 0.f;
+    for (int k = grp8; k < K; k += 8) { const float x = p_t[k * kProR + lane32]; ss = fmaf(x, x, ss); }
+    part_s[grp8][lane32] = ss;
+    __syncthreads();
+    if (tid < kProR) {
+      float t = 0.f;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) t += part_s[g][tid];
+      norm_s[tid] = sqrtf(t + 1e-8f);
+    }
+    __syncthreads();
+    const float nr = norm_s[lane32];
+    for (int k = grp8; k < K; k += 8) p_t[k * kProR + lane32] = p_t[k * kProR + lane32] / nr;
+  }
+  // ---- sweep 2: W[r][d] = sum_k Phat[r][k] form[k][d]; thread = rows 4*grp8 .. +3, dims 4*lane32 .. +3
+  float w[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) w[a][b] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += kProC) {
+    __syncthreads();
+    {  // stage form[k0 .. k0+63][:] as is
+      const int d0 = (tid & 15) * 8;
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        const int k = (tid >> 4) + pass * 16;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (k0 + k < K) v = __ldg(reinterpret_cast<const uint4*>(form_b + (int64_t)(k0 + k) * kHeadDim + d0));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+        float* dst = chunk + k * kHeadDim + d0;
+        *reinterpret_cast<float4*>(dst) = make_float4(__low2float(h[0]), __high2float(h[0]), __low2float(h[1]), __high2float(h[1]));
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(__low2float(h[2]), __high2float(h[2]), __low2float(h[3]), __high2float(h[3]));
+      }
+    }
     __syncthreads();
     const int kn = min(kProC, K - k0);
+#pragma unroll 4
     for (int k = 0; k < kn; ++k) {
-      const float f = chunk_s[k * kProLd + d];
+      const float4 p = *reinterpret_cast<const float4*>(p_t + (k0 + k) * kProR + 4 * grp8);
+      const float4 f = *reinterpret_cast<const float4*>(chunk + k * kHeadDim + 4 * lane32);
+      const float pr[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
-      for (int u = 0; u < 16; ++u) w[u] = fmaf(p_s[(rg * 16 + u) * Kld + k0 + k], f, w[u]);
+      for (int a = 0; a < 4; ++a) {
+        w[a][0] = fmaf(pr[a], f.x, w[a][0]); w[a][1] = fmaf(pr[a], f.y, w[a][1]);
+        w[a][2] = fmaf(pr[a], f.z, w[a][2]); w[a][3] = fmaf(pr[a], f.w, w[a][3]);
+      }
     }
   }
 #pragma unroll
-  for (int u = 0; u < 16; ++u) {
-    const int j = j0 + rg * 16 + u;
+  for (int a = 0; a < 4; ++a) {
+    const int j = j0 + 4 * grp8 + a;
     if (j < Jpad) {
-      const float val = (j < J) ? w[u] : 0.f;
-      const bf16 hi = __float2bfloat16_rn(val);
-      const bf16 lo = __float2bfloat16_rn(val - __bfloat162float(hi));
-      w_hi[((int64_t)bh * Jpad + j) * kHeadDim + d] = hi;
-      w_lo[((int64_t)bh * Jpad + j) * kHeadDim + d] = lo;
+      __align__(8) bf16 hi[4];
+      __align__(8) bf16 lo[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const float val = (j < J) ? w[a][b] : 0.f;
+        hi[b] = __float2bfloat16_rn(val);
+        lo[b] = __float2bfloat16_rn(val - __bfloat162float(hi[b]));
+      }
+      const int64_t o = ((int64_t)bh * Jpad + j) * kHeadDim + 4 * lane32;
+      *reinterpret_cast<uint2*>(w_hi + o) = *reinterpret_cast<const uint2*>(hi);
+      *reinterpret_cast<uint2*>(w_lo + o) = *reinterpret_cast<const uint2*>(lo);
     }
   }
 }
@@ -383,13 +412,12 @@ cudaError_t launch_gather_rows(const void* x, const int32_t* idx, void* out, int
 cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void* w_lo, int64_t BH, int64_t J,
                             int64_t K, cudaStream_t st) {
   const int Jpad = pad_clusters(J);
-  const int Kld = (int)K | 1;                                   // odd row length: conflict-free column walks
-  const size_t smem = (size_t)((kProR + kProC) * kProLd + kProR * Kld) * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 176 * 1024);
+  const size_t smem = (size_t)(kHeadDim * kProR + kHeadDim * kProC + K * kProR) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)(Jpad / kProR), (unsigned)BH);
   profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo,
-                                                   (int)J, (int)K, Jpad, Kld);
+                                                   (int)J, (int)K, Jpad);
   count_launches(1);
   return cudaGetLastError();
 }

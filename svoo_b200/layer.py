@@ -50,12 +50,9 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
                            num_k_centroids: int, kmeans_iters: int, top_p: float, min_kc_ratio=0, max_kc_ratio=0,
                            init_indices=None, clustering: Optional[ops.Clustering] = None,
                            context_length: int = 0, prompt_length: Optional[int] = None,
-                           return_state: bool = False, timer: Optional[StageTimer] = None,
-                           fuse_gather: bool = False):
+                           return_state: bool = False, timer: Optional[StageTimer] = None):
     """query/key/value: [1, H, S, 128] bf16 CUDA, S = video tokens + context_length text
-    tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order.
-    fuse_gather=True skips the three permute passes and lets the attention kernel gather Q, K, V
-    rows through the sorted indices instead (less memory, slower loads)."""
+    tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order."""
     cfg, H, S, D = query.shape
     assert cfg == 1, "Batch size must be 1 for kmeans block sparse attention"
     assert query.is_cuda and query.dtype == torch.bfloat16, "bf16 CUDA tensors expected"
@@ -96,14 +93,9 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
         k_idx = torch.cat([c.k_sorted_idx, text_rows], 1).contiguous()
     m = m_full
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    if fuse_gather:
-        mark("permute")
-        out = ops.sparse_attn(q, k, v, m.contiguous(), q_off, k_off, D ** -0.5, q_row_idx=q_idx, kv_row_idx=k_idx,
-                              out_row_idx=q_idx)
-    else:
-        qp, kp, vp = ops.permute(q, q_idx), ops.permute(k, k_idx), ops.permute(v, k_idx)
-        mark("permute")
-        out = ops.sparse_attn(qp, kp, vp, m.contiguous(), q_off, k_off, D ** -0.5, out_row_idx=q_idx)
+    qp, kp, vp = ops.permute(q, q_idx), ops.permute(k, k_idx), ops.permute(v, k_idx)
+    mark("permute")
+    out = ops.sparse_attn(qp, kp, vp, m.contiguous(), q_off, k_off, D ** -0.5, out_row_idx=q_idx)
     mark("attention")
     out = out.unsqueeze(0)
     if return_state:

@@ -199,12 +199,10 @@ def offsets_from_sizes(sizes: torch.Tensor) -> torch.Tensor:
 def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_map_u8: torch.Tensor,
                 q_offsets: torch.Tensor, k_offsets: torch.Tensor, sm_scale: Optional[float] = None,
                 out_row_idx: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                kernel: str = "tcgen05", q_row_idx: Optional[torch.Tensor] = None,
-                kv_row_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
+                kernel: str = "tcgen05") -> torch.Tensor:
     """Block-sparse attention over cluster-ordered q,k,v [BH,S,128].  With out_row_idx the
-    result rows are scattered to their original positions (fused inverse permutation); with
-    q_row_idx / kv_row_idx the query / key+value rows are gathered from tensors in their
-    original order (fused permutation).  kernel="simt" selects the mma.sync cross-check kernel."""
+    result rows are scattered to their original positions (fused inverse permutation).
+    kernel="simt" selects the mma.sync cross-check kernel."""
     _need_cuda(q, k, v, block_map_u8, q_offsets, k_offsets)
     BH, S, D = _tokens(q)
     QC, KC = q_offsets.shape[1] - 1, k_offsets.shape[1] - 1
@@ -218,14 +216,8 @@ def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_map_u8:
     ridx = 0 if out_row_idx is None else out_row_idx.data_ptr()
     head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), block_map_u8.data_ptr(), q_offsets.data_ptr(),
             k_offsets.data_ptr(), BH, S, D, QC, KC, scale, y.data_ptr())
-    if kernel == "tcgen05":
-        qidx = 0 if q_row_idx is None else q_row_idx.data_ptr()
-        kidx = 0 if kv_row_idx is None else kv_row_idx.data_ptr()
-        rc = LIB.svoo_b200_sparse_attn(*head, qidx, kidx, ridx, ws.data_ptr(), ws.numel(), _stream())
-    else:
-        if q_row_idx is not None or kv_row_idx is not None:
-            raise ValueError("the simt kernel takes cluster-ordered inputs only")
-        rc = LIB.svoo_b200_sparse_attn_simt(*head, ridx, ws.data_ptr(), ws.numel(), _stream())
+    fn = LIB.svoo_b200_sparse_attn if kernel == "tcgen05" else LIB.svoo_b200_sparse_attn_simt
+    rc = fn(*head, ridx, ws.data_ptr(), ws.numel(), _stream())
     check(rc, "sparse_attn")
     return y
 

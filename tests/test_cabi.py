@@ -65,5 +65,25 @@ def test_host_side_argument_checks(lib):
     assert L.svoo_b200_permute(p + 2, p, 1, 4, 128, 4, 4, p, None) == -5
     assert L.svoo_b200_permute(p, p, 1, 4, 128, 2, 4, p, None) == -2
     assert L.svoo_b200_sort_labels(p, 1, 4, 4, p, p, p, 16, None) == -4
-    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 2, 2000, 0.1, p, None, None, None, p, 1 << 30, None) == -6
+    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 2, 2000, 0.1, p, None, p, 1 << 30, None) == -6
     assert L.svoo_b200_cocluster(p, p, p, p, 1, 4, 128, 2, 2, 0, p, p, p, p, p, p, p, p, p, p, p, 1 << 30, None) == -2
+
+
+def test_tensor_core_kernels_do_not_spill():
+    """tcgen05.ld fills registers asynchronously; a spill store scheduled between the load and
+    its tcgen05.wait::ld would save garbage, so the tcgen05 kernels must compile spill-free."""
+    import subprocess
+    from svoo_b200 import build
+    out = []
+    for src in ("attn_tc.cu", "assign_tc.cu"):
+        res = subprocess.run([build._nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-Xptxas", "-v",
+                              "-c", os.path.join(build.CSRC, src), "-o", os.devnull], capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
+        out.append(res.stderr)
+    text = "\n".join(out)
+    blocks = re.findall(r"Function properties for (\S+)\n\s*(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads",
+                        text)
+    tc = [b for b in blocks if "_tc_kernel" in b[0]]
+    assert len(tc) >= 3
+    for name, stack, st, ld in tc:
+        assert int(st) == 0 and int(ld) == 0, f"{name} spills {st}/{ld} bytes"

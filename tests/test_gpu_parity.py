@@ -308,24 +308,6 @@ def test_sparse_attention_fused_inverse_permutation(dev):
     assert torch.equal(fused, ops.inverse_permute(plain, idx))
 
 
-def test_sparse_attention_fused_gathers_equal_explicit_permutes(dev):
-    """q_row_idx / kv_row_idx / out_row_idx fuse permute -> attention -> inverse permute;
-    the result must equal the three-kernel path bit for bit."""
-    ops = _mods()[0]
-    g = torch.Generator("cpu").manual_seed(31)
-    H, S = 2, 3000
-    q, k, v = (torch.randn(H, S, 128, generator=g).bfloat16().to(dev) for _ in range(3))
-    ql = random_labels(H, S, 7, 1).to(dev)
-    kl = random_labels(H, S, 19, 2, empty=(3,)).to(dev)
-    q_idx, q_off = ops.sort_labels(ql, 7)
-    k_idx, k_off = ops.sort_labels(kl, 19)
-    m = (torch.rand(H, 7, 19, generator=g) < 0.5).to(torch.uint8).to(dev)
-    fused = ops.sparse_attn(q, k, v, m, q_off, k_off, q_row_idx=q_idx, kv_row_idx=k_idx, out_row_idx=q_idx)
-    assert ops.attention_status(dev, H, S, 7, 19) == 0
-    plain = ops.sparse_attn(ops.permute(q, q_idx), ops.permute(k, k_idx), ops.permute(v, k_idx), m, q_off, k_off)
-    assert torch.equal(fused, ops.inverse_permute(plain, q_idx))
-
-
 def test_tensor_core_kernel_against_mma_sync_kernel(dev):
     """The tcgen05 kernel and the independent mma.sync kernel on a problem too large for the
     CPU oracle: 2 heads x 32,760 tokens, 100 x 500 clusters of random sizes, density 0.15."""
