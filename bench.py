@@ -240,19 +240,21 @@ def run_gpu_arm(args, cfg):
             return parallel.head_to_seq_shard(out[0], parts)
         return out
 
-    dev_in = [torch.empty_like(t, device=dev) for t in host_in]
+    if world > 1:
+        dev_in = [torch.empty_like(t, device=dev) for t in host_in]
 
-    def step_e2e():
-        for d_t, h_t in zip(dev_in, host_in):
-            d_t.copy_(h_t, non_blocking=True)
-        if world > 1:
+        def step_e2e():
+            for d_t, h_t in zip(dev_in, host_in):
+                d_t.copy_(h_t, non_blocking=True)
             q, k, v = (parallel.seq_to_head_shard(t, parts)[None] for t in dev_in)
-        else:
-            q, k, v = dev_in
-        out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki), **kw)
-        if world > 1:
-            out = parallel.head_to_seq_shard(out[0], parts)
-        host_out.copy_(out, non_blocking=True)
+            out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki), **kw)
+            host_out.copy_(parallel.head_to_seq_shard(out[0], parts), non_blocking=True)
+    else:
+        # host buffers in, host buffer out: copies of one head group overlap the compute of another
+        pipe = layer.HostLayerPipeline(dev, H, N, heads_per_group=args.e2e_group)
+
+        def step_e2e():
+            pipe(q_h, k_h, v_h, host_out, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki), **kw)
 
     def barrier():
         if world > 1:
@@ -363,6 +365,7 @@ def main():
     ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS))
     ap.add_argument("--heads", type=int, default=0, help="override the head count (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-group", type=int, default=5, help="heads per copy/compute group of the host-buffer path")
     args = ap.parse_args()
     cfg = synth.CONFIGS[args.config]
     if args.heads:

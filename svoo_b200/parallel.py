@@ -36,35 +36,51 @@ def head_partition(num_heads: int, world: int, weights: Optional[Sequence[float]
     return [sorted(p) for p in parts]
 
 
+_order_cache = {}
+
+
+def _order(parts: List[List[int]], device) -> torch.Tensor:
+    """Head index vector [hr * P]: entry i * P + p is the i-th head of rank p (cached per device)."""
+    key = (tuple(tuple(p) for p in parts), str(device))
+    t = _order_cache.get(key)
+    if t is None:
+        hr = len(parts[0])
+        t = torch.tensor([parts[p][i] for i in range(hr) for p in range(len(parts))], dtype=torch.long, device=device)
+        _order_cache[key] = t
+    return t
+
+
 def seq_to_head_shard(x: torch.Tensor, parts: List[List[int]], group=None) -> torch.Tensor:
     """x: this rank's sequence shard [N/P, H, D] -> this rank's heads over the whole
-    sequence [H_r, N, D].  Needs the same number of heads on every rank."""
+    sequence [H_r, N, D].  Needs the same number of heads on every rank.
+
+    One pass packs the shard as [hr, P, N/P, D] (block (i, p) = the i-th head of rank p); then
+    one all-to-all per local head index i exchanges its [P, N/P, D] blocks, which land as that
+    head's [N, D] rows directly -- no copy after the exchange."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     n_loc, H, D = x.shape
     hr = len(parts[rank])
     assert all(len(p) == hr for p in parts), "equal head counts per rank are required"
-    order = [h for p in parts for h in p]
-    send = x[:, order, :].reshape(n_loc, world, hr, D).permute(1, 0, 2, 3).contiguous()   # [P, N/P, hr, D]
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)
-    return recv.reshape(world * n_loc, hr, D).permute(1, 0, 2).contiguous()              # [hr, N, D]
+    send = x.transpose(0, 1)[_order(parts, x.device)]                    # [hr * P, N/P, D], the one copy
+    out = torch.empty(hr, world * n_loc, D, dtype=x.dtype, device=x.device)
+    for i in range(hr):
+        dist.all_to_all_single(out[i], send[i * world:(i + 1) * world].view(world * n_loc, D), group=group)
+    return out
 
 
 def head_to_seq_shard(y: torch.Tensor, parts: List[List[int]], group=None) -> torch.Tensor:
-    """Inverse of seq_to_head_shard: [H_r, N, D] -> [N/P, H, D]."""
+    """Inverse of seq_to_head_shard: [H_r, N, D] -> [N/P, H, D].  The head rows are sent as
+    they lie; one pass unpacks the received [hr, P, N/P, D] blocks."""
     world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
     hr, N, D = y.shape
     n_loc = N // world
-    send = y.permute(1, 0, 2).reshape(world, n_loc, hr, D).contiguous()                  # [P, N/P, hr, D]
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)
-    out = recv.permute(1, 0, 2, 3).reshape(n_loc, world * hr, D)                        # heads in `order`
-    order = [h for p in parts for h in p]
-    inv = torch.empty(len(order), dtype=torch.long, device=y.device)
-    inv[torch.tensor(order, device=y.device)] = torch.arange(len(order), device=y.device)
-    return out[:, inv, :].contiguous()
+    recv = torch.empty(hr * world, n_loc, D, dtype=y.dtype, device=y.device)
+    for i in range(hr):
+        dist.all_to_all_single(recv[i * world:(i + 1) * world].view(N, D), y[i], group=group)
+    out = torch.empty(n_loc, world * hr, D, dtype=y.dtype, device=y.device)
+    out[:, _order(parts, y.device)] = recv.transpose(0, 1)
+    return out
 
 
 def sparse_attention_layer_sharded(q_seq, k_seq, v_seq, parts, *, densities, init_indices, group=None, **layer_kw):
