@@ -6,7 +6,7 @@ block-sparse attention + inverse permute) on B200.
 N = 1: the Wan-14B 720p layer (40 heads x 75,600 tokens, 100/500 clusters, 5 iterations,
 per-head density U[0.05, 0.25]) on one GPU.  N > 1 (under torch.distributed.run): the same
 layer, heads sharded over the ranks, activations arriving and leaving sharded by sequence
-(one all-to-all each way inside the timed region) -- total work is fixed ("strong" scaling).
+(one peer-store re-shard each way inside the timed region) -- total work is fixed ("strong" scaling).
 
 `value` is effective TFLOP/s: the reference algorithm's flops for this layer
     F = iters*H*[2*N*D*(QC+KC) + 4*N*QC*KC]  +  sum_h 4*N^2*D*rho_h
@@ -225,19 +225,18 @@ def run_gpu_arm(args, cfg):
         host_out = torch.empty_like(q_h).pin_memory()
 
     state = {}
+    xchg = parallel.PeerExchange(parts, N, dev) if world > 1 else None
 
     def step(timer=None):
         if world > 1:
-            q = parallel.seq_to_head_shard(q_s, parts)[None]
-            k = parallel.seq_to_head_shard(k_s, parts)[None]
-            v = parallel.seq_to_head_shard(v_s, parts)[None]
+            q, k, v = (t[None] for t in xchg.to_heads(q_s, k_s, v_s))
         else:
             q, k, v = q_d, k_d, v_d
         out, st = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine,
                                                init_indices=(qi, ki), return_state=True, timer=timer, **kw)
         state["st"] = st
         if world > 1:
-            return parallel.head_to_seq_shard(out[0], parts)
+            return xchg.to_seq(out[0])
         return out
 
     if world > 1:
@@ -246,9 +245,9 @@ def run_gpu_arm(args, cfg):
         def step_e2e():
             for d_t, h_t in zip(dev_in, host_in):
                 d_t.copy_(h_t, non_blocking=True)
-            q, k, v = (parallel.seq_to_head_shard(t, parts)[None] for t in dev_in)
+            q, k, v = (t[None] for t in xchg.to_heads(*dev_in))
             out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki), **kw)
-            host_out.copy_(parallel.head_to_seq_shard(out[0], parts), non_blocking=True)
+            host_out.copy_(xchg.to_seq(out[0]), non_blocking=True)
     else:
         # host buffers in, host buffer out: copies of one head group overlap the compute of another
         pipe = layer.HostLayerPipeline(dev, H, N, heads_per_group=args.e2e_group)
@@ -316,7 +315,7 @@ def run_gpu_arm(args, cfg):
             "config": {"workload": cfg.name, "heads": H, "tokens": N, "q_clusters": cfg.num_q, "k_clusters": cfg.num_k,
                        "kmeans_iters": cfg.iters, "density_budget": list(cfg.density),
                        "realised_density_mean_rank0": sum(rho) / len(rho),
-                       "parallelism": f"heads/{world}" + ("+ulysses-a2a" if world > 1 else ""),
+                       "parallelism": f"heads/{world}" + ("+peer-store re-shard" if world > 1 else ""),
                        "l2": "inputs (2.3 GB of Q,K,V) are larger than L2; no flush between steps"},
             "stage_ms_rank0": {k: round(v, 4) for k, v in stage.items()},
             "roofline": {"kernel": "sparse_attn", "bound": "tensor", "achieved": achieved, "peak": peak,
@@ -365,7 +364,7 @@ def main():
     ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS))
     ap.add_argument("--heads", type=int, default=0, help="override the head count (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-group", type=int, default=5, help="heads per copy/compute group of the host-buffer path")
+    ap.add_argument("--e2e-group", type=int, default=4, help="heads per copy/compute group of the host-buffer path")
     args = ap.parse_args()
     cfg = synth.CONFIGS[args.config]
     if args.heads:

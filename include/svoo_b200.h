@@ -164,6 +164,30 @@ int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64
  * (the torch.cumsum of svoo/co_clustering.py:1147-1148). */
 int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, int32_t* offsets, void* stream);
 
+/* Multi-GPU re-sharding by stores into peer memory.  The reference runs on one GPU
+ * (svoo/processor.py:60-200 receives all heads of the whole sequence); these two entry
+ * points have no counterpart there.  They move [*,128] bf16 rows between the "sequence
+ * shard" layout of a sequence-parallel caller ([n_loc, H, 128] per rank, N = world *
+ * n_loc tokens) and the "head shard" layout the path computes in ([H / world, N, 128]
+ * per rank), over NVLink, with no wait on another GPU inside the kernels.
+ *
+ * peer_dst: HOST array of `world` device pointers, entry p = rank p's destination
+ * array, mapped into this process (CUDA IPC / symmetric memory).  The caller orders the
+ * launches against the other ranks: a stream-ordered collective after the call before a
+ * destination is read, and before a destination is overwritten again.
+ *   - world in [1,16], H in [1,128], H % world == 0, n_loc >= 1.
+ *
+ * svoo_b200_push_heads: x = this rank's [n_loc, H, 128]; row (r, h) is stored into rank
+ *   owner[h] at [slot[h], rank * n_loc + r, :] of its [H/world, N, 128] array.
+ *   owner/slot: HOST int32 [H]; every (owner, slot) pair must be distinct, slot < H/world.
+ * svoo_b200_push_seq: y = this rank's [H/world, N, 128]; row (i, n) is stored into rank
+ *   n / n_loc at [n % n_loc, my_heads[i], :] of its [n_loc, H, 128] array.
+ *   my_heads: HOST int32 [H/world], distinct, in [0, H). */
+int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* owner, const int32_t* slot,
+                         int32_t world, int32_t rank, int64_t n_loc, int64_t H, int64_t D, void* stream);
+int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int32_t world, int64_t n_loc,
+                       int64_t H, int64_t D, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

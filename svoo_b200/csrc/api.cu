@@ -23,6 +23,9 @@ cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, void*, 
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, void*, const int32_t*, const int4*,
                                    const int32_t*, const int2*, const int32_t*, int64_t, int64_t, int64_t, int64_t,
                                    float, cudaStream_t);
+cudaError_t launch_push_heads(const void*, void* const*, const int32_t*, const int32_t*, int, int, int64_t, int,
+                              cudaStream_t);
+cudaError_t launch_push_seq(const void*, void* const*, const int32_t*, int, int64_t, int, int, cudaStream_t);
 }  // namespace svoo
 
 namespace svoo {
@@ -267,6 +270,53 @@ int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64
   SVOO_TRY(check_clusters(QC));
   SVOO_TRY(check_clusters(KC));
   *offset_out = workspace_layout(BH, N, QC, KC).status;
+  return SVOO_OK;
+}
+
+namespace {
+int check_exchange(void* const* peer_dst, int32_t world, int64_t n_loc, int64_t H, int64_t D) {
+  if (!peer_dst) return SVOO_ERR_NULL;
+  if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
+  if (world < 1 || world > 16 || H < 1 || H > 128 || H % world != 0 || n_loc < 1 || n_loc * world > (int64_t)1 << 30)
+    return SVOO_ERR_SHAPE;
+  for (int p = 0; p < world; ++p) {
+    if (!peer_dst[p]) return SVOO_ERR_NULL;
+    if (!aligned16(peer_dst[p])) return SVOO_ERR_ALIGN;
+  }
+  return SVOO_OK;
+}
+}  // namespace
+
+int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* owner, const int32_t* slot,
+                         int32_t world, int32_t rank, int64_t n_loc, int64_t H, int64_t D, void* stream) {
+  if (!x || !owner || !slot) return SVOO_ERR_NULL;
+  SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
+  if (rank < 0 || rank >= world) return SVOO_ERR_SHAPE;
+  if (!aligned16(x)) return SVOO_ERR_ALIGN;
+  const int64_t hr = H / world;
+  bool seen[16 * 128] = {};
+  for (int64_t h = 0; h < H; ++h) {
+    if (owner[h] < 0 || owner[h] >= world || slot[h] < 0 || slot[h] >= hr) return SVOO_ERR_SHAPE;
+    bool& s = seen[owner[h] * 128 + slot[h]];
+    if (s) return SVOO_ERR_SHAPE;
+    s = true;
+  }
+  SVOO_CUDA(launch_push_heads(x, peer_dst, owner, slot, world, rank, n_loc, (int)H, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int32_t world, int64_t n_loc,
+                       int64_t H, int64_t D, void* stream) {
+  if (!y || !my_heads) return SVOO_ERR_NULL;
+  SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
+  if (!aligned16(y)) return SVOO_ERR_ALIGN;
+  const int64_t hr = H / world;
+  bool seen[128] = {};
+  for (int64_t i = 0; i < hr; ++i) {
+    if (my_heads[i] < 0 || my_heads[i] >= H || seen[my_heads[i]]) return SVOO_ERR_SHAPE;
+    seen[my_heads[i]] = true;
+  }
+  SVOO_CUDA(launch_push_seq(y, peer_dst, my_heads, world, n_loc, (int)H, (int)hr, (cudaStream_t)stream));
   return SVOO_OK;
 }
 

@@ -83,18 +83,98 @@ def head_to_seq_shard(y: torch.Tensor, parts: List[List[int]], group=None) -> to
     return out
 
 
-def sparse_attention_layer_sharded(q_seq, k_seq, v_seq, parts, *, densities, init_indices, group=None, **layer_kw):
+def exchange_tables(parts: List[List[int]]) -> Tuple[List[int], List[int]]:
+    """owner[h] = rank that computes head h, slot[h] = index of h among that rank's heads."""
+    H = sum(len(p) for p in parts)
+    owner, slot = [0] * H, [0] * H
+    for r, heads in enumerate(parts):
+        for i, h in enumerate(heads):
+            owner[h], slot[h] = r, i
+    return owner, slot
+
+
+class PeerExchange:
+    """The two re-shardings of the layer as stores into the peers' memory (one kernel launch
+    per tensor, no library all-to-all).  The receive arrays live in symmetric memory that
+    every rank of the group maps; a one-element all-reduce on the launching stream is the
+    ordering point between "my stores are issued" and "my array is complete".
+
+    Per layer call: push q, k, v -> fence -> compute -> push out -> fence.  The first fence
+    also tells every rank that its peers have finished the previous call, so the receive
+    arrays are reused without a third one."""
+
+    def __init__(self, parts: List[List[int]], n_tokens: int, device, group=None, head_dim: int = 128):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.parts = parts
+        self.H = sum(len(p) for p in parts)
+        self.hr = len(parts[self.rank])
+        if any(len(p) != self.hr for p in parts) or n_tokens % self.world:
+            raise ValueError("heads and tokens must split evenly over the ranks")
+        self.N, self.n_loc, self.D = n_tokens, n_tokens // self.world, head_dim
+        self.heads_in = symm_mem.empty((3, self.hr, self.N, head_dim), dtype=torch.bfloat16, device=device)
+        self.seq_out = symm_mem.empty((self.n_loc, self.H, head_dim), dtype=torch.bfloat16, device=device)
+        h_in = symm_mem.rendezvous(self.heads_in, self.group)
+        h_out = symm_mem.rendezvous(self.seq_out, self.group)
+        per = self.hr * self.N * head_dim * 2
+        self._in_ptrs = [(ctypes.c_void_p * self.world)(*[int(p) + t * per for p in h_in.buffer_ptrs]) for t in range(3)]
+        self._out_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in h_out.buffer_ptrs])
+        owner, slot = exchange_tables(parts)
+        self._owner = (ctypes.c_int32 * self.H)(*owner)
+        self._slot = (ctypes.c_int32 * self.H)(*slot)
+        self._mine = (ctypes.c_int32 * self.hr)(*parts[self.rank])
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self._handles = (h_in, h_out)
+
+    def fence(self):
+        dist.all_reduce(self._flag, group=self.group)
+
+    def to_heads(self, q_seq, k_seq, v_seq):
+        """[N/P, H, 128] shards of q, k, v -> views [H_r, N, 128] of the receive arrays."""
+        from . import _lib
+        stream = torch.cuda.current_stream(q_seq.device).cuda_stream
+        for t, x in enumerate((q_seq, k_seq, v_seq)):
+            if tuple(x.shape) != (self.n_loc, self.H, self.D) or x.dtype != torch.bfloat16 or not x.is_contiguous():
+                raise ValueError("sequence shards must be contiguous bf16 [N/P, H, 128]")
+            _lib.check(_lib.LIB.svoo_b200_push_heads(x.data_ptr(), self._in_ptrs[t], self._owner, self._slot, self.world,
+                                                     self.rank, self.n_loc, self.H, self.D, stream), "push_heads")
+        self.fence()
+        return self.heads_in[0], self.heads_in[1], self.heads_in[2]
+
+    def to_seq(self, y):
+        """This rank's [H_r, N, 128] result -> the [N/P, H, 128] shard (a view of the receive array)."""
+        from . import _lib
+        if tuple(y.shape) != (self.hr, self.N, self.D) or y.dtype != torch.bfloat16 or not y.is_contiguous():
+            raise ValueError("head-sharded result must be contiguous bf16 [H_r, N, 128]")
+        stream = torch.cuda.current_stream(y.device).cuda_stream
+        _lib.check(_lib.LIB.svoo_b200_push_seq(y.data_ptr(), self._out_ptrs, self._mine, self.world, self.n_loc, self.H,
+                                               self.D, stream), "push_seq")
+        self.fence()
+        return self.seq_out
+
+
+def sparse_attention_layer_sharded(q_seq, k_seq, v_seq, parts, *, densities, init_indices, group=None, exchange=None,
+                                   **layer_kw):
     """Ulysses-style layer: q/k/v_seq are this rank's [N/P, H, 128] shards; returns the
     [N/P, H, 128] shard of the output.  `densities` and `init_indices` are for all H heads;
-    each rank takes the entries of its own heads."""
+    each rank takes the entries of its own heads.  With `exchange` (a PeerExchange) the two
+    re-shardings are peer stores; without it they are torch.distributed all-to-alls."""
     from .layer import sparse_attention_layer
     rank = dist.get_rank(group)
     mine = parts[rank]
-    q = seq_to_head_shard(q_seq, parts, group)
-    k = seq_to_head_shard(k_seq, parts, group)
-    v = seq_to_head_shard(v_seq, parts, group)
+    if exchange is not None:
+        q, k, v = exchange.to_heads(q_seq, k_seq, v_seq)
+    else:
+        q = seq_to_head_shard(q_seq, parts, group)
+        k = seq_to_head_shard(k_seq, parts, group)
+        v = seq_to_head_shard(v_seq, parts, group)
     qi, ki = init_indices
     d = [densities[h] for h in mine]
     out = sparse_attention_layer(q[None], k[None], v[None], min_kc_ratio=d, max_kc_ratio=d,
                                  init_indices=(qi[mine], ki[mine]), **layer_kw)
+    if exchange is not None:
+        return exchange.to_seq(out[0])
     return head_to_seq_shard(out[0], parts, group)

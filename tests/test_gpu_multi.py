@@ -1,0 +1,63 @@
+"""Two-GPU checks of the head-sharded layer: the peer-store re-shard against the
+torch.distributed all-to-all, and the sharded layer against the one-GPU layer.
+Runs as child processes (one per GPU); skipped with fewer than two GPUs."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CHILD = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["SVOO_ROOT"])
+from svoo_b200 import layer, parallel, synth
+import dataclasses
+rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(local); dev = torch.device("cuda", local)
+dist.init_process_group("nccl", device_id=dev)
+cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=4)
+H, N = cfg.heads, cfg.n_tokens
+assert N % world == 0
+dens = synth.head_densities(cfg)
+parts = parallel.head_partition(H, world, dens)
+q, k, v = (t.to(dev) for t in synth.make_qkv(cfg))                      # all heads, on every rank
+n_loc = N // world
+shard = lambda t: t[0, :, rank * n_loc:(rank + 1) * n_loc].transpose(0, 1).contiguous()   # [n_loc, H, D]
+qs, ks, vs = shard(q), shard(k), shard(v)
+x = parallel.PeerExchange(parts, N, dev)
+for rep in range(2):                                                    # twice: the receive arrays are reused
+    got = x.to_heads(qs, ks, vs)
+    want = [parallel.seq_to_head_shard(t, parts) for t in (qs, ks, vs)]
+    for g, w, full in zip(got, want, (q, k, v)):
+        assert torch.equal(g, w), "push_heads differs from the all-to-all"
+        assert torch.equal(g, full[0, parts[rank]]), "push_heads differs from the unsharded heads"
+    y = got[0].clone()
+    back = x.to_seq(y)
+    assert torch.equal(back, parallel.head_to_seq_shard(y, parts)), "push_seq differs from the all-to-all"
+    assert torch.equal(back, qs), "round trip"
+qi, ki = synth.init_indices(cfg)
+kw = dict(num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k, kmeans_iters=cfg.iters, top_p=cfg.top_p)
+out = parallel.sparse_attention_layer_sharded(qs, ks, vs, parts, densities=dens, init_indices=(qi.to(dev), ki.to(dev)),
+                                              exchange=x, **kw)
+ref = layer.sparse_attention_layer(q, k, v, min_kc_ratio=dens, max_kc_ratio=dens, init_indices=(qi.to(dev), ki.to(dev)), **kw)
+assert torch.equal(out, shard(ref)), "sharded layer differs from the one-GPU layer"
+torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
+print("OK", rank)
+'''
+
+
+@pytest.mark.gpu
+def test_peer_exchange_and_sharded_layer_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "child.py"
+    script.write_text(CHILD)
+    env = dict(os.environ, SVOO_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
+                         env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count("OK") == 2

@@ -55,3 +55,36 @@ def _worker(rank, world, port, H, N, weights):
 @pytest.mark.parametrize("world,H,weights", [(2, 4, None), (2, 6, [0.3, 0.1, 0.2, 0.05, 0.25, 0.1]), (4, 8, None)])
 def test_ulysses_layout_round_trip(world, H, weights):
     mp.spawn(_worker, args=(world, _free_port(), H, 24, weights), nprocs=world, join=True)
+
+
+def test_exchange_tables_reproduce_the_all_to_all_layout():
+    """The owner/slot tables the peer-store kernels index with, replayed in numpy with the
+    kernels' row arithmetic, give the head-shard layout and its inverse."""
+    import numpy as np
+    from svoo_b200.parallel import exchange_tables, head_partition
+    world, H, n_loc, D = 4, 8, 5, 3
+    N = world * n_loc
+    parts = head_partition(H, world, [0.3, 0.1, 0.2, 0.25, 0.05, 0.15, 0.22, 0.12])
+    owner, slot = exchange_tables(parts)
+    hr = H // world
+    assert sorted(zip(owner, slot)) == [(r, i) for r in range(world) for i in range(hr)]
+    rng = np.random.default_rng(0)
+    full = rng.standard_normal((H, N, D)).astype(np.float32)
+    recv = [np.zeros((hr, N, D), np.float32) for _ in range(world)]
+    for rank in range(world):                                   # push_heads of every rank
+        x = full[:, rank * n_loc:(rank + 1) * n_loc].transpose(1, 0, 2).reshape(n_loc * H, D)
+        for t in range(n_loc * H):
+            r, h = divmod(t, H)
+            recv[owner[h]].reshape(hr * N, D)[slot[h] * N + rank * n_loc + r] = x[t]
+    for rank in range(world):
+        assert np.array_equal(recv[rank], full[parts[rank]])
+    seq = [np.zeros((n_loc * H, D), np.float32) for _ in range(world)]
+    for rank in range(world):                                   # push_seq of every rank
+        y = recv[rank].reshape(hr * N, D)
+        for t in range(hr * N):
+            i, n = divmod(t, N)
+            p = n // n_loc
+            seq[p][(n - p * n_loc) * H + parts[rank][i]] = y[t]
+    for rank in range(world):
+        want = full[:, rank * n_loc:(rank + 1) * n_loc].transpose(1, 0, 2).reshape(n_loc * H, D)
+        assert np.array_equal(seq[rank], want)
