@@ -233,7 +233,8 @@ def run_gpu_arm(args, cfg):
         else:
             q, k, v = q_d, k_d, v_d
         out, st = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine,
-                                               init_indices=(qi, ki), return_state=True, timer=timer, **kw)
+                                               init_indices=(qi, ki), return_state=True, timer=timer,
+                                               value_ready=xchg.value_ready if xchg else None, **kw)
         state["st"] = st
         if world > 1:
             return xchg.to_seq(out[0])
@@ -246,7 +247,8 @@ def run_gpu_arm(args, cfg):
             for d_t, h_t in zip(dev_in, host_in):
                 d_t.copy_(h_t, non_blocking=True)
             q, k, v = (t[None] for t in xchg.to_heads(*dev_in))
-            out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki), **kw)
+            out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki),
+                                               value_ready=xchg.value_ready, **kw)
             host_out.copy_(xchg.to_seq(out[0]), non_blocking=True)
     else:
         # host buffers in, host buffer out: copies of one head group overlap the compute of another
@@ -277,10 +279,11 @@ def run_gpu_arm(args, cfg):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item()), timers
 
-    for _ in range(args.warmup):
-        step()
-    launches0 = _lib.LIB.svoo_b200_launch_count()
-    with ClockSampler(local) as clocks:
+    with ClockSampler(local) as clocks:            # samples cover the warm-up and the timed steps (same load)
+        for _ in range(args.warmup):
+            step()
+        torch.cuda.synchronize()
+        launches0 = _lib.LIB.svoo_b200_launch_count()
         total_ms, timers = timed(step, args.steps, with_timers=True)
     launches = _lib.LIB.svoo_b200_launch_count() - launches0
     for _ in range(min(args.warmup, 2)):

@@ -32,148 +32,175 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int32_t* __
 
 // ---------------------------------------------------------------------------------------
 // Prologue: P = bf16(own . form^T), Phat = P / sqrt(sum P^2 + 1e-8) (fp32),
-//           W = Phat . form (fp32) -> (hi, lo) bf16.     One CTA = 32 rows j of one head.
-// `form` is swept twice through shared memory in chunks of 64 centroids; both sweeps are
-// register-tiled (4x2 and 4x4 outputs per thread, operands read as float2 / float4).
+//           W = Phat . form (fp32) -> (hi, lo) bf16.     One CTA = 16 rows j of one head.
+// Both products run on mma.sync (m16n8k16, fp32 accumulation): the problem is a few MFLOP
+// per head and latency-bound, so the point is the short dependency chain, not throughput.
+// `form` is streamed twice through a double-buffered shared-memory ring of 64-row chunks
+// (cp.async).  Phat (fp32) enters the second product as three bf16 terms hi + mid + lo,
+// which carries 24 mantissa bits, so W matches an fp32 product to rounding.
 // (svoo/co_clustering.py:2427-2428 and svoo/kernels/triton/l2norm.py:36-41)
 // ---------------------------------------------------------------------------------------
-constexpr int kProR = 32;            // own rows per CTA
+constexpr int kProR = 16;            // own rows per CTA
 constexpr int kProC = 64;            // form rows per chunk
+
+__host__ __device__ inline int pro_kround(int K) { return (K + kProC - 1) / kProC * kProC; }
+__host__ __device__ inline int pro_p_stride(int K) { return pro_kround(K) + 4; }       // floats
+__host__ __device__ inline int pro_hat_stride(int K) { return pro_kround(K) + 8; }     // bf16: 16 bytes past a multiple of 128
+inline size_t pro_smem_bytes(int K) {
+  return (size_t)kProR * kRowBytes + 2 * (size_t)kProC * kRowBytes + (size_t)kProR * pro_p_stride(K) * 4 +
+         3 * (size_t)kProR * pro_hat_stride(K) * 2;
+}
 
 __global__ void __launch_bounds__(256) profile_prologue_kernel(
     const bf16* __restrict__ own, const bf16* __restrict__ form, bf16* __restrict__ w_hi,
     bf16* __restrict__ w_lo, int J, int K, int Jpad) {
-  extern __shared__ __align__(16) float sm[];
-  float* own_t = sm;                            // [128 d][32 r]
-  float* chunk = own_t + kHeadDim * kProR;      // sweep 1: [128 d][64 k]; sweep 2: [64 k][128 d]
-  float* p_t = chunk + kHeadDim * kProC;        // [K][32 r]
-  __shared__ float part_s[8][kProR];
-  __shared__ float norm_s[kProR];
+  extern __shared__ __align__(128) unsigned char pro_sm[];
   const int bh = blockIdx.y, j0 = blockIdx.x * kProR;
-  const int tid = threadIdx.x;
-  const int lane32 = tid & 31, grp8 = tid >> 5;         // grp8: 0..7
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (j0 >= J) {                                        // padding rows of W: zeros
     const int d = tid & 127, rg = tid >> 7;
-    for (int r = rg * 16; r < rg * 16 + 16; ++r)
+    for (int r = rg * 8; r < rg * 8 + 8; ++r)
       if (j0 + r < Jpad) {
         w_hi[((int64_t)bh * Jpad + j0 + r) * kHeadDim + d] = __float2bfloat16_rn(0.f);
         w_lo[((int64_t)bh * Jpad + j0 + r) * kHeadDim + d] = __float2bfloat16_rn(0.f);
       }
     return;
   }
+  const int pstride = pro_p_stride(K), hstride = pro_hat_stride(K);
+  unsigned char* own_p = pro_sm;                                    // [16][128] bf16, swizzled
+  unsigned char* form_p = own_p + kProR * kRowBytes;                // 2 x [64][128] bf16, swizzled
+  float* p_s = reinterpret_cast<float*>(form_p + 2 * kProC * kRowBytes);       // [16][pstride]
+  bf16* hat = reinterpret_cast<bf16*>(p_s + kProR * pstride);                  // 3 x [16][hstride]
+  const uint32_t own_s = smem_u32(own_p), form_s = smem_u32(form_p), hat_s = smem_u32(hat);
   const bf16* form_b = form + (int64_t)bh * K * kHeadDim;
-  for (int i = tid; i < kProR * kHeadDim; i += 256) {
-    const int r = i >> 7, d = i & 127;
-    own_t[d * kProR + r] = (j0 + r < J) ? __bfloat162float(own[((int64_t)bh * J + j0 + r) * kHeadDim + d]) : 0.f;
-  }
-  // ---- sweep 1: P[r][k]; thread = rows 4*grp8 .. +3, centroids 2*lane32, 2*lane32 + 1 of the chunk
-  for (int k0 = 0; k0 < K; k0 += kProC) {
-    __syncthreads();
-    {  // stage form[k0 .. k0+63][:] transposed: a warp writes 32 consecutive k of one d
-      const int k = tid & 63;
+  const int nch = (K + kProC - 1) / kProC;
+
+  auto load_chunk = [&](int c, int buf) {               // rows past K arrive as zeros
 #pragma unroll
-      for (int pass = 0; pass < 4; ++pass) {
-        const int d0 = ((tid >> 6) + pass * 4) * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (k0 + k < K) v = __ldg(reinterpret_cast<const uint4*>(form_b + (int64_t)(k0 + k) * kHeadDim + d0));
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          chunk[(d0 + 2 * e) * kProC + k] = __low2float(h[e]);
-          chunk[(d0 + 2 * e + 1) * kProC + k] = __high2float(h[e]);
-        }
-      }
+    for (int pass = 0; pass < 4; ++pass) {
+      const int i = tid + pass * 256, row = i >> 4, ch = i & 15;
+      const int k = c * kProC + row;
+      cp_async16(form_s + buf * (kProC * kRowBytes) + swz(row, ch),
+                 form_b + (int64_t)min(k, K - 1) * kHeadDim + ch * 8, k < K);
     }
-    __syncthreads();
-    float acc[4][2];
-#pragma unroll
-    for (int a = 0; a < 4; ++a) acc[a][0] = acc[a][1] = 0.f;
-#pragma unroll 8
-    for (int d = 0; d < kHeadDim; ++d) {
-      const float4 o = *reinterpret_cast<const float4*>(own_t + d * kProR + 4 * grp8);
-      const float2 c = *reinterpret_cast<const float2*>(chunk + d * kProC + 2 * lane32);
-      acc[0][0] = fmaf(o.x, c.x, acc[0][0]); acc[0][1] = fmaf(o.x, c.y, acc[0][1]);
-      acc[1][0] = fmaf(o.y, c.x, acc[1][0]); acc[1][1] = fmaf(o.y, c.y, acc[1][1]);
-      acc[2][0] = fmaf(o.z, c.x, acc[2][0]); acc[2][1] = fmaf(o.z, c.y, acc[2][1]);
-      acc[3][0] = fmaf(o.w, c.x, acc[3][0]); acc[3][1] = fmaf(o.w, c.y, acc[3][1]);
-    }
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int k = k0 + 2 * lane32 + u;
-      if (k < K)       // torch.matmul of bf16 tensors returns bf16
-        *reinterpret_cast<float4*>(p_t + k * kProR + 4 * grp8) =
-            make_float4(bf16_round(acc[0][u]), bf16_round(acc[1][u]), bf16_round(acc[2][u]), bf16_round(acc[3][u]));
-    }
-  }
-  __syncthreads();
-  // ---- row norms and Phat in place: thread = (row lane32, every 8th centroid starting at grp8)
+  };
   {
+    const int row = tid >> 4, ch = tid & 15;
+    const int j = j0 + row;
+    cp_async16(own_s + swz(row, ch), own + ((int64_t)bh * J + min(j, J - 1)) * kHeadDim + ch * 8, j < J);
+  }
+  load_chunk(0, 0);
+  cp_async_commit();
+
+  // ---- sweep 1: P[16][K]; warps 0..3 take 16 form rows of the chunk each
+  uint32_t qa[8][4];
+  for (int c = 0; c < nch; ++c) {
+    if (c + 1 < nch) load_chunk(c + 1, (c + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (warp < 4) {
+      if (c == 0) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          ldmatrix_x4(qa[ks], own_s + swz((lane % 8) + ((lane / 8) % 2) * 8, ks * 2 + lane / 16));
+      }
+      const uint32_t f = form_s + (c & 1) * (kProC * kRowBytes);
+      float acc[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t b[4];
+        ldmatrix_x4(b, f + swz(warp * 16 + (lane % 8) + (lane / 16) * 8, ks * 2 + ((lane / 8) % 2)));
+        mma_bf16(acc[0], qa[ks], b[0], b[1]);
+        mma_bf16(acc[1], qa[ks], b[2], b[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {                   // torch.matmul of bf16 tensors returns bf16
+          const int row = lane / 4 + (e >> 1) * 8;
+          const int k = c * kProC + warp * 16 + nt * 8 + 2 * (lane % 4) + (e & 1);
+          p_s[row * pstride + k] = bf16_round(acc[nt][e]);
+        }
+    }
+    __syncthreads();
+  }
+  load_chunk(0, 0);                                     // first chunk of sweep 2, in flight during the norms
+  cp_async_commit();
+
+  // ---- row norms (16 threads per row, fixed order), Phat = P / norm split into three bf16 terms
+  {
+    const int row = tid >> 4, sub = tid & 15;
+    const int kr = pro_kround(K);
     float ss = 0.f;
-    for (int k = grp8; k < K; k += 8) { const float x = p_t[k * kProR + lane32]; ss = fmaf(x, x, ss); }
-    part_s[grp8][lane32] = ss;
-    __syncthreads();
-    if (tid < kProR) {
-      float t = 0.f;
+    for (int k = sub; k < kr; k += 16) { const float x = p_s[row * pstride + k]; ss = fmaf(x, x, ss); }
 #pragma unroll
-      for (int g = 0; g < 8; ++g) t += part_s[g][tid];
-      norm_s[tid] = sqrtf(t + 1e-8f);
+    for (int o = 8; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float nr = sqrtf(ss + 1e-8f);
+    for (int k = sub; k < kr; k += 16) {
+      const float x = p_s[row * pstride + k] / nr;
+      const bf16 h = __float2bfloat16_rn(x);
+      const float r1 = x - __bfloat162float(h);
+      const bf16 m = __float2bfloat16_rn(r1);
+      const bf16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+      hat[(0 * kProR + row) * hstride + k] = h;
+      hat[(1 * kProR + row) * hstride + k] = m;
+      hat[(2 * kProR + row) * hstride + k] = l;
     }
-    __syncthreads();
-    const float nr = norm_s[lane32];
-    for (int k = grp8; k < K; k += 8) p_t[k * kProR + lane32] = p_t[k * kProR + lane32] / nr;
   }
-  // ---- sweep 2: W[r][d] = sum_k Phat[r][k] form[k][d]; thread = rows 4*grp8 .. +3, dims 4*lane32 .. +3
-  float w[4][4];
+
+  // ---- sweep 2: W[16][128] = sum_k Phat[r][k] form[k][d]; warp w owns dims 16w .. 16w+15
+  float wacc[3][2][4];
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int t = 0; t < 3; ++t)
 #pragma unroll
-    for (int b = 0; b < 4; ++b) w[a][b] = 0.f;
-  for (int k0 = 0; k0 < K; k0 += kProC) {
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) wacc[t][i][e] = 0.f;
+  for (int c = 0; c < nch; ++c) {
+    if (c + 1 < nch) load_chunk(c + 1, (c + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
     __syncthreads();
-    {  // stage form[k0 .. k0+63][:] as is
-      const int d0 = (tid & 15) * 8;
+    const uint32_t f = form_s + (c & 1) * (kProC * kRowBytes);
 #pragma unroll
-      for (int pass = 0; pass < 4; ++pass) {
-        const int k = (tid >> 4) + pass * 16;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (k0 + k < K) v = __ldg(reinterpret_cast<const uint4*>(form_b + (int64_t)(k0 + k) * kHeadDim + d0));
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-        float* dst = chunk + k * kHeadDim + d0;
-        *reinterpret_cast<float4*>(dst) = make_float4(__low2float(h[0]), __high2float(h[0]), __low2float(h[1]), __high2float(h[1]));
-        *reinterpret_cast<float4*>(dst + 4) = make_float4(__low2float(h[2]), __high2float(h[2]), __low2float(h[3]), __high2float(h[3]));
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, f + swz(kk * 16 + (lane % 8) + ((lane / 8) % 2) * 8, warp * 2 + lane / 16));
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+        uint32_t a[4];
+        const int arow = (lane % 8) + ((lane / 8) % 2) * 8;
+        const int acol = c * kProC + kk * 16 + (lane / 16) * 8;
+        ldmatrix_x4(a, hat_s + (uint32_t)(((t * kProR + arow) * hstride + acol) * 2));
+        mma_bf16(wacc[t][0], a, b[0], b[1]);
+        mma_bf16(wacc[t][1], a, b[2], b[3]);
       }
     }
     __syncthreads();
-    const int kn = min(kProC, K - k0);
-#pragma unroll 4
-    for (int k = 0; k < kn; ++k) {
-      const float4 p = *reinterpret_cast<const float4*>(p_t + (k0 + k) * kProR + 4 * grp8);
-      const float4 f = *reinterpret_cast<const float4*>(chunk + k * kHeadDim + 4 * lane32);
-      const float pr[4] = {p.x, p.y, p.z, p.w};
-#pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        w[a][0] = fmaf(pr[a], f.x, w[a][0]); w[a][1] = fmaf(pr[a], f.y, w[a][1]);
-        w[a][2] = fmaf(pr[a], f.z, w[a][2]); w[a][3] = fmaf(pr[a], f.w, w[a][3]);
-      }
-    }
   }
 #pragma unroll
-  for (int a = 0; a < 4; ++a) {
-    const int j = j0 + 4 * grp8 + a;
-    if (j < Jpad) {
-      __align__(8) bf16 hi[4];
-      __align__(8) bf16 lo[4];
+  for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const float val = (j < J) ? w[a][b] : 0.f;
-        hi[b] = __float2bfloat16_rn(val);
-        lo[b] = __float2bfloat16_rn(val - __bfloat162float(hi[b]));
+    for (int half = 0; half < 2; ++half) {
+      const int j = j0 + lane / 4 + half * 8;
+      if (j < Jpad) {
+        float v0 = wacc[0][nt][half * 2] + (wacc[1][nt][half * 2] + wacc[2][nt][half * 2]);
+        float v1 = wacc[0][nt][half * 2 + 1] + (wacc[1][nt][half * 2 + 1] + wacc[2][nt][half * 2 + 1]);
+        if (j >= J) v0 = v1 = 0.f;
+        const bf16 h0 = __float2bfloat16_rn(v0), h1 = __float2bfloat16_rn(v1);
+        const bf16 l0 = __float2bfloat16_rn(v0 - __bfloat162float(h0)), l1 = __float2bfloat16_rn(v1 - __bfloat162float(h1));
+        const int64_t o = ((int64_t)bh * Jpad + j) * kHeadDim + warp * 16 + nt * 8 + 2 * (lane % 4);
+        __nv_bfloat162 hv, lv;
+        hv.x = h0; hv.y = h1; lv.x = l0; lv.y = l1;
+        *reinterpret_cast<__nv_bfloat162*>(w_hi + o) = hv;
+        *reinterpret_cast<__nv_bfloat162*>(w_lo + o) = lv;
       }
-      const int64_t o = ((int64_t)bh * Jpad + j) * kHeadDim + 4 * lane32;
-      *reinterpret_cast<uint2*>(w_hi + o) = *reinterpret_cast<const uint2*>(hi);
-      *reinterpret_cast<uint2*>(w_lo + o) = *reinterpret_cast<const uint2*>(lo);
     }
-  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -206,10 +233,15 @@ __global__ void __launch_bounds__(1024) label_scan_kernel(int32_t* __restrict__ 
   int total = 0;
   if (k < K) {
     int32_t* col = chunk_hist + (int64_t)bh * nchunks * K + k;
-    for (int c = 0; c < nchunks; ++c) {
-      const int v = col[(int64_t)c * K];
-      col[(int64_t)c * K] = total;
-      total += v;
+    for (int c0 = 0; c0 < nchunks; c0 += 8) {          // 8 independent loads in flight, then the stores
+      int v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (c0 + u < nchunks) ? col[(int64_t)(c0 + u) * K] : 0;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (c0 + u < nchunks) col[(int64_t)(c0 + u) * K] = total;
+        total += v[u];
+      }
     }
     if (sizes) sizes[(int64_t)bh * K + k] = total;
   }
@@ -412,8 +444,8 @@ cudaError_t launch_gather_rows(const void* x, const int32_t* idx, void* out, int
 cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void* w_lo, int64_t BH, int64_t J,
                             int64_t K, cudaStream_t st) {
   const int Jpad = pad_clusters(J);
-  const size_t smem = (size_t)(kHeadDim * kProR + kHeadDim * kProC + K * kProR) * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+  const size_t smem = pro_smem_bytes((int)K);
+  cudaError_t e = cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)(Jpad / kProR), (unsigned)BH);
   profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo,

@@ -50,9 +50,12 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
                            num_k_centroids: int, kmeans_iters: int, top_p: float, min_kc_ratio=0, max_kc_ratio=0,
                            init_indices=None, clustering: Optional[ops.Clustering] = None,
                            context_length: int = 0, prompt_length: Optional[int] = None,
-                           return_state: bool = False, timer: Optional[StageTimer] = None):
+                           return_state: bool = False, timer: Optional[StageTimer] = None,
+                           value_ready: Optional[torch.cuda.Event] = None):
     """query/key/value: [1, H, S, 128] bf16 CUDA, S = video tokens + context_length text
-    tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order."""
+    tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order.
+    `value_ready`: an event the launching stream waits for before it first reads `value`
+    (the clustering only reads query and key, so V may still be arriving while it runs)."""
     cfg, H, S, D = query.shape
     assert cfg == 1, "Batch size must be 1 for kmeans block sparse attention"
     assert query.is_cuda and query.dtype == torch.bfloat16, "bf16 CUDA tensors expected"
@@ -92,6 +95,8 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
         q_idx = torch.cat([c.q_sorted_idx, text_rows], 1).contiguous()
         k_idx = torch.cat([c.k_sorted_idx, text_rows], 1).contiguous()
     m = m_full
+    if value_ready is not None:
+        torch.cuda.current_stream(q.device).wait_event(value_ready)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     qp, kp, vp = ops.permute(q, q_idx), ops.permute(k, k_idx), ops.permute(v, k_idx)
     mark("permute")

@@ -99,9 +99,10 @@ class PeerExchange:
     every rank of the group maps; a one-element all-reduce on the launching stream is the
     ordering point between "my stores are issued" and "my array is complete".
 
-    Per layer call: push q, k, v -> fence -> compute -> push out -> fence.  The first fence
-    also tells every rank that its peers have finished the previous call, so the receive
-    arrays are reused without a third one."""
+    Per layer call: push q, k -> fence -> clustering ... attention -> push out -> fence; V is
+    pushed (and fenced) on a side stream while the clustering runs and joined through
+    `value_ready` before its first use.  A rank passes a fence only after every peer has
+    finished the previous call, so the receive arrays are reused without further ordering."""
 
     def __init__(self, parts: List[List[int]], n_tokens: int, device, group=None, head_dim: int = 128):
         import ctypes
@@ -126,22 +127,41 @@ class PeerExchange:
         self._owner = (ctypes.c_int32 * self.H)(*owner)
         self._slot = (ctypes.c_int32 * self.H)(*slot)
         self._mine = (ctypes.c_int32 * self.hr)(*parts[self.rank])
-        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self._flag = torch.zeros(2, dtype=torch.int32, device=device)
         self._handles = (h_in, h_out)
+        self._side = torch.cuda.Stream(device)
+        self.value_ready: Optional[torch.cuda.Event] = None
 
-    def fence(self):
-        dist.all_reduce(self._flag, group=self.group)
+    def fence(self, which: int = 0):
+        dist.all_reduce(self._flag[which:which + 1], group=self.group)
 
-    def to_heads(self, q_seq, k_seq, v_seq):
-        """[N/P, H, 128] shards of q, k, v -> views [H_r, N, 128] of the receive arrays."""
+    def _push_heads(self, t: int, x: torch.Tensor, stream: int):
         from . import _lib
-        stream = torch.cuda.current_stream(q_seq.device).cuda_stream
-        for t, x in enumerate((q_seq, k_seq, v_seq)):
-            if tuple(x.shape) != (self.n_loc, self.H, self.D) or x.dtype != torch.bfloat16 or not x.is_contiguous():
-                raise ValueError("sequence shards must be contiguous bf16 [N/P, H, 128]")
-            _lib.check(_lib.LIB.svoo_b200_push_heads(x.data_ptr(), self._in_ptrs[t], self._owner, self._slot, self.world,
-                                                     self.rank, self.n_loc, self.H, self.D, stream), "push_heads")
-        self.fence()
+        if tuple(x.shape) != (self.n_loc, self.H, self.D) or x.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise ValueError("sequence shards must be contiguous bf16 [N/P, H, 128]")
+        _lib.check(_lib.LIB.svoo_b200_push_heads(x.data_ptr(), self._in_ptrs[t], self._owner, self._slot, self.world,
+                                                 self.rank, self.n_loc, self.H, self.D, stream), "push_heads")
+
+    def to_heads(self, q_seq, k_seq, v_seq, overlap_value: bool = True):
+        """[N/P, H, 128] shards of q, k, v -> views [H_r, N, 128] of the receive arrays.  With
+        `overlap_value` the V array is complete only after `self.value_ready`."""
+        main = torch.cuda.current_stream(q_seq.device)
+        self._push_heads(0, q_seq, main.cuda_stream)
+        self._push_heads(1, k_seq, main.cuda_stream)
+        if not overlap_value:
+            self._push_heads(2, v_seq, main.cuda_stream)
+            self.value_ready = None
+            self.fence()
+        else:
+            here = torch.cuda.Event()
+            here.record(main)
+            self.fence()
+            self._side.wait_event(here)
+            with torch.cuda.stream(self._side):
+                self._push_heads(2, v_seq, self._side.cuda_stream)
+                self.fence(1)
+                self.value_ready = torch.cuda.Event()
+                self.value_ready.record(self._side)
         return self.heads_in[0], self.heads_in[1], self.heads_in[2]
 
     def to_seq(self, y):
@@ -174,7 +194,8 @@ def sparse_attention_layer_sharded(q_seq, k_seq, v_seq, parts, *, densities, ini
     qi, ki = init_indices
     d = [densities[h] for h in mine]
     out = sparse_attention_layer(q[None], k[None], v[None], min_kc_ratio=d, max_kc_ratio=d,
-                                 init_indices=(qi[mine], ki[mine]), **layer_kw)
+                                 init_indices=(qi[mine], ki[mine]),
+                                 value_ready=exchange.value_ready if exchange is not None else None, **layer_kw)
     if exchange is not None:
         return exchange.to_seq(out[0])
     return head_to_seq_shard(out[0], parts, group)

@@ -29,7 +29,9 @@ shard = lambda t: t[0, :, rank * n_loc:(rank + 1) * n_loc].transpose(0, 1).conti
 qs, ks, vs = shard(q), shard(k), shard(v)
 x = parallel.PeerExchange(parts, N, dev)
 for rep in range(2):                                                    # twice: the receive arrays are reused
-    got = x.to_heads(qs, ks, vs)
+    got = x.to_heads(qs, ks, vs, overlap_value=bool(rep))
+    if x.value_ready is not None:
+        torch.cuda.current_stream().wait_event(x.value_ready)
     want = [parallel.seq_to_head_shard(t, parts) for t in (qs, ks, vs)]
     for g, w, full in zip(got, want, (q, k, v)):
         assert torch.equal(g, w), "push_heads differs from the all-to-all"
