@@ -323,7 +323,9 @@ def run_gpu_arm(args, cfg):
             "stage_ms_rank0": {k: round(v, 4) for k, v in stage.items()},
             "roofline": {"kernel": "sparse_attn", "bound": "tensor", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_kind} sustained bf16",
-                         "traffic": ATTN_DRAM_TRAFFIC_BYTES, "algorithmic_flops_per_launch": attn_flops_rank},
+                         "traffic": ATTN_DRAM_TRAFFIC_BYTES_PER_HEAD * len(mine) * (N / 75600.0),
+                         "traffic_source": "ncu capture at 4 heads x 75,600 tokens, scaled by heads and tokens",
+                         "algorithmic_flops_per_launch": attn_flops_rank},
             "roofline_layer": {"time_at_roofline_ms": layer_roofline_ms(cfg, len(mine), rho, N, peaks),
                                "frac": layer_roofline_ms(cfg, len(mine), rho, N, peaks) / ms_per_step},
             "e2e": {"value": flops_total / (e2e_ms / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -341,9 +343,9 @@ def run_gpu_arm(args, cfg):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one sparse_attn launch, from an ncu capture
-# (see profiles/); None until a capture of this kernel version exists.
-ATTN_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one sparse_attn launch per head of 75,600
+# tokens, from an ncu capture of a 4-head launch (profiles/sparse_attn_tc_kernel_wan14b_4heads.md).
+ATTN_DRAM_TRAFFIC_BYTES_PER_HEAD = 280.7e6 / 4
 
 
 def layer_roofline_ms(cfg, heads, rho, n_tokens, peaks):
