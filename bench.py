@@ -229,15 +229,21 @@ def run_gpu_arm(args, cfg):
 
     def step(timer=None):
         if world > 1:
+            if timer is not None:
+                timer.mark("begin")
             q, k, v = (t[None] for t in xchg.to_heads(q_s, k_s, v_s))
         else:
             q, k, v = q_d, k_d, v_d
         out, st = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine,
                                                init_indices=(qi, ki), return_state=True, timer=timer,
-                                               value_ready=xchg.value_ready if xchg else None, **kw)
+                                               value_ready=xchg.value_ready if xchg else None,
+                                               peer_out=xchg.peer_out if xchg else None, **kw)
         state["st"] = st
         if world > 1:
-            return xchg.to_seq(out[0])
+            res = xchg.seq_result()
+            if timer is not None:
+                timer.mark("reshard_out")
+            return res
         return out
 
     if world > 1:
@@ -248,8 +254,8 @@ def run_gpu_arm(args, cfg):
                 d_t.copy_(h_t, non_blocking=True)
             q, k, v = (t[None] for t in xchg.to_heads(*dev_in))
             out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki),
-                                               value_ready=xchg.value_ready, **kw)
-            host_out.copy_(xchg.to_seq(out[0]), non_blocking=True)
+                                               value_ready=xchg.value_ready, peer_out=xchg.peer_out, **kw)
+            host_out.copy_(xchg.seq_result(), non_blocking=True)
     else:
         # host buffers in, host buffer out: copies of one head group overlap the compute of another
         pipe = layer.HostLayerPipeline(dev, H, N, heads_per_group=args.e2e_group)
@@ -301,6 +307,7 @@ def run_gpu_arm(args, cfg):
     stage = {}
     for t in timers:
         for name, ms in t.stage_ms().items():
+            name = "reshard_in" if name == "start" else name
             stage[name] = stage.get(name, 0.0) + ms / len(timers)
     peaks, peak_kind = measured_peaks()
     attn_ms = stage.get("attention", float("nan"))

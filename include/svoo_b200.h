@@ -183,6 +183,17 @@ int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, in
  * svoo_b200_push_seq: y = this rank's [H/world, N, 128]; row (i, n) is stored into rank
  *   n / n_loc at [n % n_loc, my_heads[i], :] of its [n_loc, H, 128] array.
  *   my_heads: HOST int32 [H/world], distinct, in [0, H). */
+/* svoo_b200_sparse_attn with the head -> sequence re-shard fused into its store: output row
+ * n of local head i (after out_row_idx, if given) is written by the attention kernel straight
+ * into rank n / n_loc at [n % n_loc, my_heads[i], :] of that rank's [n_loc, H, 128] array
+ * (peer_dst as for svoo_b200_push_seq).  BH must equal H / world and S must equal
+ * world * n_loc.  The caller fences as after svoo_b200_push_seq.  No counterpart in the
+ * reference. */
+int svoo_b200_sparse_attn_push(const void* q, const void* k, const void* v, const uint8_t* map,
+                               const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
+                               int64_t QC, int64_t KC, float sm_scale, void* const* peer_dst, const int32_t* my_heads,
+                               int32_t world, int64_t n_loc, int64_t H, const int32_t* out_row_idx, void* workspace,
+                               int64_t workspace_bytes, void* stream);
 int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* owner, const int32_t* slot,
                          int32_t world, int32_t rank, int64_t n_loc, int64_t H, int64_t D, void* stream);
 int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int32_t world, int64_t n_loc,

@@ -43,6 +43,9 @@ SIGNATURES = {
                                            c_void_p]),
     "svoo_b200_status_offset": (c_int, [c_int64, c_int64, c_int64, c_int64, _I64P]),
     "svoo_b200_offsets_from_sizes": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "svoo_b200_sparse_attn_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                           c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_int32, c_int64,
+                                           c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
     "svoo_b200_push_heads": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int64, c_int64,
                                      c_void_p]),
     "svoo_b200_push_seq": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p]),

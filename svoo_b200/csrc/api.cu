@@ -19,7 +19,7 @@ cudaError_t launch_build_runs(const uint8_t*, const int32_t*, int2*, int32_t*, i
 cudaError_t launch_build_qtiles(const int32_t*, int4*, int32_t*, int64_t, int64_t, int64_t, int, cudaStream_t);
 cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, void*, const int32_t*, const int4*,
                                   const int32_t*, const int2*, const int32_t*, int32_t*, int64_t, int64_t, int64_t,
-                                  int64_t, float, cudaStream_t);
+                                  int64_t, float, void* const*, const int32_t*, int, int64_t, int, cudaStream_t);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, void*, const int32_t*, const int4*,
                                    const int32_t*, const int2*, const int32_t*, int64_t, int64_t, int64_t, int64_t,
                                    float, cudaStream_t);
@@ -217,16 +217,32 @@ int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, in
   return SVOO_OK;
 }
 
+namespace {
+int check_exchange(void* const* peer_dst, int32_t world, int64_t n_loc, int64_t H, int64_t D) {
+  if (!peer_dst) return SVOO_ERR_NULL;
+  if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
+  if (world < 1 || world > 16 || H < 1 || H > 128 || H % world != 0 || n_loc < 1 || n_loc * world > (int64_t)1 << 30)
+    return SVOO_ERR_SHAPE;
+  for (int p = 0; p < world; ++p) {
+    if (!peer_dst[p]) return SVOO_ERR_NULL;
+    if (!aligned16(peer_dst[p])) return SVOO_ERR_ALIGN;
+  }
+  return SVOO_OK;
+}
+}  // namespace
+
 static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, const void* v, const uint8_t* map,
                             const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
                             int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx,
-                            void* workspace, int64_t workspace_bytes, void* stream) {
-  if (!q || !k || !v || !map || !q_offsets || !k_offsets || !out || !workspace) return SVOO_ERR_NULL;
+                            void* workspace, int64_t workspace_bytes, void* stream, void* const* peer_dst = nullptr,
+                            const int32_t* my_heads = nullptr, int world = 0, int64_t n_loc = 0, int H = 0) {
+  if (!q || !k || !v || !map || !q_offsets || !k_offsets || (!out && !peer_dst) || !workspace) return SVOO_ERR_NULL;
   SVOO_TRY(check_tokens(BH, S, D));
   SVOO_TRY(check_clusters(QC));
   SVOO_TRY(check_clusters(KC));
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(workspace))
     return SVOO_ERR_ALIGN;
+  if (!tensor_core && peer_dst) return SVOO_ERR_SHAPE;
   const Workspace w = workspace_layout(BH, S, QC, KC);
   if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
@@ -240,7 +256,7 @@ static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, cons
   if (tensor_core) {
     SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));                     // word 0: attention kernel
     SVOO_CUDA(launch_sparse_attn_tc(q, k, v, out, out_row_idx, qtiles, nqtiles, runs, nruns, status, BH, S, QC, KC,
-                                    sm_scale, st));
+                                    sm_scale, peer_dst, my_heads, world, n_loc, H, st));
   } else {
     SVOO_CUDA(launch_sparse_attn_mma(q, k, v, out, out_row_idx, qtiles, nqtiles, runs, nruns, BH, S, QC, KC, sm_scale,
                                      st));
@@ -254,6 +270,23 @@ int svoo_b200_sparse_attn(const void* q, const void* k, const void* v, const uin
                           int64_t workspace_bytes, void* stream) {
   return sparse_attn_impl(true, q, k, v, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, out, out_row_idx,
                           workspace, workspace_bytes, stream);
+}
+
+int svoo_b200_sparse_attn_push(const void* q, const void* k, const void* v, const uint8_t* map,
+                               const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
+                               int64_t QC, int64_t KC, float sm_scale, void* const* peer_dst, const int32_t* my_heads,
+                               int32_t world, int64_t n_loc, int64_t H, const int32_t* out_row_idx, void* workspace,
+                               int64_t workspace_bytes, void* stream) {
+  if (!my_heads) return SVOO_ERR_NULL;
+  SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
+  if (BH != H / world || S != n_loc * world) return SVOO_ERR_SHAPE;
+  bool seen[128] = {};
+  for (int64_t i = 0; i < BH; ++i) {
+    if (my_heads[i] < 0 || my_heads[i] >= H || seen[my_heads[i]]) return SVOO_ERR_SHAPE;
+    seen[my_heads[i]] = true;
+  }
+  return sparse_attn_impl(true, q, k, v, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, nullptr, out_row_idx,
+                          workspace, workspace_bytes, stream, peer_dst, my_heads, world, n_loc, (int)H);
 }
 
 int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, const uint8_t* map,
@@ -272,20 +305,6 @@ int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64
   *offset_out = workspace_layout(BH, N, QC, KC).status;
   return SVOO_OK;
 }
-
-namespace {
-int check_exchange(void* const* peer_dst, int32_t world, int64_t n_loc, int64_t H, int64_t D) {
-  if (!peer_dst) return SVOO_ERR_NULL;
-  if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
-  if (world < 1 || world > 16 || H < 1 || H > 128 || H % world != 0 || n_loc < 1 || n_loc * world > (int64_t)1 << 30)
-    return SVOO_ERR_SHAPE;
-  for (int p = 0; p < world; ++p) {
-    if (!peer_dst[p]) return SVOO_ERR_NULL;
-    if (!aligned16(peer_dst[p])) return SVOO_ERR_ALIGN;
-  }
-  return SVOO_OK;
-}
-}  // namespace
 
 int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* owner, const int32_t* slot,
                          int32_t world, int32_t rank, int64_t n_loc, int64_t H, int64_t D, void* stream) {

@@ -49,6 +49,15 @@ struct AttnMaps {
   CUtensorMap k[kBoxHeights];
   CUtensorMap v[kBoxHeights];
 };
+// Optional destination of the output rows on other GPUs: row n of local head bh goes to rank
+// n / n_loc, row n % n_loc, head head[bh] of that rank's [n_loc, H, 128] array.  n_loc == 0: the
+// rows go to `out` of this GPU.
+struct OutPeers {
+  bf16* dst[16];
+  int n_loc;
+  int H;
+  int16_t head[128];
+};
 constexpr float kRescaleThreshold = 8.0f;
 
 enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_DONE = 13, NUM_BARS = 15 };
@@ -160,7 +169,8 @@ __device__ long long g_trace[8 * 64 * 4];
 #endif
 
 __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
-    const __grid_constant__ AttnMaps maps, bf16* __restrict__ out, const int32_t* __restrict__ out_row_idx, const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles,
+    const __grid_constant__ AttnMaps maps, const __grid_constant__ OutPeers peers, bf16* __restrict__ out,
+    const int32_t* __restrict__ out_row_idx, const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles,
     const int2* __restrict__ runs, const int32_t* __restrict__ nruns, int S, int QC, int max_tiles, int max_runs,
     float scale_log2, int32_t* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
@@ -400,7 +410,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       const bool store = row < row1;
       int dst = row;
       if (store && out_row_idx) dst = out_row_idx[(int64_t)bh * S + row];
-      bf16* orow = out + ((int64_t)bh * S + (store ? min(max(dst, 0), S - 1) : 0)) * kHeadDim;
+      dst = store ? min(max(dst, 0), S - 1) : 0;
+      bf16* orow;
+      if (peers.n_loc == 0) {
+        orow = out + ((int64_t)bh * S + dst) * kHeadDim;
+      } else {                                           // store straight into the owning rank's sequence shard
+        const int p = dst / peers.n_loc;
+        orow = peers.dst[p] + ((int64_t)(dst - p * peers.n_loc) * peers.H + peers.head[bh]) * kHeadDim;
+      }
       if (T == 0) {
         if (store) {
 #pragma unroll
@@ -448,7 +465,15 @@ extern "C" int svoo_b200_debug_trace(long long* host_out) {
 cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, void* out, const int32_t* out_row_idx,
                                   const int4* qtiles, const int32_t* nqtiles, const int2* runs, const int32_t* nruns,
                                   int32_t* status, int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale,
+                                  void* const* peer_dst, const int32_t* my_heads, int world, int64_t n_loc, int H,
                                   cudaStream_t st) {
+  tc::OutPeers peers{};
+  if (peer_dst) {
+    for (int p = 0; p < world; ++p) peers.dst[p] = (bf16*)peer_dst[p];
+    for (int64_t i = 0; i < BH; ++i) peers.head[i] = (int16_t)my_heads[i];
+    peers.n_loc = (int)n_loc;
+    peers.H = H;
+  }
   alignas(64) tc::AttnMaps maps;
   bool ok = tc::make_row_tensor_map(&maps.q, q, BH * S, 128);
   for (int i = 0; i < tc::kBoxHeights && ok; ++i)
@@ -459,7 +484,7 @@ cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, v
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)max_qtiles(S, QC), (unsigned)BH);
   tc::sparse_attn_tc_kernel<<<grid, tc::kThreads, tc::kSmemBytes, st>>>(
-      maps, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), max_runs(KC),
+      maps, peers, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), max_runs(KC),
       sm_scale * 1.4426950408889634f, status);
   count_launches(1);
   return cudaGetLastError();

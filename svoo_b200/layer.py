@@ -51,11 +51,13 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
                            init_indices=None, clustering: Optional[ops.Clustering] = None,
                            context_length: int = 0, prompt_length: Optional[int] = None,
                            return_state: bool = False, timer: Optional[StageTimer] = None,
-                           value_ready: Optional[torch.cuda.Event] = None):
+                           value_ready: Optional[torch.cuda.Event] = None, peer_out=None):
     """query/key/value: [1, H, S, 128] bf16 CUDA, S = video tokens + context_length text
     tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order.
     `value_ready`: an event the launching stream waits for before it first reads `value`
-    (the clustering only reads query and key, so V may still be arriving while it runs)."""
+    (the clustering only reads query and key, so V may still be arriving while it runs).
+    `peer_out` (see ops.sparse_attn): the output rows are stored into the ranks' sequence
+    shards by the attention kernel itself and the returned tensor is None."""
     cfg, H, S, D = query.shape
     assert cfg == 1, "Batch size must be 1 for kmeans block sparse attention"
     assert query.is_cuda and query.dtype == torch.bfloat16, "bf16 CUDA tensors expected"
@@ -100,9 +102,10 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     qp, kp, vp = ops.permute(q, q_idx), ops.permute(k, k_idx), ops.permute(v, k_idx)
     mark("permute")
-    out = ops.sparse_attn(qp, kp, vp, m.contiguous(), q_off, k_off, D ** -0.5, out_row_idx=q_idx)
+    out = ops.sparse_attn(qp, kp, vp, m.contiguous(), q_off, k_off, D ** -0.5, out_row_idx=q_idx, peer_out=peer_out)
     mark("attention")
-    out = out.unsqueeze(0)
+    if out is not None:
+        out = out.unsqueeze(0)
     if return_state:
         return out, LayerState(c, m, q_off, k_off)
     return out

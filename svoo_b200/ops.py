@@ -199,10 +199,12 @@ def offsets_from_sizes(sizes: torch.Tensor) -> torch.Tensor:
 def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_map_u8: torch.Tensor,
                 q_offsets: torch.Tensor, k_offsets: torch.Tensor, sm_scale: Optional[float] = None,
                 out_row_idx: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                kernel: str = "tcgen05") -> torch.Tensor:
+                kernel: str = "tcgen05", peer_out=None) -> Optional[torch.Tensor]:
     """Block-sparse attention over cluster-ordered q,k,v [BH,S,128].  With out_row_idx the
     result rows are scattered to their original positions (fused inverse permutation).
-    kernel="simt" selects the mma.sync cross-check kernel."""
+    kernel="simt" selects the mma.sync cross-check kernel.  peer_out = (peer pointer array,
+    head id array, world, n_loc, H): the rows are stored into the ranks' sequence shards
+    instead of a local tensor (svoo_b200_sparse_attn_push) and nothing is returned."""
     _need_cuda(q, k, v, block_map_u8, q_offsets, k_offsets)
     BH, S, D = _tokens(q)
     QC, KC = q_offsets.shape[1] - 1, k_offsets.shape[1] - 1
@@ -210,10 +212,19 @@ def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_map_u8:
         raise ValueError("block map must be uint8/bool [BH, QC, KC]")
     if kernel not in ("tcgen05", "simt"):
         raise ValueError("kernel must be 'tcgen05' or 'simt'")
-    y = torch.empty_like(q) if out is None else out
     ws = workspace(q.device, BH, S, QC, KC)
     scale = D ** -0.5 if sm_scale is None else float(sm_scale)
     ridx = 0 if out_row_idx is None else out_row_idx.data_ptr()
+    if peer_out is not None:
+        if kernel != "tcgen05":
+            raise ValueError("peer stores need the tcgen05 kernel")
+        ptrs, heads, world, n_loc, H = peer_out
+        rc = LIB.svoo_b200_sparse_attn_push(q.data_ptr(), k.data_ptr(), v.data_ptr(), block_map_u8.data_ptr(),
+                                            q_offsets.data_ptr(), k_offsets.data_ptr(), BH, S, D, QC, KC, scale, ptrs,
+                                            heads, world, n_loc, H, ridx, ws.data_ptr(), ws.numel(), _stream())
+        check(rc, "sparse_attn_push")
+        return None
+    y = torch.empty_like(q) if out is None else out
     head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), block_map_u8.data_ptr(), q_offsets.data_ptr(),
             k_offsets.data_ptr(), BH, S, D, QC, KC, scale, y.data_ptr())
     fn = LIB.svoo_b200_sparse_attn if kernel == "tcgen05" else LIB.svoo_b200_sparse_attn_simt

@@ -164,6 +164,17 @@ class PeerExchange:
                 self.value_ready.record(self._side)
         return self.heads_in[0], self.heads_in[1], self.heads_in[2]
 
+    @property
+    def peer_out(self):
+        """Argument for sparse_attention_layer(peer_out=...): the attention kernel then stores its
+        rows into the ranks' sequence shards itself; call `seq_result()` afterwards."""
+        return (self._out_ptrs, self._mine, self.world, self.n_loc, self.H)
+
+    def seq_result(self):
+        """After a layer call with `peer_out`: fence, then this rank's [N/P, H, 128] shard."""
+        self.fence()
+        return self.seq_out
+
     def to_seq(self, y):
         """This rank's [H_r, N, 128] result -> the [N/P, H, 128] shard (a view of the receive array)."""
         from . import _lib
@@ -177,11 +188,12 @@ class PeerExchange:
 
 
 def sparse_attention_layer_sharded(q_seq, k_seq, v_seq, parts, *, densities, init_indices, group=None, exchange=None,
-                                   **layer_kw):
+                                   fused_store: bool = True, **layer_kw):
     """Ulysses-style layer: q/k/v_seq are this rank's [N/P, H, 128] shards; returns the
     [N/P, H, 128] shard of the output.  `densities` and `init_indices` are for all H heads;
     each rank takes the entries of its own heads.  With `exchange` (a PeerExchange) the two
-    re-shardings are peer stores; without it they are torch.distributed all-to-alls."""
+    re-shardings are peer stores (the second one issued by the attention kernel itself when
+    `fused_store`); without it they are torch.distributed all-to-alls."""
     from .layer import sparse_attention_layer
     rank = dist.get_rank(group)
     mine = parts[rank]
@@ -195,7 +207,9 @@ def sparse_attention_layer_sharded(q_seq, k_seq, v_seq, parts, *, densities, ini
     d = [densities[h] for h in mine]
     out = sparse_attention_layer(q[None], k[None], v[None], min_kc_ratio=d, max_kc_ratio=d,
                                  init_indices=(qi[mine], ki[mine]),
-                                 value_ready=exchange.value_ready if exchange is not None else None, **layer_kw)
+                                 value_ready=exchange.value_ready if exchange is not None else None,
+                                 peer_out=exchange.peer_out if (exchange is not None and fused_store) else None,
+                                 **layer_kw)
     if exchange is not None:
-        return exchange.to_seq(out[0])
+        return exchange.seq_result() if fused_store else exchange.to_seq(out[0])
     return head_to_seq_shard(out[0], parts, group)

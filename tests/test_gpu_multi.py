@@ -42,8 +42,10 @@ for rep in range(2):                                                    # twice:
     assert torch.equal(back, qs), "round trip"
 qi, ki = synth.init_indices(cfg)
 kw = dict(num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k, kmeans_iters=cfg.iters, top_p=cfg.top_p)
-out = parallel.sparse_attention_layer_sharded(qs, ks, vs, parts, densities=dens, init_indices=(qi.to(dev), ki.to(dev)),
-                                              exchange=x, **kw)
+outs = [parallel.sparse_attention_layer_sharded(qs, ks, vs, parts, densities=dens, init_indices=(qi.to(dev), ki.to(dev)),
+                                                exchange=x, fused_store=f, **kw).clone() for f in (False, True)]
+assert torch.equal(outs[0], outs[1]), "fused peer store differs from push_seq"
+out = outs[1]
 ref = layer.sparse_attention_layer(q, k, v, min_kc_ratio=dens, max_kc_ratio=dens, init_indices=(qi.to(dev), ki.to(dev)), **kw)
 assert torch.equal(out, shard(ref)), "sharded layer differs from the one-GPU layer"
 torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
