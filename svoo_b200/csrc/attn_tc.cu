@@ -35,7 +35,7 @@ constexpr int kMaxRunsSmem = SVOO_MAX_CLUSTERS / 2 + 2;
 constexpr int kRunTableBytes = (kMaxRunsSmem * 8 + 255) / 256 * 256;
 constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 1024;   // + barriers, run table, slack
 #ifndef SVOO_SINGLE_PASS
-#define SVOO_SINGLE_PASS 0
+#define SVOO_SINGLE_PASS 1
 #endif
 constexpr int kKWarp = 8, kVWarp = 9, kMmaWarp = 10;     // after the 8 softmax warps
 // 11 warps; registers are allotted to a CTA in groups of four warps: 65536 / (12 * 32) = 170.
@@ -71,9 +71,34 @@ __device__ __forceinline__ void row_max_masked(const uint32_t (&r)[32], float& m
 #pragma unroll
   for (int i = 0; i < 32; ++i) m = fmaxf(m, i < valid ? __uint_as_float(r[i]) : -INFINITY);
 }
+#ifndef SVOO_EXP_BF16X2
+#define SVOO_EXP_BF16X2 0
+#endif
+// Two exponentials per special-function instruction: the arguments are rounded to bf16 first,
+// the results are the bf16 pair that P needs anyway.  An argument x <= 0 carries an absolute error
+// of at most |x| 2^-9, so p is off by at most p |x| ln2 2^-9 <= 7e-4 of the row maximum -- the
+// size of P's own bf16 rounding.  The row sum adds the rounded values, i.e. exactly the weights
+// the PV product uses.
+__device__ __forceinline__ uint32_t ex2_bf16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
 // p = exp2(s * scale + neg_m) for 32 columns -> 16 packed bf16 pairs; columns >= valid give 0.
 __device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale, float neg_m,
                                          float& l0, float& l1, int valid) {
+#if SVOO_EXP_BF16X2
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float x0 = fmaf(__uint_as_float(r[2 * i]), scale, neg_m);
+    const float x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale, neg_m);
+    uint32_t e = ex2_bf16x2(pack_bf16x2(x0, x1));
+    if (valid < 32) e &= (2 * i < valid ? 0x0000ffffu : 0u) | (2 * i + 1 < valid ? 0xffff0000u : 0u);
+    l0 += __uint_as_float(e << 16);
+    l1 += __uint_as_float(e & 0xffff0000u);
+    pk[i] = e;
+  }
+#else
   if (valid >= 32) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -95,6 +120,7 @@ __device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], uint32_t (&pk)
       pk[i] = pack_bf16x2(p0, p1);
     }
   }
+#endif
 }
 
 // 16 columns: x = s * scale + neg_m, running max of x, p = exp2(x) -> 8 packed bf16 pairs.
@@ -264,12 +290,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         const bool has_next = j + 1 < T;
         if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) break;
         for (int w = 0; w < nq && ok; ++w) {
+          TRACE(7, j, w);
           ok = mbar_wait(bar(P_READY + w), j & 1, abort_flag);
           TRACE(2, j, w);
           if (!ok) break;
           tc_fence_after();
           issue_pv(w, s, j > 0);
-          tc_commit(bar(O_DONE + w));
+          if (!has_next) tc_commit(bar(O_DONE + w));      // only the last PV needs its own signal (see the rescale path)
+          TRACE(7, j, 2 + w);
           if (has_next) {
             if (w == 0) {
               ok = mbar_wait(bar(K_FULL + sn), ((j + 1) >> 1) & 1, abort_flag);
@@ -301,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       for (int j = 0; j < T; ++j) {
         const int valid = min(L - j * kBN, kBN);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + w), j & 1, abort_flag));
-        if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 0);
+        if (lane == 0) TRACE(5 + w, j, warp & 3);
         if (!ok) break;
         tc_fence_after();
         if (SVOO_SINGLE_PASS && j > 0 && valid >= kBN) {
@@ -330,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(P_READY + w));
-            if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 1);
+            if (lane == 0) TRACE(w, j, warp & 3);
             continue;
           }
         }
@@ -362,9 +390,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         } else {
           const bool need = m_tile > m_used + kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + w), (j - 1) & 1, abort_flag));
-            if (!ok) break;
-            tc_fence_after();
+            // S_FULL of this tile was committed after the PV of the previous tile by the same thread,
+            // and a commit tracks every earlier tcgen05 operation of that thread: O is complete here.
             const float alpha = need ? fast_exp2(m_used - m_tile) : 1.0f;
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {
@@ -403,7 +430,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(P_READY + w));
-        if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 2);
+        if (lane == 0) TRACE(w, j, warp & 3);
       }
       // epilogue: O / l -> bf16 rows
       const int row = row0 + w * kBM + r_local;
@@ -423,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
 #pragma unroll
           for (int ch = 0; ch < 16; ++ch) reinterpret_cast<uint4*>(orow)[ch] = make_uint4(0, 0, 0, 0);
         }
-      } else if (ok && __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + w), (T - 1) & 1, abort_flag))) {
+      } else if (ok && __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + w), 0, abort_flag))) {
         tc_fence_after();
         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
 #pragma unroll 1

@@ -33,6 +33,30 @@ def head_partition(num_heads: int, world: int, weights: Optional[Sequence[float]
         r = min((r for r in range(world) if len(parts[r]) < room[r]), key=lambda r: (load[r], r))
         parts[r].append(h)
         load[r] += float(weights[h])
+    # refinement: swap one head of the heaviest rank with one of another rank while that lowers
+    # the larger of the two loads (counts stay equal); deterministic, a few dozen swaps at most
+    for _ in range(16 * num_heads):
+        hi = max(range(world), key=lambda r: (load[r], -r))
+        best = None
+        for r in range(world):
+            if r == hi:
+                continue
+            for a in parts[hi]:
+                for b in parts[r]:
+                    delta = float(weights[a]) - float(weights[b])
+                    if delta <= 0:
+                        continue
+                    new_max = max(load[hi] - delta, load[r] + delta)
+                    if new_max < load[hi] - 1e-12 and (best is None or new_max < best[0]):
+                        best = (new_max, r, a, b)
+        if best is None:
+            break
+        _, r, a, b = best
+        parts[hi].remove(a); parts[r].remove(b)
+        parts[hi].append(b); parts[r].append(a)
+        delta = float(weights[a]) - float(weights[b])
+        load[hi] -= delta
+        load[r] += delta
     return [sorted(p) for p in parts]
 
 
