@@ -21,6 +21,7 @@
 //
 // TMEM columns (512 allocated): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).
 // Semantics: svoo/co_clustering.py:949-1108 (scale D^-0.5, zero output without keys).
+#include <type_traits>
 #include "tc_common.cuh"
 
 namespace svoo {
@@ -39,7 +40,8 @@ constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 1024;   // + barr
 #endif
 constexpr int kKWarp = 8, kVWarp = 9, kMmaWarp = 10;     // after the 8 softmax warps
 // 11 warps; registers are allotted to a CTA in groups of four warps: 65536 / (12 * 32) = 170.
-constexpr int kThreads = (kMmaWarp + 1) * 32;
+constexpr int kThreads = 12 * 32;       // warp 11 only completes the service warpgroup (register hand-over below)
+constexpr int kRegsService = 104, kRegsSoftmax = 200;
 constexpr int kBoxHeights = 8;                           // TMA boxes of 1, 2, 4, ..., 128 rows
 
 // Tensor maps of one launch: Q with 128-row boxes; K and V with one map per box height, so a
@@ -123,17 +125,40 @@ __device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], uint32_t (&pk)
 #endif
 }
 
-// 16 columns: x = s * scale + neg_m, running max of x, p = exp2(x) -> 8 packed bf16 pairs.
-__device__ __forceinline__ void exp_pack16(const uint32_t (&r)[16], uint32_t* pk, float scale, float neg_m, float& l0,
-                                           float& l1, float& mx) {
+// Packed fp32 pairs (one instruction for two lanes of data): x = s * scale + neg_m and the
+// running pair of row sums.
+__device__ __forceinline__ void fma2(float& x0, float& x1, uint32_t a0, uint32_t a1, uint64_t scale2, uint64_t negm2) {
+  asm("{\n\t.reg .b64 a, x;\n\t"
+      "mov.b64 a, {%2, %3};\n\t"
+      "fma.rn.f32x2 x, a, %4, %5;\n\t"
+      "mov.b64 {%0, %1}, x;\n\t}\n"
+      : "=f"(x0), "=f"(x1) : "r"(a0), "r"(a1), "l"(scale2), "l"(negm2));
+}
+__device__ __forceinline__ void add2(uint64_t& acc, float p0, float p1) {
+  asm("{\n\t.reg .b64 p;\n\t"
+      "mov.b64 p, {%1, %2};\n\t"
+      "add.rn.f32x2 %0, %0, p;\n\t}\n"
+      : "+l"(acc) : "f"(p0), "f"(p1));
+}
+__device__ __forceinline__ uint64_t pair2(float v) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float pair_sum(uint64_t acc) {
+  float a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(acc));
+  return a + b;
+}
+// 16 columns: p = exp2(s * scale + neg_m) -> 8 packed bf16 pairs, row sums into `acc`.
+__device__ __forceinline__ void exp_pack16(const uint32_t (&r)[16], uint32_t* pk, uint64_t scale2, uint64_t negm2,
+                                           uint64_t& acc) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float x0 = fmaf(__uint_as_float(r[2 * i]), scale, neg_m);
-    const float x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale, neg_m);
-    mx = fmaxf(mx, fmaxf(x0, x1));
+    float x0, x1;
+    fma2(x0, x1, r[2 * i], r[2 * i + 1], scale2, negm2);
     const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-    l0 += p0;
-    l1 += p1;
+    add2(acc, p0, p1);
     pk[i] = pack_bf16x2(p0, p1);
   }
 }
@@ -239,6 +264,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   const int L = runs_s[nr].y;                      // selected key rows in total
   const int T = (L + kBN - 1) / kBN;               // packed key tiles
 
+  // Registers move from the service warpgroup (TMA producers, MMA issuer, one idle warp) to the
+  // two softmax warpgroups: 12 warps leave 168 registers per thread at launch; the softmax keeps
+  // a whole tile of exponentials in registers and needs about 190.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsService));
   if (warp == kKWarp || warp == kVWarp) {
     // ---------------------------------------------------------------- TMA producers (K + Q, V)
     if (lane == 0 && T > 0) {
@@ -265,57 +295,91 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     }
   } else if (warp == kMmaWarp) {
     // ---------------------------------------------------------------- MMA issuer
+    // One thread issues every tcgen05.mma of the CTA, sharing its scheduler with two softmax
+    // warps, so each instruction it executes between two MMAs is tensor-pipe idle time.  All 48
+    // shared-memory descriptors are therefore built once (only their low words differ) and the
+    // tile loop is specialised on the ring stage, which leaves a register move and the MMA per step.
     if (lane == 0 && T > 0) {
-      auto issue_qk = [&](int w, int s) {
+      constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+      // low descriptor words of the first Q / K / V tile; every other operand is a compile-time
+      // offset (in 16-byte units) from these
+      const uint32_t q_lo = ((q_s & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t k_lo = ((k_s & 0x3FFFFu) >> 4) | (1u << 16);
+      const uint32_t v_lo = ((v_s & 0x3FFFFu) >> 4) | ((uint32_t)(kBox >> 4) << 16);
+      auto issue_qk = [&](auto wc, auto sc) {
+        constexpr int w = decltype(wc)::value, st = decltype(sc)::value;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * kBox + (ks & 3) * 32;
-          umma_ss(tmem + w * 128, desc_kmajor(q_s + w * kTile + off), desc_kmajor(k_s + s * kTile + off), kIdescQK, ks > 0);
+          const uint32_t off = ((ks >> 2) * kBox + (ks & 3) * 32) >> 4;
+          umma_ss_lo(tmem + w * 128, q_lo + ((w * kTile) >> 4) + off, k_lo + ((st * kTile) >> 4) + off, kDescHi, kIdescQK,
+                     ks > 0);
         }
       };
-      auto issue_pv = [&](int w, int s, bool accumulate) {
+      auto issue_pv = [&](auto wc, auto sc, bool accumulate) {
+        constexpr int w = decltype(wc)::value, st = decltype(sc)::value;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tmem + 256 + w * 128, tmem + w * 128 + ks * 8, desc_mnmajor(v_s + s * kTile + ks * 2048), kIdescPV,
-                  (accumulate || ks > 0) ? 1u : 0u);
+          umma_ts_lo(tmem + 256 + w * 128, tmem + w * 128 + ks * 8, v_lo + ((st * kTile + ks * 2048) >> 4), kDescHi, kIdescPV,
+                     (accumulate || ks > 0) ? 1u : 0u);
       };
+      using I0 = std::integral_constant<int, 0>;
+      using I1 = std::integral_constant<int, 1>;
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        for (int w = 0; w < nq; ++w) { issue_qk(w, 0); tc_commit(bar(S_FULL + w)); }
+        issue_qk(I0{}, I0{});
+        tc_commit(bar(S_FULL));
+        if (nq > 1) { issue_qk(I1{}, I0{}); tc_commit(bar(S_FULL + 1)); }
         tc_commit(bar(K_EMPTY));
       }
-      for (int j = 0; ok && j < T; ++j) {
-        const int s = j & 1, sn = s ^ 1;
+      // one key tile: PV of both query tiles on stage `st`, QK of the next tile on the other stage
+      auto tile = [&](auto sc, int j) -> bool {
+        constexpr int st = decltype(sc)::value, sn = st ^ 1;
+        using SN = std::integral_constant<int, sn>;
         const bool has_next = j + 1 < T;
-        if (!mbar_wait(bar(V_FULL + s), (j >> 1) & 1, abort_flag)) break;
-        for (int w = 0; w < nq && ok; ++w) {
-          TRACE(7, j, w);
-          ok = mbar_wait(bar(P_READY + w), j & 1, abort_flag);
-          TRACE(2, j, w);
-          if (!ok) break;
+        const uint32_t ph = (j >> 1) & 1, phn = ((j + 1) >> 1) & 1;
+        TRACE(7, j, 0);
+        if (!mbar_wait(bar(V_FULL + st), ph, abort_flag)) return false;
+        TRACE(7, j, 1);
+        if (!mbar_wait(bar(P_READY), j & 1, abort_flag)) return false;
+        TRACE(2, j, 0);
+        tc_fence_after();
+        issue_pv(I0{}, sc, j > 0);
+        if (!has_next) tc_commit(bar(O_DONE));          // only the last PV needs its own signal (see the rescale path)
+        if (has_next) {
+          TRACE(7, j, 2);
+          if (!mbar_wait(bar(K_FULL + sn), phn, abort_flag)) return false;
+          TRACE(7, j, 3);
           tc_fence_after();
-          issue_pv(w, s, j > 0);
-          if (!has_next) tc_commit(bar(O_DONE + w));      // only the last PV needs its own signal (see the rescale path)
-          TRACE(7, j, 2 + w);
+          issue_qk(I0{}, SN{});
+          tc_commit(bar(S_FULL));
+          TRACE(2, j, 2);
+        }
+        if (nq > 1) {
+          if (!mbar_wait(bar(P_READY + 1), j & 1, abort_flag)) return false;
+          TRACE(2, j, 1);
+          tc_fence_after();
+          issue_pv(I1{}, sc, j > 0);
+          if (!has_next) tc_commit(bar(O_DONE + 1));
           if (has_next) {
-            if (w == 0) {
-              ok = mbar_wait(bar(K_FULL + sn), ((j + 1) >> 1) & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-            }
-            issue_qk(w, sn);
-            tc_commit(bar(S_FULL + w));
-            TRACE(2, j, 2 + w);
+            issue_qk(I1{}, SN{});
+            tc_commit(bar(S_FULL + 1));
+            TRACE(2, j, 3);
           }
         }
-        if (!ok) break;
-        tc_commit(bar(V_EMPTY + s));
+        tc_commit(bar(V_EMPTY + st));
         if (has_next) tc_commit(bar(K_EMPTY + sn));
+        return true;
+      };
+      for (int j = 0; ok && j < T; j += 2) {
+        ok = tile(I0{}, j);
+        if (ok && j + 1 < T) ok = tile(I1{}, j + 1);
       }
     }
+  }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     const int w = warp >> 2;
     if (w < nq) {
       const int quad = warp & 3;
@@ -336,8 +400,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
           // Common case, one TMEM pass: exponentials are taken against the running maximum of
           // the previous tiles and kept in registers; they are stored only if no row of the
           // warp outgrew that maximum by more than 2^8, otherwise the two-pass path redoes the tile.
-          const float neg_m0 = -m_used;
-          float mx = -INFINITY, la = 0.f, lb = 0.f;
+          // Scale-and-subtract and the row sums run as packed fp32 pairs, so the special-function
+          // unit (two ex2 per pair), not instruction issue, bounds the tile.
+          const uint64_t scale2 = pair2(scale_log2), negm2 = pair2(-m_used);
+          uint64_t acc = 0;                                // two fp32 zeros
           uint32_t pk[64];
           uint32_t xa[16], xb[16];
           tmem_ld16_nowait(s_t, xa);
@@ -345,16 +411,19 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
 #pragma unroll
           for (int c = 0; c < 8; c += 2) {
             tmem_ld16_nowait(s_t + (c + 1) * 16, xb);
-            exp_pack16(xa, &pk[c * 8], scale_log2, neg_m0, la, lb, mx);
+            exp_pack16(xa, &pk[c * 8], scale2, negm2, acc);
             tmem_wait_ld();
             if (c + 2 < 8) tmem_ld16_nowait(s_t + (c + 2) * 16, xa);
-            exp_pack16(xb, &pk[(c + 1) * 8], scale_log2, neg_m0, la, lb, mx);
+            exp_pack16(xb, &pk[(c + 1) * 8], scale2, negm2, acc);
             tmem_wait_ld();
           }
-          if (!__any_sync(0xffffffffu, mx > kRescaleThreshold)) {
+          // every p is at most the tile's row sum: a sum within 2^8 means no score outgrew the
+          // running maximum by more than 8 (an overflow to inf or a NaN fails the test as well)
+          const float tile_sum = pair_sum(acc);
+          if (__all_sync(0xffffffffu, tile_sum <= 256.0f)) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_st16(s_t + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[c * 16]));
-            l_sum += la + lb;
+            l_sum += tile_sum;
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(P_READY + w));

@@ -54,6 +54,27 @@ __device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
       ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same two forms with the descriptors given as (low word, shared high word): the 64-bit
+// values are assembled next to the instruction instead of living in register pairs.
+__device__ __forceinline__ void umma_ss_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}\n"
+      ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_ts_lo(uint32_t d, uint32_t a, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}\n"
+      ::"r"(d), "r"(a), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate) : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
