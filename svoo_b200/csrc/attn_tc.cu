@@ -150,14 +150,59 @@ __device__ __forceinline__ float pair_sum(uint64_t acc) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(acc));
   return a + b;
 }
-// 16 columns: p = exp2(s * scale + neg_m) -> 8 packed bf16 pairs, row sums into `acc`.
+#ifndef SVOO_POLY_PAIRS
+#define SVOO_POLY_PAIRS 2
+#endif
+// exp2 of a pair on the FMA pipe instead of the special-function unit (which is the scarcer
+// resource of this kernel): x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic with
+// relative error 7.5e-5 (P is rounded to bf16, 4e-3, afterwards); n goes into the exponent field
+// with one shift-add.  Arguments below -126 are clamped (their result flushes to zero either way).
+struct PolyConst {
+  uint64_t magic, neg_magic, c0, c1, c2, c3;
+};
+__device__ __forceinline__ PolyConst poly_const() {
+  PolyConst k;
+  k.magic = pair2(12582912.0f);
+  k.neg_magic = pair2(-12582912.0f);
+  k.c0 = pair2(0.9999280571937561f);
+  k.c1 = pair2(0.6932609677314758f);
+  k.c2 = pair2(0.2426111251115799f);
+  k.c3 = pair2(0.0551716685295105f);
+  return k;
+}
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, const PolyConst& k, float& p0, float& p1) {
+  x0 = fmaxf(x0, -126.0f);
+  x1 = fmaxf(x1, -126.0f);
+  uint32_t t0, t1, q0, q1;
+  asm("{\n\t.reg .b64 x, t, n, f, p;\n\t"
+      "mov.b64 x, {%4, %5};\n\t"
+      "add.rn.f32x2 t, x, %6;\n\t"
+      "add.rn.f32x2 n, t, %7;\n\t"
+      "sub.rn.f32x2 f, x, n;\n\t"
+      "fma.rn.f32x2 p, %11, f, %10;\n\t"
+      "fma.rn.f32x2 p, p, f, %9;\n\t"
+      "fma.rn.f32x2 p, p, f, %8;\n\t"
+      "mov.b64 {%0, %1}, t;\n\t"
+      "mov.b64 {%2, %3}, p;\n\t}\n"
+      : "=r"(t0), "=r"(t1), "=r"(q0), "=r"(q1)
+      : "f"(x0), "f"(x1), "l"(k.magic), "l"(k.neg_magic), "l"(k.c0), "l"(k.c1), "l"(k.c2), "l"(k.c3));
+  p0 = __uint_as_float((t0 << 23) + q0);
+  p1 = __uint_as_float((t1 << 23) + q1);
+}
+// 16 columns: p = exp2(s * scale + neg_m) -> 8 packed bf16 pairs, row sums into `acc`.  The first
+// SVOO_POLY_PAIRS of the 8 pairs take the polynomial, the others ex2.approx.
 __device__ __forceinline__ void exp_pack16(const uint32_t (&r)[16], uint32_t* pk, uint64_t scale2, uint64_t negm2,
-                                           uint64_t& acc) {
+                                           const PolyConst& k, uint64_t& acc) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    float x0, x1;
+    float x0, x1, p0, p1;
     fma2(x0, x1, r[2 * i], r[2 * i + 1], scale2, negm2);
-    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    if (i < SVOO_POLY_PAIRS) {
+      exp2_poly2(x0, x1, k, p0, p1);
+    } else {
+      p0 = fast_exp2(x0);
+      p1 = fast_exp2(x1);
+    }
     add2(acc, p0, p1);
     pk[i] = pack_bf16x2(p0, p1);
   }
@@ -246,7 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   if (tid == 0) {
     for (int i = 0; i < NUM_BARS; ++i) {
       int count = 1;
-      if (i == P_READY || i == P_READY + 1) count = kBM;
+      if (i == P_READY || i == P_READY + 1) count = 4;       // one arrival per softmax warp
       mbar_init(bar(i), count);
     }
     *abort_flag = 0;
@@ -389,6 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       const uint32_t o_t = tmem + lane_addr + 256 + w * 128;      // O columns
       float m_used = -INFINITY, l_sum = 0.f;
       bool ok = true;
+      const PolyConst pc = poly_const();
       uint32_t ra[32], rb[32];
       for (int j = 0; j < T; ++j) {
         const int valid = min(L - j * kBN, kBN);
@@ -411,10 +457,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
 #pragma unroll
           for (int c = 0; c < 8; c += 2) {
             tmem_ld16_nowait(s_t + (c + 1) * 16, xb);
-            exp_pack16(xa, &pk[c * 8], scale2, negm2, acc);
+            exp_pack16(xa, &pk[c * 8], scale2, negm2, pc, acc);
             tmem_wait_ld();
             if (c + 2 < 8) tmem_ld16_nowait(s_t + (c + 2) * 16, xa);
-            exp_pack16(xb, &pk[(c + 1) * 8], scale2, negm2, acc);
+            exp_pack16(xb, &pk[(c + 1) * 8], scale2, negm2, pc, acc);
             tmem_wait_ld();
           }
           // every p is at most the tile's row sum: a sum within 2^8 means no score outgrew the
@@ -426,7 +472,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
             l_sum += tile_sum;
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(P_READY + w));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(P_READY + w));
             if (lane == 0) TRACE(w, j, warp & 3);
             continue;
           }
@@ -498,7 +545,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         l_sum += l0 + l1;
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(bar(P_READY + w));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_READY + w));
         if (lane == 0) TRACE(w, j, warp & 3);
       }
       // epilogue: O / l -> bf16 rows
