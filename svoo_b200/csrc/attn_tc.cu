@@ -35,13 +35,13 @@ constexpr int kSmemTiles = 6 * kTile;    // Q0 Q1 | K0 K1 | V0 V1
 constexpr int kMaxRunsSmem = SVOO_MAX_CLUSTERS / 2 + 2;
 constexpr int kRunTableBytes = (kMaxRunsSmem * 8 + 255) / 256 * 256;
 constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 1024;   // + barriers, run table, slack
-#ifndef SVOO_SINGLE_PASS
-#define SVOO_SINGLE_PASS 1
-#endif
 constexpr int kKWarp = 8, kVWarp = 9, kMmaWarp = 10;     // after the 8 softmax warps
 // 11 warps; registers are allotted to a CTA in groups of four warps: 65536 / (12 * 32) = 170.
 constexpr int kThreads = 12 * 32;       // warp 11 only completes the service warpgroup (register hand-over below)
-constexpr int kRegsService = 104, kRegsSoftmax = 200;
+#ifndef SVOO_REGS_SERVICE
+#define SVOO_REGS_SERVICE 104        // 128 * 104 + 256 * 200 = 64512 = the 12 warps' launch allotment
+#endif
+constexpr int kRegsService = SVOO_REGS_SERVICE, kRegsSoftmax = 200;
 constexpr int kBoxHeights = 8;                           // TMA boxes of 1, 2, 4, ..., 128 rows
 
 // Tensor maps of one launch: Q with 128-row boxes; K and V with one map per box height, so a
@@ -62,68 +62,9 @@ struct OutPeers {
 };
 constexpr float kRescaleThreshold = 8.0f;
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, O_DONE = 13, NUM_BARS = 15 };
-
-__device__ __forceinline__ void row_max(const uint32_t (&r)[32], float& m) {
-#pragma unroll
-  for (int i = 0; i < 32; i += 2) m = fmaxf(m, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
-}
-// Only the first `valid` of the 32 columns count (valid may be <= 0 or >= 32).
-__device__ __forceinline__ void row_max_masked(const uint32_t (&r)[32], float& m, int valid) {
-#pragma unroll
-  for (int i = 0; i < 32; ++i) m = fmaxf(m, i < valid ? __uint_as_float(r[i]) : -INFINITY);
-}
-#ifndef SVOO_EXP_BF16X2
-#define SVOO_EXP_BF16X2 0
-#endif
-// Two exponentials per special-function instruction: the arguments are rounded to bf16 first,
-// the results are the bf16 pair that P needs anyway.  An argument x <= 0 carries an absolute error
-// of at most |x| 2^-9, so p is off by at most p |x| ln2 2^-9 <= 7e-4 of the row maximum -- the
-// size of P's own bf16 rounding.  The row sum adds the rounded values, i.e. exactly the weights
-// the PV product uses.
-__device__ __forceinline__ uint32_t ex2_bf16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-// p = exp2(s * scale + neg_m) for 32 columns -> 16 packed bf16 pairs; columns >= valid give 0.
-__device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale, float neg_m,
-                                         float& l0, float& l1, int valid) {
-#if SVOO_EXP_BF16X2
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float x0 = fmaf(__uint_as_float(r[2 * i]), scale, neg_m);
-    const float x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale, neg_m);
-    uint32_t e = ex2_bf16x2(pack_bf16x2(x0, x1));
-    if (valid < 32) e &= (2 * i < valid ? 0x0000ffffu : 0u) | (2 * i + 1 < valid ? 0xffff0000u : 0u);
-    l0 += __uint_as_float(e << 16);
-    l1 += __uint_as_float(e & 0xffff0000u);
-    pk[i] = e;
-  }
-#else
-  if (valid >= 32) {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * i]), scale, neg_m));
-      const float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), scale, neg_m));
-      l0 += p0;
-      l1 += p1;
-      pk[i] = pack_bf16x2(p0, p1);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * i]), scale, neg_m));
-      float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), scale, neg_m));
-      p0 = (2 * i < valid) ? p0 : 0.f;
-      p1 = (2 * i + 1 < valid) ? p1 : 0.f;
-      l0 += p0;
-      l1 += p1;
-      pk[i] = pack_bf16x2(p0, p1);
-    }
-  }
-#endif
-}
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 11, P_FREE = 13, S_FREE = 15, NUM_BARS = 17 };
+// TMEM columns: one S accumulator shared by the two query tiles, then P0, P1 (packed bf16), O0, O1.
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 256;
 
 // Packed fp32 pairs (one instruction for two lanes of data): x = s * scale + neg_m and the
 // running pair of row sums.
@@ -150,59 +91,14 @@ __device__ __forceinline__ float pair_sum(uint64_t acc) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(acc));
   return a + b;
 }
-#ifndef SVOO_POLY_PAIRS
-#define SVOO_POLY_PAIRS 2
-#endif
-// exp2 of a pair on the FMA pipe instead of the special-function unit (which is the scarcer
-// resource of this kernel): x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic with
-// relative error 7.5e-5 (P is rounded to bf16, 4e-3, afterwards); n goes into the exponent field
-// with one shift-add.  Arguments below -126 are clamped (their result flushes to zero either way).
-struct PolyConst {
-  uint64_t magic, neg_magic, c0, c1, c2, c3;
-};
-__device__ __forceinline__ PolyConst poly_const() {
-  PolyConst k;
-  k.magic = pair2(12582912.0f);
-  k.neg_magic = pair2(-12582912.0f);
-  k.c0 = pair2(0.9999280571937561f);
-  k.c1 = pair2(0.6932609677314758f);
-  k.c2 = pair2(0.2426111251115799f);
-  k.c3 = pair2(0.0551716685295105f);
-  return k;
-}
-__device__ __forceinline__ void exp2_poly2(float x0, float x1, const PolyConst& k, float& p0, float& p1) {
-  x0 = fmaxf(x0, -126.0f);
-  x1 = fmaxf(x1, -126.0f);
-  uint32_t t0, t1, q0, q1;
-  asm("{\n\t.reg .b64 x, t, n, f, p;\n\t"
-      "mov.b64 x, {%4, %5};\n\t"
-      "add.rn.f32x2 t, x, %6;\n\t"
-      "add.rn.f32x2 n, t, %7;\n\t"
-      "sub.rn.f32x2 f, x, n;\n\t"
-      "fma.rn.f32x2 p, %11, f, %10;\n\t"
-      "fma.rn.f32x2 p, p, f, %9;\n\t"
-      "fma.rn.f32x2 p, p, f, %8;\n\t"
-      "mov.b64 {%0, %1}, t;\n\t"
-      "mov.b64 {%2, %3}, p;\n\t}\n"
-      : "=r"(t0), "=r"(t1), "=r"(q0), "=r"(q1)
-      : "f"(x0), "f"(x1), "l"(k.magic), "l"(k.neg_magic), "l"(k.c0), "l"(k.c1), "l"(k.c2), "l"(k.c3));
-  p0 = __uint_as_float((t0 << 23) + q0);
-  p1 = __uint_as_float((t1 << 23) + q1);
-}
-// 16 columns: p = exp2(s * scale + neg_m) -> 8 packed bf16 pairs, row sums into `acc`.  The first
-// SVOO_POLY_PAIRS of the 8 pairs take the polynomial, the others ex2.approx.
+// 16 columns: p = exp2(s * scale + neg_m) -> 8 packed bf16 pairs, row sums into `acc`.
 __device__ __forceinline__ void exp_pack16(const uint32_t (&r)[16], uint32_t* pk, uint64_t scale2, uint64_t negm2,
-                                           const PolyConst& k, uint64_t& acc) {
+                                           uint64_t& acc) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    float x0, x1, p0, p1;
+    float x0, x1;
     fma2(x0, x1, r[2 * i], r[2 * i + 1], scale2, negm2);
-    if (i < SVOO_POLY_PAIRS) {
-      exp2_poly2(x0, x1, k, p0, p1);
-    } else {
-      p0 = fast_exp2(x0);
-      p1 = fast_exp2(x1);
-    }
+    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
     add2(acc, p0, p1);
     pk[i] = pack_bf16x2(p0, p1);
   }
@@ -291,7 +187,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   if (tid == 0) {
     for (int i = 0; i < NUM_BARS; ++i) {
       int count = 1;
-      if (i == P_READY || i == P_READY + 1) count = 4;       // one arrival per softmax warp
+      if (i == P_READY || i == P_READY + 1 || i == S_FREE || i == S_FREE + 1) count = 4;   // one arrival per softmax warp
       mbar_init(bar(i), count);
     }
     *abort_flag = 0;
@@ -306,6 +202,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (tid == 0) TRACE(7, 0, 0);
+#ifdef SVOO_TRACE
+  if (tid == 0 && blockIdx.x == SVOO_TRACE && blockIdx.y == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    g_trace[(7 * 64 + 2) * 4 + 0] = (long long)ns;
+  }
+#endif
   const int L = runs_s[nr].y;                      // selected key rows in total
   const int T = (L + kBN - 1) / kBN;               // packed key tiles
 
@@ -356,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t off = ((ks >> 2) * kBox + (ks & 3) * 32) >> 4;
-          umma_ss_lo(tmem + w * 128, q_lo + ((w * kTile) >> 4) + off, k_lo + ((st * kTile) >> 4) + off, kDescHi, kIdescQK,
+          umma_ss_lo(tmem + kColS, q_lo + ((w * kTile) >> 4) + off, k_lo + ((st * kTile) >> 4) + off, kDescHi, kIdescQK,
                      ks > 0);
         }
       };
@@ -364,61 +268,81 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         constexpr int w = decltype(wc)::value, st = decltype(sc)::value;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts_lo(tmem + 256 + w * 128, tmem + w * 128 + ks * 8, v_lo + ((st * kTile + ks * 2048) >> 4), kDescHi, kIdescPV,
-                     (accumulate || ks > 0) ? 1u : 0u);
+          umma_ts_lo(tmem + kColO + w * 128, tmem + kColP + w * 64 + ks * 8, v_lo + ((st * kTile + ks * 2048) >> 4), kDescHi,
+                     kIdescPV, (accumulate || ks > 0) ? 1u : 0u);
       };
       using I0 = std::integral_constant<int, 0>;
       using I1 = std::integral_constant<int, 1>;
+      // The softmax jobs run in the order (tile 0, query tile 0), (0, 1), (1, 0), (1, 1), ...  Job n
+      // copies S into registers and frees it at once (S_FREE), so the QK of job n + 1 is issued
+      // while job n is still computing; the PV of job n - 1 follows when its P is complete.
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
       if (ok) {
         tc_fence_after();
+        TRACE(7, 0, 1);
         issue_qk(I0{}, I0{});
         tc_commit(bar(S_FULL));
-        if (nq > 1) { issue_qk(I1{}, I0{}); tc_commit(bar(S_FULL + 1)); }
-        tc_commit(bar(K_EMPTY));
+        if (nq == 1) tc_commit(bar(K_EMPTY));
       }
-      // one key tile: PV of both query tiles on stage `st`, QK of the next tile on the other stage
-      auto tile = [&](auto sc, int j) -> bool {
-        constexpr int st = decltype(sc)::value, sn = st ^ 1;
-        using SN = std::integral_constant<int, sn>;
-        const bool has_next = j + 1 < T;
-        const uint32_t ph = (j >> 1) & 1, phn = ((j + 1) >> 1) & 1;
-        TRACE(7, j, 0);
-        if (!mbar_wait(bar(V_FULL + st), ph, abort_flag)) return false;
-        TRACE(7, j, 1);
-        if (!mbar_wait(bar(P_READY), j & 1, abort_flag)) return false;
-        TRACE(2, j, 0);
+      // PV of (query tile w, key tile j) on V stage `st`
+      auto pv = [&](auto wc, auto sc, int j) -> bool {
+        constexpr int w = decltype(wc)::value, st = decltype(sc)::value;
+        if (w == 0 && !mbar_wait(bar(V_FULL + st), (j >> 1) & 1, abort_flag)) return false;
+        if (!mbar_wait(bar(P_READY + w), j & 1, abort_flag)) return false;
+        TRACE(2, j, w);
         tc_fence_after();
-        issue_pv(I0{}, sc, j > 0);
-        if (!has_next) tc_commit(bar(O_DONE));          // only the last PV needs its own signal (see the rescale path)
-        if (has_next) {
-          TRACE(7, j, 2);
-          if (!mbar_wait(bar(K_FULL + sn), phn, abort_flag)) return false;
-          TRACE(7, j, 3);
-          tc_fence_after();
-          issue_qk(I0{}, SN{});
-          tc_commit(bar(S_FULL));
-          TRACE(2, j, 2);
-        }
-        if (nq > 1) {
-          if (!mbar_wait(bar(P_READY + 1), j & 1, abort_flag)) return false;
-          TRACE(2, j, 1);
-          tc_fence_after();
-          issue_pv(I1{}, sc, j > 0);
-          if (!has_next) tc_commit(bar(O_DONE + 1));
-          if (has_next) {
-            issue_qk(I1{}, SN{});
-            tc_commit(bar(S_FULL + 1));
-            TRACE(2, j, 3);
-          }
-        }
-        tc_commit(bar(V_EMPTY + st));
-        if (has_next) tc_commit(bar(K_EMPTY + sn));
+        issue_pv(wc, sc, j > 0);
+        tc_commit(bar(P_FREE + w));
+        if (w == nq - 1) tc_commit(bar(V_EMPTY + st));
         return true;
       };
-      for (int j = 0; ok && j < T; j += 2) {
-        ok = tile(I0{}, j);
-        if (ok && j + 1 < T) ok = tile(I1{}, j + 1);
+      if (nq == 2) {
+        auto tile2 = [&](auto sc, int j) -> bool {
+          constexpr int st = decltype(sc)::value, sn = st ^ 1;
+          using SN = std::integral_constant<int, sn>;
+          // job (j, 0) has taken its S: QK of (j, 1); then PV of (j - 1, 1)
+          if (!mbar_wait(bar(S_FREE), j & 1, abort_flag)) return false;
+          tc_fence_after();
+          issue_qk(I1{}, sc);
+          tc_commit(bar(S_FULL + 1));
+          tc_commit(bar(K_EMPTY + st));
+          TRACE(2, j, 2);
+          if (j > 0 && !pv(I1{}, SN{}, j - 1)) return false;
+          // job (j, 1) has taken its S: QK of (j + 1, 0); then PV of (j, 0)
+          if (j + 1 < T) {
+            if (!mbar_wait(bar(S_FREE + 1), j & 1, abort_flag)) return false;
+            if (!mbar_wait(bar(K_FULL + sn), ((j + 1) >> 1) & 1, abort_flag)) return false;
+            tc_fence_after();
+            issue_qk(I0{}, SN{});
+            tc_commit(bar(S_FULL));
+            TRACE(2, j, 3);
+          }
+          return pv(I0{}, sc, j);
+        };
+        for (int j = 0; ok && j < T; j += 2) {
+          ok = tile2(I0{}, j);
+          if (ok && j + 1 < T) ok = tile2(I1{}, j + 1);
+        }
+        if (ok) ok = ((T - 1) & 1) ? pv(I1{}, I1{}, T - 1) : pv(I1{}, I0{}, T - 1);
+      } else {
+        auto tile1 = [&](auto sc, int j) -> bool {
+          constexpr int st = decltype(sc)::value, sn = st ^ 1;
+          using SN = std::integral_constant<int, sn>;
+          if (j + 1 < T) {
+            if (!mbar_wait(bar(S_FREE), j & 1, abort_flag)) return false;
+            if (!mbar_wait(bar(K_FULL + sn), ((j + 1) >> 1) & 1, abort_flag)) return false;
+            tc_fence_after();
+            issue_qk(I0{}, SN{});
+            tc_commit(bar(S_FULL));
+            tc_commit(bar(K_EMPTY + sn));
+          }
+          return j > 0 ? pv(I0{}, SN{}, j - 1) : true;
+        };
+        for (int j = 0; ok && j < T; j += 2) {
+          ok = tile1(I0{}, j);
+          if (ok && j + 1 < T) ok = tile1(I1{}, j + 1);
+        }
+        if (ok) ok = ((T - 1) & 1) ? pv(I0{}, I1{}, T - 1) : pv(I0{}, I0{}, T - 1);
       }
     }
   }
@@ -430,125 +354,98 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       const int quad = warp & 3;
       const int r_local = quad * 32 + lane;                       // row of the query tile == TMEM lane
       const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-      const uint32_t s_t = tmem + lane_addr + w * 128;            // S (and P) columns
-      const uint32_t o_t = tmem + lane_addr + 256 + w * 128;      // O columns
+      const uint32_t s_t = tmem + lane_addr + kColS;              // S, shared with the other query tile
+      const uint32_t p_t = tmem + lane_addr + kColP + w * 64;     // P of this query tile (packed bf16)
+      const uint32_t o_t = tmem + lane_addr + kColO + w * 128;    // O of this query tile
       float m_used = -INFINITY, l_sum = 0.f;
       bool ok = true;
-      const PolyConst pc = poly_const();
-      uint32_t ra[32], rb[32];
+      const uint64_t scale2 = pair2(scale_log2);
       for (int j = 0; j < T; ++j) {
         const int valid = min(L - j * kBN, kBN);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + w), j & 1, abort_flag));
         if (lane == 0) TRACE(5 + w, j, warp & 3);
         if (!ok) break;
         tc_fence_after();
-        if (SVOO_SINGLE_PASS && j > 0 && valid >= kBN) {
-          // Common case, one TMEM pass: exponentials are taken against the running maximum of
-          // the previous tiles and kept in registers; they are stored only if no row of the
-          // warp outgrew that maximum by more than 2^8, otherwise the two-pass path redoes the tile.
-          // Scale-and-subtract and the row sums run as packed fp32 pairs, so the special-function
-          // unit (two ex2 per pair), not instruction issue, bounds the tile.
-          const uint64_t scale2 = pair2(scale_log2), negm2 = pair2(-m_used);
-          uint64_t acc = 0;                                // two fp32 zeros
-          uint32_t pk[64];
-          uint32_t xa[16], xb[16];
-          tmem_ld16_nowait(s_t, xa);
-          tmem_wait_ld();
+        // the whole score row goes to registers; S is handed back at once so that the tensor pipe
+        // can compute the next score tile (of the other query tile) while this one is processed
+        uint32_t sc[128];
 #pragma unroll
-          for (int c = 0; c < 8; c += 2) {
-            tmem_ld16_nowait(s_t + (c + 1) * 16, xb);
-            exp_pack16(xa, &pk[c * 8], scale2, negm2, pc, acc);
-            tmem_wait_ld();
-            if (c + 2 < 8) tmem_ld16_nowait(s_t + (c + 2) * 16, xa);
-            exp_pack16(xb, &pk[(c + 1) * 8], scale2, negm2, pc, acc);
-            tmem_wait_ld();
-          }
-          // every p is at most the tile's row sum: a sum within 2^8 means no score outgrew the
-          // running maximum by more than 8 (an overflow to inf or a NaN fails the test as well)
-          const float tile_sum = pair_sum(acc);
-          if (__all_sync(0xffffffffu, tile_sum <= 256.0f)) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_st16(s_t + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[c * 16]));
-            l_sum += tile_sum;
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(P_READY + w));
-            if (lane == 0) TRACE(w, j, warp & 3);
-            continue;
-          }
-        }
-        // pass 1: row maximum of the raw scores (the scale is positive), two loads in flight
-        float m_raw = -INFINITY;
-        tmem_ld32_nowait(s_t, ra);
-        tmem_ld32_nowait(s_t + 32, rb);
+        for (int c = 0; c < 4; ++c) tmem_ld32_nowait(s_t + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sc[c * 32]));
         tmem_wait_ld();
-        if (valid >= kBN) {
-          row_max(ra, m_raw);
-          row_max(rb, m_raw);
-          tmem_ld32_nowait(s_t + 64, ra);
-          tmem_ld32_nowait(s_t + 96, rb);
-          tmem_wait_ld();
-          row_max(ra, m_raw);
-          row_max(rb, m_raw);
-        } else {
-          row_max_masked(ra, m_raw, valid);
-          row_max_masked(rb, m_raw, valid - 32);
-          tmem_ld32_nowait(s_t + 64, ra);
-          tmem_ld32_nowait(s_t + 96, rb);
-          tmem_wait_ld();
-          row_max_masked(ra, m_raw, valid - 64);
-          row_max_masked(rb, m_raw, valid - 96);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(S_FREE + w));
+        if (valid < kBN) {                                        // last tile only: columns past the last key
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (i >= valid) sc[i] = 0xff800000u;
         }
-        const float m_tile = m_raw * scale_log2;
+        float mr[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 128; i += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mr[u] = fmaxf(mr[u], fmaxf(__uint_as_float(sc[i + 2 * u]), __uint_as_float(sc[i + 2 * u + 1])));
+        }
+        const float m_tile = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * scale_log2;   // the scale is positive
+        bool pv_done = (j == 0);                                  // PV of the previous tile complete (O and P free)
         if (j == 0) {
           m_used = m_tile;
         } else {
+          // O is rescaled only when a row maximum grows by more than 2^8; the running sum keeps
+          // the same stale maximum, so O / l stays exact
           const bool need = m_tile > m_used + kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
-            // S_FULL of this tile was committed after the PV of the previous tile by the same thread,
-            // and a commit tracks every earlier tcgen05 operation of that thread: O is complete here.
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P_FREE + w), (j - 1) & 1, abort_flag));
+            if (!ok) break;
+            tc_fence_after();
+            pv_done = true;
             const float alpha = need ? fast_exp2(m_used - m_tile) : 1.0f;
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-              tmem_ld32(o_t + ch * 32, ra);
+            for (int ch = 0; ch < 8; ++ch) {
+              uint32_t t[16];
+              tmem_ld16_nowait(o_t + ch * 16, t);
+              tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
-              tmem_st32(o_t + ch * 32, ra);
+              for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+              tmem_st16(o_t + ch * 16, t);
             }
             tmem_wait_st();
             l_sum *= alpha;
             if (need) m_used = m_tile;
           }
         }
-        // pass 2: P = exp2(s * scale - m) as packed bf16 over the first 64 columns of S; the
-        // load of the next 32 columns is in flight while the current 32 are processed
-        const float neg_m = -m_used;
-        float l0 = 0.f, l1 = 0.f;
-        uint32_t pk[16];
-        tmem_ld32_nowait(s_t, ra);
-        tmem_wait_ld();
-        tmem_ld32_nowait(s_t + 32, rb);
-        exp_pack(ra, pk, scale_log2, neg_m, l0, l1, valid);
-        tmem_st16(s_t, pk);
-        tmem_wait_ld();
-        tmem_ld32_nowait(s_t + 64, ra);
-        exp_pack(rb, pk, scale_log2, neg_m, l0, l1, valid - 32);
-        tmem_st16(s_t + 16, pk);
-        tmem_wait_ld();
-        tmem_ld32_nowait(s_t + 96, rb);
-        exp_pack(ra, pk, scale_log2, neg_m, l0, l1, valid - 64);
-        tmem_st16(s_t + 32, pk);
-        tmem_wait_ld();
-        exp_pack(rb, pk, scale_log2, neg_m, l0, l1, valid - 96);
-        tmem_st16(s_t + 48, pk);
-        l_sum += l0 + l1;
+        // P = exp2(s * scale - m) as packed bf16.  The first half is kept in registers until the PV
+        // of the previous tile (which reads the same P columns) is known to be complete.
+        const uint64_t negm2 = pair2(-m_used);
+        uint64_t acc = 0;                                         // two fp32 zeros
+        uint32_t pkh[32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          exp_pack16(*reinterpret_cast<const uint32_t(*)[16]>(&sc[c * 16]), &pkh[c * 8], scale2, negm2, acc);
+        if (!pv_done) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bar(P_FREE + w), (j - 1) & 1, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+        }
+        tmem_st16(p_t, *reinterpret_cast<uint32_t(*)[16]>(&pkh[0]));
+        tmem_st16(p_t + 16, *reinterpret_cast<uint32_t(*)[16]>(&pkh[16]));
+#pragma unroll
+        for (int c = 4; c < 8; c += 2) {
+          uint32_t pk[16];
+          exp_pack16(*reinterpret_cast<const uint32_t(*)[16]>(&sc[c * 16]), &pk[0], scale2, negm2, acc);
+          exp_pack16(*reinterpret_cast<const uint32_t(*)[16]>(&sc[(c + 1) * 16]), &pk[8], scale2, negm2, acc);
+          tmem_st16(p_t + c * 8, pk);
+        }
+        l_sum += pair_sum(acc);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_READY + w));
         if (lane == 0) TRACE(w, j, warp & 3);
       }
+      uint32_t ra[32];
+      if (tid == 0) TRACE(7, 0, 2);
       // epilogue: O / l -> bf16 rows
       const int row = row0 + w * kBM + r_local;
       const bool store = row < row1;
@@ -567,7 +464,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
 #pragma unroll
           for (int ch = 0; ch < 16; ++ch) reinterpret_cast<uint4*>(orow)[ch] = make_uint4(0, 0, 0, 0);
         }
-      } else if (ok && __all_sync(0xffffffffu, mbar_wait(bar(O_DONE + w), 0, abort_flag))) {
+      } else if (ok && __all_sync(0xffffffffu, mbar_wait(bar(P_FREE + w), (T - 1) & 1, abort_flag))) {
         tc_fence_after();
         const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
 #pragma unroll 1
@@ -589,8 +486,17 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     }
   }
   // ------------------------------------------------------------------ teardown
+  if (tid == 0) TRACE(7, 0, 3);
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) TRACE(7, 1, 0);
+#ifdef SVOO_TRACE
+  if (tid == 0 && blockIdx.x == SVOO_TRACE && blockIdx.y == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    g_trace[(7 * 64 + 2) * 4 + 1] = (long long)ns;
+  }
+#endif
   if (tid == 0 && *abort_flag) atomicExch(status, 1);
   if (warp == kMmaWarp) {
     tc_fence_after();
@@ -611,6 +517,9 @@ cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, v
                                   int32_t* status, int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale,
                                   void* const* peer_dst, const int32_t* my_heads, int world, int64_t n_loc, int H,
                                   cudaStream_t st) {
+  // a build whose register hand-over does not add up (the spill-check build) must never launch:
+  // its softmax warps would wait for registers that nobody frees
+  if (128 * tc::kRegsService + 256 * tc::kRegsSoftmax > 168 * tc::kThreads) return cudaErrorInvalidConfiguration;
   tc::OutPeers peers{};
   if (peer_dst) {
     for (int p = 0; p < world; ++p) peers.dst[p] = (bf16*)peer_dst[p];
