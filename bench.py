@@ -338,6 +338,7 @@ def run_gpu_arm(args, cfg):
             "e2e": {"value": flops_total / (e2e_ms / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
             "gpu_launches": int(launches),
+            "exchange_status": (xchg.status() if xchg else 0),
             "clocks": clocks.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:

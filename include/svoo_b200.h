@@ -40,6 +40,7 @@ enum {
 
 #define SVOO_MAX_CLUSTERS 1024   /* per side; the reference ships QC=256, KC=1024 */
 #define SVOO_MAX_HEADS 256       /* BH limit of svoo_b200_block_map              */
+#define SVOO_BARRIER_CHANNELS 4  /* independent flag sets of svoo_b200_peer_barrier */
 
 int svoo_b200_version(void);
 const char* svoo_b200_error_string(int code);
@@ -198,6 +199,17 @@ int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* ow
                          int32_t world, int32_t rank, int64_t n_loc, int64_t H, int64_t D, void* stream);
 int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int32_t world, int64_t n_loc,
                        int64_t H, int64_t D, void* stream);
+
+/* Barrier over the ranks of one node, as a kernel on `stream`: publishes this rank's earlier
+ * peer stores on that stream and waits (at most ~2 s) for the same call of every other rank.
+ * peer_flags: HOST array of `world` device pointers, entry p = rank p's flag array of
+ * SVOO_BARRIER_CHANNELS * 16 uint32 words (zeroed before the first call, mapped into every
+ * process).  `epoch` must grow by one per call and be the same on all ranks for the same
+ * call; calls that may overlap in time (different streams) use different channels.  *status
+ * (device int32) is set to 1 if a rank did not arrive in time.  Every rank runs its call on
+ * its own GPU.  No counterpart in the reference (one GPU). */
+int svoo_b200_peer_barrier(void* const* peer_flags, int32_t world, int32_t rank, int32_t channel, uint32_t epoch,
+                           int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

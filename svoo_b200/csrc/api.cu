@@ -26,6 +26,7 @@ cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, void*,
 cudaError_t launch_push_heads(const void*, void* const*, const int32_t*, const int32_t*, int, int, int64_t, int,
                               cudaStream_t);
 cudaError_t launch_push_seq(const void*, void* const*, const int32_t*, int, int64_t, int, int, cudaStream_t);
+cudaError_t launch_peer_barrier(void* const*, int, int, int, uint32_t, int32_t*, cudaStream_t);
 }  // namespace svoo
 
 namespace svoo {
@@ -336,6 +337,17 @@ int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_h
     seen[my_heads[i]] = true;
   }
   SVOO_CUDA(launch_push_seq(y, peer_dst, my_heads, world, n_loc, (int)H, (int)hr, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_peer_barrier(void* const* peer_flags, int32_t world, int32_t rank, int32_t channel, uint32_t epoch,
+                           int32_t* status, void* stream) {
+  if (!peer_flags || !status) return SVOO_ERR_NULL;
+  if (world < 1 || world > 16 || rank < 0 || rank >= world || channel < 0 || channel >= SVOO_BARRIER_CHANNELS)
+    return SVOO_ERR_SHAPE;
+  for (int p = 0; p < world; ++p)
+    if (!peer_flags[p]) return SVOO_ERR_NULL;
+  SVOO_CUDA(launch_peer_barrier(peer_flags, world, rank, channel * 16, epoch, status, (cudaStream_t)stream));
   return SVOO_OK;
 }
 

@@ -80,6 +80,48 @@ __global__ void __launch_bounds__(256) push_seq_kernel(const uint4* __restrict__
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Barrier over the ranks of one node through flag words in peer-mapped memory: lane p stores this
+// rank's epoch into rank p's flag array and then waits until rank p's epoch has arrived in its own.
+// Launched after the kernels whose stores it publishes, on the same stream: a kernel's stores to
+// peer memory are performed when it completes, the release store of the flag comes after that,
+// and the acquire load on the other side orders the reader's later kernels behind it.
+// Each rank runs this kernel on its own GPU.  The wait is bounded (~2 s of clock64); on expiry the
+// status word is set and the kernel returns, so a missing rank cannot hang the others.
+// ---------------------------------------------------------------------------------------------
+struct PeerFlagTable {
+  uint32_t* flags[kMaxPeers];
+};
+constexpr long long kBarrierCycles = 4000000000LL;
+
+__global__ void peer_barrier_kernel(const __grid_constant__ PeerFlagTable tab, int rank, int world, int slot0,
+                                    uint32_t epoch, int32_t* __restrict__ status) {
+  const int p = threadIdx.x;
+  if (p >= world) return;
+  uint32_t* remote = tab.flags[p] + slot0 + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const uint32_t* mine = tab.flags[rank] + slot0 + p;
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if ((int32_t)(seen - epoch) >= 0) break;             // epochs only grow; the difference is wrap-safe
+    if (clock64() - t0 > kBarrierCycles) {
+      atomicExch(status, 1);
+      break;
+    }
+  }
+}
+
+cudaError_t launch_peer_barrier(void* const* peer_flags, int world, int rank, int slot0, uint32_t epoch, int32_t* status,
+                                cudaStream_t st) {
+  PeerFlagTable tab{};
+  for (int p = 0; p < world; ++p) tab.flags[p] = (uint32_t*)peer_flags[p];
+  peer_barrier_kernel<<<1, 32, 0, st>>>(tab, rank, world, slot0, epoch, status);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
 static int exchange_grid() {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);

@@ -120,7 +120,8 @@ def exchange_tables(parts: List[List[int]]) -> Tuple[List[int], List[int]]:
 class PeerExchange:
     """The two re-shardings of the layer as stores into the peers' memory (one kernel launch
     per tensor, no library all-to-all).  The receive arrays live in symmetric memory that
-    every rank of the group maps; a one-element all-reduce on the launching stream is the
+    every rank of the group maps; a flag barrier kernel on the launching stream
+    (svoo_b200_peer_barrier; `fence="nccl"` selects a one-element all-reduce instead) is the
     ordering point between "my stores are issued" and "my array is complete".
 
     Per layer call: push q, k -> fence -> clustering ... attention -> push out -> fence; V is
@@ -128,7 +129,8 @@ class PeerExchange:
     `value_ready` before its first use.  A rank passes a fence only after every peer has
     finished the previous call, so the receive arrays are reused without further ordering."""
 
-    def __init__(self, parts: List[List[int]], n_tokens: int, device, group=None, head_dim: int = 128):
+    def __init__(self, parts: List[List[int]], n_tokens: int, device, group=None, head_dim: int = 128,
+                 fence: str = "flags"):
         import ctypes
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
@@ -152,12 +154,36 @@ class PeerExchange:
         self._slot = (ctypes.c_int32 * self.H)(*slot)
         self._mine = (ctypes.c_int32 * self.hr)(*parts[self.rank])
         self._flag = torch.zeros(2, dtype=torch.int32, device=device)
-        self._handles = (h_in, h_out)
+        if fence not in ("flags", "nccl"):
+            raise ValueError("fence must be 'flags' or 'nccl'")
+        self._fence_kind = fence
+        self._flags = symm_mem.empty((64,), dtype=torch.int32, device=device)     # 4 channels x 16 ranks
+        self._flags.zero_()
+        h_flags = symm_mem.rendezvous(self._flags, self.group)
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in h_flags.buffer_ptrs])
+        self._epoch = [0, 0, 0, 0]
+        self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)                       # every rank's flags are zero before the first epoch
+        self._handles = (h_in, h_out, h_flags)
         self._side = torch.cuda.Stream(device)
         self.value_ready: Optional[torch.cuda.Event] = None
 
     def fence(self, which: int = 0):
-        dist.all_reduce(self._flag[which:which + 1], group=self.group)
+        """Orders this rank's earlier peer stores on the current stream before every rank's later
+        kernels.  Channel `which` must be used from one stream at a time."""
+        if self._fence_kind == "nccl":
+            dist.all_reduce(self._flag[which:which + 1], group=self.group)
+            return
+        from . import _lib
+        self._epoch[which] += 1
+        stream = torch.cuda.current_stream(self._status.device).cuda_stream
+        _lib.check(_lib.LIB.svoo_b200_peer_barrier(self._flag_ptrs, self.world, self.rank, which, self._epoch[which],
+                                                   self._status.data_ptr(), stream), "peer_barrier")
+
+    def status(self) -> int:
+        """Non-zero if a flag barrier gave up waiting for a rank (synchronises)."""
+        return int(self._status.item())
 
     def _push_heads(self, t: int, x: torch.Tensor, stream: int):
         from . import _lib

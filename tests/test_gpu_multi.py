@@ -48,6 +48,11 @@ assert torch.equal(outs[0], outs[1]), "fused peer store differs from push_seq"
 out = outs[1]
 ref = layer.sparse_attention_layer(q, k, v, min_kc_ratio=dens, max_kc_ratio=dens, init_indices=(qi.to(dev), ki.to(dev)), **kw)
 assert torch.equal(out, shard(ref)), "sharded layer differs from the one-GPU layer"
+assert x.status() == 0, "a flag barrier timed out"
+y = parallel.PeerExchange(parts, N, dev, fence="nccl")
+out2 = parallel.sparse_attention_layer_sharded(qs, ks, vs, parts, densities=dens, init_indices=(qi.to(dev), ki.to(dev)),
+                                               exchange=y, **kw)
+assert torch.equal(out2, out), "NCCL-fenced run differs from the flag-fenced run"
 torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
 print("OK", rank)
 '''

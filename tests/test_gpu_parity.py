@@ -335,6 +335,34 @@ def test_tensor_core_kernel_against_mma_sync_kernel(dev):
     assert (a[0, rows] == 0).all()
 
 
+@pytest.mark.parametrize("direction", ["rising", "falling"])
+def test_sparse_attention_with_drifting_row_maxima(dev, direction):
+    """Scores that grow (or shrink) by several powers of two from one key tile to the next: the
+    running row maximum is outgrown again and again, so the accumulator in tensor memory has to be
+    rescaled between tiles (rising), or almost every later exponential underflows (falling)."""
+    ops = _mods()[0]
+    g = torch.Generator("cpu").manual_seed(33)
+    H, S = 2, 2304
+    u = torch.randn(128, generator=g)
+    u = u / u.norm() * 128 ** 0.5
+    ramp = torch.linspace(0.0, 4.0, S) if direction == "rising" else torch.linspace(4.0, 0.0, S)
+    q = (u + 0.1 * torch.randn(1, H, S, 128, generator=g)).bfloat16()
+    k = (ramp[:, None] * u + 0.3 * torch.randn(1, H, S, 128, generator=g)).bfloat16()
+    v = torch.randn(1, H, S, 128, generator=g).bfloat16()
+    q_sizes, k_sizes = [256, 300, 1748], [1152, 1152]
+    m = torch.ones(1, H, 3, 2, dtype=torch.bool)
+    m[:, :, 1, 0] = False
+    qs = torch.tensor(q_sizes, dtype=torch.int32).expand(1, H, -1).contiguous()
+    ks = torch.tensor(k_sizes, dtype=torch.int32).expand(1, H, -1).contiguous()
+    ref = O.block_sparse_attention(q, k, v, m, qs, ks)
+    got = ops.sparse_attn(q[0].to(dev), k[0].to(dev), v[0].to(dev), m[0].to(dev).view(torch.uint8),
+                          ops.offsets_from_sizes(qs[0].to(dev)), ops.offsets_from_sizes(ks[0].to(dev)))
+    assert ops.attention_status(dev, H, S, 3, 2) == 0
+    assert torch.isfinite(got.float()).all()
+    assert (got.cpu().float() - ref[0].float()).abs().max() <= ATTN_ATOL
+    assert cosine(got.cpu(), ref[0]) >= ATTN_COS
+
+
 @pytest.mark.parametrize("kernel", ["tcgen05", "simt"])
 def test_both_attention_kernels_against_oracle(dev, kernel):
     ops = _mods()[0]
