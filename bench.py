@@ -250,9 +250,9 @@ def run_gpu_arm(args, cfg):
         dev_in = [torch.empty_like(t, device=dev) for t in host_in]
 
         def step_e2e():
-            for d_t, h_t in zip(dev_in, host_in):
+            for d_t, h_t in zip(dev_in[:2], host_in[:2]):
                 d_t.copy_(h_t, non_blocking=True)
-            q, k, v = (t[None] for t in xchg.to_heads(*dev_in))
+            q, k, v = (t[None] for t in xchg.to_heads(*dev_in, v_host=host_in[2]))    # V is copied behind the clustering
             out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki),
                                                value_ready=xchg.value_ready, peer_out=xchg.peer_out, **kw)
             host_out.copy_(xchg.seq_result(), non_blocking=True)

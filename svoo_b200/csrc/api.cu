@@ -6,9 +6,9 @@ namespace svoo {
 cudaError_t launch_gather_rows(const void*, const int32_t*, void*, int64_t, int64_t, int64_t, cudaStream_t);
 cudaError_t launch_prologue(const void*, const void*, void*, void*, int64_t, int64_t, int64_t, cudaStream_t);
 cudaError_t launch_assign_tc(const void*, const void*, const void*, int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t,
-                             cudaStream_t);
+                             int32_t*, cudaStream_t);
 cudaError_t launch_sort_labels(const int32_t*, int64_t, int64_t, int64_t, int32_t*, int32_t*, int32_t*, int32_t*,
-                               cudaStream_t);
+                               cudaStream_t, bool);
 cudaError_t launch_centroid_update(const void*, const int32_t*, const int32_t*, const void*, void*, int32_t*, float*,
                                    int64_t, int64_t, int64_t, cudaStream_t);
 cudaError_t launch_offsets_from_sizes(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
@@ -103,7 +103,8 @@ int svoo_b200_cocluster_assign(const void* x, const void* form_centroids, const 
                             ws_at<void>(workspace, w.w_lo), BH, J, K, st));
   SVOO_CUDA(cudaMemsetAsync(ws_at<int32_t>(workspace, w.status) + 1, 0, 4, st));
   SVOO_CUDA(launch_assign_tc(x, ws_at<void>(workspace, w.w_hi), ws_at<void>(workspace, w.w_lo), labels,
-                             ws_at<int2>(workspace, w.assign_partial), ws_at<int32_t>(workspace, w.status) + 1, BH, N, J, st));
+                             ws_at<int2>(workspace, w.assign_partial), ws_at<int32_t>(workspace, w.status) + 1, BH, N, J, nullptr,
+                             st));
   return SVOO_OK;
 }
 
@@ -115,7 +116,7 @@ int svoo_b200_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int64_t 
   const Workspace w = workspace_layout(BH, N, K, K);
   if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
   SVOO_CUDA(launch_sort_labels(labels, BH, N, K, sorted_idx, offsets, nullptr, ws_at<int32_t>(workspace, w.chunk_hist),
-                               (cudaStream_t)stream));
+                               (cudaStream_t)stream, false));
   return SVOO_OK;
 }
 
@@ -164,13 +165,13 @@ int svoo_b200_cocluster(const void* q, const void* k, const int32_t* q_init_idx,
   for (int it = 0; it < iters; ++it) {
     // keys: profile over the query centroids
     SVOO_CUDA(launch_prologue(kcentroids, qcentroids, w_hi, w_lo, BH, KC, QC, st));
-    SVOO_CUDA(launch_assign_tc(k, w_hi, w_lo, klabels, apart, status, BH, N, KC, st));
-    SVOO_CUDA(launch_sort_labels(klabels, BH, N, KC, k_sorted_idx, k_offsets, nullptr, hist, st));
+    SVOO_CUDA(launch_assign_tc(k, w_hi, w_lo, klabels, apart, status, BH, N, KC, hist, st));
+    SVOO_CUDA(launch_sort_labels(klabels, BH, N, KC, k_sorted_idx, k_offsets, nullptr, hist, st, true));
     SVOO_CUDA(launch_centroid_update(k, k_sorted_idx, k_offsets, kcentroids, kcentroids, ksizes, partial, BH, N, KC, st));
     // queries: profile over the just-updated key centroids
     SVOO_CUDA(launch_prologue(qcentroids, kcentroids, w_hi, w_lo, BH, QC, KC, st));
-    SVOO_CUDA(launch_assign_tc(q, w_hi, w_lo, qlabels, apart, status, BH, N, QC, st));
-    SVOO_CUDA(launch_sort_labels(qlabels, BH, N, QC, q_sorted_idx, q_offsets, nullptr, hist, st));
+    SVOO_CUDA(launch_assign_tc(q, w_hi, w_lo, qlabels, apart, status, BH, N, QC, hist, st));
+    SVOO_CUDA(launch_sort_labels(qlabels, BH, N, QC, q_sorted_idx, q_offsets, nullptr, hist, st, true));
     SVOO_CUDA(launch_centroid_update(q, q_sorted_idx, q_offsets, qcentroids, qcentroids, qsizes, partial, BH, N, QC, st));
   }
   return SVOO_OK;

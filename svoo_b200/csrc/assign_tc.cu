@@ -228,6 +228,36 @@ __global__ void __launch_bounds__(256) assign_reduce_kernel(const int2* __restri
   labels[i] = b.y;
 }
 
+// The same reduction fused with the first pass of the label sort: one CTA per (2048-token chunk,
+// head) also leaves the chunk's label histogram, which saves a kernel and a second read of the labels.
+__global__ void __launch_bounds__(256) assign_reduce_hist_kernel(const int2* __restrict__ partial,
+                                                                 int32_t* __restrict__ labels,
+                                                                 int32_t* __restrict__ chunk_hist, int BH, int N, int K,
+                                                                 int groups, int nchunks) {
+  __shared__ int hist[SVOO_MAX_CLUSTERS];
+  const int bh = blockIdx.y, chunk = blockIdx.x;
+  for (int k = threadIdx.x; k < K; k += 256) hist[k] = 0;
+  __syncthreads();
+  const int64_t BHN = (int64_t)BH * N;
+  const int base = chunk * kSortChunk;
+  for (int t = threadIdx.x; t < kSortChunk; t += 256) {
+    const int n = base + t;
+    if (n < N) {
+      const int64_t i = (int64_t)bh * N + n;
+      int2 b = partial[i];
+      for (int g = 1; g < groups; ++g) {
+        const int2 c = partial[(int64_t)g * BHN + i];
+        if (__int_as_float(c.x) > __int_as_float(b.x)) b = c;
+      }
+      labels[i] = b.y;
+      if (b.y >= 0 && b.y < K) atomicAdd(&hist[b.y], 1);
+    }
+  }
+  __syncthreads();
+  int32_t* out = chunk_hist + ((int64_t)bh * nchunks + chunk) * K;
+  for (int k = threadIdx.x; k < K; k += 256) out[k] = hist[k];
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -278,15 +308,22 @@ static cudaError_t launch_assign_tc_jb(const void* x, const void* w_hi, const vo
   return cudaGetLastError();
 }
 
+// chunk_hist != nullptr: also write the per-chunk label histograms of the sort (its first pass).
 cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int2* partial,
-                             int32_t* status, int64_t BH, int64_t N, int64_t J, cudaStream_t st) {
+                             int32_t* status, int64_t BH, int64_t N, int64_t J, int32_t* chunk_hist, cudaStream_t st) {
   const int Jpad = pad_clusters(J);
   const int jb = J <= 128 ? 128 : 256;
   cudaError_t e = jb == 128 ? launch_assign_tc_jb<128>(x, w_hi, w_lo, partial, status, BH, N, J, Jpad, st)
                             : launch_assign_tc_jb<256>(x, w_hi, w_lo, partial, status, BH, N, J, Jpad, st);
   if (e != cudaSuccess) return e;
   const int groups = 2 * (int)ceil_div64(J, jb);
-  tc::assign_reduce_kernel<<<(unsigned)ceil_div64(BH * N, 256), 256, 0, st>>>(partial, labels, BH * N, groups);
+  if (chunk_hist) {
+    const int nchunks = sort_chunks(N);
+    tc::assign_reduce_hist_kernel<<<dim3((unsigned)nchunks, (unsigned)BH), 256, 0, st>>>(partial, labels, chunk_hist, (int)BH,
+                                                                                       (int)N, (int)J, groups, nchunks);
+  } else {
+    tc::assign_reduce_kernel<<<(unsigned)ceil_div64(BH * N, 256), 256, 0, st>>>(partial, labels, BH * N, groups);
+  }
   count_launches(2);
   return cudaGetLastError();
 }

@@ -454,8 +454,10 @@ cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void*
   return cudaGetLastError();
 }
 
+// hist_done: chunk_hist already holds the per-chunk label histograms (written by the assignment's
+// reduction), so the first pass is skipped.
 cudaError_t launch_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int64_t K, int32_t* sorted_idx,
-                               int32_t* offsets, int32_t* sizes, int32_t* chunk_hist, cudaStream_t st) {
+                               int32_t* offsets, int32_t* sizes, int32_t* chunk_hist, cudaStream_t st, bool hist_done) {
   const int nchunks = sort_chunks(N);
   static bool attr_done = false;
   if (!attr_done) {
@@ -464,10 +466,10 @@ cudaError_t launch_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int
     attr_done = true;
   }
   dim3 grid((unsigned)nchunks, (unsigned)BH);
-  label_hist_kernel<<<grid, 256, 0, st>>>(labels, chunk_hist, (int)N, (int)K, nchunks);
+  if (!hist_done) label_hist_kernel<<<grid, 256, 0, st>>>(labels, chunk_hist, (int)N, (int)K, nchunks);
   label_scan_kernel<<<(unsigned)BH, 1024, 0, st>>>(chunk_hist, offsets, sizes, (int)K, nchunks);
   label_scatter_kernel<<<grid, 256, 8 * K * 4, st>>>(labels, chunk_hist, offsets, sorted_idx, (int)N, (int)K, nchunks);
-  count_launches(3);
+  count_launches(hist_done ? 2 : 3);
   return cudaGetLastError();
 }
 
@@ -535,6 +537,6 @@ extern "C" int svoo_b200_sort_labels_static(const int32_t* labels, int64_t BH, i
   }
   // Nothing in the array has to start at zero: label_hist_kernel writes every
   // [head, chunk, cluster] entry that the scan and scatter kernels read afterwards.
-  e = launch_sort_labels(labels, BH, N, K, sorted_idx, offsets, nullptr, scratch, (cudaStream_t)stream);
+  e = launch_sort_labels(labels, BH, N, K, sorted_idx, offsets, nullptr, scratch, (cudaStream_t)stream, false);
   return e == cudaSuccess ? SVOO_OK : (int)e;
 }

@@ -192,9 +192,11 @@ class PeerExchange:
         _lib.check(_lib.LIB.svoo_b200_push_heads(x.data_ptr(), self._in_ptrs[t], self._owner, self._slot, self.world,
                                                  self.rank, self.n_loc, self.H, self.D, stream), "push_heads")
 
-    def to_heads(self, q_seq, k_seq, v_seq, overlap_value: bool = True):
+    def to_heads(self, q_seq, k_seq, v_seq, overlap_value: bool = True, v_host: Optional[torch.Tensor] = None):
         """[N/P, H, 128] shards of q, k, v -> views [H_r, N, 128] of the receive arrays.  With
-        `overlap_value` the V array is complete only after `self.value_ready`."""
+        `overlap_value` the V array is complete only after `self.value_ready`.  `v_host`: a pinned
+        host copy of the V shard that the side stream first copies into `v_seq` (so that this
+        transfer, too, runs behind the clustering)."""
         main = torch.cuda.current_stream(q_seq.device)
         self._push_heads(0, q_seq, main.cuda_stream)
         self._push_heads(1, k_seq, main.cuda_stream)
@@ -208,6 +210,8 @@ class PeerExchange:
             self.fence()
             self._side.wait_event(here)
             with torch.cuda.stream(self._side):
+                if v_host is not None:
+                    v_seq.copy_(v_host, non_blocking=True)
                 self._push_heads(2, v_seq, self._side.cuda_stream)
                 self.fence(1)
                 self.value_ready = torch.cuda.Event()
