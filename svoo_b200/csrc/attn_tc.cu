@@ -5,21 +5,25 @@
 // their concatenation 128 keys at a time, so key tiles are always full except the last one
 // (a tile is packed across run boundaries from several TMA boxes of power-of-two heights).
 //
-//   warps 0-3   softmax of query tile 0: thread r owns row r (TMEM lane r): running max and
-//   warps 4-7   sum, P written back over S as packed bf16; same for tile 1
+//   warps 0-3   softmax of query tile 0: thread r owns row r (TMEM lane r).  The 128 scores of the
+//   warps 4-7   row are copied to registers and S is handed back at once; row max, exp2, row sum,
+//               P packed to bf16 into the tile's own TMEM columns; same for query tile 1
 //   warp 8      TMA producer for Q (once) and K, warp 9 for V: cp.async.bulk.tensor 2-D boxes of
 //               64 columns with the 128-byte swizzle, no multicast; two-stage rings for K and V
-//   warp 10     MMA issuer (one elected thread): S_w = Q_w K^T into TMEM (tcgen05.mma, both
+//   warp 10     MMA issuer (one elected thread): S = Q_w K^T into TMEM (tcgen05.mma, both
 //               operands from shared memory), then O_w += P_w V with P_w read from TMEM
+//   warp 11     idle; it completes the service warpgroup, which gives registers to the softmax
+//               warpgroups (setmaxnreg)
 //
-// The two query tiles ping-pong: while one tile's rows are in the softmax, the tensor
-// core works on the other tile's products.  O stays in TMEM; it is rescaled by the owning
-// softmax thread only when a row maximum grows by more than 2^8 (the running sum uses the
-// same stale maximum, so the final normalisation is exact).  Every mbarrier wait is bounded;
+// The softmax jobs alternate between the two query tiles and share ONE S accumulator: because a
+// job frees S as soon as its scores are in registers, the tensor core computes the next score
+// tile while the previous one is still in its exponentials.  O stays in TMEM; it is rescaled by
+// the owning softmax thread only when a row maximum grows by more than 2^8 (the running sum uses
+// the same stale maximum, so the final normalisation is exact).  Every mbarrier wait is bounded;
 // on expiry the CTA raises an abort flag, sets the status word and leaves through the
 // normal teardown.
 //
-// TMEM columns (512 allocated): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).
+// TMEM columns (512 allocated): S [0,128)  P0 [128,192)  P1 [192,256)  O0 [256,384)  O1 [384,512).
 // Semantics: svoo/co_clustering.py:949-1108 (scale D^-0.5, zero output without keys).
 #include <type_traits>
 #include "tc_common.cuh"
@@ -36,7 +40,7 @@ constexpr int kMaxRunsSmem = SVOO_MAX_CLUSTERS / 2 + 2;
 constexpr int kRunTableBytes = (kMaxRunsSmem * 8 + 255) / 256 * 256;
 constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 1024;   // + barriers, run table, slack
 constexpr int kKWarp = 8, kVWarp = 9, kMmaWarp = 10;     // after the 8 softmax warps
-// 11 warps; registers are allotted to a CTA in groups of four warps: 65536 / (12 * 32) = 170.
+// 12 warps; 65536 / (12 * 32) leaves 168 registers per thread at launch.
 constexpr int kThreads = 12 * 32;       // warp 11 only completes the service warpgroup (register hand-over below)
 #ifndef SVOO_REGS_SERVICE
 #define SVOO_REGS_SERVICE 104        // 128 * 104 + 256 * 200 = 64512 = the 12 warps' launch allotment

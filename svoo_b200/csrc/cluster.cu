@@ -325,9 +325,10 @@ __global__ void __launch_bounds__(256) label_scatter_kernel(const int32_t* __res
 // ---------------------------------------------------------------------------------------
 constexpr int kSlabMin = 256;
 
-__device__ __forceinline__ void slab_range(int begin, int end, int z, int& s0, int& s1) {
+// Rows [s0, s1) of slab z when a cluster is cut into `nslabs` pieces of at least kSlabMin rows.
+__device__ __forceinline__ void slab_range(int begin, int end, int z, int nslabs, int& s0, int& s1) {
   const int size = end - begin;
-  int per = (size + kCentroidSlabs - 1) / kCentroidSlabs;
+  int per = (size + nslabs - 1) / nslabs;
   per = per < kSlabMin ? kSlabMin : per;
   s0 = begin + z * per;
   s1 = s0 + per < end ? s0 + per : end;
@@ -336,12 +337,12 @@ __device__ __forceinline__ void slab_range(int begin, int end, int z, int& s0, i
 __global__ void __launch_bounds__(256) centroid_partial_kernel(const bf16* __restrict__ x,
                                                                const int32_t* __restrict__ sorted_idx,
                                                                const int32_t* __restrict__ offsets,
-                                                               float* __restrict__ partial, int N, int K) {
+                                                               float* __restrict__ partial, int N, int K, int nslabs) {
   __shared__ float red[16][kHeadDim + 4];
   const int c = blockIdx.x, z = blockIdx.y, bh = blockIdx.z;
   const int begin = offsets[(int64_t)bh * (K + 1) + c], end = offsets[(int64_t)bh * (K + 1) + c + 1];
   int s0, s1;
-  slab_range(begin, end, z, s0, s1);
+  slab_range(begin, end, z, nslabs, s0, s1);
   if (s0 >= s1) return;
   const int grp = threadIdx.x / 16, lane = threadIdx.x % 16;
   const int32_t* idx = sorted_idx + (int64_t)bh * N;
@@ -385,15 +386,15 @@ __global__ void __launch_bounds__(256) centroid_partial_kernel(const bf16* __res
 __global__ void __launch_bounds__(128) centroid_finalize_kernel(const float* __restrict__ partial,
                                                                 const int32_t* __restrict__ offsets,
                                                                 const bf16* __restrict__ old_c, bf16* __restrict__ new_c,
-                                                                int32_t* __restrict__ sizes, int K) {
+                                                                int32_t* __restrict__ sizes, int K, int nslabs) {
   const int c = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
   const int begin = offsets[(int64_t)bh * (K + 1) + c], end = offsets[(int64_t)bh * (K + 1) + c + 1];
   const int cnt = end - begin;
   const int64_t o = ((int64_t)bh * K + c) * kHeadDim + d;
   float s = 0.f;
-  for (int z = 0; z < kCentroidSlabs; ++z) {
+  for (int z = 0; z < nslabs; ++z) {
     int s0, s1;
-    slab_range(begin, end, z, s0, s1);
+    slab_range(begin, end, z, nslabs, s0, s1);
     if (s0 < s1) s += partial[(((int64_t)bh * K + c) * kCentroidSlabs + z) * kHeadDim + d];
   }
   const bf16 keep = old_c[o];
@@ -476,10 +477,15 @@ cudaError_t launch_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int
 cudaError_t launch_centroid_update(const void* x, const int32_t* sorted_idx, const int32_t* offsets,
                                    const void* old_c, void* new_c, int32_t* sizes, float* partial, int64_t BH,
                                    int64_t N, int64_t K, cudaStream_t st) {
-  dim3 grid((unsigned)K, kCentroidSlabs, (unsigned)BH);
-  centroid_partial_kernel<<<grid, 256, 0, st>>>((const bf16*)x, sorted_idx, offsets, partial, (int)N, (int)K);
+  // slabs per cluster: enough for clusters of four times the mean size to keep the 256-row minimum,
+  // at most kCentroidSlabs; larger clusters just get longer slabs (most launched CTAs of a finer
+  // split would find their slab empty)
+  int nslabs = (int)ceil_div64(4 * ceil_div64(N, K), kSlabMin);
+  nslabs = nslabs < 1 ? 1 : (nslabs > kCentroidSlabs ? kCentroidSlabs : nslabs);
+  dim3 grid((unsigned)K, (unsigned)nslabs, (unsigned)BH);
+  centroid_partial_kernel<<<grid, 256, 0, st>>>((const bf16*)x, sorted_idx, offsets, partial, (int)N, (int)K, nslabs);
   dim3 grid2((unsigned)K, (unsigned)BH);
-  centroid_finalize_kernel<<<grid2, 128, 0, st>>>(partial, offsets, (const bf16*)old_c, (bf16*)new_c, sizes, (int)K);
+  centroid_finalize_kernel<<<grid2, 128, 0, st>>>(partial, offsets, (const bf16*)old_c, (bf16*)new_c, sizes, (int)K, nslabs);
   count_launches(2);
   return cudaGetLastError();
 }
