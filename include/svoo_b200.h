@@ -200,6 +200,26 @@ int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* ow
 int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int32_t world, int64_t n_loc,
                        int64_t H, int64_t D, void* stream);
 
+/* The producer of the path's Q and K (and V), one pass over the projection output:
+ *   y = bf16(x * rstd * weight), rstd = 1 / sqrt(mean_row(x^2) + eps)      if weight != NULL
+ *       (triton_rmsnorm_forward, svoo/kernels/triton/rmsnorm.py:9-46, called from
+ *        get_qk_norm, svoo/models/wan/attention.py:112-125; the norm runs over all H*D columns)
+ *   out[2i]   = y[2i] cos[2i] - y[2i+1] sin[2i+1]                          if cos != NULL
+ *   out[2i+1] = y[2i] sin[2i+1] + y[2i+1] cos[2i]       (apply_rotary_emb, attention.py:179-190)
+ *   result stored as [H, S, D]                 (transpose(1, 2).contiguous(), attention.py:127-131)
+ * x: [S, H*D] bf16; weight: [H*D] fp32; cos, sin: [S, D] fp32 (the full-width tables the
+ * caller's rotary module produces; even entries of cos and odd entries of sin are used).
+ * With weight == NULL and cos == NULL it is the plain head transpose (V).  H <= 128. */
+int svoo_b200_qk_prep(const void* x, const float* weight, float eps, const float* cos, const float* sin, int64_t S,
+                      int64_t H, int64_t D, void* out, void* stream);
+/* The same for a sequence-parallel caller: x is this rank's [n_loc, H*D] rows (cos, sin
+ * [n_loc, D]) and every head's row is stored straight into the rank that owns the head, at
+ * [slot[h], rank * n_loc + r, :] of its [H/world, N, D] array -- svoo_b200_push_heads fused
+ * into the producer (peer_dst, owner, slot as there).  No counterpart in the reference. */
+int svoo_b200_qk_prep_push(const void* x, const float* weight, float eps, const float* cos, const float* sin,
+                           void* const* peer_dst, const int32_t* owner, const int32_t* slot, int32_t world, int32_t rank,
+                           int64_t n_loc, int64_t H, int64_t D, void* stream);
+
 /* Barrier over the ranks of one node, as a kernel on `stream`: publishes this rank's earlier
  * peer stores on that stream and waits (at most ~2 s) for the same call of every other rank.
  * peer_flags: HOST array of `world` device pointers, entry p = rank p's flag array of

@@ -20,6 +20,9 @@ Reference locations restated here (paths inside the reference project):
   * weighted_softmax / dynamic map    svoo/co_clustering.py:544-633
   * block-sparse attention semantics  svoo/co_clustering.py:949-1108
   * Hunyuan text-block post-process   svoo/models/hunyuan10/attention.py:977-1021
+  * producer of Q, K, V (RMS norm, rotary embedding, head transpose)
+                                      svoo/kernels/triton/rmsnorm.py:9-46,
+                                      svoo/models/wan/attention.py:112-131,177-195
 """
 from __future__ import annotations
 
@@ -30,6 +33,46 @@ import numpy as np
 import torch
 
 Ratio = Union[float, int, Sequence[float], torch.Tensor, None]
+
+
+# --------------------------------------------------------------------------------------
+# Producer of the path's inputs
+# --------------------------------------------------------------------------------------
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, truncate: bool = False) -> torch.Tensor:
+    """y = (x * rstd * w) in fp32, rounded to x's dtype; rstd = 1 / sqrt(mean(x^2) + eps) over the
+    last dimension (svoo/kernels/triton/rmsnorm.py:32-42).  `truncate`: drop the low 16 bits
+    instead of rounding to nearest even -- what the Triton *interpreter* does for an in-kernel
+    fp32 -> bf16 cast (on a GPU the cast rounds to nearest even); only used to compare with
+    fixtures that were produced under the interpreter."""
+    xf = x.float()
+    var = (xf * xf).sum(-1, keepdim=True) / x.shape[-1]
+    rstd = 1.0 / torch.sqrt(var + eps)
+    y = xf * rstd * weight.float()
+    if truncate and x.dtype == torch.bfloat16:
+        return (y.view(torch.int32) & -65536).view(torch.float32).to(x.dtype)
+    return y.to(x.dtype)
+
+
+def rotary_interleaved(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [B,S,H,D]; cos, sin broadcastable [.,S,1,D]: pairs (2i, 2i+1) rotated with cos[2i], sin[2i+1]
+    (svoo/models/wan/attention.py:179-190); fp32 arithmetic, result in x's dtype."""
+    x1, x2 = x.unflatten(-1, (-1, 2)).unbind(-1)
+    c, s_ = cos[..., 0::2], sin[..., 1::2]
+    out = torch.empty_like(x)
+    out[..., 0::2] = x1 * c - x2 * s_
+    out[..., 1::2] = x1 * s_ + x2 * c
+    return out
+
+
+def qk_prep(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+            sin: Optional[torch.Tensor], heads: int, truncate_norm: bool = False) -> torch.Tensor:
+    """x [B,S,H*D] -> [B,H,S,D]: norm over all H*D columns, rotary embedding, head transpose
+    (svoo/models/wan/attention.py:112-131,173-195)."""
+    y = x if weight is None else rmsnorm_rows(x, weight, eps, truncate_norm)
+    y = y.unflatten(2, (heads, -1))
+    if cos is not None:
+        y = rotary_interleaved(y, cos, sin)
+    return y.transpose(1, 2).contiguous()
 
 
 # --------------------------------------------------------------------------------------

@@ -46,6 +46,10 @@ SIGNATURES = {
     "svoo_b200_sparse_attn_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_int32, c_int64,
                                            c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+    "svoo_b200_qk_prep": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
+                                  c_void_p]),
+    "svoo_b200_qk_prep_push": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                       c_int32, c_int64, c_int64, c_int64, c_void_p]),
     "svoo_b200_peer_barrier": (c_int, [c_void_p, c_int32, c_int32, c_int32, ctypes.c_uint32, c_void_p, c_void_p]),
     "svoo_b200_push_heads": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int64, c_int64,
                                      c_void_p]),

@@ -27,6 +27,8 @@ cudaError_t launch_push_heads(const void*, void* const*, const int32_t*, const i
                               cudaStream_t);
 cudaError_t launch_push_seq(const void*, void* const*, const int32_t*, int, int64_t, int, int, cudaStream_t);
 cudaError_t launch_peer_barrier(void* const*, int, int, int, uint32_t, int32_t*, cudaStream_t);
+cudaError_t launch_qk_prep(const void*, const float*, float, const float*, const float*, int64_t, int, void*, void* const*,
+                           const int32_t*, const int32_t*, int, int, cudaStream_t);
 }  // namespace svoo
 
 namespace svoo {
@@ -349,6 +351,47 @@ int svoo_b200_peer_barrier(void* const* peer_flags, int32_t world, int32_t rank,
   for (int p = 0; p < world; ++p)
     if (!peer_flags[p]) return SVOO_ERR_NULL;
   SVOO_CUDA(launch_peer_barrier(peer_flags, world, rank, channel * 16, epoch, status, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+namespace {
+int check_prep(const void* x, const float* weight, const float* cosv, const float* sinv, int64_t S, int64_t H, int64_t D) {
+  if (!x) return SVOO_ERR_NULL;
+  if ((cosv == nullptr) != (sinv == nullptr)) return SVOO_ERR_NULL;
+  if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
+  if (S < 1 || S > ((int64_t)1 << 30) || H < 1 || H > 128) return SVOO_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(cosv) || !aligned16(sinv)) return SVOO_ERR_ALIGN;
+  return SVOO_OK;
+}
+}  // namespace
+
+int svoo_b200_qk_prep(const void* x, const float* weight, float eps, const float* cosv, const float* sinv, int64_t S,
+                      int64_t H, int64_t D, void* out, void* stream) {
+  SVOO_TRY(check_prep(x, weight, cosv, sinv, S, H, D));
+  if (!out) return SVOO_ERR_NULL;
+  if (!aligned16(out)) return SVOO_ERR_ALIGN;
+  SVOO_CUDA(launch_qk_prep(x, weight, eps, cosv, sinv, S, (int)H, out, nullptr, nullptr, nullptr, 0, 0,
+                           (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_qk_prep_push(const void* x, const float* weight, float eps, const float* cosv, const float* sinv,
+                           void* const* peer_dst, const int32_t* owner, const int32_t* slot, int32_t world, int32_t rank,
+                           int64_t n_loc, int64_t H, int64_t D, void* stream) {
+  SVOO_TRY(check_prep(x, weight, cosv, sinv, n_loc, H, D));
+  if (!owner || !slot) return SVOO_ERR_NULL;
+  SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
+  if (rank < 0 || rank >= world) return SVOO_ERR_SHAPE;
+  const int64_t hr = H / world;
+  bool seen[16 * 128] = {};
+  for (int64_t h = 0; h < H; ++h) {
+    if (owner[h] < 0 || owner[h] >= world || slot[h] < 0 || slot[h] >= hr) return SVOO_ERR_SHAPE;
+    bool& sref = seen[owner[h] * 128 + slot[h]];
+    if (sref) return SVOO_ERR_SHAPE;
+    sref = true;
+  }
+  SVOO_CUDA(launch_qk_prep(x, weight, eps, cosv, sinv, n_loc, (int)H, nullptr, peer_dst, owner, slot, world, rank,
+                           (cudaStream_t)stream));
   return SVOO_OK;
 }
 

@@ -1,0 +1,150 @@
+// Producer of the path's inputs: RMS norm over the whole projection row, rotary embedding and the
+// [S, H*128] -> [H, S, 128] head transpose in ONE pass over the projection output.
+//
+// Reference (three to four passes): triton_rmsnorm_forward, svoo/kernels/triton/rmsnorm.py:9-46
+// (y = bf16(x * rstd * w), rstd = 1 / sqrt(mean(x^2) + eps), fp32 arithmetic), the interleaved-pair
+// rotation of svoo/models/wan/attention.py:179-190 (out[2i] = x[2i] cos[2i] - x[2i+1] sin[2i+1],
+// out[2i+1] = x[2i] sin[2i+1] + x[2i+1] cos[2i], fp32 arithmetic on the bf16-rounded normed values,
+// rounded to bf16) and transpose(1, 2).contiguous() of svoo/models/wan/attention.py:127-131.
+// The roundings are kept where the reference has them, so results differ from it only through the
+// order of the sum of squares (at most one bf16 ulp on isolated elements).
+//
+// One CTA per token: 256 threads hold the row in registers (8 bf16 per 128-bit chunk, up to 8
+// chunks per thread, H*128 <= 16384), reduce the sum of squares in a fixed order, and store every
+// head's 128 values as one 256-byte segment -- into this GPU's [H, S, 128] array or, for a
+// sequence-parallel caller, straight into the arrays of the ranks that own the heads (the same
+// destination rule as push_heads), which folds the re-shard's send pass into the producer.
+// HBM-bound: 2 * H*128*2 bytes per token.
+#include "common.cuh"
+
+namespace svoo {
+
+constexpr int kPrepThreads = 256;
+constexpr int kPrepMaxChunks = 8;      // per thread: H * 128 / 8 / 256
+
+struct PrepDest {
+  uint4* dst[16];       // [0] only when world == 0 (local [H, S, 128]); else every rank's [H/world, N, 128]
+  int16_t owner[128];
+  int16_t slot[128];
+  int world;            // 0: local
+  int rank;
+  int64_t n_loc;        // tokens of this rank (== S); N = n_loc * world
+};
+
+__global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
+                                                               float eps, const float* __restrict__ cosv,
+                                                               const float* __restrict__ sinv, int64_t S, int H,
+                                                               const __grid_constant__ PrepDest dest) {
+  __shared__ float warp_sum[kPrepThreads / 32];
+  __shared__ float rstd_s;
+  const int64_t s = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+  const int nchunks = H * 16;                                       // 16 chunks of 8 values per head
+  const uint4* row = x + s * nchunks;
+  uint4 v[kPrepMaxChunks];
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < kPrepMaxChunks; ++u) {
+    const int c = tid + u * kPrepThreads;
+    if (c < nchunks) {
+      v[u] = __ldcs(row + c);
+      if (weight) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float a = __low2float(h[i]), b = __high2float(h[i]);
+          ss = fmaf(a, a, ss);
+          ss = fmaf(b, b, ss);
+        }
+      }
+    }
+  }
+  float rstd = 1.f;
+  if (weight) {                                                      // fixed-order block reduction
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) warp_sum[warp] = ss;
+    __syncthreads();
+    if (tid == 0) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < kPrepThreads / 32; ++w) t += warp_sum[w];
+      rstd_s = 1.0f / sqrtf(t / (float)(H * kHeadDim) + eps);
+    }
+    __syncthreads();
+    rstd = rstd_s;
+  }
+#pragma unroll
+  for (int u = 0; u < kPrepMaxChunks; ++u) {
+    const int c = tid + u * kPrepThreads;
+    if (c >= nchunks) continue;
+    const int h = c >> 4, d0 = (c & 15) * 8;
+    const __nv_bfloat162* hin = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      y[2 * i] = __low2float(hin[i]);
+      y[2 * i + 1] = __high2float(hin[i]);
+    }
+    if (weight) {
+      const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + c * 8));
+      const float4 w1 = __ldg(reinterpret_cast<const float4*>(weight + c * 8 + 4));
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = bf16_round(y[i] * rstd * wv[i]);          // the norm's output is bf16
+    }
+    if (cosv) {
+      const float4 c0 = __ldg(reinterpret_cast<const float4*>(cosv + s * kHeadDim + d0));
+      const float4 c1 = __ldg(reinterpret_cast<const float4*>(cosv + s * kHeadDim + d0 + 4));
+      const float4 s0 = __ldg(reinterpret_cast<const float4*>(sinv + s * kHeadDim + d0));
+      const float4 s1 = __ldg(reinterpret_cast<const float4*>(sinv + s * kHeadDim + d0 + 4));
+      const float ce[4] = {c0.x, c0.z, c1.x, c1.z};                                 // cos[..., 0::2]
+      const float so[4] = {s0.y, s0.w, s1.y, s1.w};                                 // sin[..., 1::2]
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a = y[2 * i], b = y[2 * i + 1];
+        // two rounded products, then the sum: the reference evaluates x1 * cos - x2 * sin with
+        // separate multiply and subtract kernels, not a fused multiply-add
+        y[2 * i] = __fsub_rn(__fmul_rn(a, ce[i]), __fmul_rn(b, so[i]));
+        y[2 * i + 1] = __fadd_rn(__fmul_rn(a, so[i]), __fmul_rn(b, ce[i]));
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(y[0], y[1]);
+    o.y = pack_bf16x2(y[2], y[3]);
+    o.z = pack_bf16x2(y[4], y[5]);
+    o.w = pack_bf16x2(y[6], y[7]);
+    uint4* d;
+    if (dest.world == 0) {
+      d = dest.dst[0] + ((int64_t)h * S + s) * 16;
+    } else {
+      const int64_t N = dest.n_loc * dest.world;
+      d = dest.dst[dest.owner[h]] + ((int64_t)dest.slot[h] * N + (int64_t)dest.rank * dest.n_loc + s) * 16;
+    }
+    d[c & 15] = o;
+  }
+}
+
+cudaError_t launch_qk_prep(const void* x, const float* weight, float eps, const float* cosv, const float* sinv, int64_t S,
+                           int H, void* out_local, void* const* peer_dst, const int32_t* owner, const int32_t* slot,
+                           int world, int rank, cudaStream_t st) {
+  PrepDest dest{};
+  if (peer_dst) {
+    for (int p = 0; p < world; ++p) dest.dst[p] = (uint4*)peer_dst[p];
+    for (int h = 0; h < H; ++h) {
+      dest.owner[h] = (int16_t)owner[h];
+      dest.slot[h] = (int16_t)slot[h];
+    }
+    dest.world = world;
+    dest.rank = rank;
+    dest.n_loc = S;
+  } else {
+    dest.dst[0] = (uint4*)out_local;
+    dest.world = 0;
+  }
+  qk_prep_kernel<<<(unsigned)S, kPrepThreads, 0, st>>>((const uint4*)x, weight, eps, cosv, sinv, S, H, dest);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+}  // namespace svoo

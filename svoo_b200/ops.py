@@ -250,3 +250,26 @@ def cluster_status(device: torch.device, BH: int, N: int, QC: int, KC: int) -> i
     check(LIB.svoo_b200_status_offset(BH, N, QC, KC, ctypes.byref(off)), "status_offset")
     ws = workspace(device, BH, N, QC, KC)
     return int(ws[off.value + 4:off.value + 8].view(torch.int32).item())
+
+
+def qk_prep(x: torch.Tensor, heads: int, weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+            cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The producer of the path's inputs in one pass: x [S, H*128] bf16 (a projection output) ->
+    [H, S, 128] with the RMS norm over all H*128 columns (weight [H*128], any float dtype),
+    the interleaved-pair rotary embedding (cos, sin [S, 128], the full-width tables; even cos and
+    odd sin entries are used) and the head transpose.  weight / cos None skip that part (V)."""
+    _need_cuda(x)
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.shape[1] != heads * 128:
+        raise ValueError("x must be contiguous bf16 [S, H*128]")
+    S = x.shape[0]
+    w = None if weight is None else weight.detach().to(device=x.device, dtype=torch.float32).contiguous()
+    if w is not None and w.numel() != heads * 128:
+        raise ValueError("weight must have H*128 entries")
+    c = s_ = None
+    if cos is not None:
+        c = cos.to(device=x.device, dtype=torch.float32).reshape(S, 128).contiguous()
+        s_ = sin.to(device=x.device, dtype=torch.float32).reshape(S, 128).contiguous()
+    out = torch.empty(heads, S, 128, dtype=torch.bfloat16, device=x.device)
+    check(LIB.svoo_b200_qk_prep(x.data_ptr(), 0 if w is None else w.data_ptr(), float(eps), 0 if c is None else c.data_ptr(),
+                                0 if s_ is None else s_.data_ptr(), S, heads, 128, out.data_ptr(), _stream()), "qk_prep")
+    return out

@@ -218,6 +218,42 @@ class PeerExchange:
                 self.value_ready.record(self._side)
         return self.heads_in[0], self.heads_in[1], self.heads_in[2]
 
+    def producer_to_heads(self, xq, xk, xv, norm_q, norm_k, cos, sin):
+        """to_heads fused with the producer: xq, xk, xv are this rank's [N/P, H*128] projection
+        outputs; the RMS norm (norm_q / norm_k = (weight, eps)), the rotary embedding (cos, sin
+        [N/P, 128] fp32, this rank's rows) and the head transpose run in the kernel that stores the
+        rows into the owning ranks (svoo_b200_qk_prep_push).  Returns the [H_r, N, 128] views;
+        V is complete after `self.value_ready`."""
+        from . import _lib
+        main = torch.cuda.current_stream(xq.device)
+        cos = cos.to(torch.float32).reshape(self.n_loc, self.D).contiguous()
+        sin = sin.to(torch.float32).reshape(self.n_loc, self.D).contiguous()
+
+        def push(t, x, norm, rope, stream):
+            if tuple(x.shape) != (self.n_loc, self.H * self.D) or x.dtype != torch.bfloat16 or not x.is_contiguous():
+                raise ValueError("projection outputs must be contiguous bf16 [N/P, H*128]")
+            w = None if norm is None else norm[0].detach().to(device=x.device, dtype=torch.float32).contiguous()
+            rc = _lib.LIB.svoo_b200_qk_prep_push(x.data_ptr(), 0 if w is None else w.data_ptr(),
+                                                 0.0 if norm is None else float(norm[1]),
+                                                 cos.data_ptr() if rope else 0, sin.data_ptr() if rope else 0,
+                                                 self._in_ptrs[t], self._owner, self._slot, self.world, self.rank,
+                                                 self.n_loc, self.H, self.D, stream)
+            _lib.check(rc, "qk_prep_push")
+            return w                                                  # keep the fp32 weight alive until the launch is queued
+
+        keep = [push(0, xq, norm_q, True, main.cuda_stream), push(1, xk, norm_k, True, main.cuda_stream)]
+        here = torch.cuda.Event()
+        here.record(main)
+        self.fence()
+        self._side.wait_event(here)
+        with torch.cuda.stream(self._side):
+            push(2, xv, None, False, self._side.cuda_stream)
+            self.fence(1)
+            self.value_ready = torch.cuda.Event()
+            self.value_ready.record(self._side)
+        del keep
+        return self.heads_in[0], self.heads_in[1], self.heads_in[2]
+
     @property
     def peer_out(self):
         """Argument for sparse_attention_layer(peer_out=...): the attention kernel then stores its

@@ -138,6 +138,33 @@ class WanAttn_SAPAttn_Processor(_SAPBase):
         out[..., 1::2] = x1 * sin + x2 * cos
         return out.type_as(hidden_states)
 
+    @staticmethod
+    def _fused_producer_applies(attn, query, key, rotary_emb) -> bool:
+        """One-pass norm + rotary + head transpose (svoo_b200_qk_prep): self-attention on one bf16
+        CUDA sample with 128-wide heads and weight-only RMS norms over the whole projection."""
+        if not (query.is_cuda and query.dtype == torch.bfloat16 and query.shape[0] == 1 and query.shape == key.shape):
+            return False
+        if query.shape[-1] != attn.heads * 128 or attn.heads > 128:
+            return False
+        for name in ("norm_q", "norm_k"):
+            n = getattr(attn, name, None)
+            if n is None or getattr(n, "weight", None) is None or getattr(n, "bias", None) is not None:
+                return False
+            if n.weight.numel() != query.shape[-1]:
+                return False
+        return True
+
+    @staticmethod
+    def fused_producer(attn, query, key, value, rotary_emb):
+        """Replaces get_qk_norm + apply_rotary_emb + get_transpose_qkv of the reference
+        (svoo/models/wan/attention.py:112-131,177-195) for the case _fused_producer_applies accepts."""
+        H = attn.heads
+        cos, sin = (None, None) if rotary_emb is None else rotary_emb
+        q = ops.qk_prep(query[0].contiguous(), H, attn.norm_q.weight, attn.norm_q.eps, cos, sin)
+        k = ops.qk_prep(key[0].contiguous(), H, attn.norm_k.weight, attn.norm_k.eps, cos, sin)
+        v = ops.qk_prep(value[0].contiguous(), H)
+        return q[None], k[None], v[None]
+
     def get_o(self, attn, query, hidden_states, hidden_states_img=None):
         if hidden_states.dim() == 4:
             hidden_states = hidden_states.transpose(1, 2).flatten(2, 3)
@@ -150,14 +177,17 @@ class WanAttn_SAPAttn_Processor(_SAPBase):
     def __call__(self, attn, hidden_states, encoder_hidden_states=None, attention_mask=None, rotary_emb=None,
                  timestep=None):
         query, key, value = self.get_qkv(attn, hidden_states, encoder_hidden_states)
-        query, key = self.get_qk_norm(attn, query, key)
-        query = query.unflatten(2, (attn.heads, -1))
-        key = key.unflatten(2, (attn.heads, -1))
-        value = value.unflatten(2, (attn.heads, -1))
-        if rotary_emb is not None:
-            query = self.apply_rotary_emb(query, *rotary_emb)
-            key = self.apply_rotary_emb(key, *rotary_emb)
-        query, key, value = (t.transpose(1, 2).contiguous() for t in (query, key, value))
+        if self._fused_producer_applies(attn, query, key, rotary_emb):
+            query, key, value = self.fused_producer(attn, query, key, value, rotary_emb)
+        else:
+            query, key = self.get_qk_norm(attn, query, key)
+            query = query.unflatten(2, (attn.heads, -1))
+            key = key.unflatten(2, (attn.heads, -1))
+            value = value.unflatten(2, (attn.heads, -1))
+            if rotary_emb is not None:
+                query = self.apply_rotary_emb(query, *rotary_emb)
+                key = self.apply_rotary_emb(key, *rotary_emb)
+            query, key, value = (t.transpose(1, 2).contiguous() for t in (query, key, value))
         if timestep is None:
             out = F.scaled_dot_product_attention(query, key, value, attn_mask=attention_mask)
             out = out.transpose(1, 2).flatten(2, 3)

@@ -150,11 +150,85 @@ def lookup_case():
     print("lookup fixture written")
 
 
+def producer_case(name, S, H, seed, eps=1e-6):
+    """What the reference's processor hands to attention_core_logic: to_q/to_k/to_v, RMS norm over
+    the whole projection (its Triton kernel, ENABLE_FAST_KERNEL=1), interleaved-pair rotary
+    embedding, head transpose.  The processor module imports diffusers at its top, which is not
+    installed here; the four names it imports are replaced by empty stand-ins (none of them is
+    executed on this route), `torch.compile` is made the identity (the module compiles
+    flex_attention at import), and `attention_core_logic` is replaced on the instance to capture
+    its arguments.  Everything between is the reference's code, unmodified."""
+    import types
+    os.environ["ENABLE_FAST_KERNEL"] = "1"
+
+    def mod(mname, **attrs):
+        m = types.ModuleType(mname)
+        m.__dict__.update(attrs)
+        sys.modules.setdefault(mname, m)
+
+    mod("diffusers")
+    mod("diffusers.models")
+    mod("diffusers.models.attention_processor", Attention=type("Attention", (torch.nn.Module,), {}))
+    mod("diffusers.models.normalization", RMSNorm=type("RMSNorm", (torch.nn.Module,), {}))
+    mod("diffusers.models.transformers")
+    mod("diffusers.models.transformers.transformer_wan", _get_added_kv_projections=None, dispatch_attention_fn=None)
+    real_compile = torch.compile
+    torch.compile = lambda f=None, **kw: f
+    try:
+        import svoo.models.wan.attention as ref_attn
+    finally:
+        torch.compile = real_compile
+
+    D = 128
+    g = torch.Generator("cpu").manual_seed(seed)
+    hidden = torch.randn(1, S, H * D, generator=g).bfloat16()
+    attn = torch.nn.Module()
+    for nm in ("to_q", "to_k", "to_v"):
+        lin = torch.nn.Linear(H * D, H * D, bias=True)
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(H * D, H * D, generator=g) / (H * D) ** 0.5)
+            lin.bias.copy_(torch.randn(H * D, generator=g) * 0.1)
+        setattr(attn, nm, lin.bfloat16())
+    for nm in ("norm_q", "norm_k"):
+        nrm = torch.nn.Module()
+        nrm.weight = torch.nn.Parameter((1.0 + 0.2 * torch.randn(H * D, generator=g)).bfloat16())
+        nrm.eps = eps
+        setattr(attn, nm, nrm)
+    attn.heads = H
+    attn.add_k_proj = None
+    attn.to_out = torch.nn.ModuleList([torch.nn.Identity(), torch.nn.Identity()])
+    # rotary tables in the layout the caller's rotary module produces: [1, S, 1, D] fp32
+    ang = torch.rand(S, D // 2, generator=g) * 6.2831853
+    cos = torch.cos(ang).repeat_interleave(2, dim=-1)[None, :, None, :].contiguous()
+    sin = torch.sin(ang).repeat_interleave(2, dim=-1)[None, :, None, :].contiguous()
+
+    proc = ref_attn.WanAttn_SAPAttn_Processor(0)
+    proc.measure_attention_sparsity = False
+    seen = {}
+
+    def capture(query, key, value, timestep):
+        seen.update(q=query, k=key, v=value)
+        return torch.zeros(1, S, H * D, dtype=query.dtype)
+
+    proc.attention_core_logic = capture
+    with torch.no_grad():
+        proc(attn, hidden, rotary_emb=(cos, sin), timestep=torch.tensor([5]))
+        xq, xk, xv = attn.to_q(hidden), attn.to_k(hidden), attn.to_v(hidden)
+    assert seen["q"].shape == (1, H, S, D) and seen["q"].is_contiguous()
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), xq=f32(xq), xk=f32(xk), xv=f32(xv),
+                        wq=f32(attn.norm_q.weight.detach()), wk=f32(attn.norm_k.weight.detach()), eps=np.float32(eps),
+                        cos=cos.numpy(), sin=sin.numpy(), q=f32(seen["q"]), k=f32(seen["k"]), v=f32(seen["v"]))
+    print(name, "written")
+
+
 def main():
     import dataclasses
     only = sys.argv[1:]
     tiny = synth.LayerConfig("tiny-fp32", 90, 2, (4, 16, 16), torch.float32, 8, 16, 3, (0.25, 0.25), 1, False)
     if only:
+        if "producer" in only:
+            producer_case("producer_h6", 96, 6, 21)
+            producer_case("producer_h4", 80, 4, 22)
         if "layer_tiny_bf16" in only:
             tiny_b = dataclasses.replace(tiny, name="tiny-bf16", cfg_id=91, dtype=torch.bfloat16, rope=True,
                                          num_q=12, num_k=40, grid=(3, 16, 20))
@@ -173,6 +247,8 @@ def main():
     map_case("map_bf16_big", 2, 256, 1024, torch.bfloat16, 0.9, [0.15, 0.2], None, 16)
     map_case("map_all_ones", 2, 8, 16, torch.bfloat16, 1.0, 0.1, None, 17)
     lookup_case()
+    producer_case("producer_h6", 96, 6, 21)
+    producer_case("producer_h4", 80, 4, 22)
 
 
 if __name__ == "__main__":

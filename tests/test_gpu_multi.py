@@ -53,6 +53,22 @@ y = parallel.PeerExchange(parts, N, dev, fence="nccl")
 out2 = parallel.sparse_attention_layer_sharded(qs, ks, vs, parts, densities=dens, init_indices=(qi.to(dev), ki.to(dev)),
                                                exchange=y, **kw)
 assert torch.equal(out2, out), "NCCL-fenced run differs from the flag-fenced run"
+# producer fused with the re-shard: projections of this rank's tokens -> heads on their owners
+g = torch.Generator("cpu").manual_seed(5)
+xq, xk, xv = ((torch.randn(N, H * 128, generator=g) * 1.3).bfloat16() for _ in range(3))
+wq, wk = ((1.0 + 0.2 * torch.randn(H * 128, generator=g)).bfloat16() for _ in range(2))
+ang = torch.rand(N, 64, generator=g) * 6.2831853
+cos, sin = torch.cos(ang).repeat_interleave(2, -1), torch.sin(ang).repeat_interleave(2, -1)
+lo, hi = rank * n_loc, (rank + 1) * n_loc
+from svoo_b200 import ops
+full = [ops.qk_prep(xq.to(dev), H, wq.to(dev), 1e-6, cos.to(dev), sin.to(dev)),
+        ops.qk_prep(xk.to(dev), H, wk.to(dev), 1e-6, cos.to(dev), sin.to(dev)), ops.qk_prep(xv.to(dev), H)]
+got = x.producer_to_heads(xq[lo:hi].contiguous().to(dev), xk[lo:hi].contiguous().to(dev), xv[lo:hi].contiguous().to(dev),
+                          (wq, 1e-6), (wk, 1e-6), cos[lo:hi].to(dev), sin[lo:hi].to(dev))
+torch.cuda.current_stream().wait_event(x.value_ready)
+for gt, fl in zip(got, full):
+    assert torch.equal(gt, fl[parts[rank]]), "fused producer + re-shard differs from the one-GPU producer"
+assert x.status() == 0
 torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
 print("OK", rank)
 '''

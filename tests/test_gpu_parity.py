@@ -4,6 +4,7 @@ Bars: integer / index work bit-exact; one assignment step from identical centroi
 >= 99.9 % equal labels; attention max-abs-err <= 2e-2 and cosine >= 0.999 in bf16.
 """
 import dataclasses
+import os
 
 import numpy as np
 import pytest
@@ -380,6 +381,52 @@ def test_both_attention_kernels_against_oracle(dev, kernel):
                           ops.offsets_from_sizes(qs[0].to(dev)), ops.offsets_from_sizes(ks[0].to(dev)), kernel=kernel)
     assert (got.cpu().float() - ref[0].float()).abs().max() <= ATTN_ATOL
     assert cosine(got.cpu(), ref[0]) >= ATTN_COS
+
+
+# ----------------------------------------------------------------------------------------
+# producer of Q, K, V: RMS norm + rotary embedding + head transpose in one pass
+# ----------------------------------------------------------------------------------------
+def _ulp_close(got, ref, exact_frac):
+    """>= exact_frac of the elements bit-identical, the rest within two bf16 ulps of the larger
+    element of their rotation pair (a one-ulp change of one normed value moves both outputs)."""
+    got, ref = got.float(), ref.float()
+    assert (got == ref).float().mean().item() >= exact_frac
+    pair = ref.abs().unflatten(-1, (-1, 2)).amax(-1, keepdim=True).expand(*ref.shape[:-1], ref.shape[-1] // 2, 2)
+    assert ((got - ref).abs() <= 2.0 ** -6 * pair.flatten(-2) + 1e-6).all()
+
+
+@pytest.mark.parametrize("name", ["producer_h6", "producer_h4"])
+def test_producer_against_oracle_and_reference(dev, name):
+    ops = _mods()[0]
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", name + ".npz"))
+    H = z["q"].shape[1]
+    cos, sin = torch.from_numpy(z["cos"]), torch.from_numpy(z["sin"])
+    for x, w, want in (("xq", "wq", "q"), ("xk", "wk", "k")):
+        xt, wt = torch.from_numpy(z[x]).bfloat16(), torch.from_numpy(z[w]).bfloat16()
+        got = ops.qk_prep(xt[0].to(dev), H, wt.to(dev), float(z["eps"]), cos.to(dev), sin.to(dev)).cpu()
+        # oracle (same roundings as the kernel; only the order of the sum of squares differs)
+        _ulp_close(got, O.qk_prep(xt, wt, float(z["eps"]), cos, sin, H)[0], 0.999)
+        # the reference's own output; its norm was cast by truncation (Triton interpreter), so
+        # about half of the normed values sit one ulp lower than with the GPU's rounding
+        _ulp_close(got, torch.from_numpy(z[want])[0], 0.2)
+    v = ops.qk_prep(torch.from_numpy(z["xv"]).bfloat16()[0].to(dev), H).cpu()
+    assert torch.equal(v.float(), torch.from_numpy(z["v"])[0])
+
+
+def test_producer_full_width(dev):
+    """40 heads (5120 columns, the Wan-14B width) and a ragged token count against the oracle."""
+    ops = _mods()[0]
+    g = torch.Generator("cpu").manual_seed(41)
+    S, H = 777, 40
+    x = (torch.randn(1, S, H * 128, generator=g) * 1.7).bfloat16()
+    w = (1.0 + 0.3 * torch.randn(H * 128, generator=g)).bfloat16()
+    ang = torch.rand(S, 64, generator=g) * 6.2831853
+    cos = torch.cos(ang).repeat_interleave(2, -1)[None, :, None, :]
+    sin = torch.sin(ang).repeat_interleave(2, -1)[None, :, None, :]
+    got = ops.qk_prep(x[0].to(dev), H, w.to(dev), 1e-6, cos.to(dev), sin.to(dev)).cpu()
+    _ulp_close(got, O.qk_prep(x, w, 1e-6, cos, sin, H)[0], 0.999)
+    plain = ops.qk_prep(x[0].to(dev), H).cpu()
+    assert torch.equal(plain, x[0].unflatten(1, (H, 128)).transpose(0, 1))
 
 
 # ----------------------------------------------------------------------------------------

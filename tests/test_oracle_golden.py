@@ -1,4 +1,6 @@
 """The CPU oracle against outputs of the unmodified reference (tests/golden)."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -103,3 +105,28 @@ def test_exp_is_accurate():
     got = O.exp_f32(x)
     ref = np.exp(x.astype(np.float64))
     assert np.max(np.abs(got - ref) / np.maximum(ref, 1e-38)) < 1e-6
+
+
+@pytest.mark.parametrize("name", ["producer_h6", "producer_h4"])
+def test_producer_matches_reference_processor(name):
+    """RMS norm + rotary embedding + head transpose against what the reference's processor passed
+    to attention_core_logic (fixtures made by tests/golden/make_golden.py producer).  The fixture's
+    norm ran under the Triton interpreter, whose in-kernel fp32 -> bf16 cast truncates; with that
+    one cast emulated the restatement is bit-identical up to the order of the sum of squares, and
+    with the GPU's round-to-nearest cast it moves the normed values by at most one bf16 ulp."""
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", name + ".npz"))
+    H = z["q"].shape[1]
+    cos, sin = torch.from_numpy(z["cos"]), torch.from_numpy(z["sin"])
+    for x, w, want in (("xq", "wq", "q"), ("xk", "wk", "k")):
+        xt, wt = torch.from_numpy(z[x]).bfloat16(), torch.from_numpy(z[w]).bfloat16()
+        got = O.qk_prep(xt, wt, float(z["eps"]), cos, sin, H, truncate_norm=True).float()
+        ref = torch.from_numpy(z[want])
+        # tolerance: >= 99.9 % of the elements bit-identical, the rest (a sum of squares added in
+        # another order can move one row's scale by an fp32 ulp) within two bf16 ulps
+        assert (got == ref).float().mean().item() >= 0.999, x
+        assert ((got - ref).abs() <= 2.0 ** -6 * ref.abs() + 1e-6).all(), x
+        near, trunc = O.rmsnorm_rows(xt, wt, float(z["eps"])).float(), O.rmsnorm_rows(xt, wt, float(z["eps"]), True).float()
+        ulp = torch.maximum(near.abs(), trunc.abs()) * 2.0 ** -7
+        assert ((near - trunc).abs() <= ulp).all()
+    got = O.qk_prep(torch.from_numpy(z["xv"]).bfloat16(), None, 0.0, None, None, H)
+    assert torch.equal(got.float(), torch.from_numpy(z["v"]))
