@@ -296,6 +296,8 @@ def run_gpu_arm(args, cfg):
         step_e2e()
     e2e_ms, _ = timed(step_e2e, args.steps)
 
+    producer = measure_producer(cfg, dev, peaks_hbm=measured_peaks()[0]["hbm_gbs"]) if world == 1 else None
+
     st = state["st"]
     rho = realised_density(st.block_map, st.q_offsets, st.k_offsets)
     flops = torch.tensor([cluster_flops_reference(cfg, len(mine)) + attention_flops(rho, N),
@@ -338,6 +340,7 @@ def run_gpu_arm(args, cfg):
             "e2e": {"value": flops_total / (e2e_ms / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": bytes_in, "d2h_bytes_per_step": bytes_out},
             "gpu_launches": int(launches),
+            "producer": producer,
             "exchange_status": (xchg.status() if xchg else 0),
             "clocks": clocks.summary(),
         }
@@ -349,6 +352,41 @@ def run_gpu_arm(args, cfg):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_producer(cfg, dev, peaks_hbm, reps=5):
+    """The step before the layer (RMS norm + rotary embedding + head transpose of the Q, K, V
+    projections, one kernel launch per tensor), timed on its own: not part of `value`."""
+    from svoo_b200 import ops
+    if cfg.text_tokens:
+        return None
+    H, S = cfg.heads, cfg.n_tokens
+    g = torch.Generator("cpu").manual_seed(3)
+    x = [torch.randn(S, H * D, generator=g, dtype=torch.float32).bfloat16().to(dev) for _ in range(3)]
+    w = [(1.0 + 0.1 * torch.randn(H * D, generator=g)).to(dev) for _ in range(2)]
+    ang = torch.rand(S, D // 2, generator=g) * 6.2831853
+    cos, sin = torch.cos(ang).repeat_interleave(2, -1).to(dev), torch.sin(ang).repeat_interleave(2, -1).to(dev)
+
+    def run():
+        ops.qk_prep(x[0], H, w[0], 1e-6, cos, sin)
+        ops.qk_prep(x[1], H, w[1], 1e-6, cos, sin)
+        ops.qk_prep(x[2], H)
+
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    nbytes = 3 * 2 * S * H * D * 2 + 2 * 2 * S * D * 4          # x read + y written per tensor; cos, sin for Q and K
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"what": "rmsnorm + rope + head transpose of the Q, K, V projections (3 launches)", "ms": ms,
+            "algorithmic_bytes": nbytes, "achieved": gbs, "peak": peaks_hbm, "unit": "GB/s", "frac": gbs / peaks_hbm,
+            "bound": "hbm"}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one sparse_attn launch per head of 75,600

@@ -20,7 +20,9 @@
 namespace svoo {
 
 constexpr int kPrepThreads = 256;
-constexpr int kPrepMaxChunks = 8;      // per thread: H * 128 / 8 / 256
+#ifndef SVOO_PREP_MINB
+#define SVOO_PREP_MINB 4
+#endif
 
 struct PrepDest {
   uint4* dst[16];       // [0] only when world == 0 (local [H, S, 128]); else every rank's [H/world, N, 128]
@@ -31,24 +33,49 @@ struct PrepDest {
   int64_t n_loc;        // tokens of this rank (== S); N = n_loc * world
 };
 
-__global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
+// CPT = chunks per thread (ceil(H * 16 / 256)).  For CPT <= 4 the norm weights and the rotary
+// tables of the thread's chunks are fetched together with the row, before the reduction, so the
+// CTA pays one memory latency instead of two.
+template <int CPT>
+__global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
                                                                float eps, const float* __restrict__ cosv,
                                                                const float* __restrict__ sinv, int64_t S, int H,
                                                                const __grid_constant__ PrepDest dest) {
+  constexpr bool kPrefetch = CPT <= 4;
   __shared__ float warp_sum[kPrepThreads / 32];
   __shared__ float rstd_s;
   const int64_t s = blockIdx.x;
   const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
   const int nchunks = H * 16;                                       // 16 chunks of 8 values per head
   const uint4* row = x + s * nchunks;
-  uint4 v[kPrepMaxChunks];
-  float ss = 0.f;
+  uint4 v[CPT];
+  float4 wv[kPrefetch ? CPT : 1][2], cv[kPrefetch ? CPT : 1][2], sv[kPrefetch ? CPT : 1][2];
 #pragma unroll
-  for (int u = 0; u < kPrepMaxChunks; ++u) {
+  for (int u = 0; u < CPT; ++u) {
     const int c = tid + u * kPrepThreads;
     if (c < nchunks) {
       v[u] = __ldcs(row + c);
-      if (weight) {
+      if (kPrefetch) {
+        if (weight) {
+          wv[u][0] = __ldg(reinterpret_cast<const float4*>(weight + c * 8));
+          wv[u][1] = __ldg(reinterpret_cast<const float4*>(weight + c * 8 + 4));
+        }
+        if (cosv) {
+          const int d0 = (c & 15) * 8;
+          cv[u][0] = __ldg(reinterpret_cast<const float4*>(cosv + s * kHeadDim + d0));
+          cv[u][1] = __ldg(reinterpret_cast<const float4*>(cosv + s * kHeadDim + d0 + 4));
+          sv[u][0] = __ldg(reinterpret_cast<const float4*>(sinv + s * kHeadDim + d0));
+          sv[u][1] = __ldg(reinterpret_cast<const float4*>(sinv + s * kHeadDim + d0 + 4));
+        }
+      }
+    }
+  }
+  float ss = 0.f;
+  if (weight) {
+#pragma unroll
+    for (int u = 0; u < CPT; ++u) {
+      const int c = tid + u * kPrepThreads;
+      if (c < nchunks) {
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -75,7 +102,7 @@ __global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const uint4* __re
     rstd = rstd_s;
   }
 #pragma unroll
-  for (int u = 0; u < kPrepMaxChunks; ++u) {
+  for (int u = 0; u < CPT; ++u) {
     const int c = tid + u * kPrepThreads;
     if (c >= nchunks) continue;
     const int h = c >> 4, d0 = (c & 15) * 8;
@@ -87,17 +114,19 @@ __global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const uint4* __re
       y[2 * i + 1] = __high2float(hin[i]);
     }
     if (weight) {
-      const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + c * 8));
-      const float4 w1 = __ldg(reinterpret_cast<const float4*>(weight + c * 8 + 4));
-      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      const float4 w0 = kPrefetch ? wv[kPrefetch ? u : 0][0] : __ldg(reinterpret_cast<const float4*>(weight + c * 8));
+      const float4 w1 = kPrefetch ? wv[kPrefetch ? u : 0][1] : __ldg(reinterpret_cast<const float4*>(weight + c * 8 + 4));
+      const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) y[i] = bf16_round(y[i] * rstd * wv[i]);          // the norm's output is bf16
+      for (int i = 0; i < 8; ++i) y[i] = bf16_round(y[i] * rstd * wf[i]);          // the norm's output is bf16
     }
     if (cosv) {
-      const float4 c0 = __ldg(reinterpret_cast<const float4*>(cosv + s * kHeadDim + d0));
-      const float4 c1 = __ldg(reinterpret_cast<const float4*>(cosv + s * kHeadDim + d0 + 4));
-      const float4 s0 = __ldg(reinterpret_cast<const float4*>(sinv + s * kHeadDim + d0));
-      const float4 s1 = __ldg(reinterpret_cast<const float4*>(sinv + s * kHeadDim + d0 + 4));
+      const float* cb = cosv + s * kHeadDim + d0;
+      const float* sb = sinv + s * kHeadDim + d0;
+      const float4 c0 = kPrefetch ? cv[kPrefetch ? u : 0][0] : __ldg(reinterpret_cast<const float4*>(cb));
+      const float4 c1 = kPrefetch ? cv[kPrefetch ? u : 0][1] : __ldg(reinterpret_cast<const float4*>(cb + 4));
+      const float4 s0 = kPrefetch ? sv[kPrefetch ? u : 0][0] : __ldg(reinterpret_cast<const float4*>(sb));
+      const float4 s1 = kPrefetch ? sv[kPrefetch ? u : 0][1] : __ldg(reinterpret_cast<const float4*>(sb + 4));
       const float ce[4] = {c0.x, c0.z, c1.x, c1.z};                                 // cos[..., 0::2]
       const float so[4] = {s0.y, s0.w, s1.y, s1.w};                                 // sin[..., 1::2]
 #pragma unroll
@@ -142,7 +171,13 @@ cudaError_t launch_qk_prep(const void* x, const float* weight, float eps, const 
     dest.dst[0] = (uint4*)out_local;
     dest.world = 0;
   }
-  qk_prep_kernel<<<(unsigned)S, kPrepThreads, 0, st>>>((const uint4*)x, weight, eps, cosv, sinv, S, H, dest);
+  const int cpt = ceil_div(H * 16, kPrepThreads);
+  const uint4* xp = (const uint4*)x;
+  if (cpt <= 1) qk_prep_kernel<1><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
+  else if (cpt == 2) qk_prep_kernel<2><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
+  else if (cpt == 3) qk_prep_kernel<3><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
+  else if (cpt == 4) qk_prep_kernel<4><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
+  else qk_prep_kernel<8><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
   count_launches(1);
   return cudaGetLastError();
 }
