@@ -33,9 +33,9 @@ struct PrepDest {
   int64_t n_loc;        // tokens of this rank (== S); N = n_loc * world
 };
 
-// CPT = chunks per thread (ceil(H * 16 / 256)).  For CPT <= 4 the norm weights and the rotary
-// tables of the thread's chunks are fetched together with the row, before the reduction, so the
-// CTA pays one memory latency instead of two.
+// One CTA per token, for rows too wide for the warp kernel below (H > 48).  CPT = chunks per
+// thread (ceil(H * 16 / 256)).  For CPT <= 4 the norm weights of the thread's chunks are fetched
+// together with the row, before the reduction, so the CTA pays one memory latency instead of two.
 template <int CPT>
 __global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
                                                                float eps, const float* __restrict__ cosv,
@@ -49,7 +49,18 @@ __global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(c
   const int nchunks = H * 16;                                       // 16 chunks of 8 values per head
   const uint4* row = x + s * nchunks;
   uint4 v[CPT];
-  float4 wv[kPrefetch ? CPT : 1][2], cv[kPrefetch ? CPT : 1][2], sv[kPrefetch ? CPT : 1][2];
+  float4 wv[kPrefetch ? CPT : 1][2];
+  // every chunk of a thread starts at the same head-dim offset ((tid + 256 u) & 15 == tid & 15), so
+  // the thread's rotary coefficients are fetched once
+  float ce[4] = {1.f, 1.f, 1.f, 1.f}, so[4] = {0.f, 0.f, 0.f, 0.f};
+  if (cosv) {
+    const float* cb = cosv + s * kHeadDim + (tid & 15) * 8;
+    const float* sb = sinv + s * kHeadDim + (tid & 15) * 8;
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cb)), c1 = __ldg(reinterpret_cast<const float4*>(cb + 4));
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sb)), s1 = __ldg(reinterpret_cast<const float4*>(sb + 4));
+    ce[0] = c0.x; ce[1] = c0.z; ce[2] = c1.x; ce[3] = c1.z;                        // cos[..., 0::2]
+    so[0] = s0.y; so[1] = s0.w; so[2] = s1.y; so[3] = s1.w;                        // sin[..., 1::2]
+  }
 #pragma unroll
   for (int u = 0; u < CPT; ++u) {
     const int c = tid + u * kPrepThreads;
@@ -59,13 +70,6 @@ __global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(c
         if (weight) {
           wv[u][0] = __ldg(reinterpret_cast<const float4*>(weight + c * 8));
           wv[u][1] = __ldg(reinterpret_cast<const float4*>(weight + c * 8 + 4));
-        }
-        if (cosv) {
-          const int d0 = (c & 15) * 8;
-          cv[u][0] = __ldg(reinterpret_cast<const float4*>(cosv + s * kHeadDim + d0));
-          cv[u][1] = __ldg(reinterpret_cast<const float4*>(cosv + s * kHeadDim + d0 + 4));
-          sv[u][0] = __ldg(reinterpret_cast<const float4*>(sinv + s * kHeadDim + d0));
-          sv[u][1] = __ldg(reinterpret_cast<const float4*>(sinv + s * kHeadDim + d0 + 4));
         }
       }
     }
@@ -105,7 +109,7 @@ __global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(c
   for (int u = 0; u < CPT; ++u) {
     const int c = tid + u * kPrepThreads;
     if (c >= nchunks) continue;
-    const int h = c >> 4, d0 = (c & 15) * 8;
+    const int h = c >> 4;
     const __nv_bfloat162* hin = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
     float y[8];
 #pragma unroll
@@ -121,14 +125,6 @@ __global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(c
       for (int i = 0; i < 8; ++i) y[i] = bf16_round(y[i] * rstd * wf[i]);          // the norm's output is bf16
     }
     if (cosv) {
-      const float* cb = cosv + s * kHeadDim + d0;
-      const float* sb = sinv + s * kHeadDim + d0;
-      const float4 c0 = kPrefetch ? cv[kPrefetch ? u : 0][0] : __ldg(reinterpret_cast<const float4*>(cb));
-      const float4 c1 = kPrefetch ? cv[kPrefetch ? u : 0][1] : __ldg(reinterpret_cast<const float4*>(cb + 4));
-      const float4 s0 = kPrefetch ? sv[kPrefetch ? u : 0][0] : __ldg(reinterpret_cast<const float4*>(sb));
-      const float4 s1 = kPrefetch ? sv[kPrefetch ? u : 0][1] : __ldg(reinterpret_cast<const float4*>(sb + 4));
-      const float ce[4] = {c0.x, c0.z, c1.x, c1.z};                                 // cos[..., 0::2]
-      const float so[4] = {s0.y, s0.w, s1.y, s1.w};                                 // sin[..., 1::2]
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float a = y[2 * i], b = y[2 * i + 1];
@@ -154,6 +150,108 @@ __global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(c
   }
 }
 
+// One WARP per token (rows of at most 24 * 32 chunks, i.e. H <= 48): the row lives in the
+// registers of 32 lanes (CPL chunks each), the sum of squares is a shuffle reduction, and nothing
+// waits on a block barrier, so many more bytes are in flight per SM than with one CTA per token.
+#ifndef SVOO_PREPW_MINB
+#define SVOO_PREPW_MINB 3
+#endif
+template <int CPL>
+__global__ void __launch_bounds__(128, SVOO_PREPW_MINB) qk_prep_warp_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
+                                                           float eps, const float* __restrict__ cosv,
+                                                           const float* __restrict__ sinv, int64_t S, int H,
+                                                           const __grid_constant__ PrepDest dest) {
+  const int lane = threadIdx.x % 32;
+  const int64_t s = (int64_t)blockIdx.x * 4 + threadIdx.x / 32;
+  if (s >= S) return;
+  const int nchunks = H * 16;
+  const uint4* row = x + s * nchunks;
+  uint4 v[CPL];
+#pragma unroll
+  for (int u = 0; u < CPL; ++u) {
+    const int c = lane + u * 32;
+    if (c < nchunks) v[u] = __ldcs(row + c);
+  }
+  float rstd = 1.f;
+  if (weight) {
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < CPL; ++u) {
+      const int c = lane + u * 32;
+      if (c < nchunks) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float a = __low2float(h[i]), b = __high2float(h[i]);
+          ss = fmaf(a, a, ss);
+          ss = fmaf(b, b, ss);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    rstd = 1.0f / sqrtf(ss / (float)(H * kHeadDim) + eps);
+  }
+  const int64_t N = dest.n_loc * (dest.world > 0 ? dest.world : 1);
+  // every chunk of a lane starts at the same head-dim offset ((lane + 32 u) & 15 == lane & 15), so
+  // the lane's rotary coefficients are fetched once per token
+  const int d0 = (lane & 15) * 8;
+  float ce[4] = {1.f, 1.f, 1.f, 1.f}, so[4] = {0.f, 0.f, 0.f, 0.f};
+  if (cosv) {
+    const float* cb = cosv + s * kHeadDim + d0;
+    const float* sb = sinv + s * kHeadDim + d0;
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cb)), c1 = __ldg(reinterpret_cast<const float4*>(cb + 4));
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sb)), s1 = __ldg(reinterpret_cast<const float4*>(sb + 4));
+    ce[0] = c0.x; ce[1] = c0.z; ce[2] = c1.x; ce[3] = c1.z;                        // cos[..., 0::2]
+    so[0] = s0.y; so[1] = s0.w; so[2] = s1.y; so[3] = s1.w;                        // sin[..., 1::2]
+  }
+#pragma unroll
+  for (int u = 0; u < CPL; ++u) {
+    const int c = lane + u * 32;
+    if (c >= nchunks) continue;
+    const int h = c >> 4;
+    const __nv_bfloat162* hin = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      y[2 * i] = __low2float(hin[i]);
+      y[2 * i + 1] = __high2float(hin[i]);
+    }
+    if (weight) {
+      const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + c * 8));
+      const float4 w1 = __ldg(reinterpret_cast<const float4*>(weight + c * 8 + 4));
+      const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = bf16_round(y[i] * rstd * wf[i]);
+    }
+    if (cosv) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a = y[2 * i], b = y[2 * i + 1];
+        y[2 * i] = __fsub_rn(__fmul_rn(a, ce[i]), __fmul_rn(b, so[i]));          // separate products and sum, as above
+        y[2 * i + 1] = __fadd_rn(__fmul_rn(a, so[i]), __fmul_rn(b, ce[i]));
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(y[0], y[1]);
+    o.y = pack_bf16x2(y[2], y[3]);
+    o.z = pack_bf16x2(y[4], y[5]);
+    o.w = pack_bf16x2(y[6], y[7]);
+    uint4* d;
+    if (dest.world == 0)
+      d = dest.dst[0] + ((int64_t)h * S + s) * 16;
+    else
+      d = dest.dst[dest.owner[h]] + ((int64_t)dest.slot[h] * N + (int64_t)dest.rank * dest.n_loc + s) * 16;
+    d[c & 15] = o;
+  }
+}
+
+template <int CPL>
+static void launch_prep_warp(const uint4* xp, const float* weight, float eps, const float* cosv, const float* sinv, int64_t S,
+                             int H, const PrepDest& dest, cudaStream_t st) {
+  qk_prep_warp_kernel<CPL><<<(unsigned)ceil_div64(S, 4), 128, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
+}
+
 cudaError_t launch_qk_prep(const void* x, const float* weight, float eps, const float* cosv, const float* sinv, int64_t S,
                            int H, void* out_local, void* const* peer_dst, const int32_t* owner, const int32_t* slot,
                            int world, int rank, cudaStream_t st) {
@@ -171,13 +269,19 @@ cudaError_t launch_qk_prep(const void* x, const float* weight, float eps, const 
     dest.dst[0] = (uint4*)out_local;
     dest.world = 0;
   }
-  const int cpt = ceil_div(H * 16, kPrepThreads);
   const uint4* xp = (const uint4*)x;
-  if (cpt <= 1) qk_prep_kernel<1><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
-  else if (cpt == 2) qk_prep_kernel<2><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
-  else if (cpt == 3) qk_prep_kernel<3><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
-  else if (cpt == 4) qk_prep_kernel<4><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
-  else qk_prep_kernel<8><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
+  const int cpl = ceil_div(H * 16, 32);                 // chunks per lane of the warp-per-token kernel
+  if (cpl <= 4) launch_prep_warp<4>(xp, weight, eps, cosv, sinv, S, H, dest, st);
+  else if (cpl <= 8) launch_prep_warp<8>(xp, weight, eps, cosv, sinv, S, H, dest, st);
+  else if (cpl <= 12) launch_prep_warp<12>(xp, weight, eps, cosv, sinv, S, H, dest, st);
+  else if (cpl <= 16) launch_prep_warp<16>(xp, weight, eps, cosv, sinv, S, H, dest, st);
+  else if (cpl <= 20) launch_prep_warp<20>(xp, weight, eps, cosv, sinv, S, H, dest, st);
+  else if (cpl <= 24) launch_prep_warp<24>(xp, weight, eps, cosv, sinv, S, H, dest, st);
+  else {                                                // wide rows: one CTA per token
+    const int cpt = ceil_div(H * 16, kPrepThreads);
+    if (cpt <= 4) qk_prep_kernel<4><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
+    else qk_prep_kernel<8><<<(unsigned)S, kPrepThreads, 0, st>>>(xp, weight, eps, cosv, sinv, S, H, dest);
+  }
   count_launches(1);
   return cudaGetLastError();
 }

@@ -413,11 +413,12 @@ def test_producer_against_oracle_and_reference(dev, name):
     assert torch.equal(v.float(), torch.from_numpy(z["v"])[0])
 
 
-def test_producer_full_width(dev):
-    """40 heads (5120 columns, the Wan-14B width) and a ragged token count against the oracle."""
+@pytest.mark.parametrize("S,H", [(777, 40), (130, 64), (65, 100), (33, 128), (5, 1)])
+def test_producer_full_width(dev, S, H):
+    """40 heads (5120 columns, the Wan-14B width; warp-per-token kernel), wider rows (CTA-per-token
+    kernel) and ragged token counts against the oracle."""
     ops = _mods()[0]
     g = torch.Generator("cpu").manual_seed(41)
-    S, H = 777, 40
     x = (torch.randn(1, S, H * 128, generator=g) * 1.7).bfloat16()
     w = (1.0 + 0.3 * torch.randn(H * 128, generator=g)).bfloat16()
     ang = torch.rand(S, 64, generator=g) * 6.2831853
