@@ -200,6 +200,21 @@ int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* ow
 int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int32_t world, int64_t n_loc,
                        int64_t H, int64_t D, void* stream);
 
+/* The whole layer in one call, for hosts that bind only one entry point: co-clustering
+ * (svoo_b200_cocluster), cluster-block map (svoo_b200_block_map; top_p >= 1 gives the all-ones
+ * map, svoo/co_clustering.py:575-576), cluster-order gathers of Q, K, V and the block-sparse
+ * attention with the inverse permutation fused into its store -- the sparse branch of
+ * attention_core_logic, svoo/models/wan/attention.py:1110-1216, for inputs without text tokens.
+ * q, k, v, out: [BH, S, D] bf16 in the original token order; init indices and the per-head
+ * preserve / cap arrays as in the calls it wraps.  Every intermediate lives in `scratch`
+ * (svoo_b200_layer_scratch_bytes) and stays valid after the call: permuted Q/K/V, labels,
+ * permutations, offsets, centroids, sizes, map, in that order, each 256-byte aligned. */
+int svoo_b200_layer_scratch_bytes(int64_t BH, int64_t S, int64_t QC, int64_t KC, int64_t* bytes_out);
+int svoo_b200_layer(const void* q, const void* k, const void* v, const int32_t* q_init_idx, const int32_t* k_init_idx,
+                    int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, int32_t iters, float top_p,
+                    const int32_t* preserve_host, const int32_t* cap_host, float sm_scale, void* out, void* scratch,
+                    int64_t scratch_bytes, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* The producer of the path's Q and K (and V), one pass over the projection output:
  *   y = bf16(x * rstd * weight), rstd = 1 / sqrt(mean_row(x^2) + eps)      if weight != NULL
  *       (triton_rmsnorm_forward, svoo/kernels/triton/rmsnorm.py:9-46, called from

@@ -46,6 +46,10 @@ SIGNATURES = {
     "svoo_b200_sparse_attn_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_int32, c_int64,
                                            c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+    "svoo_b200_layer_scratch_bytes": (c_int, [c_int64, c_int64, c_int64, c_int64, _I64P]),
+    "svoo_b200_layer": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                c_int32, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                                c_void_p]),
     "svoo_b200_qk_prep": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                   c_void_p]),
     "svoo_b200_qk_prep_push": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,

@@ -395,4 +395,82 @@ int svoo_b200_qk_prep_push(const void* x, const float* weight, float eps, const 
   return SVOO_OK;
 }
 
+// --------------------------------------------------------------------------------------------
+// The whole layer behind one call: every intermediate lives in a caller-provided scratch block.
+// --------------------------------------------------------------------------------------------
+namespace {
+struct LayerScratch {
+  int64_t qp, kp, vp, qlabels, klabels, qsorted, ksorted, qoff, koff, qcent, kcent, qsizes, ksizes, map, total;
+};
+LayerScratch layer_scratch_layout(int64_t BH, int64_t S, int64_t QC, int64_t KC) {
+  LayerScratch l{};
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    const int64_t at = off;
+    off += align_up(bytes, 256);
+    return at;
+  };
+  l.qp = take(BH * S * kRowBytes);
+  l.kp = take(BH * S * kRowBytes);
+  l.vp = take(BH * S * kRowBytes);
+  l.qlabels = take(BH * S * 4);
+  l.klabels = take(BH * S * 4);
+  l.qsorted = take(BH * S * 4);
+  l.ksorted = take(BH * S * 4);
+  l.qoff = take(BH * (QC + 1) * 4);
+  l.koff = take(BH * (KC + 1) * 4);
+  l.qcent = take(BH * QC * kRowBytes);
+  l.kcent = take(BH * KC * kRowBytes);
+  l.qsizes = take(BH * QC * 4);
+  l.ksizes = take(BH * KC * 4);
+  l.map = take(BH * QC * KC);
+  l.total = off;
+  return l;
+}
+}  // namespace
+
+int svoo_b200_layer_scratch_bytes(int64_t BH, int64_t S, int64_t QC, int64_t KC, int64_t* bytes_out) {
+  if (!bytes_out) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, S, kHeadDim));
+  SVOO_TRY(check_clusters(QC));
+  SVOO_TRY(check_clusters(KC));
+  *bytes_out = layer_scratch_layout(BH, S, QC, KC).total;
+  return SVOO_OK;
+}
+
+int svoo_b200_layer(const void* q, const void* k, const void* v, const int32_t* q_init_idx, const int32_t* k_init_idx,
+                    int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, int32_t iters, float top_p,
+                    const int32_t* preserve_host, const int32_t* cap_host, float sm_scale, void* out, void* scratch,
+                    int64_t scratch_bytes, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!scratch) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, S, D));
+  SVOO_TRY(check_clusters(QC));
+  SVOO_TRY(check_clusters(KC));
+  if (BH > SVOO_MAX_HEADS) return SVOO_ERR_SHAPE;
+  if (!aligned16(scratch)) return SVOO_ERR_ALIGN;
+  const LayerScratch l = layer_scratch_layout(BH, S, QC, KC);
+  if (scratch_bytes < l.total) return SVOO_ERR_WORKSPACE;
+  auto at = [&](int64_t off) { return static_cast<void*>(static_cast<char*>(scratch) + off); };
+  int32_t* qsorted = static_cast<int32_t*>(at(l.qsorted));
+  int32_t* ksorted = static_cast<int32_t*>(at(l.ksorted));
+  int32_t* qoff = static_cast<int32_t*>(at(l.qoff));
+  int32_t* koff = static_cast<int32_t*>(at(l.koff));
+  SVOO_TRY(svoo_b200_cocluster(q, k, q_init_idx, k_init_idx, BH, S, D, QC, KC, iters, static_cast<int32_t*>(at(l.qlabels)),
+                               static_cast<int32_t*>(at(l.klabels)), at(l.qcent), at(l.kcent),
+                               static_cast<int32_t*>(at(l.qsizes)), static_cast<int32_t*>(at(l.ksizes)), qsorted, qoff,
+                               ksorted, koff, workspace, workspace_bytes, stream));
+  uint8_t* map = static_cast<uint8_t*>(at(l.map));
+  if (top_p >= 1.0f) {
+    SVOO_CUDA(cudaMemsetAsync(map, 1, (size_t)(BH * QC * KC), (cudaStream_t)stream));
+  } else {
+    SVOO_TRY(svoo_b200_block_map(at(l.qcent), at(l.kcent), static_cast<int32_t*>(at(l.ksizes)), BH, QC, KC, D, top_p,
+                                 preserve_host, cap_host, map, stream));
+  }
+  SVOO_TRY(svoo_b200_permute(q, qsorted, BH, S, D, S, S, at(l.qp), stream));
+  SVOO_TRY(svoo_b200_permute(k, ksorted, BH, S, D, S, S, at(l.kp), stream));
+  SVOO_TRY(svoo_b200_permute(v, ksorted, BH, S, D, S, S, at(l.vp), stream));
+  return svoo_b200_sparse_attn(at(l.qp), at(l.kp), at(l.vp), map, qoff, koff, BH, S, D, QC, KC, sm_scale, out, qsorted,
+                               workspace, workspace_bytes, stream);
+}
+
 }  // extern "C"

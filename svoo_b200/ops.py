@@ -273,3 +273,28 @@ def qk_prep(x: torch.Tensor, heads: int, weight: Optional[torch.Tensor] = None, 
     check(LIB.svoo_b200_qk_prep(x.data_ptr(), 0 if w is None else w.data_ptr(), float(eps), 0 if c is None else c.data_ptr(),
                                 0 if s_ is None else s_.data_ptr(), S, heads, 128, out.data_ptr(), _stream()), "qk_prep")
     return out
+
+
+def layer(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_init_idx: torch.Tensor, k_init_idx: torch.Tensor,
+          iters: int, top_p: float, preserve: Sequence[int], cap: Sequence[int],
+          sm_scale: Optional[float] = None) -> torch.Tensor:
+    """The whole layer through the single C entry point svoo_b200_layer: q, k, v [BH, S, 128] bf16
+    in token order -> out [BH, S, 128].  Intermediates live in a scratch block that is released
+    with the returned tensor's call frame; use the separate ops when they are needed."""
+    _need_cuda(q, k, v, q_init_idx, k_init_idx)
+    BH, S, D = _tokens(q)
+    QC, KC = q_init_idx.shape[-1], k_init_idx.shape[-1]
+    if len(preserve) != BH or len(cap) != BH:
+        raise ValueError("preserve and cap need one entry per head")
+    nbytes = ctypes.c_int64(0)
+    check(LIB.svoo_b200_layer_scratch_bytes(BH, S, QC, KC, ctypes.byref(nbytes)), "layer_scratch_bytes")
+    scratch = torch.empty(nbytes.value, dtype=torch.uint8, device=q.device)
+    ws = workspace(q.device, BH, S, QC, KC)
+    out = torch.empty_like(q)
+    arr = ctypes.c_int32 * BH
+    qi, ki = q_init_idx.to(torch.int32).contiguous(), k_init_idx.to(torch.int32).contiguous()
+    check(LIB.svoo_b200_layer(q.data_ptr(), k.data_ptr(), v.data_ptr(), qi.data_ptr(), ki.data_ptr(), BH, S, D, QC, KC,
+                              int(iters), float(top_p), arr(*[int(x) for x in preserve]), arr(*[int(x) for x in cap]),
+                              D ** -0.5 if sm_scale is None else float(sm_scale), out.data_ptr(), scratch.data_ptr(),
+                              scratch.numel(), ws.data_ptr(), ws.numel(), _stream()), "layer")
+    return out

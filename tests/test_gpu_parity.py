@@ -477,6 +477,24 @@ def test_layer_against_oracle_and_reference(dev, name):
             assert diff[tok_ok].max() <= ATTN_ATOL
 
 
+def test_single_call_layer_equals_staged_layer(dev):
+    """svoo_b200_layer (one C call, caller-provided scratch) against the stage-by-stage layer."""
+    ops, cc, _, layer = _mods()
+    cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=3)
+    q, k, v = (t.to(dev) for t in synth.make_qkv(cfg))
+    qi, ki = (t.to(dev) for t in synth.init_indices(cfg))
+    dens = synth.head_densities(cfg)
+    want = layer.sparse_attention_layer(q, k, v, num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k,
+                                        kmeans_iters=cfg.iters, top_p=cfg.top_p, min_kc_ratio=dens, max_kc_ratio=dens,
+                                        init_indices=(qi, ki))
+    preserve, cap = cc.keep_limits(cfg.num_k, cfg.heads, dens, dens)
+    got = ops.layer(q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), qi, ki, cfg.iters, cfg.top_p, preserve, cap)
+    assert torch.equal(got, want[0])
+    dense = ops.layer(q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), qi, ki, 1, 1.0, preserve, cap)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())[0]
+    assert (dense.float() - ref).abs().max() <= ATTN_ATOL
+
+
 def test_layer_with_text_blocks(dev):
     """Hunyuan layout: video tokens clustered, 2 text blocks appended (prompt 40, unused 24)."""
     _, _, _, layer = _mods()
