@@ -209,6 +209,44 @@ def test_cocluster_teacher_forced_larger(dev):
     assert torch.equal(full.k_sorted_idx.cpu(), idx_ref) and torch.equal(full.k_offsets.cpu(), off_ref)
 
 
+def test_shipped_operating_point_256_1024(dev):
+    """The reference's shipped setting (256 query / 1024 key clusters, 2 iterations; the largest
+    cluster counts the library accepts) on one head of 32,760 tokens: one assignment step per side
+    against the oracle, the sort and the map bit-exact, the attention against the independent
+    mma.sync kernel."""
+    ops, cc, _, layer = _mods()
+    cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=1, num_q=256, num_k=1024, iters=2)
+    q, k, v = synth.make_qkv(cfg)
+    qi, ki = synth.init_indices(cfg)
+    D = 128
+    qc = torch.gather(q[0], 1, qi[..., None].expand(-1, -1, D))
+    kc = torch.gather(k[0], 1, ki[..., None].expand(-1, -1, D))
+    qd, kd, vd = q[0].to(dev), k[0].to(dev), v[0].to(dev)
+    kl_ref = _oracle_assign(k[0], qc, kc)
+    kl = ops.cocluster_assign(kd, qc.to(dev), kc.to(dev))
+    assert (kl.cpu().long() == kl_ref).float().mean() >= LABEL_AGREE
+    kc1, _ = O.centroid_update(k[0], kl_ref, kc)
+    ql_ref = _oracle_assign(q[0], kc1, qc)
+    ql = ops.cocluster_assign(qd, kc1.to(dev), qc.to(dev))
+    assert (ql.cpu().long() == ql_ref).float().mean() >= LABEL_AGREE
+    full = ops.cocluster(qd, kd, qi.to(dev), ki.to(dev), cfg.iters)
+    assert ops.cluster_status(dev, 1, cfg.n_video, 256, 1024) == 0
+    for lab, idx, off, K in ((full.qlabels, full.q_sorted_idx, full.q_offsets, 256),
+                             (full.klabels, full.k_sorted_idx, full.k_offsets, 1024)):
+        idx_ref, off_ref = O.sort_labels(lab.cpu().long(), K)
+        assert torch.equal(idx.cpu(), idx_ref) and torch.equal(off.cpu(), off_ref)
+    m_ref = O.identify_dynamic_map(full.qcentroids.cpu()[None], full.kcentroids.cpu()[None], full.qsizes.cpu()[None],
+                                   full.ksizes.cpu()[None], 0.9, 0.1, 0.1)
+    preserve, cap = cc.keep_limits(1024, 1, 0.1, 0.1)
+    m = ops.block_map(full.qcentroids, full.kcentroids, full.ksizes, 0.9, preserve, cap)
+    assert torch.equal(m.cpu().bool(), m_ref[0])
+    qp, kp, vp = ops.permute(qd, full.q_sorted_idx), ops.permute(kd, full.k_sorted_idx), ops.permute(vd, full.k_sorted_idx)
+    a = ops.sparse_attn(qp, kp, vp, m, full.q_offsets, full.k_offsets, out_row_idx=full.q_sorted_idx)
+    assert ops.attention_status(dev, 1, cfg.n_video, 256, 1024) == 0
+    b = ops.sparse_attn(qp, kp, vp, m, full.q_offsets, full.k_offsets, out_row_idx=full.q_sorted_idx, kernel="simt")
+    assert (a.float() - b.float()).abs().max() <= ATTN_ATOL and cosine(a, b) >= ATTN_COS
+
+
 # ----------------------------------------------------------------------------------------
 # cluster-block map: bit-exact given identical centroids and sizes
 # ----------------------------------------------------------------------------------------
