@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory from the UNMODIFIED reference.
 
 Run once, in a container that has the reference checkout (path in $SVOO_REFERENCE,
-default /root/reference):
+default: a directory `reference` beside this repository):
 
     python tests/golden/make_golden.py            # all fixtures (about 4 minutes)
     python tests/golden/make_golden.py layer_tiny_bf16   # just that one
@@ -20,8 +20,8 @@ import sys
 import time
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = os.environ.get("SVOO_REFERENCE", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("SVOO_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
