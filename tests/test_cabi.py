@@ -93,3 +93,29 @@ def test_tensor_core_kernels_do_not_spill():
         assert st == 0 and ld == 0, f"{name} spills {st}/{ld} bytes"
     for name, st, ld in spills("attn_tc.cu"):
         assert st <= 32, f"{name}: service branch spills {st} bytes"
+
+
+def test_header_is_plain_c_and_links(tmp_path):
+    """include/svoo_b200.h compiles as C99 (no C++ or torch types in the ABI) and a C program
+    links against the shared library."""
+    import shutil
+    import subprocess
+    from svoo_b200 import build
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "t.c"
+    src.write_text('#include "svoo_b200.h"\n#include <stdio.h>\n'
+                   'int main(void) { long long b = 0; int rc = svoo_b200_workspace_bytes(2, 4096, 32, 128, (int64_t*)&b);\n'
+                   '  printf("%d %d %lld\\n", svoo_b200_version(), rc, b); return rc; }\n')
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = tmp_path / "t"
+    lib_dir = os.path.dirname(build.LIB_PATH)
+    res = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(root, "include"),
+                          str(src), "-o", str(exe), "-L", lib_dir, "-l:libsvoo_b200.so", f"-Wl,-rpath,{lib_dir}"],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr
+    version, rc, nbytes = run.stdout.split()
+    assert int(version) == 100 and int(rc) == 0 and int(nbytes) > 0
