@@ -36,100 +36,150 @@ struct HeadLimits {
   int32_t cap[SVOO_MAX_HEADS];
 };
 
-__global__ void __launch_bounds__(256) block_map_kernel(const bf16* __restrict__ qc, const bf16* __restrict__ kc,
+// One CTA = 8 consecutive query clusters of one head, one warp each.  The score phase is shared:
+// a thread reads a key centroid once and accumulates its product with all 8 query centroids
+// (each (query, key) sum still runs over d in ascending order).  Everything after it -- exp,
+// the sequential sum, the sort, the sequential bf16 prefix sum -- is per query cluster and runs in
+// the 8 warps side by side, which is what the fixed summation orders leave to parallelise.
+constexpr int kMapRows = 8;
+
+__global__ void __launch_bounds__(256, 2) block_map_kernel(const bf16* __restrict__ qc, const bf16* __restrict__ kc,
                                                         const int32_t* __restrict__ ksizes, uint8_t* __restrict__ map,
                                                         int QC, int KC, int KCpad, float sqrt_d, float top_p,
                                                         const __grid_constant__ HeadLimits lim) {
-  __shared__ float q_s[kHeadDim];
-  __shared__ float val[SVOO_MAX_CLUSTERS];        // scores, then weighted exps, then bf16 prefix sums
-  __shared__ uint32_t key[SVOO_MAX_CLUSTERS];
-  __shared__ float red[8];
-  __shared__ float bcast;
-  const int i = blockIdx.x, bh = blockIdx.y, tid = threadIdx.x;
-  uint8_t* out = map + ((int64_t)bh * QC + i) * KC;
+  extern __shared__ __align__(16) unsigned char map_sm[];
+  float* q_s = reinterpret_cast<float*>(map_sm);                       // [8][128]
+  float* val = q_s + kMapRows * kHeadDim;                              // [8][KCpad]: scores, weighted exps, prefix sums
+  uint32_t* key = reinterpret_cast<uint32_t*>(val + kMapRows * KCpad); // [8][KCpad]
+  __shared__ float red[8][kMapRows];
+  const int i0 = blockIdx.x * kMapRows, bh = blockIdx.y, tid = threadIdx.x;
+  const int lane = tid % 32, warp = tid / 32;
   if (top_p >= 1.0f) {
-    for (int j = tid; j < KC; j += 256) out[j] = 1;
+    for (int r = 0; r < kMapRows && i0 + r < QC; ++r)
+      for (int j = tid; j < KC; j += 256) map[((int64_t)bh * QC + i0 + r) * KC + j] = 1;
     return;
   }
-  if (tid < kHeadDim) q_s[tid] = __bfloat162float(qc[((int64_t)bh * QC + i) * kHeadDim + tid]);
+  for (int t = tid; t < kMapRows * kHeadDim; t += 256) {
+    const int r = t / kHeadDim, d = t % kHeadDim;
+    q_s[t] = i0 + r < QC ? __bfloat162float(qc[((int64_t)bh * QC + i0 + r) * kHeadDim + d]) : 0.f;
+  }
   __syncthreads();
 
-  float lmax = -INFINITY;
+  float lmax[kMapRows];
+#pragma unroll
+  for (int r = 0; r < kMapRows; ++r) lmax[r] = -INFINITY;
   for (int j = tid; j < KC; j += 256) {
     const uint4* row = reinterpret_cast<const uint4*>(kc + ((int64_t)bh * KC + j) * kHeadDim);
-    float acc = 0.f;
-#pragma unroll 4
+    float acc[kMapRows];
+#pragma unroll
+    for (int r = 0; r < kMapRows; ++r) acc[r] = 0.f;
+#pragma unroll 2
     for (int c = 0; c < 16; ++c) {
       const uint4 v = __ldg(row + c);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+      float kv[8];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        acc = __fadd_rn(acc, __fmul_rn(q_s[c * 8 + 2 * e], __low2float(h[e])));
-        acc = __fadd_rn(acc, __fmul_rn(q_s[c * 8 + 2 * e + 1], __high2float(h[e])));
+        kv[2 * e] = __low2float(h[e]);
+        kv[2 * e + 1] = __high2float(h[e]);
+      }
+#pragma unroll
+      for (int r = 0; r < kMapRows; ++r) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[r] = __fadd_rn(acc[r], __fmul_rn(q_s[r * kHeadDim + c * 8 + e], kv[e]));
       }
     }
-    float s = bf16_round(acc);
-    s = bf16_round(__fdiv_rn(s, sqrt_d));
-    val[j] = s;
-    lmax = fmaxf(lmax, s);
+#pragma unroll
+    for (int r = 0; r < kMapRows; ++r) {
+      float sc = bf16_round(acc[r]);
+      sc = bf16_round(__fdiv_rn(sc, sqrt_d));
+      val[r * KCpad + j] = sc;
+      lmax[r] = fmaxf(lmax[r], sc);
+    }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
-  if (tid % 32 == 0) red[tid / 32] = lmax;
-  __syncthreads();
-  float mx = red[0];
+  for (int r = 0; r < kMapRows; ++r) {
 #pragma unroll
-  for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
-  for (int j = tid; j < KC; j += 256) {
-    const float e = exp_f32_fixed(__fsub_rn(val[j], mx));
-    val[j] = __fmul_rn((float)ksizes[(int64_t)bh * KC + j], e);
+    for (int o = 16; o > 0; o >>= 1) lmax[r] = fmaxf(lmax[r], __shfl_xor_sync(0xffffffffu, lmax[r], o));
+    if (lane == 0) red[warp][r] = lmax[r];
   }
   __syncthreads();
-  if (tid == 0) {
-    float tot = 0.f;
-    for (int j = 0; j < KC; ++j) tot = __fadd_rn(tot, val[j]);
-    bcast = fmaxf(tot, 1e-12f);
+
+  // ---- from here on: warp w works on query cluster i0 + w
+  const int i = i0 + warp;
+  if (i >= QC) return;
+  float* vw = val + warp * KCpad;
+  uint32_t* kw = key + warp * KCpad;
+  float mx = red[0][warp];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w][warp]);
+  for (int j = lane; j < KC; j += 32) {
+    const float e = exp_f32_fixed(__fsub_rn(vw[j], mx));
+    vw[j] = __fmul_rn((float)ksizes[(int64_t)bh * KC + j], e);
   }
-  __syncthreads();
-  const float tot = bcast;
-  for (int j = tid; j < KCpad; j += 256) {
+  __syncwarp();
+  float tot = 0.f;
+  if (lane == 0) {                                   // j ascending; four values per shared-memory read
+    int j = 0;
+    if (KCpad >= 4)
+      for (; j + 4 <= KC; j += 4) {
+        const float4 t4 = *reinterpret_cast<const float4*>(vw + j);
+        tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, t4.x), t4.y), t4.z), t4.w);
+      }
+    for (; j < KC; ++j) tot = __fadd_rn(tot, vw[j]);
+    tot = fmaxf(tot, 1e-12f);
+  }
+  tot = __shfl_sync(0xffffffffu, tot, 0);
+  for (int j = lane; j < KCpad; j += 32) {
     uint32_t kk = 0;
     if (j < KC) {
-      const bf16 pb = __float2bfloat16_rn(__fdiv_rn(val[j], tot));
+      const bf16 pb = __float2bfloat16_rn(__fdiv_rn(vw[j], tot));
       kk = ((uint32_t)__bfloat16_as_ushort(pb) << 16) | (uint32_t)(0xFFFF - j);
     }
-    key[j] = kk;
+    kw[j] = kk;
   }
-  __syncthreads();
-  // bitonic sort, descending
+  __syncwarp();
+  // bitonic sort, descending (keys are unique: the cluster index is part of the key)
   for (int k = 2; k <= KCpad; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = tid; t < KCpad; t += 256) {
+      for (int t = lane; t < KCpad; t += 32) {
         const int u = t ^ j;
         if (u > t) {
-          const uint32_t a = key[t], b = key[u];
+          const uint32_t a = kw[t], b = kw[u];
           const bool desc = (t & k) == 0;
-          if (desc ? (a < b) : (a > b)) { key[t] = b; key[u] = a; }
+          if (desc ? (a < b) : (a > b)) { kw[t] = b; kw[u] = a; }
         }
       }
-      __syncthreads();
+      __syncwarp();
     }
   }
-  if (tid == 0) {
+  if (lane == 0) {                                   // r ascending; padding keys are zero probabilities
     float run = 0.f;
-    for (int r = 0; r < KC; ++r) {
-      run = __fadd_rn(run, __bfloat162float(__ushort_as_bfloat16((unsigned short)(key[r] >> 16))));
-      val[r] = bf16_round(run);
+    int r = 0;
+    if (KCpad >= 4)
+      for (; r + 4 <= KCpad; r += 4) {
+        const uint4 k4 = *reinterpret_cast<const uint4*>(kw + r);
+        float4 o;
+        run = __fadd_rn(run, __uint_as_float(k4.x & 0xFFFF0000u)); o.x = bf16_round(run);
+        run = __fadd_rn(run, __uint_as_float(k4.y & 0xFFFF0000u)); o.y = bf16_round(run);
+        run = __fadd_rn(run, __uint_as_float(k4.z & 0xFFFF0000u)); o.z = bf16_round(run);
+        run = __fadd_rn(run, __uint_as_float(k4.w & 0xFFFF0000u)); o.w = bf16_round(run);
+        *reinterpret_cast<float4*>(vw + r) = o;
+      }
+    for (; r < KC; ++r) {
+      run = __fadd_rn(run, __uint_as_float(kw[r] & 0xFFFF0000u));
+      vw[r] = bf16_round(run);
     }
   }
-  __syncthreads();
+  __syncwarp();
   const float p_b = bf16_round(top_p);
   const int preserve = lim.preserve[bh], cap = lim.cap[bh];
-  for (int r = tid; r < KC; r += 256) {
-    bool remove = (r >= 1) && (val[r - 1] > p_b);
+  uint8_t* out = map + ((int64_t)bh * QC + i) * KC;
+  for (int r = lane; r < KC; r += 32) {
+    bool remove = (r >= 1) && (vw[r - 1] > p_b);
     if (r < preserve) remove = false;
     if (r >= cap) remove = true;
-    out[0xFFFF - (key[r] & 0xFFFFu)] = remove ? 0 : 1;
+    out[0xFFFF - (kw[r] & 0xFFFFu)] = remove ? 0 : 1;
   }
 }
 
@@ -231,9 +281,12 @@ cudaError_t launch_block_map(const void* qc, const void* kc, const int32_t* ksiz
   }
   int KCpad = 2;
   while (KCpad < KC) KCpad <<= 1;
-  dim3 grid((unsigned)QC, (unsigned)BH);
-  block_map_kernel<<<grid, 256, 0, st>>>((const bf16*)qc, (const bf16*)kc, ksizes, map, (int)QC, (int)KC, KCpad,
-                                         (float)sqrt((double)kHeadDim), top_p, lim);
+  const size_t smem = (size_t)kMapRows * (kHeadDim + 2 * KCpad) * 4;           // at most 68 KB (1024 clusters)
+  cudaError_t e = cudaFuncSetAttribute(block_map_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+  if (e != cudaSuccess) return e;
+  dim3 grid((unsigned)ceil_div64(QC, kMapRows), (unsigned)BH);
+  block_map_kernel<<<grid, 256, smem, st>>>((const bf16*)qc, (const bf16*)kc, ksizes, map, (int)QC, (int)KC, KCpad,
+                                            (float)sqrt((double)kHeadDim), top_p, lim);
   count_launches(1);
   return cudaGetLastError();
 }
