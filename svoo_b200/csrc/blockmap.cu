@@ -36,6 +36,62 @@ struct HeadLimits {
   int32_t cap[SVOO_MAX_HEADS];
 };
 
+// Bitonic sort (descending) of 32 * M keys held by one warp, element t in register t / 32 of lane
+// t % 32: partners at distance >= 32 are other registers of the same lane, closer ones come by
+// shuffle.  Keys are unique (the cluster index is part of the key) except for the zero padding.
+template <int M>
+__device__ __forceinline__ void warp_sort_desc(uint32_t (&v)[M], int lane) {
+#pragma unroll
+  for (int k = 2; k <= 32 * M; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j >= 32) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const int pm = m ^ (j >> 5);
+          if (pm > m) {
+            const bool desc = ((lane + 32 * m) & k) == 0;
+            const uint32_t a = v[m], b = v[pm];
+            if (desc ? (a < b) : (a > b)) { v[m] = b; v[pm] = a; }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const uint32_t a = v[m];
+          const uint32_t b = __shfl_xor_sync(0xffffffffu, a, j);
+          const bool lower = (lane & j) == 0;                      // this lane holds the smaller index of the pair
+          const bool desc = ((lane + 32 * m) & k) == 0;
+          v[m] = (lower == desc) ? max(a, b) : min(a, b);
+        }
+      }
+    }
+  }
+}
+
+// Keys of one query cluster: (bf16 probability << 16) | (0xFFFF - cluster index), sorted descending
+// into kw[0 .. KCpad).
+template <int M>
+__device__ __forceinline__ void make_sorted_keys(const float* vw, uint32_t* kw, float tot, int KC, int KCpad, int lane) {
+  uint32_t v[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const int j = lane + 32 * m;
+    uint32_t kk = 0;
+    if (j < KC) {
+      const bf16 pb = __float2bfloat16_rn(__fdiv_rn(vw[j], tot));
+      kk = ((uint32_t)__bfloat16_as_ushort(pb) << 16) | (uint32_t)(0xFFFF - j);
+    }
+    v[m] = kk;
+  }
+  warp_sort_desc<M>(v, lane);
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const int t = lane + 32 * m;
+    if (t < KCpad) kw[t] = v[m];
+  }
+}
+
 // One CTA = 8 consecutive query clusters of one head, one warp each.  The score phase is shared:
 // a thread reads a key centroid once and accumulates its product with all 8 query centroids
 // (each (query, key) sum still runs over d in ascending order).  Everything after it -- exp,
@@ -130,29 +186,15 @@ __global__ void __launch_bounds__(256, 2) block_map_kernel(const bf16* __restric
     tot = fmaxf(tot, 1e-12f);
   }
   tot = __shfl_sync(0xffffffffu, tot, 0);
-  for (int j = lane; j < KCpad; j += 32) {
-    uint32_t kk = 0;
-    if (j < KC) {
-      const bf16 pb = __float2bfloat16_rn(__fdiv_rn(vw[j], tot));
-      kk = ((uint32_t)__bfloat16_as_ushort(pb) << 16) | (uint32_t)(0xFFFF - j);
-    }
-    kw[j] = kk;
+  switch (KCpad <= 32 ? 1 : KCpad / 32) {           // registers per lane
+    case 1: make_sorted_keys<1>(vw, kw, tot, KC, KCpad, lane); break;
+    case 2: make_sorted_keys<2>(vw, kw, tot, KC, KCpad, lane); break;
+    case 4: make_sorted_keys<4>(vw, kw, tot, KC, KCpad, lane); break;
+    case 8: make_sorted_keys<8>(vw, kw, tot, KC, KCpad, lane); break;
+    case 16: make_sorted_keys<16>(vw, kw, tot, KC, KCpad, lane); break;
+    default: make_sorted_keys<32>(vw, kw, tot, KC, KCpad, lane); break;
   }
   __syncwarp();
-  // bitonic sort, descending (keys are unique: the cluster index is part of the key)
-  for (int k = 2; k <= KCpad; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = lane; t < KCpad; t += 32) {
-        const int u = t ^ j;
-        if (u > t) {
-          const uint32_t a = kw[t], b = kw[u];
-          const bool desc = (t & k) == 0;
-          if (desc ? (a < b) : (a > b)) { kw[t] = b; kw[u] = a; }
-        }
-      }
-      __syncwarp();
-    }
-  }
   if (lane == 0) {                                   // r ascending; padding keys are zero probabilities
     float run = 0.f;
     int r = 0;
