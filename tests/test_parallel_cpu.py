@@ -88,3 +88,26 @@ def test_exchange_tables_reproduce_the_all_to_all_layout():
     for rank in range(world):
         want = full[:, rank * n_loc:(rank + 1) * n_loc].transpose(1, 0, 2).reshape(n_loc * H, D)
         assert np.array_equal(seq[rank], want)
+
+
+def test_head_partition_properties():
+    """Every head exactly once, equal counts when H divides by P, deterministic, and the heaviest
+    rank never heavier than with contiguous blocks of heads."""
+    import random
+    from svoo_b200.parallel import head_partition
+    rnd = random.Random(3)
+    for H, P in ((40, 8), (40, 4), (24, 8), (12, 4), (7, 3), (5, 5)):
+        w = [rnd.uniform(0.05, 0.3) for _ in range(H)]
+        parts = head_partition(H, P, w)
+        assert parts == head_partition(H, P, w)
+        assert sorted(h for p in parts for h in p) == list(range(H))
+        sizes = sorted(len(p) for p in parts)
+        assert sizes[-1] - sizes[0] <= 1
+        load = max(sum(w[h] for h in p) for p in parts)
+        plain = head_partition(H, P)
+        assert load <= max(sum(w[h] for h in p) for p in plain) + 1e-12
+    # the bench configuration: 40 heads with the seeded density budget over 8 ranks
+    from svoo_b200 import synth
+    d = synth.head_densities(synth.CONFIGS["cfg2"])
+    loads = [sum(d[h] for h in p) for p in head_partition(40, 8, d)]
+    assert max(loads) / (sum(loads) / 8) < 1.01
