@@ -141,12 +141,14 @@ def cpu_layer_sample(cfg, head: int):
     d = synth.head_densities(cfg)[head]
     torch.set_num_threads(os.cpu_count() or 1)
     t0 = time.perf_counter()
-    if cfg.text_tokens:
-        raise NotImplementedError("CPU arm covers the Wan layer configs")
     out, aux = O.sparse_attention_layer(q, k, v, qi[head:head + 1], ki[head:head + 1], cfg.num_q, cfg.num_k, cfg.iters,
-                                        cfg.top_p, [d], [d])
+                                        cfg.top_p, [d], [d], cfg.text_tokens, cfg.text_tokens)
     dt = time.perf_counter() - t0
-    rho = O.realised_density(aux["map"], aux["qsizes"][None], aux["ksizes"][None])[0].tolist()
+    qs, ks = aux["qsizes"][None], aux["ksizes"][None]
+    if cfg.text_tokens:                                      # the two text blocks (prompt = all text tokens)
+        tail = torch.tensor([cfg.text_tokens, 0], dtype=qs.dtype).expand(1, 1, 2)
+        qs, ks = torch.cat([qs, tail], -1), torch.cat([ks, tail], -1)
+    rho = O.realised_density(aux["map"], qs, ks)[0].tolist()
     return dt, cluster_flops_reference(one, 1) + attention_flops(rho, cfg.n_tokens)
 
 
@@ -197,8 +199,8 @@ def run_gpu_arm(args, cfg):
         dist.init_process_group("nccl", device_id=dev)
 
     H, N = cfg.heads, cfg.n_tokens
-    if cfg.text_tokens and world > 1:
-        raise SystemExit("multi-GPU bench covers the Wan layer configs")
+    if N % world:
+        raise SystemExit(f"{N} tokens do not split evenly over {world} ranks")
     dens = synth.head_densities(cfg)
     parts = parallel.head_partition(H, world, dens if world > 1 else None)
     if world > 1 and len({len(p) for p in parts}) != 1:
@@ -298,6 +300,18 @@ def run_gpu_arm(args, cfg):
 
     producer = measure_producer(cfg, dev, peaks_hbm=measured_peaks()[0]["hbm_gbs"]) if world == 1 else None
 
+    parity = None
+    if world > 1:
+        # one untimed step through the library all-to-all path (torch.distributed all_to_all_single both ways,
+        # unfused store): the peer-store path must give the same bits
+        got = step().clone()
+        want = parallel.sparse_attention_layer_sharded(q_s, k_s, v_s, parts, densities=dens,
+                                                       init_indices=(qi_all.to(dev), ki_all.to(dev)), exchange=None, **kw)
+        same = torch.tensor([1 if torch.equal(got, want) else 0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        parity = {"vs": "nccl all_to_all path", "equal": bool(same.item())}
+        del got, want
+
     st = state["st"]
     rho = realised_density(st.block_map, st.q_offsets, st.k_offsets)
     flops = torch.tensor([cluster_flops_reference(cfg, len(mine)) + attention_flops(rho, N),
@@ -328,7 +342,8 @@ def run_gpu_arm(args, cfg):
                        "kmeans_iters": cfg.iters, "density_budget": list(cfg.density),
                        "realised_density_mean_rank0": sum(rho) / len(rho),
                        "parallelism": f"heads/{world}" + ("+peer-store re-shard" if world > 1 else ""),
-                       "l2": "inputs (2.3 GB of Q,K,V) are larger than L2; no flush between steps"},
+                       "l2": f"inputs ({3 * len(mine) * N * D * 2 / 1e9:.2f} GB of Q,K,V on rank 0) are larger than the 126 MB L2; "
+                             "no flush between steps"},
             "stage_ms_rank0": {k: round(v, 4) for k, v in stage.items()},
             "roofline": {"kernel": "sparse_attn", "bound": "tensor", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_kind} sustained bf16",
@@ -342,6 +357,7 @@ def run_gpu_arm(args, cfg):
             "gpu_launches": int(launches),
             "producer": producer,
             "exchange_status": (xchg.status() if xchg else 0),
+            "parity_check": parity,
             "clocks": clocks.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -352,6 +368,8 @@ def run_gpu_arm(args, cfg):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["equal"]:
+        raise SystemExit("the peer-store path and the all-to-all path disagree")
 
 
 def measure_producer(cfg, dev, peaks_hbm, reps=5):
@@ -359,7 +377,7 @@ def measure_producer(cfg, dev, peaks_hbm, reps=5):
     projections, one kernel launch per tensor), timed on its own: not part of `value`."""
     from svoo_b200 import ops
     if cfg.text_tokens:
-        return None
+        return None                                          # the Wan producer (norm over the whole projection row)
     H, S = cfg.heads, cfg.n_tokens
     g = torch.Generator("cpu").manual_seed(3)
     x = [torch.randn(S, H * D, generator=g, dtype=torch.float32).bfloat16().to(dev) for _ in range(3)]

@@ -7,6 +7,9 @@
  *   - Every pointer is a DEVICE pointer unless its name ends in `_host`.
  *   - Token tensors are bf16, row-major [BH, N, 128] (BH = batch*heads flattened,
  *     head dim D must be 128).  Labels, indices, sizes, offsets are int32.
+ *     bf16 is the only element type: there is no dtype argument, and a caller that
+ *     holds fp16 or fp32 activations casts them before the call (the Python front end
+ *     does that and casts results back).  BH * N must be below 2^31.
  *   - The library allocates nothing: outputs and the workspace are caller-owned.
  *     `stream` is a cudaStream_t passed as void*; all work is enqueued on it and
  *     no entry point synchronises with the host.
@@ -25,7 +28,7 @@
 extern "C" {
 #endif
 
-#define SVOO_B200_VERSION 100
+#define SVOO_B200_VERSION 101
 
 enum {
   SVOO_OK = 0,
@@ -39,6 +42,10 @@ enum {
 };
 
 #define SVOO_MAX_CLUSTERS 1024   /* per side; the reference ships QC=256, KC=1024 */
+/* Blocks per side that the attention-side entry points accept (svoo_b200_sparse_attn*,
+ * svoo_b200_offsets_from_sizes, svoo_b200_workspace_bytes): the clusters plus the two text
+ * blocks of a joint-attention layer. */
+#define SVOO_MAX_ATTN_CLUSTERS (SVOO_MAX_CLUSTERS + 2)
 #define SVOO_MAX_HEADS 256       /* BH limit of svoo_b200_block_map              */
 #define SVOO_BARRIER_CHANNELS 4  /* independent flag sets of svoo_b200_peer_barrier */
 
@@ -59,7 +66,11 @@ int svoo_b200_workspace_bytes(int64_t BH, int64_t N, int64_t QC, int64_t KC, int
  * centroid token indices, which the reference draws inside the call, are inputs.
  * Also returns the stable cluster-order permutation of each side (sorted_idx,
  * offsets[BH,K+1]), which the reference recomputes with torch.argsort in
- * svoo/kernels/triton/permute.py:90.  Centroids are bf16 [BH,K,128]. */
+ * svoo/kernels/triton/permute.py:90.  Centroids are bf16 [BH,K,128].
+ * Warm start (no counterpart in the reference, which re-draws the centroids at every call,
+ * svoo/models/wan/attention.py:641-647): with q_init_idx == NULL and k_init_idx == NULL the
+ * iterations start from the values already in qcentroids / kcentroids, for example the
+ * centroids of the previous denoising step. */
 int svoo_b200_cocluster(const void* q, const void* k,
                         const int32_t* q_init_idx, const int32_t* k_init_idx,
                         int64_t BH, int64_t N, int64_t D, int64_t QC, int64_t KC, int32_t iters,
@@ -76,6 +87,15 @@ int svoo_b200_cocluster(const void* q, const void* k,
 int svoo_b200_cocluster_assign(const void* x, const void* form_centroids, const void* own_centroids,
                                int64_t BH, int64_t N, int64_t D, int64_t K, int64_t J,
                                int32_t* labels, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Nearest centroid in Euclidean distance: labels[bh,n] = first argmin_j |x_n - c_j|^2 with the
+ * centroid norms taken as in the reference's kernel for bf16 inputs (every c_d^2 rounded to bf16,
+ * summed in fp32).  Replaces _euclid_assign_kernel / euclid_assign_triton
+ * (svoo/co_clustering.py:335-483), the assignment step of batch_kmeans_Euclid (:502-541); the
+ * reference's clamp of negative distances to zero is not applied (it only matters when a token
+ * is within rounding error of two distinct centroids).  centroids: bf16 [BH,K,128]. */
+int svoo_b200_euclid_assign(const void* x, const void* centroids, int64_t BH, int64_t N, int64_t D, int64_t K,
+                            int32_t* labels, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Stable counting sort of labels in [0,K): sorted_idx[BH,N] and offsets[BH,K+1]
  * (replaces torch.argsort in svoo/kernels/triton/permute.py:90 and torch.sort in
@@ -98,7 +118,10 @@ int svoo_b200_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int64_t 
  *   - All calls on one GPU share the one array.  It holds whatever the previous call left
  *     (the kernels overwrite every entry they later read, so no clearing is needed), and
  *     two calls that run concurrently on the same GPU -- different streams, or different
- *     host threads -- would overwrite each other's histograms: order them. */
+ *     host threads -- would overwrite each other's histograms: order them.
+ *   - The looked-up address is kept for the life of the process.  cudaDeviceReset() destroys the
+ *     context it belongs to, so a process that resets a device must not call this entry point
+ *     on that device afterwards. */
 int svoo_b200_sort_labels_static(const int32_t* labels, int64_t BH, int64_t N, int64_t K,
                                  int32_t* sorted_idx, int32_t* offsets, void* stream);
 
@@ -137,11 +160,15 @@ int svoo_b200_block_map(const void* qcentroids, const void* kcentroids, const in
  * without a selected key give 0.  q_offsets [BH,QC+1], k_offsets [BH,KC+1] are
  * the cluster row offsets.  If out_row_idx is not null the result row s is
  * written to row out_row_idx[bh,s] (the inverse permutation fused into the
- * store); otherwise to row s. */
+ * store); otherwise to row s.  QC, KC <= SVOO_MAX_ATTN_CLUSTERS.
+ * lse (may be NULL): fp32 [BH,S]; entry [bh,r], r the row the output row is written to, receives
+ * log2(sum_j exp(s_j * sm_scale)) over the selected keys -- the base-2 log-sum-exp that FlashInfer
+ * returns with return_lse=True and that the reference's error-aware merge consumes
+ * (svoo/co_clustering.py:1866-1868, 1998); -inf for a row without keys. */
 int svoo_b200_sparse_attn(const void* q, const void* k, const void* v, const uint8_t* map,
                           const int32_t* q_offsets, const int32_t* k_offsets,
                           int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, float sm_scale,
-                          void* out, const int32_t* out_row_idx,
+                          void* out, const int32_t* out_row_idx, float* lse,
                           void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Same contract as svoo_b200_sparse_attn, computed by the warp-level-MMA (mma.sync)
@@ -165,9 +192,22 @@ int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64
  * (the torch.cumsum of svoo/co_clustering.py:1147-1148). */
 int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, int32_t* offsets, void* stream);
 
-/* Multi-GPU re-sharding by stores into peer memory.  The reference runs on one GPU
- * (svoo/processor.py:60-200 receives all heads of the whole sequence); these two entry
- * points have no counterpart there.  They move [*,128] bf16 rows between the "sequence
+/* Text tokens of a joint-attention layer as two extra blocks (dynamic_map_post_processing,
+ * svoo/models/hunyuan10/attention.py:999-1019): `text` rows follow the N clustered video rows of
+ * every head; the first `prompt` of them form the "prompt" block, the rest the "unused prompt"
+ * block.  map [BH,QC,KC] -> map_out [BH,QC+2,KC+2] (prompt queries attend all video and prompt
+ * keys, all queries except the unused prompt attend the prompt keys, the unused prompt attends
+ * itself); offsets [BH,K+1] -> [BH,K+3]; sorted_idx [BH,N] -> [BH,N+text], identity on the text
+ * rows.  0 <= prompt <= text. */
+int svoo_b200_append_text_blocks(const uint8_t* map, const int32_t* q_offsets, const int32_t* k_offsets,
+                                 const int32_t* q_sorted_idx, const int32_t* k_sorted_idx, int64_t BH, int64_t N,
+                                 int64_t QC, int64_t KC, int64_t text, int64_t prompt, uint8_t* map_out,
+                                 int32_t* q_offsets_out, int32_t* k_offsets_out, int32_t* q_idx_out, int32_t* k_idx_out,
+                                 void* stream);
+
+/* Multi-GPU re-sharding by stores into peer memory.  The reference runs on one GPU (its
+ * processors, svoo/models/wan/attention.py:153-260, receive all heads of the whole sequence);
+ * these entry points have no counterpart there.  They move [*,128] bf16 rows between the "sequence
  * shard" layout of a sequence-parallel caller ([n_loc, H, 128] per rank, N = world *
  * n_loc tokens) and the "head shard" layout the path computes in ([H / world, N, 128]
  * per rank), over NVLink, with no wait on another GPU inside the kernels.
@@ -204,16 +244,21 @@ int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_h
  * (svoo_b200_cocluster), cluster-block map (svoo_b200_block_map; top_p >= 1 gives the all-ones
  * map, svoo/co_clustering.py:575-576), cluster-order gathers of Q, K, V and the block-sparse
  * attention with the inverse permutation fused into its store -- the sparse branch of
- * attention_core_logic, svoo/models/wan/attention.py:1110-1216, for inputs without text tokens.
- * q, k, v, out: [BH, S, D] bf16 in the original token order; init indices and the per-head
- * preserve / cap arrays as in the calls it wraps.  Every intermediate lives in `scratch`
- * (svoo_b200_layer_scratch_bytes) and stays valid after the call: permuted Q/K/V, labels,
- * permutations, offsets, centroids, sizes, map, in that order, each 256-byte aligned. */
-int svoo_b200_layer_scratch_bytes(int64_t BH, int64_t S, int64_t QC, int64_t KC, int64_t* bytes_out);
+ * attention_core_logic, svoo/models/wan/attention.py:1110-1216, and, with text > 0, of the joint
+ * attention of svoo/models/hunyuan10/attention.py:1031-1110 (the last `text` rows of every head
+ * are text tokens: never clustered, appended as the two blocks of svoo_b200_append_text_blocks).
+ * q, k, v, out: [BH, S, D] bf16 in the original token order, S = video tokens + text; init
+ * indices (into the video tokens) and the per-head preserve / cap arrays as in the calls it
+ * wraps.  Every intermediate lives in `scratch` (svoo_b200_layer_scratch_bytes) and stays valid
+ * after the call: permuted Q/K/V [BH,S,D], labels, permutations, offsets, centroids, sizes, map,
+ * then (text > 0 only) the padded map, offsets and row indices, each 256-byte aligned.  The
+ * workspace must cover svoo_b200_workspace_bytes(BH, S, QC + 2, KC + 2) when text > 0. */
+int svoo_b200_layer_scratch_bytes(int64_t BH, int64_t S, int64_t QC, int64_t KC, int64_t text, int64_t* bytes_out);
 int svoo_b200_layer(const void* q, const void* k, const void* v, const int32_t* q_init_idx, const int32_t* k_init_idx,
                     int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, int32_t iters, float top_p,
-                    const int32_t* preserve_host, const int32_t* cap_host, float sm_scale, void* out, void* scratch,
-                    int64_t scratch_bytes, void* workspace, int64_t workspace_bytes, void* stream);
+                    const int32_t* preserve_host, const int32_t* cap_host, float sm_scale, int64_t text, int64_t prompt,
+                    void* out, void* scratch, int64_t scratch_bytes, void* workspace, int64_t workspace_bytes,
+                    void* stream);
 
 /* The producer of the path's Q and K (and V), one pass over the projection output:
  *   y = bf16(x * rstd * weight), rstd = 1 / sqrt(mean_row(x^2) + eps)      if weight != NULL

@@ -137,6 +137,41 @@ def co_cluster_tokens(q, k, q_init_idx, k_init_idx, max_iters: int):
     return ql, qc, qs, kl, kc, ks
 
 
+def cocluster_assign_one_gemm(x, c, own) -> torch.Tensor:
+    """The same assignment in a different fp32 evaluation order: label = first argmax_j x . W_j with
+    W = l2norm(own . c^T) . c (the token's norm does not depend on j and the double sum is linear
+    in x).  Not a restatement of reference code: a second, equally valid fp32 implementation, kept
+    to measure how far two correct implementations drift apart over k-means iterations."""
+    pc = l2norm_rows(torch.matmul(own, c.transpose(-1, -2)))
+    w = torch.matmul(pc, c.float())
+    return torch.argmax(torch.matmul(x.float(), w.transpose(-1, -2)), dim=-1)
+
+
+def co_cluster_tokens_one_gemm(q, k, q_init_idx, k_init_idx, max_iters: int):
+    """co_cluster_tokens with cocluster_assign_one_gemm as the assignment step."""
+    B, N, D = q.shape
+    qc = torch.gather(q, 1, q_init_idx[..., None].expand(-1, -1, D))
+    kc = torch.gather(k, 1, k_init_idx[..., None].expand(-1, -1, D))
+    ql = kl = qs = ks = None
+    for _ in range(max_iters):
+        kl = cocluster_assign_one_gemm(k, qc, kc)
+        kc, ks = centroid_update(k, kl, kc)
+        ql = cocluster_assign_one_gemm(q, kc, qc)
+        qc, qs = centroid_update(q, ql, qc)
+    return ql, qc, qs, kl, kc, ks
+
+
+def clustering_objective(x, form, own, labels) -> float:
+    """Mean cosine between a token's profile over `form` and the profile of its own centroid: the
+    quantity the assignment maximises, a measure of a clustering that does not depend on which of
+    two near-tied centroids a token went to."""
+    pc = l2norm_rows(torch.matmul(own, form.transpose(-1, -2)))                  # [B,J,K]
+    prof = torch.matmul(x.float(), form.float().transpose(-1, -2))
+    prof = prof / profile_norm(x, form)[..., None]
+    mine = torch.gather(pc, 1, labels[..., None].expand(-1, -1, pc.shape[-1]))
+    return float((prof * mine).sum(-1).mean())
+
+
 # --------------------------------------------------------------------------------------
 # permutation
 # --------------------------------------------------------------------------------------
@@ -373,19 +408,75 @@ def realised_density(dyn_map, q_sizes, k_sizes) -> torch.Tensor:
     return torch.einsum("bhi,bhij,bhj->bh", qs, dyn_map.double(), ks) / (n * n)
 
 
+def attention_given_clustering(q, k, v, clustering, top_p, min_kc_ratio=0, max_kc_ratio=0, context_length=0,
+                                prompt_length=0):
+    """Everything after the clustering for [1,H,S,D] inputs whose last `context_length` rows are
+    text tokens: stable permute of the video rows, map (+ the two text blocks), masked attention,
+    inverse permute.  `clustering` = (qlabels, qcentroids, qsizes, klabels, kcentroids, ksizes) of the
+    video rows -- fresh, or cached from an earlier denoising step as the reference's processors reuse
+    it (wan/attention.py:682-715; hunyuan10/attention.py:977-1110).  Returns (out [1,H,S,D], aux)."""
+    ql, qc, qs, kl, kc, ks = clustering
+    B, H, S, D = q.shape
+    assert B == 1
+    n = S - context_length
+    num_q, num_k = qc.shape[1], kc.shape[1]
+    q_idx, q_off = sort_labels(ql, num_q)
+    k_idx, k_off = sort_labels(kl, num_k)
+    qp, kp, vp = permute(q[0, :, :n], q_idx), permute(k[0, :, :n], k_idx), permute(v[0, :, :n], k_idx)
+    m = identify_dynamic_map(qc[None], kc[None], qs[None], ks[None], top_p, min_kc_ratio, max_kc_ratio)
+    m_video = m
+    qs_b, ks_b, idx_full = qs[None], ks[None], q_idx
+    if context_length:
+        qp, kp, vp = (torch.cat([a, b[0, :, n:]], 1) for a, b in ((qp, q), (kp, k), (vp, v)))
+        m, qs_b, ks_b, idx_full = hunyuan_text_blocks(m, qs[None], ks[None], q_idx, n, context_length, prompt_length)
+    op = block_sparse_attention(qp[None], kp[None], vp[None], m, qs_b, ks_b)
+    out = inverse_permute(op[0], idx_full)[None]
+    return out, dict(qlabels=ql, klabels=kl, qcentroids=qc, kcentroids=kc, qsizes=qs, ksizes=ks, q_idx=q_idx,
+                     k_idx=k_idx, q_off=q_off, k_off=k_off, map=m, map_video=m_video, out_permuted=op)
+
+
 def sparse_attention_layer(q, k, v, q_init_idx, k_init_idx, num_q, num_k, iters, top_p,
-                           min_kc_ratio=0, max_kc_ratio=0):
-    """The whole path for [1,H,S,D] inputs: co-clustering -> stable permute -> map ->
-    masked attention -> inverse permute (wan/attention.py:958-1088,1159-1216).
+                           min_kc_ratio=0, max_kc_ratio=0, context_length=0, prompt_length=0):
+    """The whole path for [1,H,S,D] inputs: co-clustering (of the video rows) -> stable permute ->
+    map -> masked attention -> inverse permute (wan/attention.py:958-1088,1159-1216).
     Returns (out [1,H,S,D], dict of intermediates)."""
     B, H, S, D = q.shape
     assert B == 1
-    ql, qc, qs, kl, kc, ks = co_cluster_tokens(q[0], k[0], q_init_idx, k_init_idx, iters)
-    q_idx, q_off = sort_labels(ql, num_q)
-    k_idx, k_off = sort_labels(kl, num_k)
-    qp, kp, vp = permute(q[0], q_idx), permute(k[0], k_idx), permute(v[0], k_idx)
-    m = identify_dynamic_map(qc[None], kc[None], qs[None], ks[None], top_p, min_kc_ratio, max_kc_ratio)
-    op = block_sparse_attention(qp[None], kp[None], vp[None], m, qs[None], ks[None])
-    out = inverse_permute(op[0], q_idx)[None]
-    return out, dict(qlabels=ql, klabels=kl, qcentroids=qc, kcentroids=kc, qsizes=qs, ksizes=ks,
-                     q_idx=q_idx, k_idx=k_idx, q_off=q_off, k_off=k_off, map=m, out_permuted=op)
+    n = S - context_length
+    clustering = co_cluster_tokens(q[0, :, :n].contiguous(), k[0, :, :n].contiguous(), q_init_idx, k_init_idx, iters)
+    return attention_given_clustering(q, k, v, clustering, top_p, min_kc_ratio, max_kc_ratio, context_length,
+                                      prompt_length)
+
+
+# --------------------------------------------------------------------------------------
+# Euclidean k-means (the reference's non-co-clustering mode)
+# --------------------------------------------------------------------------------------
+def euclid_assign(x, centroids):
+    """first argmin_j max(|x|^2 + |c_j|^2 - 2 x.c_j, 0) (co_clustering.py:335-416).  For bf16 inputs the
+    squares are rounded to bf16 before they are summed, as `c_tile * c_tile` and `x ** 2` are there;
+    the token norm is rounded to bf16 once more (torch.sum of a bf16 tensor, :516)."""
+    lowp = x.dtype == torch.bfloat16
+    sq = (lambda t: (t * t).float()) if lowp else (lambda t: t.float() * t.float())
+    x_sq = sq(x).sum(-1)
+    if lowp:
+        x_sq = x_sq.bfloat16().float()
+    c_sq = sq(centroids).sum(-1)
+    cross = torch.matmul(x.float(), centroids.float().transpose(-1, -2))
+    dist = (x_sq[..., None] + c_sq[..., None, :] - 2.0 * cross).clamp_min(0.0)
+    return torch.argmin(dist, dim=-1)
+
+
+def batch_kmeans_euclid(x, init_centroids, max_iters, tol=1e-4):
+    """batch_kmeans_Euclid from given initial centroids (co_clustering.py:502-541): returns
+    (labels, centroids, sizes, iterations); on a `tol` stop the centroids of the last assignment."""
+    centroids = init_centroids
+    labels = sizes = None
+    it = -1
+    for it in range(max_iters):
+        labels = euclid_assign(x, centroids)
+        new, sizes = centroid_update(x, labels, centroids)
+        shift = (new.float() - centroids.float()).norm(dim=-1).max()
+        if shift < tol:
+            break
+        centroids = new
+    return labels, centroids, sizes, it + 1

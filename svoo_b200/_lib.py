@@ -25,6 +25,11 @@ SIGNATURES = {
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "svoo_b200_cocluster_assign": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                            c_void_p, c_void_p, c_int64, c_void_p]),
+    "svoo_b200_euclid_assign": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64,
+                                        c_void_p]),
+    "svoo_b200_append_text_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                             c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p]),
     "svoo_b200_sort_labels": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                       c_void_p]),
     "svoo_b200_sort_labels_static": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
@@ -36,7 +41,7 @@ SIGNATURES = {
     "svoo_b200_block_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float,
                                     _I32P, _I32P, c_void_p, c_void_p]),
     "svoo_b200_sparse_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
-                                      c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
+                                      c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                       c_void_p]),
     "svoo_b200_sparse_attn_simt": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
@@ -46,10 +51,10 @@ SIGNATURES = {
     "svoo_b200_sparse_attn_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_int32, c_int64,
                                            c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
-    "svoo_b200_layer_scratch_bytes": (c_int, [c_int64, c_int64, c_int64, c_int64, _I64P]),
+    "svoo_b200_layer_scratch_bytes": (c_int, [c_int64, c_int64, c_int64, c_int64, c_int64, _I64P]),
     "svoo_b200_layer": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
-                                c_int32, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
-                                c_void_p]),
+                                c_int32, c_float, c_void_p, c_void_p, c_float, c_int64, c_int64, c_void_p, c_void_p, c_int64,
+                                c_void_p, c_int64, c_void_p]),
     "svoo_b200_qk_prep": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                   c_void_p]),
     "svoo_b200_qk_prep_push": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
@@ -59,6 +64,9 @@ SIGNATURES = {
                                      c_void_p]),
     "svoo_b200_push_seq": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p]),
 }
+
+
+VERSION = 101          # SVOO_B200_VERSION of include/svoo_b200.h this binding was written for
 
 
 class SvooB200Error(RuntimeError):
@@ -78,8 +86,8 @@ def _load() -> ctypes.CDLL:
             raise ImportError(f"{path} does not export {name}; rebuild it")
         fn.restype = res
         fn.argtypes = args
-    if lib.svoo_b200_version() != 100:
-        raise ImportError(f"{path} is version {lib.svoo_b200_version()}, expected 100; rebuild it")
+    if lib.svoo_b200_version() != VERSION:
+        raise ImportError(f"{path} is version {lib.svoo_b200_version()}, expected {VERSION}; rebuild it")
     return lib
 
 

@@ -46,8 +46,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Compile every .cu under csrc/ into one shared library; returns its path."""
     if not force and not is_stale():
         return LIB_PATH
-    extra = os.environ.get("SVOO_B200_NVCC_EXTRA", "").split()      # experiments: extra -D switches
-    cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + sources()
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + sources()
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

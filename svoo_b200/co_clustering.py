@@ -29,11 +29,17 @@ def draw_init_indices(BH: int, N: int, num_q: int, num_k: int, device, generator
 
 
 def co_cluster(q_flat: torch.Tensor, k_flat: torch.Tensor, num_q_centroids: int, num_k_centroids: int,
-               max_iters: int = 10, *, init_indices=None, generator=None) -> ops.Clustering:
+               max_iters: int = 10, *, init_indices=None, generator=None, init_centroids=None) -> ops.Clustering:
     """co_cluster_tokens returning the full device-side result (labels, centroids, sizes and
-    the stable cluster-order permutations), everything int32 / bf16."""
+    the stable cluster-order permutations), everything int32 / bf16.  `init_centroids` =
+    (q centroids, k centroids) starts from those instead of drawing tokens (warm start; the
+    reference always draws, svoo/models/wan/attention.py:641-647)."""
     assert q_flat.is_cuda and k_flat.is_cuda, "tensors must be on CUDA"
     BH, N, D = q_flat.shape
+    if init_centroids is not None:
+        qc0, kc0 = init_centroids
+        return ops.cocluster(_as_bf16(q_flat).contiguous(), _as_bf16(k_flat).contiguous(), None, None, max_iters,
+                             init_centroids=(_as_bf16(qc0).contiguous(), _as_bf16(kc0).contiguous()))
     if init_indices is None:
         init_indices = draw_init_indices(BH, N, num_q_centroids, num_k_centroids, q_flat.device, generator)
     q_idx, k_idx = init_indices
@@ -50,6 +56,54 @@ def co_cluster_tokens(q_flat, k_flat, num_q_centroids, num_k_centroids, max_iter
                    generator=generator)
     dt = q_flat.dtype
     return (c.qlabels.long(), c.qcentroids.to(dt), c.qsizes, c.klabels.long(), c.kcentroids.to(dt), c.ksizes)
+
+
+def euclid_assign_triton(x: torch.Tensor, centroids: torch.Tensor, x_sq: Optional[torch.Tensor] = None,
+                         out: Optional[torch.Tensor] = None, **_tile_sizes) -> torch.Tensor:
+    """Nearest-centroid labels [B, N] int64 (svoo/co_clustering.py:420-483).  `x_sq` (the token
+    norms) does not change the argmin and is ignored; tile-size keywords are accepted and unused."""
+    assert x.is_cuda and centroids.is_cuda, "All tensors must be on CUDA"
+    assert centroids.dtype == x.dtype, "centroids dtype mismatch"
+    B, N, D = x.shape
+    assert centroids.shape == (B, centroids.shape[1], D), "centroids shape mismatch"
+    lab = ops.euclid_assign(_as_bf16(x).contiguous(), _as_bf16(centroids).contiguous()).long()
+    if out is not None:
+        out.copy_(lab)
+        return out
+    return lab
+
+
+def batch_kmeans_Euclid(x, n_clusters, max_iters=100, tol=1e-4, init_centroids=None, verbose=False, *,
+                        init_indices=None, generator=None):
+    """Batched Euclidean k-means with the reference's loop (svoo/co_clustering.py:502-541):
+    assign, centroid update, stop when the largest centroid shift is below `tol` (one host read
+    per iteration, as there).  Returns (cluster_ids int64 [B,N], centroids [B,K,D],
+    cluster_sizes int32 [B,K], iterations run).  As in the reference the returned centroids
+    are the ones the last assignment used when the loop stops on `tol`, else the updated ones."""
+    assert x.is_cuda, "tensors must be on CUDA"
+    B, N, D = x.shape
+    xb = _as_bf16(x).contiguous()
+    if init_centroids is None:
+        if init_indices is None:
+            init_indices = torch.randint(0, N, (B, n_clusters), device=x.device, generator=generator)
+        centroids = torch.gather(xb, 1, init_indices.to(x.device)[..., None].expand(-1, -1, D))
+    else:
+        centroids = _as_bf16(init_centroids)
+    centroids = centroids.reshape(B, n_clusters, D).contiguous()
+    cluster_ids = cluster_sizes = None
+    it = -1
+    for it in range(max_iters):
+        labels = ops.euclid_assign(xb, centroids)
+        idx, off = ops.sort_labels(labels, n_clusters)
+        new, cluster_sizes = ops.centroid_update(xb, idx, off, centroids)
+        cluster_ids = labels
+        shift = (new.float() - centroids.float()).norm(dim=-1).max()
+        if verbose:
+            print(f"Iter {it}, center shift: {shift.item():.6f}")
+        if shift < tol:
+            break
+        centroids = new
+    return cluster_ids.long(), centroids.to(x.dtype), cluster_sizes, it + 1
 
 
 def _ratio_values(r: Ratio, H: int):

@@ -19,7 +19,12 @@ cudaError_t launch_build_runs(const uint8_t*, const int32_t*, int2*, int32_t*, i
 cudaError_t launch_build_qtiles(const int32_t*, int4*, int32_t*, int64_t, int64_t, int64_t, int, cudaStream_t);
 cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, void*, const int32_t*, const int4*,
                                   const int32_t*, const int2*, const int32_t*, int32_t*, int64_t, int64_t, int64_t,
-                                  int64_t, float, void* const*, const int32_t*, int, int64_t, int, cudaStream_t);
+                                  int64_t, float, void* const*, const int32_t*, int, int64_t, int, float*, cudaStream_t);
+cudaError_t launch_euclid_assign_tc(const void*, const void*, float*, int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t,
+                                    int32_t*, cudaStream_t);
+cudaError_t launch_append_text_blocks(const uint8_t*, const int32_t*, const int32_t*, const int32_t*, const int32_t*,
+                                      uint8_t*, int32_t*, int32_t*, int32_t*, int32_t*, int64_t, int64_t, int64_t, int64_t,
+                                      int64_t, int64_t, cudaStream_t);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, void*, const int32_t*, const int4*,
                                    const int32_t*, const int2*, const int32_t*, int64_t, int64_t, int64_t, int64_t,
                                    float, cudaStream_t);
@@ -46,11 +51,18 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int check_tokens(int64_t BH, int64_t N, int64_t D) {
   if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
   if (BH < 1 || BH > 65535 || N < 1 || N > (1 << 24)) return SVOO_ERR_SHAPE;
+  if (BH * N > (int64_t)INT32_MAX) return SVOO_ERR_SHAPE;         // the kernels index token rows with 32-bit ints
   return SVOO_OK;
 }
 int check_clusters(int64_t K) {
   if (K < 1) return SVOO_ERR_SHAPE;
   if (K > SVOO_MAX_CLUSTERS) return SVOO_ERR_CLUSTERS;
+  return SVOO_OK;
+}
+// attention side: the clusters plus the two text blocks of a joint-attention layer
+int check_attn_clusters(int64_t K) {
+  if (K < 1) return SVOO_ERR_SHAPE;
+  if (K > SVOO_MAX_ATTN_CLUSTERS) return SVOO_ERR_CLUSTERS;
   return SVOO_OK;
 }
 #define SVOO_TRY(expr) do { int _rc = (expr); if (_rc != SVOO_OK) return _rc; } while (0)
@@ -74,7 +86,7 @@ const char* svoo_b200_error_string(int code) {
     case SVOO_ERR_HEAD_DIM: return "head dimension must be 128";
     case SVOO_ERR_WORKSPACE: return "workspace too small";
     case SVOO_ERR_ALIGN: return "tensor pointer is not 16-byte aligned";
-    case SVOO_ERR_CLUSTERS: return "cluster count above 1024";
+    case SVOO_ERR_CLUSTERS: return "cluster count above 1024 (1026 blocks for the attention)";
     case SVOO_ERR_STATIC_SCRATCH: return "problem too large for the built-in scratch array (BH*ceil(N/2048)*K > 1048576)";
     default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown svoo_b200 error";
   }
@@ -83,8 +95,8 @@ const char* svoo_b200_error_string(int code) {
 int svoo_b200_workspace_bytes(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* bytes_out) {
   if (!bytes_out) return SVOO_ERR_NULL;
   SVOO_TRY(check_tokens(BH, N, kHeadDim));
-  SVOO_TRY(check_clusters(QC));
-  SVOO_TRY(check_clusters(KC));
+  SVOO_TRY(check_attn_clusters(QC));
+  SVOO_TRY(check_attn_clusters(KC));
   *bytes_out = workspace_layout(BH, N, QC, KC).total;
   return SVOO_OK;
 }
@@ -107,6 +119,22 @@ int svoo_b200_cocluster_assign(const void* x, const void* form_centroids, const 
   SVOO_CUDA(launch_assign_tc(x, ws_at<void>(workspace, w.w_hi), ws_at<void>(workspace, w.w_lo), labels,
                              ws_at<int2>(workspace, w.assign_partial), ws_at<int32_t>(workspace, w.status) + 1, BH, N, J, nullptr,
                              st));
+  return SVOO_OK;
+}
+
+int svoo_b200_euclid_assign(const void* x, const void* centroids, int64_t BH, int64_t N, int64_t D, int64_t K,
+                            int32_t* labels, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!x || !centroids || !labels || !workspace) return SVOO_ERR_NULL;
+  SVOO_TRY(check_tokens(BH, N, D));
+  SVOO_TRY(check_clusters(K));
+  if (!aligned16(x) || !aligned16(centroids) || !aligned16(workspace)) return SVOO_ERR_ALIGN;
+  const Workspace w = workspace_layout(BH, N, K, K);
+  if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t* status = ws_at<int32_t>(workspace, w.status) + 1;
+  SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));
+  SVOO_CUDA(launch_euclid_assign_tc(x, centroids, ws_at<float>(workspace, w.w_hi), labels,
+                                    ws_at<int2>(workspace, w.assign_partial), status, BH, N, K, nullptr, st));
   return SVOO_OK;
 }
 
@@ -142,9 +170,10 @@ int svoo_b200_cocluster(const void* q, const void* k, const int32_t* q_init_idx,
                         int32_t* klabels, void* qcentroids, void* kcentroids, int32_t* qsizes, int32_t* ksizes,
                         int32_t* q_sorted_idx, int32_t* q_offsets, int32_t* k_sorted_idx, int32_t* k_offsets,
                         void* workspace, int64_t workspace_bytes, void* stream) {
-  if (!q || !k || !q_init_idx || !k_init_idx || !qlabels || !klabels || !qcentroids || !kcentroids || !qsizes ||
-      !ksizes || !q_sorted_idx || !q_offsets || !k_sorted_idx || !k_offsets || !workspace)
+  if (!q || !k || !qlabels || !klabels || !qcentroids || !kcentroids || !qsizes || !ksizes || !q_sorted_idx ||
+      !q_offsets || !k_sorted_idx || !k_offsets || !workspace)
     return SVOO_ERR_NULL;
+  if ((q_init_idx == nullptr) != (k_init_idx == nullptr)) return SVOO_ERR_NULL;   // both (fresh start) or neither (warm start)
   SVOO_TRY(check_tokens(BH, N, D));
   SVOO_TRY(check_clusters(QC));
   SVOO_TRY(check_clusters(KC));
@@ -162,8 +191,10 @@ int svoo_b200_cocluster(const void* q, const void* k, const int32_t* q_init_idx,
   int32_t* status = ws_at<int32_t>(workspace, w.status) + 1;       // word 1: assignment kernel
 
   SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));
-  SVOO_CUDA(launch_gather_rows(q, q_init_idx, qcentroids, BH, N, QC, st));
-  SVOO_CUDA(launch_gather_rows(k, k_init_idx, kcentroids, BH, N, KC, st));
+  if (q_init_idx) {
+    SVOO_CUDA(launch_gather_rows(q, q_init_idx, qcentroids, BH, N, QC, st));
+    SVOO_CUDA(launch_gather_rows(k, k_init_idx, kcentroids, BH, N, KC, st));
+  }
   for (int it = 0; it < iters; ++it) {
     // keys: profile over the query centroids
     SVOO_CUDA(launch_prologue(kcentroids, qcentroids, w_hi, w_lo, BH, KC, QC, st));
@@ -216,7 +247,7 @@ int svoo_b200_block_map(const void* qcentroids, const void* kcentroids, const in
 int svoo_b200_offsets_from_sizes(const int32_t* sizes, int64_t BH, int64_t K, int32_t* offsets, void* stream) {
   if (!sizes || !offsets) return SVOO_ERR_NULL;
   if (BH < 1 || BH > 65535) return SVOO_ERR_SHAPE;
-  SVOO_TRY(check_clusters(K));
+  SVOO_TRY(check_attn_clusters(K));
   SVOO_CUDA(launch_offsets_from_sizes(sizes, offsets, BH, K, (cudaStream_t)stream));
   return SVOO_OK;
 }
@@ -239,11 +270,13 @@ static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, cons
                             const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
                             int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx,
                             void* workspace, int64_t workspace_bytes, void* stream, void* const* peer_dst = nullptr,
-                            const int32_t* my_heads = nullptr, int world = 0, int64_t n_loc = 0, int H = 0) {
+                            const int32_t* my_heads = nullptr, int world = 0, int64_t n_loc = 0, int H = 0,
+                            float* lse = nullptr) {
   if (!q || !k || !v || !map || !q_offsets || !k_offsets || (!out && !peer_dst) || !workspace) return SVOO_ERR_NULL;
   SVOO_TRY(check_tokens(BH, S, D));
-  SVOO_TRY(check_clusters(QC));
-  SVOO_TRY(check_clusters(KC));
+  SVOO_TRY(check_attn_clusters(QC));
+  SVOO_TRY(check_attn_clusters(KC));
+  if (lse && !tensor_core) return SVOO_ERR_SHAPE;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(workspace))
     return SVOO_ERR_ALIGN;
   if (!tensor_core && peer_dst) return SVOO_ERR_SHAPE;
@@ -260,7 +293,7 @@ static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, cons
   if (tensor_core) {
     SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));                     // word 0: attention kernel
     SVOO_CUDA(launch_sparse_attn_tc(q, k, v, out, out_row_idx, qtiles, nqtiles, runs, nruns, status, BH, S, QC, KC,
-                                    sm_scale, peer_dst, my_heads, world, n_loc, H, st));
+                                    sm_scale, peer_dst, my_heads, world, n_loc, H, lse, st));
   } else {
     SVOO_CUDA(launch_sparse_attn_mma(q, k, v, out, out_row_idx, qtiles, nqtiles, runs, nruns, BH, S, QC, KC, sm_scale,
                                      st));
@@ -270,10 +303,10 @@ static int sparse_attn_impl(bool tensor_core, const void* q, const void* k, cons
 
 int svoo_b200_sparse_attn(const void* q, const void* k, const void* v, const uint8_t* map, const int32_t* q_offsets,
                           const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC,
-                          float sm_scale, void* out, const int32_t* out_row_idx, void* workspace,
+                          float sm_scale, void* out, const int32_t* out_row_idx, float* lse, void* workspace,
                           int64_t workspace_bytes, void* stream) {
   return sparse_attn_impl(true, q, k, v, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, out, out_row_idx,
-                          workspace, workspace_bytes, stream);
+                          workspace, workspace_bytes, stream, nullptr, nullptr, 0, 0, 0, lse);
 }
 
 int svoo_b200_sparse_attn_push(const void* q, const void* k, const void* v, const uint8_t* map,
@@ -304,8 +337,8 @@ int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, cons
 int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* offset_out) {
   if (!offset_out) return SVOO_ERR_NULL;
   SVOO_TRY(check_tokens(BH, N, kHeadDim));
-  SVOO_TRY(check_clusters(QC));
-  SVOO_TRY(check_clusters(KC));
+  SVOO_TRY(check_attn_clusters(QC));
+  SVOO_TRY(check_attn_clusters(KC));
   *offset_out = workspace_layout(BH, N, QC, KC).status;
   return SVOO_OK;
 }
@@ -395,15 +428,33 @@ int svoo_b200_qk_prep_push(const void* x, const float* weight, float eps, const 
   return SVOO_OK;
 }
 
+int svoo_b200_append_text_blocks(const uint8_t* map, const int32_t* q_offsets, const int32_t* k_offsets,
+                                 const int32_t* q_sorted_idx, const int32_t* k_sorted_idx, int64_t BH, int64_t N, int64_t QC,
+                                 int64_t KC, int64_t text, int64_t prompt, uint8_t* map_out, int32_t* q_offsets_out,
+                                 int32_t* k_offsets_out, int32_t* q_idx_out, int32_t* k_idx_out, void* stream) {
+  if (!map || !q_offsets || !k_offsets || !q_sorted_idx || !k_sorted_idx || !map_out || !q_offsets_out || !k_offsets_out ||
+      !q_idx_out || !k_idx_out)
+    return SVOO_ERR_NULL;
+  if (text < 1 || prompt < 0 || prompt > text) return SVOO_ERR_SHAPE;
+  SVOO_TRY(check_tokens(BH, N + text, kHeadDim));
+  SVOO_TRY(check_clusters(QC));
+  SVOO_TRY(check_clusters(KC));
+  SVOO_CUDA(launch_append_text_blocks(map, q_offsets, k_offsets, q_sorted_idx, k_sorted_idx, map_out, q_offsets_out,
+                                      k_offsets_out, q_idx_out, k_idx_out, BH, N, QC, KC, text, prompt, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
 // --------------------------------------------------------------------------------------------
 // The whole layer behind one call: every intermediate lives in a caller-provided scratch block.
 // --------------------------------------------------------------------------------------------
 namespace {
 struct LayerScratch {
-  int64_t qp, kp, vp, qlabels, klabels, qsorted, ksorted, qoff, koff, qcent, kcent, qsizes, ksizes, map, total;
+  int64_t qp, kp, vp, qlabels, klabels, qsorted, ksorted, qoff, koff, qcent, kcent, qsizes, ksizes, map;
+  int64_t map_full, qoff_full, koff_full, qidx_full, kidx_full, total;
 };
-LayerScratch layer_scratch_layout(int64_t BH, int64_t S, int64_t QC, int64_t KC) {
+LayerScratch layer_scratch_layout(int64_t BH, int64_t S, int64_t QC, int64_t KC, int64_t text) {
   LayerScratch l{};
+  const int64_t N = S - text;
   int64_t off = 0;
   auto take = [&](int64_t bytes) {
     const int64_t at = off;
@@ -413,10 +464,10 @@ LayerScratch layer_scratch_layout(int64_t BH, int64_t S, int64_t QC, int64_t KC)
   l.qp = take(BH * S * kRowBytes);
   l.kp = take(BH * S * kRowBytes);
   l.vp = take(BH * S * kRowBytes);
-  l.qlabels = take(BH * S * 4);
-  l.klabels = take(BH * S * 4);
-  l.qsorted = take(BH * S * 4);
-  l.ksorted = take(BH * S * 4);
+  l.qlabels = take(BH * N * 4);
+  l.klabels = take(BH * N * 4);
+  l.qsorted = take(BH * N * 4);
+  l.ksorted = take(BH * N * 4);
   l.qoff = take(BH * (QC + 1) * 4);
   l.koff = take(BH * (KC + 1) * 4);
   l.qcent = take(BH * QC * kRowBytes);
@@ -424,53 +475,96 @@ LayerScratch layer_scratch_layout(int64_t BH, int64_t S, int64_t QC, int64_t KC)
   l.qsizes = take(BH * QC * 4);
   l.ksizes = take(BH * KC * 4);
   l.map = take(BH * QC * KC);
+  if (text > 0) {
+    l.map_full = take(BH * (QC + 2) * (KC + 2));
+    l.qoff_full = take(BH * (QC + 3) * 4);
+    l.koff_full = take(BH * (KC + 3) * 4);
+    l.qidx_full = take(BH * S * 4);
+    l.kidx_full = take(BH * S * 4);
+  }
   l.total = off;
   return l;
 }
-}  // namespace
-
-int svoo_b200_layer_scratch_bytes(int64_t BH, int64_t S, int64_t QC, int64_t KC, int64_t* bytes_out) {
-  if (!bytes_out) return SVOO_ERR_NULL;
+int check_layer_shape(int64_t BH, int64_t S, int64_t QC, int64_t KC, int64_t text, int64_t prompt) {
   SVOO_TRY(check_tokens(BH, S, kHeadDim));
   SVOO_TRY(check_clusters(QC));
   SVOO_TRY(check_clusters(KC));
-  *bytes_out = layer_scratch_layout(BH, S, QC, KC).total;
+  if (text < 0 || text >= S || prompt < 0 || prompt > text) return SVOO_ERR_SHAPE;
+  return SVOO_OK;
+}
+}  // namespace
+
+int svoo_b200_layer_scratch_bytes(int64_t BH, int64_t S, int64_t QC, int64_t KC, int64_t text, int64_t* bytes_out) {
+  if (!bytes_out) return SVOO_ERR_NULL;
+  SVOO_TRY(check_layer_shape(BH, S, QC, KC, text, 0));
+  *bytes_out = layer_scratch_layout(BH, S, QC, KC, text).total;
   return SVOO_OK;
 }
 
 int svoo_b200_layer(const void* q, const void* k, const void* v, const int32_t* q_init_idx, const int32_t* k_init_idx,
                     int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, int32_t iters, float top_p,
-                    const int32_t* preserve_host, const int32_t* cap_host, float sm_scale, void* out, void* scratch,
-                    int64_t scratch_bytes, void* workspace, int64_t workspace_bytes, void* stream) {
-  if (!scratch) return SVOO_ERR_NULL;
-  SVOO_TRY(check_tokens(BH, S, D));
-  SVOO_TRY(check_clusters(QC));
-  SVOO_TRY(check_clusters(KC));
+                    const int32_t* preserve_host, const int32_t* cap_host, float sm_scale, int64_t text, int64_t prompt,
+                    void* out, void* scratch, int64_t scratch_bytes, void* workspace, int64_t workspace_bytes,
+                    void* stream) {
+  if (!scratch || !q || !k || !v || !out) return SVOO_ERR_NULL;
+  if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
+  SVOO_TRY(check_layer_shape(BH, S, QC, KC, text, prompt));
   if (BH > SVOO_MAX_HEADS) return SVOO_ERR_SHAPE;
-  if (!aligned16(scratch)) return SVOO_ERR_ALIGN;
-  const LayerScratch l = layer_scratch_layout(BH, S, QC, KC);
+  if (!aligned16(scratch) || !aligned16(q) || !aligned16(k)) return SVOO_ERR_ALIGN;
+  const LayerScratch l = layer_scratch_layout(BH, S, QC, KC, text);
   if (scratch_bytes < l.total) return SVOO_ERR_WORKSPACE;
+  if (text > 0 && workspace_bytes < workspace_layout(BH, S, QC + 2, KC + 2).total) return SVOO_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t N = S - text;
   auto at = [&](int64_t off) { return static_cast<void*>(static_cast<char*>(scratch) + off); };
   int32_t* qsorted = static_cast<int32_t*>(at(l.qsorted));
   int32_t* ksorted = static_cast<int32_t*>(at(l.ksorted));
   int32_t* qoff = static_cast<int32_t*>(at(l.qoff));
   int32_t* koff = static_cast<int32_t*>(at(l.koff));
-  SVOO_TRY(svoo_b200_cocluster(q, k, q_init_idx, k_init_idx, BH, S, D, QC, KC, iters, static_cast<int32_t*>(at(l.qlabels)),
+  const void* qv = q;
+  const void* kv = k;
+  if (text > 0) {
+    // the clustering reads dense [BH, N, 128] video rows: stage them where the permuted Q and K
+    // will be written once the clustering is done
+    SVOO_CUDA(cudaMemcpy2DAsync(at(l.qp), (size_t)N * kRowBytes, q, (size_t)S * kRowBytes, (size_t)N * kRowBytes, (size_t)BH,
+                                cudaMemcpyDeviceToDevice, st));
+    SVOO_CUDA(cudaMemcpy2DAsync(at(l.kp), (size_t)N * kRowBytes, k, (size_t)S * kRowBytes, (size_t)N * kRowBytes, (size_t)BH,
+                                cudaMemcpyDeviceToDevice, st));
+    qv = at(l.qp);
+    kv = at(l.kp);
+  }
+  SVOO_TRY(svoo_b200_cocluster(qv, kv, q_init_idx, k_init_idx, BH, N, D, QC, KC, iters, static_cast<int32_t*>(at(l.qlabels)),
                                static_cast<int32_t*>(at(l.klabels)), at(l.qcent), at(l.kcent),
                                static_cast<int32_t*>(at(l.qsizes)), static_cast<int32_t*>(at(l.ksizes)), qsorted, qoff,
                                ksorted, koff, workspace, workspace_bytes, stream));
   uint8_t* map = static_cast<uint8_t*>(at(l.map));
   if (top_p >= 1.0f) {
-    SVOO_CUDA(cudaMemsetAsync(map, 1, (size_t)(BH * QC * KC), (cudaStream_t)stream));
+    SVOO_CUDA(cudaMemsetAsync(map, 1, (size_t)(BH * QC * KC), st));
   } else {
     SVOO_TRY(svoo_b200_block_map(at(l.qcent), at(l.kcent), static_cast<int32_t*>(at(l.ksizes)), BH, QC, KC, D, top_p,
                                  preserve_host, cap_host, map, stream));
   }
-  SVOO_TRY(svoo_b200_permute(q, qsorted, BH, S, D, S, S, at(l.qp), stream));
-  SVOO_TRY(svoo_b200_permute(k, ksorted, BH, S, D, S, S, at(l.kp), stream));
-  SVOO_TRY(svoo_b200_permute(v, ksorted, BH, S, D, S, S, at(l.vp), stream));
-  return svoo_b200_sparse_attn(at(l.qp), at(l.kp), at(l.vp), map, qoff, koff, BH, S, D, QC, KC, sm_scale, out, qsorted,
-                               workspace, workspace_bytes, stream);
+  const int32_t* qidx = qsorted;
+  const int32_t* kidx = ksorted;
+  int64_t QCa = QC, KCa = KC;
+  if (text > 0) {
+    SVOO_TRY(svoo_b200_append_text_blocks(map, qoff, koff, qsorted, ksorted, BH, N, QC, KC, text, prompt,
+                                          static_cast<uint8_t*>(at(l.map_full)), static_cast<int32_t*>(at(l.qoff_full)),
+                                          static_cast<int32_t*>(at(l.koff_full)), static_cast<int32_t*>(at(l.qidx_full)),
+                                          static_cast<int32_t*>(at(l.kidx_full)), stream));
+    map = static_cast<uint8_t*>(at(l.map_full));
+    qoff = static_cast<int32_t*>(at(l.qoff_full));
+    koff = static_cast<int32_t*>(at(l.koff_full));
+    qidx = static_cast<int32_t*>(at(l.qidx_full));
+    kidx = static_cast<int32_t*>(at(l.kidx_full));
+    QCa = QC + 2;
+    KCa = KC + 2;
+  }
+  SVOO_TRY(svoo_b200_permute(q, qidx, BH, S, D, S, S, at(l.qp), stream));
+  SVOO_TRY(svoo_b200_permute(k, kidx, BH, S, D, S, S, at(l.kp), stream));
+  SVOO_TRY(svoo_b200_permute(v, kidx, BH, S, D, S, S, at(l.vp), stream));
+  return svoo_b200_sparse_attn(at(l.qp), at(l.kp), at(l.vp), map, qoff, koff, BH, S, D, QCa, KCa, sm_scale, out, qidx,
+                               nullptr, workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

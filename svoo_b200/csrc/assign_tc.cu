@@ -53,28 +53,37 @@ __device__ __forceinline__ AsgJob asg_job(int64_t g, int n_jb, int n_xt) {
   return j;
 }
 
-// Running first-argmax over 32 accumulator columns starting at column c0.
-__device__ __forceinline__ void argmax32(const uint32_t (&r)[32], int c0, int jlim, float& best, int& best_c) {
+// Running first-argmax over 32 accumulator columns starting at column c0; with kBias the
+// per-column bias (shared memory, indexed like the columns) is added to the score first.
+template <bool kBias>
+__device__ __forceinline__ void argmax32(const uint32_t (&r)[32], int c0, int jlim, const float* bias, float& best,
+                                         int& best_c) {
   if (c0 + 32 <= jlim) {
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
-      const float val = __uint_as_float(r[c]);
+      float val = __uint_as_float(r[c]);
+      if (kBias) val += bias[c0 + c];
       if (val > best) { best = val; best_c = c0 + c; }
     }
   } else {
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
-      const float val = __uint_as_float(r[c]);
+      float val = __uint_as_float(r[c]);
+      if (kBias) val += bias[c0 + c];
       if (c0 + c < jlim && val > best) { best = val; best_c = c0 + c; }
     }
   }
 }
 
-template <int JB>
+// kEuclid = false: scores x . (W_hi + W_lo), W rows of head bh at [bh * w_head_rows, +J).
+// kEuclid = true:  nearest centroid in Euclidean distance, argmax_j x . c_j + bias[bh, j] with
+//                  bias = -|c_j|^2 / 2 (one product per k-step: the centroids are bf16 already);
+//                  tm_hi then maps the centroid tensor itself, tm_lo is unused.
+template <int JB, bool kEuclid>
 __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
     const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_hi,
-    const __grid_constant__ CUtensorMap tm_lo, int2* __restrict__ partial, int BH, int N, int J, int Jpad,
-    int32_t* __restrict__ status) {
+    const __grid_constant__ CUtensorMap tm_lo, int2* __restrict__ partial, int BH, int N, int J, int w_head_rows,
+    const float* __restrict__ bias, int32_t* __restrict__ status) {
   using C = AsgCfg<JB>;
   constexpr int NS = C::kXStages;
   constexpr uint32_t kIdesc = idesc_bf16(128, JB, false);
@@ -118,11 +127,11 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
         const int block = job.bh * n_jb + job.jb;
         if (block != prev_block) {
           if (!mbar_wait(bar(C::W_EMPTY), (wq & 1) ^ 1, abort_flag)) break;
-          mbar_expect_tx(bar(C::W_FULL), 2 * C::kWBytes);
-          const int y = job.bh * Jpad + job.jb * JB;
+          mbar_expect_tx(bar(C::W_FULL), (kEuclid ? 1 : 2) * C::kWBytes);
+          const int y = job.bh * w_head_rows + job.jb * JB;
           for (int h = 0; h < 2; ++h) {
             tma_load_2d(whi_s + h * C::kWHalf, &tm_hi, h * 64, y, bar(C::W_FULL));
-            tma_load_2d(wlo_s + h * C::kWHalf, &tm_lo, h * 64, y, bar(C::W_FULL));
+            if (!kEuclid) tma_load_2d(wlo_s + h * C::kWHalf, &tm_lo, h * 64, y, bar(C::W_FULL));
           }
           prev_block = block;
           ++wq;
@@ -156,7 +165,7 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
           const uint64_t a = smem_desc_sw128(x_s + s * kAsgXBytes + (ks >> 2) * kAsgXHalf + (ks & 3) * 32, 16, 1024);
           const uint32_t woff = (ks >> 2) * C::kWHalf + (ks & 3) * 32;
           umma_ss(d, a, smem_desc_sw128(whi_s + woff, 16, 1024), kIdesc, ks > 0);
-          umma_ss(d, a, smem_desc_sw128(wlo_s + woff, 16, 1024), kIdesc, 1);
+          if (!kEuclid) umma_ss(d, a, smem_desc_sw128(wlo_s + woff, 16, 1024), kIdesc, 1);
         }
         tc_commit(bar(C::X_EMPTY + s));
         tc_commit(bar(C::ACC_FULL + b));
@@ -177,9 +186,22 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
     uint32_t ra[32], rb[32];
     int i = 0;
     bool ok = true;
+    // Euclidean mode: the bias of the current W block, one private copy per epilogue warp in the
+    // shared memory that the (absent) W_lo operand would occupy
+    float* bias_s = reinterpret_cast<float*>(gen_base + C::kWBytes) + (warp - 4) * HC;
+    int bias_block = -1;
     for (int64_t g = g0; g < g1 && ok; ++g, ++i) {
       const AsgJob job = asg_job(g, n_jb, n_xt);
       const int b = i & 1;
+      if (kEuclid && job.bh * n_jb + job.jb != bias_block) {
+        bias_block = job.bh * n_jb + job.jb;
+        __syncwarp();
+        for (int c = lane; c < HC; c += 32) {
+          const int j = job.jb * JB + half * HC + c;
+          bias_s[c] = j < J ? bias[(int64_t)job.bh * J + j] : 0.f;
+        }
+        __syncwarp();
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(bar(C::ACC_FULL + b), (i >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
@@ -192,10 +214,10 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
 #pragma unroll
       for (int ch = 0; ch < HC / 32; ch += 2) {
         tmem_ld32_nowait(acc + (ch + 1) * 32, rb);
-        argmax32(ra, ch * 32, jlim, best, best_c);
+        argmax32<kEuclid>(ra, ch * 32, jlim, bias_s, best, best_c);
         tmem_wait_ld();
         if (ch + 2 < HC / 32) tmem_ld32_nowait(acc + (ch + 2) * 32, ra);
-        argmax32(rb, (ch + 1) * 32, jlim, best, best_c);
+        argmax32<kEuclid>(rb, (ch + 1) * 32, jlim, bias_s, best, best_c);
         tmem_wait_ld();
       }
       tc_fence_before();
@@ -288,34 +310,30 @@ bool make_row_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int bo
 
 }  // namespace tc
 
-template <int JB>
-static cudaError_t launch_assign_tc_jb(const void* x, const void* w_hi, const void* w_lo, int2* partial, int32_t* status,
-                                       int64_t BH, int64_t N, int64_t J, int Jpad, cudaStream_t st) {
+template <int JB, bool kEuclid>
+static cudaError_t launch_assign_tc_jb(const void* x, const void* w_hi, const void* w_lo, const float* bias, int2* partial,
+                                       int32_t* status, int64_t BH, int64_t N, int64_t J, int w_head_rows,
+                                       cudaStream_t st) {
   using C = tc::AsgCfg<JB>;
   alignas(64) CUtensorMap mx, mh, ml;
-  if (!tc::make_row_tensor_map(&mx, x, BH * N, tc::kAsgXT) || !tc::make_row_tensor_map(&mh, w_hi, BH * Jpad, JB) ||
-      !tc::make_row_tensor_map(&ml, w_lo, BH * Jpad, JB))
+  if (!tc::make_row_tensor_map(&mx, x, BH * N, tc::kAsgXT) || !tc::make_row_tensor_map(&mh, w_hi, BH * w_head_rows, JB) ||
+      !tc::make_row_tensor_map(&ml, w_lo, BH * w_head_rows, JB))
     return cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(tc::assign_tc_kernel<JB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(tc::assign_tc_kernel<JB, kEuclid>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       C::kSmemBytes);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t total = BH * ceil_div64(J, JB) * ceil_div64(N, tc::kAsgXT);
   const unsigned grid = (unsigned)(total < sms ? total : sms);
-  tc::assign_tc_kernel<JB><<<grid, tc::kAsgThreads, C::kSmemBytes, st>>>(mx, mh, ml, partial, (int)BH, (int)N, (int)J, Jpad,
-                                                                         status);
+  tc::assign_tc_kernel<JB, kEuclid><<<grid, tc::kAsgThreads, C::kSmemBytes, st>>>(mx, mh, ml, partial, (int)BH, (int)N, (int)J,
+                                                                                 w_head_rows, bias, status);
   return cudaGetLastError();
 }
 
-// chunk_hist != nullptr: also write the per-chunk label histograms of the sort (its first pass).
-cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int2* partial,
-                             int32_t* status, int64_t BH, int64_t N, int64_t J, int32_t* chunk_hist, cudaStream_t st) {
-  const int Jpad = pad_clusters(J);
-  const int jb = J <= 128 ? 128 : 256;
-  cudaError_t e = jb == 128 ? launch_assign_tc_jb<128>(x, w_hi, w_lo, partial, status, BH, N, J, Jpad, st)
-                            : launch_assign_tc_jb<256>(x, w_hi, w_lo, partial, status, BH, N, J, Jpad, st);
-  if (e != cudaSuccess) return e;
+static cudaError_t launch_assign_reduce(const int2* partial, int32_t* labels, int64_t BH, int64_t N, int64_t J, int jb,
+                                        int32_t* chunk_hist, cudaStream_t st) {
   const int groups = 2 * (int)ceil_div64(J, jb);
   if (chunk_hist) {
     const int nchunks = sort_chunks(N);
@@ -326,6 +344,51 @@ cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, 
   }
   count_launches(2);
   return cudaGetLastError();
+}
+
+// chunk_hist != nullptr: also write the per-chunk label histograms of the sort (its first pass).
+cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int2* partial,
+                             int32_t* status, int64_t BH, int64_t N, int64_t J, int32_t* chunk_hist, cudaStream_t st) {
+  const int Jpad = pad_clusters(J);
+  const int jb = J <= 128 ? 128 : 256;
+  cudaError_t e = jb == 128 ? launch_assign_tc_jb<128, false>(x, w_hi, w_lo, nullptr, partial, status, BH, N, J, Jpad, st)
+                            : launch_assign_tc_jb<256, false>(x, w_hi, w_lo, nullptr, partial, status, BH, N, J, Jpad, st);
+  if (e != cudaSuccess) return e;
+  return launch_assign_reduce(partial, labels, BH, N, J, jb, chunk_hist, st);
+}
+
+// bias[bh, j] = -sum_d bf16(c_d * c_d) / 2: the centroid term of the squared distance with the
+// products rounded to the input type before the fp32 sum (svoo/co_clustering.py:389-390).
+__global__ void __launch_bounds__(256) euclid_bias_kernel(const bf16* __restrict__ c, float* __restrict__ bias, int64_t rows) {
+  const int64_t row = (int64_t)blockIdx.x * 16 + threadIdx.x / 16;
+  const int lane = threadIdx.x % 16;
+  if (row >= rows) return;
+  const uint4 v = reinterpret_cast<const uint4*>(c + row * kHeadDim)[lane];
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float a = __low2float(h[i]), b = __high2float(h[i]);
+    s += bf16_round(a * a);
+    s += bf16_round(b * b);
+  }
+#pragma unroll
+  for (int o = 8; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o, 16);
+  if (lane == 0) bias[row] = -0.5f * s;
+}
+
+// labels[bh, n] = first argmin_j |x_n - c_j|^2 (svoo/co_clustering.py:335-416): the assignment GEMM with
+// the centroids themselves as the stationary operand and -|c_j|^2 / 2 added in the epilogue.
+cudaError_t launch_euclid_assign_tc(const void* x, const void* centroids, float* bias, int32_t* labels, int2* partial,
+                                    int32_t* status, int64_t BH, int64_t N, int64_t K, int32_t* chunk_hist, cudaStream_t st) {
+  euclid_bias_kernel<<<(unsigned)ceil_div64(BH * K, 16), 256, 0, st>>>((const bf16*)centroids, bias, BH * K);
+  count_launches(1);
+  const int jb = K <= 128 ? 128 : 256;
+  cudaError_t e = jb == 128
+      ? launch_assign_tc_jb<128, true>(x, centroids, centroids, bias, partial, status, BH, N, K, (int)K, st)
+      : launch_assign_tc_jb<256, true>(x, centroids, centroids, bias, partial, status, BH, N, K, (int)K, st);
+  if (e != cudaSuccess) return e;
+  return launch_assign_reduce(partial, labels, BH, N, K, jb, chunk_hist, st);
 }
 
 }  // namespace svoo

@@ -36,7 +36,7 @@ constexpr int kBN = 128;                 // key rows per step
 constexpr int kTile = 128 * kRowBytes;   // 32 KB: one [128 x 128] bf16 tile = two 16 KB boxes
 constexpr int kBox = 128 * 128;          // 16 KB: 128 rows x 64 columns
 constexpr int kSmemTiles = 6 * kTile;    // Q0 Q1 | K0 K1 | V0 V1
-constexpr int kMaxRunsSmem = SVOO_MAX_CLUSTERS / 2 + 2;
+constexpr int kMaxRunsSmem = SVOO_MAX_ATTN_CLUSTERS / 2 + 2;
 constexpr int kRunTableBytes = (kMaxRunsSmem * 8 + 255) / 256 * 256;
 constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 1024;   // + barriers, run table, slack
 constexpr int kKWarp = 8, kVWarp = 9, kMmaWarp = 10;     // after the 8 softmax warps
@@ -156,19 +156,11 @@ __device__ __forceinline__ void tma_gather_tile(uint32_t dst, const CUtensorMap*
   }
 }
 
-#ifdef SVOO_TRACE
-// Debug builds only: clock64 stamps of pipeline events of one CTA, [role][tile][slot].
-__device__ long long g_trace[8 * 64 * 4];
-#define TRACE(role, tile, slot) do { if (blockIdx.x == SVOO_TRACE && blockIdx.y == 0 && (tile) < 64) g_trace[((role) * 64 + (tile)) * 4 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(role, tile, slot) do { } while (0)
-#endif
-
 __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     const __grid_constant__ AttnMaps maps, const __grid_constant__ OutPeers peers, bf16* __restrict__ out,
     const int32_t* __restrict__ out_row_idx, const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles,
     const int2* __restrict__ runs, const int32_t* __restrict__ nruns, int S, int QC, int max_tiles, int max_runs,
-    float scale_log2, int32_t* __restrict__ status) {
+    float scale_log2, int32_t* __restrict__ status, float* __restrict__ lse) {
   extern __shared__ unsigned char smem_raw[];
   const int bh = blockIdx.y;
   if ((int)blockIdx.x >= nqtiles[bh]) return;
@@ -206,14 +198,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (tid == 0) TRACE(7, 0, 0);
-#ifdef SVOO_TRACE
-  if (tid == 0 && blockIdx.x == SVOO_TRACE && blockIdx.y == 0) {
-    unsigned long long ns;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
-    g_trace[(7 * 64 + 2) * 4 + 0] = (long long)ns;
-  }
-#endif
   const int L = runs_s[nr].y;                      // selected key rows in total
   const int T = (L + kBN - 1) / kBN;               // packed key tiles
 
@@ -240,10 +224,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       for (int j = 0; j < T; ++j) {
         const int s = j & 1;
         if (!mbar_wait(bar(empty + s), ((j >> 1) & 1) ^ 1, abort_flag)) break;
-        TRACE(3 + is_v, j, 0);
         mbar_expect_tx(bar(full + s), kTile);
         tma_gather_tile(stage0 + s * kTile, tm, runs_s, nr, r_cur, j, L, bh * S, rows_total, bar(full + s));
-        TRACE(3 + is_v, j, 1);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -283,7 +265,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        TRACE(7, 0, 1);
         issue_qk(I0{}, I0{});
         tc_commit(bar(S_FULL));
         if (nq == 1) tc_commit(bar(K_EMPTY));
@@ -293,7 +274,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         constexpr int w = decltype(wc)::value, st = decltype(sc)::value;
         if (w == 0 && !mbar_wait(bar(V_FULL + st), (j >> 1) & 1, abort_flag)) return false;
         if (!mbar_wait(bar(P_READY + w), j & 1, abort_flag)) return false;
-        TRACE(2, j, w);
         tc_fence_after();
         issue_pv(wc, sc, j > 0);
         tc_commit(bar(P_FREE + w));
@@ -310,7 +290,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
           issue_qk(I1{}, sc);
           tc_commit(bar(S_FULL + 1));
           tc_commit(bar(K_EMPTY + st));
-          TRACE(2, j, 2);
           if (j > 0 && !pv(I1{}, SN{}, j - 1)) return false;
           // job (j, 1) has taken its S: QK of (j + 1, 0); then PV of (j, 0)
           if (j + 1 < T) {
@@ -319,7 +298,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
             tc_fence_after();
             issue_qk(I0{}, SN{});
             tc_commit(bar(S_FULL));
-            TRACE(2, j, 3);
           }
           return pv(I0{}, sc, j);
         };
@@ -367,7 +345,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       for (int j = 0; j < T; ++j) {
         const int valid = min(L - j * kBN, kBN);
         ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + w), j & 1, abort_flag));
-        if (lane == 0) TRACE(5 + w, j, warp & 3);
         if (!ok) break;
         tc_fence_after();
         // the whole score row goes to registers; S is handed back at once so that the tensor pipe
@@ -446,10 +423,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_READY + w));
-        if (lane == 0) TRACE(w, j, warp & 3);
       }
       uint32_t ra[32];
-      if (tid == 0) TRACE(7, 0, 2);
       // epilogue: O / l -> bf16 rows
       const int row = row0 + w * kBM + r_local;
       const bool store = row < row1;
@@ -463,6 +438,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         const int p = dst / peers.n_loc;
         orow = peers.dst[p] + ((int64_t)(dst - p * peers.n_loc) * peers.H + peers.head[bh]) * kHeadDim;
       }
+      // log2 of the softmax denominator, sum_j 2^(s_j * scale * log2 e); -inf for a row without keys
+      if (lse && store && (T == 0 || ok))
+        lse[(int64_t)bh * S + dst] = (T == 0 || !(l_sum > 0.f)) ? -INFINITY : m_used + __log2f(l_sum);
       if (T == 0) {
         if (store) {
 #pragma unroll
@@ -490,17 +468,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     }
   }
   // ------------------------------------------------------------------ teardown
-  if (tid == 0) TRACE(7, 0, 3);
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) TRACE(7, 1, 0);
-#ifdef SVOO_TRACE
-  if (tid == 0 && blockIdx.x == SVOO_TRACE && blockIdx.y == 0) {
-    unsigned long long ns;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
-    g_trace[(7 * 64 + 2) * 4 + 1] = (long long)ns;
-  }
-#endif
   if (tid == 0 && *abort_flag) atomicExch(status, 1);
   if (warp == kMmaWarp) {
     tc_fence_after();
@@ -510,17 +479,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
 
 }  // namespace tc
 
-#ifdef SVOO_TRACE
-extern "C" int svoo_b200_debug_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, tc::g_trace, sizeof(tc::g_trace));
-}
-#endif
 
 cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, void* out, const int32_t* out_row_idx,
                                   const int4* qtiles, const int32_t* nqtiles, const int2* runs, const int32_t* nruns,
                                   int32_t* status, int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale,
                                   void* const* peer_dst, const int32_t* my_heads, int world, int64_t n_loc, int H,
-                                  cudaStream_t st) {
+                                  float* lse, cudaStream_t st) {
   // a build whose register hand-over does not add up (the spill-check build) must never launch:
   // its softmax warps would wait for registers that nobody frees
   if (128 * tc::kRegsService + 256 * tc::kRegsSoftmax > 168 * tc::kThreads) return cudaErrorInvalidConfiguration;
@@ -542,7 +506,7 @@ cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, v
   dim3 grid((unsigned)max_qtiles(S, QC), (unsigned)BH);
   tc::sparse_attn_tc_kernel<<<grid, tc::kThreads, tc::kSmemBytes, st>>>(
       maps, peers, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), max_runs(KC),
-      sm_scale * 1.4426950408889634f, status);
+      sm_scale * 1.4426950408889634f, status, peer_dst ? nullptr : lse);
   count_launches(1);
   return cudaGetLastError();
 }

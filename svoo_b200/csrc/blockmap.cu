@@ -276,18 +276,21 @@ __global__ void __launch_bounds__(256) build_runs_kernel(const uint8_t* __restri
   }
 }
 
-// One CTA per head: the 128-row query tiles of every non-empty query cluster.
+// One CTA per head: the query tiles (`tile_rows` rows each) of every non-empty query cluster, in
+// cluster order.  Thread i owns clusters 2i and 2i + 1, so up to 2048 clusters fit one CTA.
 __global__ void __launch_bounds__(1024) build_qtiles_kernel(const int32_t* __restrict__ q_offsets,
                                                             int4* __restrict__ qtiles, int32_t* __restrict__ nqtiles,
                                                             int QC, int max_tiles, int tile_rows) {
   __shared__ int warp_tot[32];
   const int bh = blockIdx.x, i = threadIdx.x, lane = i % 32, warp = i / 32;
-  int begin = 0, end = 0;
-  if (i < QC) {
-    begin = q_offsets[(int64_t)bh * (QC + 1) + i];
-    end = q_offsets[(int64_t)bh * (QC + 1) + i + 1];
-  }
-  const int nt = (end - begin + tile_rows - 1) / tile_rows;
+  const int32_t* off = q_offsets + (int64_t)bh * (QC + 1);
+  int b[3] = {0, 0, 0};
+#pragma unroll
+  for (int u = 0; u < 3; ++u)
+    if (2 * i + u <= QC) b[u] = off[2 * i + u];
+  const int nt0 = 2 * i < QC ? (b[1] - b[0] + tile_rows - 1) / tile_rows : 0;
+  const int nt1 = 2 * i + 1 < QC ? (b[2] - b[1] + tile_rows - 1) / tile_rows : 0;
+  const int nt = nt0 + nt1;
   int incl = nt;
 #pragma unroll
   for (int s = 1; s < 32; s <<= 1) {
@@ -308,8 +311,12 @@ __global__ void __launch_bounds__(1024) build_qtiles_kernel(const int32_t* __res
   __syncthreads();
   int pos = incl - nt + (warp ? warp_tot[warp - 1] : 0);
   int4* out = qtiles + (int64_t)bh * max_tiles;
-  for (int r = begin; r < end; r += tile_rows, ++pos)
-    if (pos < max_tiles) out[pos] = make_int4(i, r, min(r + tile_rows, end), 0);
+  if (nt0)
+    for (int r = b[0]; r < b[1]; r += tile_rows, ++pos)
+      if (pos < max_tiles) out[pos] = make_int4(2 * i, r, min(r + tile_rows, b[1]), 0);
+  if (nt1)
+    for (int r = b[1]; r < b[2]; r += tile_rows, ++pos)
+      if (pos < max_tiles) out[pos] = make_int4(2 * i + 1, r, min(r + tile_rows, b[2]), 0);
   if (i == 1023) nqtiles[bh] = min(warp_tot[31], max_tiles);
 }
 
@@ -329,6 +336,55 @@ cudaError_t launch_block_map(const void* qc, const void* kc, const int32_t* ksiz
   dim3 grid((unsigned)ceil_div64(QC, kMapRows), (unsigned)BH);
   block_map_kernel<<<grid, 256, smem, st>>>((const bf16*)qc, (const bf16*)kc, ksizes, map, (int)QC, (int)KC, KCpad,
                                             (float)sqrt((double)kHeadDim), top_p, lim);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Text tokens of a joint-attention layer (svoo/models/hunyuan10/attention.py:999-1019): the
+// `text` rows that follow the N clustered video rows of every head become two more blocks,
+// "prompt" (the first `prompt` text rows) and "unused prompt" (the rest).
+//   map  [BH, QC, KC]   -> [BH, QC+2, KC+2]: prompt queries see every video and prompt key, every
+//                          query but the unused prompt sees the prompt keys, the unused prompt sees itself
+//   offsets [BH, K+1]   -> [BH, K+3]  (block sizes `prompt`, `text - prompt` appended)
+//   sorted_idx [BH, N]  -> [BH, N+text]  (identity on the text rows)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) append_text_blocks_kernel(
+    const uint8_t* __restrict__ map, const int32_t* __restrict__ q_off, const int32_t* __restrict__ k_off,
+    const int32_t* __restrict__ q_idx, const int32_t* __restrict__ k_idx, uint8_t* __restrict__ map_out,
+    int32_t* __restrict__ q_off_out, int32_t* __restrict__ k_off_out, int32_t* __restrict__ q_idx_out,
+    int32_t* __restrict__ k_idx_out, int N, int QC, int KC, int text, int prompt) {
+  const int bh = blockIdx.y;
+  const int S = N + text, QC2 = QC + 2, KC2 = KC + 2;
+  const int stride = gridDim.x * 256;
+  for (int t = blockIdx.x * 256 + threadIdx.x; t < QC2 * KC2; t += stride) {
+    const int i = t / KC2, j = t - i * KC2;
+    uint8_t v;
+    if (i < QC) v = j < KC ? (uint8_t)(map[((int64_t)bh * QC + i) * KC + j] != 0) : (uint8_t)(j == KC);
+    else if (i == QC) v = (uint8_t)(j <= KC);
+    else v = (uint8_t)(j == KC + 1);
+    map_out[(int64_t)bh * QC2 * KC2 + t] = v;
+  }
+  for (int t = blockIdx.x * 256 + threadIdx.x; t < S; t += stride) {
+    q_idx_out[(int64_t)bh * S + t] = t < N ? q_idx[(int64_t)bh * N + t] : t;
+    k_idx_out[(int64_t)bh * S + t] = t < N ? k_idx[(int64_t)bh * N + t] : t;
+  }
+  for (int t = blockIdx.x * 256 + threadIdx.x; t <= QC2; t += stride)
+    q_off_out[(int64_t)bh * (QC2 + 1) + t] = t <= QC ? q_off[(int64_t)bh * (QC + 1) + t] : (t == QC + 1 ? N + prompt : S);
+  for (int t = blockIdx.x * 256 + threadIdx.x; t <= KC2; t += stride)
+    k_off_out[(int64_t)bh * (KC2 + 1) + t] = t <= KC ? k_off[(int64_t)bh * (KC + 1) + t] : (t == KC + 1 ? N + prompt : S);
+}
+
+cudaError_t launch_append_text_blocks(const uint8_t* map, const int32_t* q_off, const int32_t* k_off, const int32_t* q_idx,
+                                      const int32_t* k_idx, uint8_t* map_out, int32_t* q_off_out, int32_t* k_off_out,
+                                      int32_t* q_idx_out, int32_t* k_idx_out, int64_t BH, int64_t N, int64_t QC, int64_t KC,
+                                      int64_t text, int64_t prompt, cudaStream_t st) {
+  const int64_t work = (QC + 2) * (KC + 2) > N + text ? (QC + 2) * (KC + 2) : N + text;
+  int64_t blocks = ceil_div64(work, 256 * 4);
+  blocks = blocks < 1 ? 1 : (blocks > 1024 ? 1024 : blocks);
+  append_text_blocks_kernel<<<dim3((unsigned)blocks, (unsigned)BH), 256, 0, st>>>(
+      map, q_off, k_off, q_idx, k_idx, map_out, q_off_out, k_off_out, q_idx_out, k_idx_out, (int)N, (int)QC, (int)KC,
+      (int)text, (int)prompt);
   count_launches(1);
   return cudaGetLastError();
 }

@@ -402,12 +402,14 @@ __global__ void __launch_bounds__(128) centroid_finalize_kernel(const float* __r
   if (d == 0 && sizes) sizes[(int64_t)bh * K + c] = cnt;
 }
 
-// sizes [BH,K] -> offsets [BH,K+1]
+// sizes [BH,K] -> offsets [BH,K+1]; thread k owns entries 2k and 2k + 1 (K <= 2048)
 __global__ void __launch_bounds__(1024) offsets_from_sizes_kernel(const int32_t* __restrict__ sizes,
                                                                   int32_t* __restrict__ offsets, int K) {
   __shared__ int warp_tot[32];
   const int bh = blockIdx.x, k = threadIdx.x, lane = k % 32, warp = k / 32;
-  const int v = k < K ? sizes[(int64_t)bh * K + k] : 0;
+  const int v0 = 2 * k < K ? sizes[(int64_t)bh * K + 2 * k] : 0;
+  const int v1 = 2 * k + 1 < K ? sizes[(int64_t)bh * K + 2 * k + 1] : 0;
+  const int v = v0 + v1;
   int incl = v;
 #pragma unroll
   for (int s = 1; s < 32; s <<= 1) {
@@ -427,8 +429,11 @@ __global__ void __launch_bounds__(1024) offsets_from_sizes_kernel(const int32_t*
   }
   __syncthreads();
   const int excl = incl - v + (warp ? warp_tot[warp - 1] : 0);
-  if (k < K) offsets[(int64_t)bh * (K + 1) + k] = excl;
-  if (k == K - 1) offsets[(int64_t)bh * (K + 1) + K] = excl + v;
+  int32_t* out = offsets + (int64_t)bh * (K + 1);
+  if (2 * k < K) out[2 * k] = excl;
+  if (2 * k + 1 < K) out[2 * k + 1] = excl + v0;
+  if (2 * k == K - 1) out[K] = excl + v0;
+  if (2 * k + 1 == K - 1) out[K] = excl + v;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -460,12 +465,7 @@ cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void*
 cudaError_t launch_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int64_t K, int32_t* sorted_idx,
                                int32_t* offsets, int32_t* sizes, int32_t* chunk_hist, cudaStream_t st, bool hist_done) {
   const int nchunks = sort_chunks(N);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(label_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         8 * SVOO_MAX_CLUSTERS * 4);
-    attr_done = true;
-  }
+  // label_scatter_kernel uses 8 * K * 4 <= 32 KB of dynamic shared memory: inside the default limit
   dim3 grid((unsigned)nchunks, (unsigned)BH);
   if (!hist_done) label_hist_kernel<<<grid, 256, 0, st>>>(labels, chunk_hist, (int)N, (int)K, nchunks);
   label_scan_kernel<<<(unsigned)BH, 1024, 0, st>>>(chunk_hist, offsets, sizes, (int)K, nchunks);
@@ -525,7 +525,7 @@ extern "C" int svoo_b200_sort_labels_static(const int32_t* labels, int64_t BH, i
                                             int32_t* sorted_idx, int32_t* offsets, void* stream) {
   using namespace svoo;
   if (!labels || !sorted_idx || !offsets) return SVOO_ERR_NULL;
-  if (BH < 1 || BH > 65535 || N < 1 || N > (1 << 24) || K < 1) return SVOO_ERR_SHAPE;
+  if (BH < 1 || BH > 65535 || N < 1 || N > (1 << 24) || K < 1 || BH * N > (int64_t)INT32_MAX) return SVOO_ERR_SHAPE;
   if (K > SVOO_MAX_CLUSTERS) return SVOO_ERR_CLUSTERS;
   if (BH * (int64_t)sort_chunks(N) * K > kStaticSortInts) return SVOO_ERR_STATIC_SCRATCH;
   // Address of the array on the current device, looked up on the first call made with that

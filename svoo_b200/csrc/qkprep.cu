@@ -20,9 +20,7 @@
 namespace svoo {
 
 constexpr int kPrepThreads = 256;
-#ifndef SVOO_PREP_MINB
-#define SVOO_PREP_MINB 4
-#endif
+constexpr int kPrepMinBlocks = 4;
 
 struct PrepDest {
   uint4* dst[16];       // [0] only when world == 0 (local [H, S, 128]); else every rank's [H/world, N, 128]
@@ -37,7 +35,7 @@ struct PrepDest {
 // thread (ceil(H * 16 / 256)).  For CPT <= 4 the norm weights of the thread's chunks are fetched
 // together with the row, before the reduction, so the CTA pays one memory latency instead of two.
 template <int CPT>
-__global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
+__global__ void __launch_bounds__(kPrepThreads, kPrepMinBlocks) qk_prep_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
                                                                float eps, const float* __restrict__ cosv,
                                                                const float* __restrict__ sinv, int64_t S, int H,
                                                                const __grid_constant__ PrepDest dest) {
@@ -153,11 +151,9 @@ __global__ void __launch_bounds__(kPrepThreads, SVOO_PREP_MINB) qk_prep_kernel(c
 // One WARP per token (rows of at most 24 * 32 chunks, i.e. H <= 48): the row lives in the
 // registers of 32 lanes (CPL chunks each), the sum of squares is a shuffle reduction, and nothing
 // waits on a block barrier, so many more bytes are in flight per SM than with one CTA per token.
-#ifndef SVOO_PREPW_MINB
-#define SVOO_PREPW_MINB 3
-#endif
+constexpr int kPrepWarpMinBlocks = 3;
 template <int CPL>
-__global__ void __launch_bounds__(128, SVOO_PREPW_MINB) qk_prep_warp_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
+__global__ void __launch_bounds__(128, kPrepWarpMinBlocks) qk_prep_warp_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
                                                            float eps, const float* __restrict__ cosv,
                                                            const float* __restrict__ sinv, int64_t S, int H,
                                                            const __grid_constant__ PrepDest dest) {

@@ -12,7 +12,6 @@ import dataclasses
 from typing import Optional
 
 import torch
-import torch.nn.functional as F
 
 from . import co_clustering as cc
 from . import ops
@@ -63,15 +62,16 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
     assert query.is_cuda and query.dtype == torch.bfloat16, "bf16 CUDA tensors expected"
     n_video = S - context_length
     q, k, v = query[0], key[0], value[0]
-    if context_length:
-        qv, kv = q[:, :n_video].contiguous(), k[:, :n_video].contiguous()
-    else:
-        qv, kv = q.contiguous(), k.contiguous()
     mark = timer.mark if timer is not None else (lambda name: None)
     mark("start")
     c = clustering
     if c is None:
+        if context_length:
+            qv, kv = q[:, :n_video].contiguous(), k[:, :n_video].contiguous()
+        else:
+            qv, kv = q.contiguous(), k.contiguous()
         c = cc.co_cluster(qv, kv, num_q_centroids, num_k_centroids, kmeans_iters, init_indices=init_indices)
+        del qv, kv
     mark("cocluster")
     preserve, cap = cc.keep_limits(num_k_centroids, H, min_kc_ratio, max_kc_ratio)
     if top_p >= 1.0:
@@ -86,16 +86,8 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
     else:
         # text tokens stay where they are, as two extra blocks (prompt, unused prompt)
         prompt = context_length if prompt_length is None else prompt_length
-        m_full = F.pad(m, (0, 2, 0, 2), value=0)
-        m_full[:, -2, :-1] = 1
-        m_full[:, :-1, -2] = 1
-        m_full[:, -1, -1] = 1
-        tail = torch.tensor([prompt, context_length - prompt], dtype=torch.int32, device=q.device)
-        q_off = ops.offsets_from_sizes(torch.cat([c.qsizes, tail.expand(H, 2)], 1))
-        k_off = ops.offsets_from_sizes(torch.cat([c.ksizes, tail.expand(H, 2)], 1))
-        text_rows = torch.arange(n_video, S, dtype=torch.int32, device=q.device).expand(H, context_length)
-        q_idx = torch.cat([c.q_sorted_idx, text_rows], 1).contiguous()
-        k_idx = torch.cat([c.k_sorted_idx, text_rows], 1).contiguous()
+        m_full, q_off, k_off, q_idx, k_idx = ops.append_text_blocks(m, c.q_offsets, c.k_offsets, c.q_sorted_idx,
+                                                                    c.k_sorted_idx, context_length, prompt)
     m = m_full
     if value_ready is not None:
         torch.cuda.current_stream(q.device).wait_event(value_ready)

@@ -67,26 +67,41 @@ class Clustering:
     k_offsets: torch.Tensor
 
 
-def cocluster(q: torch.Tensor, k: torch.Tensor, q_init_idx: torch.Tensor, k_init_idx: torch.Tensor,
-              iters: int) -> Clustering:
-    _need_cuda(q, k, q_init_idx, k_init_idx)
+def cocluster(q: torch.Tensor, k: torch.Tensor, q_init_idx: Optional[torch.Tensor],
+              k_init_idx: Optional[torch.Tensor], iters: int,
+              init_centroids: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Clustering:
+    """Co-clustering from initial centroid token indices, or (warm start) from `init_centroids` =
+    (q centroids [BH,QC,128], k centroids [BH,KC,128]), which are not modified."""
+    _need_cuda(q, k)
     BH, N, D = _tokens(q)
     if k.shape != q.shape or k.dtype != q.dtype:
         raise ValueError("q and k must have the same shape and dtype")
-    QC, KC = q_init_idx.shape[-1], k_init_idx.shape[-1]
     dev = q.device
-    qi = q_init_idx.to(torch.int32).contiguous()
-    ki = k_init_idx.to(torch.int32).contiguous()
     i32 = dict(dtype=torch.int32, device=dev)
+    if init_centroids is not None:
+        qc0, kc0 = init_centroids
+        _need_cuda(qc0, kc0)
+        QC, KC = qc0.shape[1], kc0.shape[1]
+        if qc0.shape != (BH, QC, D) or kc0.shape != (BH, KC, D) or qc0.dtype != q.dtype or kc0.dtype != q.dtype:
+            raise ValueError("initial centroids must be bf16 [BH, QC, 128] and [BH, KC, 128]")
+        qcent, kcent = qc0.clone(), kc0.clone()
+        qi_ptr = ki_ptr = 0
+    else:
+        _need_cuda(q_init_idx, k_init_idx)
+        QC, KC = q_init_idx.shape[-1], k_init_idx.shape[-1]
+        qi = q_init_idx.to(torch.int32).contiguous()
+        ki = k_init_idx.to(torch.int32).contiguous()
+        qi_ptr, ki_ptr = qi.data_ptr(), ki.data_ptr()
+        qcent = torch.empty(BH, QC, D, dtype=q.dtype, device=dev)
+        kcent = torch.empty(BH, KC, D, dtype=q.dtype, device=dev)
     c = Clustering(
-        torch.empty(BH, N, **i32), torch.empty(BH, N, **i32),
-        torch.empty(BH, QC, D, dtype=q.dtype, device=dev), torch.empty(BH, KC, D, dtype=q.dtype, device=dev),
+        torch.empty(BH, N, **i32), torch.empty(BH, N, **i32), qcent, kcent,
         torch.empty(BH, QC, **i32), torch.empty(BH, KC, **i32),
         torch.empty(BH, N, **i32), torch.empty(BH, N, **i32),
         torch.empty(BH, QC + 1, **i32), torch.empty(BH, KC + 1, **i32))
     ws = workspace(dev, BH, N, QC, KC)
     check(LIB.svoo_b200_cocluster(
-        q.data_ptr(), k.data_ptr(), qi.data_ptr(), ki.data_ptr(), BH, N, D, QC, KC, int(iters),
+        q.data_ptr(), k.data_ptr(), qi_ptr, ki_ptr, BH, N, D, QC, KC, int(iters),
         c.qlabels.data_ptr(), c.klabels.data_ptr(), c.qcentroids.data_ptr(), c.kcentroids.data_ptr(),
         c.qsizes.data_ptr(), c.ksizes.data_ptr(), c.q_sorted_idx.data_ptr(), c.q_offsets.data_ptr(),
         c.k_sorted_idx.data_ptr(), c.k_offsets.data_ptr(), ws.data_ptr(), ws.numel(), _stream()), "cocluster")
@@ -104,6 +119,40 @@ def cocluster_assign(x: torch.Tensor, form_centroids: torch.Tensor, own_centroid
                                          K, J, labels.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
           "cocluster_assign")
     return labels
+
+
+def euclid_assign(x: torch.Tensor, centroids: torch.Tensor) -> torch.Tensor:
+    """int32 labels [BH, N]: the nearest centroid of every token in Euclidean distance."""
+    _need_cuda(x, centroids)
+    BH, N, D = _tokens(x)
+    K = centroids.shape[1]
+    if centroids.shape != (BH, K, D) or centroids.dtype != x.dtype:
+        raise ValueError("centroids must be bf16 [BH, K, 128]")
+    labels = torch.empty(BH, N, dtype=torch.int32, device=x.device)
+    ws = workspace(x.device, BH, N, K, K)
+    check(LIB.svoo_b200_euclid_assign(x.data_ptr(), centroids.data_ptr(), BH, N, D, K, labels.data_ptr(), ws.data_ptr(),
+                                      ws.numel(), _stream()), "euclid_assign")
+    return labels
+
+
+def append_text_blocks(block_map_u8: torch.Tensor, q_offsets: torch.Tensor, k_offsets: torch.Tensor,
+                       q_sorted_idx: torch.Tensor, k_sorted_idx: torch.Tensor, text: int, prompt: int):
+    """Map, offsets and row indices of a joint-attention layer whose `text` text rows follow the
+    clustered video rows: (map [BH,QC+2,KC+2], q_off [BH,QC+3], k_off [BH,KC+3], q_idx, k_idx [BH,N+text])."""
+    _need_cuda(block_map_u8, q_offsets, k_offsets, q_sorted_idx, k_sorted_idx)
+    BH, QC, KC = block_map_u8.shape
+    N = q_sorted_idx.shape[1]
+    dev = block_map_u8.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    m = torch.empty(BH, QC + 2, KC + 2, dtype=torch.uint8, device=dev)
+    qo, ko = torch.empty(BH, QC + 3, **i32), torch.empty(BH, KC + 3, **i32)
+    qi, ki = torch.empty(BH, N + text, **i32), torch.empty(BH, N + text, **i32)
+    src = block_map_u8.view(torch.uint8) if block_map_u8.dtype == torch.bool else block_map_u8
+    check(LIB.svoo_b200_append_text_blocks(src.data_ptr(), q_offsets.data_ptr(), k_offsets.data_ptr(),
+                                           q_sorted_idx.data_ptr(), k_sorted_idx.data_ptr(), BH, N, QC, KC, int(text),
+                                           int(prompt), m.data_ptr(), qo.data_ptr(), ko.data_ptr(), qi.data_ptr(),
+                                           ki.data_ptr(), _stream()), "append_text_blocks")
+    return m, qo, ko, qi, ki
 
 
 def sort_labels(labels: torch.Tensor, num_clusters: int) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -199,12 +248,14 @@ def offsets_from_sizes(sizes: torch.Tensor) -> torch.Tensor:
 def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_map_u8: torch.Tensor,
                 q_offsets: torch.Tensor, k_offsets: torch.Tensor, sm_scale: Optional[float] = None,
                 out_row_idx: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                kernel: str = "tcgen05", peer_out=None) -> Optional[torch.Tensor]:
+                kernel: str = "tcgen05", peer_out=None, return_lse: bool = False):
     """Block-sparse attention over cluster-ordered q,k,v [BH,S,128].  With out_row_idx the
     result rows are scattered to their original positions (fused inverse permutation).
     kernel="simt" selects the mma.sync cross-check kernel.  peer_out = (peer pointer array,
     head id array, world, n_loc, H): the rows are stored into the ranks' sequence shards
-    instead of a local tensor (svoo_b200_sparse_attn_push) and nothing is returned."""
+    instead of a local tensor (svoo_b200_sparse_attn_push) and nothing is returned.
+    return_lse: also return fp32 [BH, S], log2 of every row's softmax denominator (-inf for a row
+    without keys), indexed like the output rows."""
     _need_cuda(q, k, v, block_map_u8, q_offsets, k_offsets)
     BH, S, D = _tokens(q)
     QC, KC = q_offsets.shape[1] - 1, k_offsets.shape[1] - 1
@@ -227,9 +278,15 @@ def sparse_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_map_u8:
     y = torch.empty_like(q) if out is None else out
     head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), block_map_u8.data_ptr(), q_offsets.data_ptr(),
             k_offsets.data_ptr(), BH, S, D, QC, KC, scale, y.data_ptr())
-    fn = LIB.svoo_b200_sparse_attn if kernel == "tcgen05" else LIB.svoo_b200_sparse_attn_simt
-    rc = fn(*head, ridx, ws.data_ptr(), ws.numel(), _stream())
-    check(rc, "sparse_attn")
+    if kernel == "tcgen05":
+        lse = torch.empty(BH, S, dtype=torch.float32, device=q.device) if return_lse else None
+        rc = LIB.svoo_b200_sparse_attn(*head, ridx, 0 if lse is None else lse.data_ptr(), ws.data_ptr(), ws.numel(),
+                                       _stream())
+        check(rc, "sparse_attn")
+        return (y, lse) if return_lse else y
+    if return_lse:
+        raise ValueError("the log-sum-exp output needs the tcgen05 kernel")
+    check(LIB.svoo_b200_sparse_attn_simt(*head, ridx, ws.data_ptr(), ws.numel(), _stream()), "sparse_attn")
     return y
 
 
@@ -277,24 +334,25 @@ def qk_prep(x: torch.Tensor, heads: int, weight: Optional[torch.Tensor] = None, 
 
 def layer(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_init_idx: torch.Tensor, k_init_idx: torch.Tensor,
           iters: int, top_p: float, preserve: Sequence[int], cap: Sequence[int],
-          sm_scale: Optional[float] = None) -> torch.Tensor:
+          sm_scale: Optional[float] = None, text: int = 0, prompt: int = 0) -> torch.Tensor:
     """The whole layer through the single C entry point svoo_b200_layer: q, k, v [BH, S, 128] bf16
-    in token order -> out [BH, S, 128].  Intermediates live in a scratch block that is released
-    with the returned tensor's call frame; use the separate ops when they are needed."""
+    in token order -> out [BH, S, 128]; the last `text` rows of every head are text tokens, of
+    which the first `prompt` are the prompt.  Intermediates live in a scratch block that is
+    released with the returned tensor's call frame; use the separate ops when they are needed."""
     _need_cuda(q, k, v, q_init_idx, k_init_idx)
     BH, S, D = _tokens(q)
     QC, KC = q_init_idx.shape[-1], k_init_idx.shape[-1]
     if len(preserve) != BH or len(cap) != BH:
         raise ValueError("preserve and cap need one entry per head")
     nbytes = ctypes.c_int64(0)
-    check(LIB.svoo_b200_layer_scratch_bytes(BH, S, QC, KC, ctypes.byref(nbytes)), "layer_scratch_bytes")
+    check(LIB.svoo_b200_layer_scratch_bytes(BH, S, QC, KC, int(text), ctypes.byref(nbytes)), "layer_scratch_bytes")
     scratch = torch.empty(nbytes.value, dtype=torch.uint8, device=q.device)
-    ws = workspace(q.device, BH, S, QC, KC)
+    ws = workspace(q.device, BH, S, QC + 2, KC + 2) if text else workspace(q.device, BH, S, QC, KC)
     out = torch.empty_like(q)
     arr = ctypes.c_int32 * BH
     qi, ki = q_init_idx.to(torch.int32).contiguous(), k_init_idx.to(torch.int32).contiguous()
     check(LIB.svoo_b200_layer(q.data_ptr(), k.data_ptr(), v.data_ptr(), qi.data_ptr(), ki.data_ptr(), BH, S, D, QC, KC,
                               int(iters), float(top_p), arr(*[int(x) for x in preserve]), arr(*[int(x) for x in cap]),
-                              D ** -0.5 if sm_scale is None else float(sm_scale), out.data_ptr(), scratch.data_ptr(),
-                              scratch.numel(), ws.data_ptr(), ws.numel(), _stream()), "layer")
+                              D ** -0.5 if sm_scale is None else float(sm_scale), int(text), int(prompt), out.data_ptr(),
+                              scratch.data_ptr(), scratch.numel(), ws.data_ptr(), ws.numel(), _stream()), "layer")
     return out

@@ -44,17 +44,54 @@ class _SAPBase:
     # reuse of a clustering across denoising steps
     start_reuse_step = None
     reuse_interval = 1
+    # not in the reference (which re-draws random tokens at every clustering call): start a
+    # re-clustering from the centroids of the previous one
+    warm_start_centroids = False
     # per-(step, layer, head) density from an offline profile
     use_dynamic_min_kc_ratio = False
     sparsity_lookup = None
     dynamic_min_kc_ratio_min = None
     dynamic_min_kc_ratio_max = None
 
+    # scheduler-timestep -> step counter shared by all layers (wan/attention.py:423-444)
+    _current_internal_timestep = None
+    _inference_step_counter = 0
+    _seen_timesteps: set = set()
+
     def __init__(self, layer_idx):
         self.layer_idx = layer_idx
         self.centroids_init = False
         self.current_inference_step = None
         self._cached_clustering_results = None
+        self._last_shape = None
+        self.last_block_map = None
+
+    def _get_inference_step(self, timestep):
+        """1-based denoising step derived from the scheduler timestep when no pipeline callback
+        sets `_step_from_callback`: a new timestep value counts one step, a timestep larger than
+        the last one starts a new run (wan/attention.py:423-444)."""
+        cls = self.__class__
+        t = timestep.flatten()[0].item() if isinstance(timestep, torch.Tensor) else timestep
+        if cls._current_internal_timestep is not None and t > cls._current_internal_timestep:
+            cls._inference_step_counter = 0
+            cls._seen_timesteps.clear()
+        if t not in cls._seen_timesteps:
+            cls._seen_timesteps.add(t)
+            cls._inference_step_counter += 1
+            cls._current_internal_timestep = t
+        return cls._inference_step_counter
+
+    def check_status(self) -> None:
+        """Raises if a tensor-core kernel of this layer's last sparse call gave up on one of its
+        bounded waits (its output rows were then left unwritten).  Reads two device words, so it
+        synchronises: call it once per denoising step or at the end of a run, not per layer."""
+        if self._last_shape is None:
+            return
+        dev, H, S, n_video, qc_attn, kc_attn = self._last_shape
+        if ops.attention_status(dev, H, S, qc_attn, kc_attn) != 0:
+            raise RuntimeError(f"layer {self.layer_idx}: the attention kernel timed out on a barrier; output incomplete")
+        if ops.cluster_status(dev, H, n_video, self.num_q_centroids, self.num_k_centroids) != 0:
+            raise RuntimeError(f"layer {self.layer_idx}: the assignment kernel timed out on a barrier; labels incomplete")
 
     # -- clustering with reuse (wan/attention.py:669-715, 793-819) -------------------------
     def _should_recluster(self) -> bool:
@@ -71,11 +108,35 @@ class _SAPBase:
             return self._cached_clustering_results
         cfg, H, N, D = query.shape
         iters = self.kmeans_iter_step if self.centroids_init else self.kmeans_iter_init
-        c = cc.co_cluster(query.reshape(cfg * H, N, D), key.reshape(cfg * H, N, D), self.num_q_centroids,
-                          self.num_k_centroids, iters)
+        q_flat, k_flat = query.reshape(cfg * H, N, D), key.reshape(cfg * H, N, D)
+        prev = self._cached_clustering_results if self.centroids_init else None
+        if self.use_svoo:
+            warm = (prev.qcentroids, prev.kcentroids) if (self.warm_start_centroids and prev is not None) else None
+            c = cc.co_cluster(q_flat, k_flat, self.num_q_centroids, self.num_k_centroids, iters, init_centroids=warm,
+                              init_indices=self.draw_init_indices(cfg * H, N, query.device))
+        else:
+            # plain Euclidean k-means per side; later calls continue from the previous centroids
+            # (kmeans_init / kmeans_step, wan/attention.py:612-667)
+            c = self._euclid_clustering(q_flat, k_flat, iters, prev)
         self.centroids_init = True
         self._cached_clustering_results = c
         return c
+
+    def draw_init_indices(self, BH, N, device):
+        """Initial centroid token indices (q [BH,QC], k [BH,KC]) of a fresh clustering, or None to
+        let co_cluster draw them on the device in the reference's order (q first, then k,
+        svoo/co_clustering.py:2417-2421).  A hook: tests replace it to replay recorded draws."""
+        return None
+
+    def _euclid_clustering(self, q_flat, k_flat, iters, prev) -> ops.Clustering:
+        out = []
+        for x, n_clusters, init in ((q_flat, self.num_q_centroids, None if prev is None else prev.qcentroids),
+                                    (k_flat, self.num_k_centroids, None if prev is None else prev.kcentroids)):
+            labels, centroids, sizes, _ = cc.batch_kmeans_Euclid(x, n_clusters, max_iters=iters, init_centroids=init)
+            idx, off = ops.sort_labels(labels, n_clusters)
+            out.append((labels.to(torch.int32), centroids.contiguous(), sizes, idx, off))
+        (ql, qc, qs, qi, qo), (kl, kc, ks, ki, ko) = out
+        return ops.Clustering(ql, kl, qc, kc, qs, ks, qi, ki, qo, ko)
 
     def _get_min_kc_ratio_for_heads_from_step(self, inference_step, num_heads):
         return min_kc_ratio_for_heads(self.sparsity_lookup, self.use_dynamic_min_kc_ratio, inference_step,
@@ -104,11 +165,16 @@ class _SAPBase:
         else:
             qv, kv = query, key
         c = self.kmeans_clustering(qv, kv, self.layer_idx)
+        extra = 2 if self.context_length else 0
+        self._last_shape = (query.device, cfg * H, S, n_video, self.num_q_centroids + extra, self.num_k_centroids + extra)
         ratio = self._get_min_kc_ratio_for_heads_from_step(self.current_inference_step, H)
-        return sparse_attention_layer(query, key, value, num_q_centroids=self.num_q_centroids,
-                                      num_k_centroids=self.num_k_centroids, kmeans_iters=0,
-                                      top_p=self.top_p_kmeans, min_kc_ratio=ratio, clustering=c,
-                                      context_length=self.context_length, prompt_length=prompt_length)
+        out, state = sparse_attention_layer(query, key, value, num_q_centroids=self.num_q_centroids,
+                                            num_k_centroids=self.num_k_centroids, kmeans_iters=0,
+                                            top_p=self.top_p_kmeans, min_kc_ratio=ratio, clustering=c,
+                                            context_length=self.context_length, prompt_length=prompt_length,
+                                            return_state=True)
+        self.last_block_map = state.block_map              # uint8 [H, QC(+2), KC(+2)] of the last sparse call
+        return out
 
 
 class WanAttn_SAPAttn_Processor(_SAPBase):
@@ -200,7 +266,12 @@ class WanAttn_SAPAttn_Processor(_SAPBase):
         cfg, H, S, D = query.size()
         assert cfg == 1, "Batch size must be 1 for kmeans block sparse attention"
         cb_step = getattr(self, "_step_from_callback", None)
-        self.current_inference_step = cb_step
+        if cb_step is not None:
+            self.current_inference_step = cb_step
+        elif timestep is not None:
+            self.current_inference_step = self._get_inference_step(timestep)
+        else:
+            self.current_inference_step = None
         assert S == self.context_length + self.num_frame * self.frame_size, (
             f"Query Shape: {S} is not equivalent to {self.context_length} + {self.num_frame} * {self.frame_size}")
         if self._full_attention_flag(timestep):
@@ -214,15 +285,98 @@ class WanAttn_SAPAttn_Processor(_SAPBase):
 
 
 class Hunyuan_SAPAttn_Processor2_0(_SAPBase):
-    """Joint-attention core for HunyuanVideo: video tokens are clustered, the text tokens
-    that follow them form two dense blocks (prompt, unused prompt)."""
+    """Joint-attention processor for HunyuanVideo blocks: video tokens are clustered, the text
+    tokens that follow them form two dense blocks (prompt, unused prompt)."""
     context_length = 256
-    prompt_length = 256
+    prompt_length = 0                  # as in the reference (hunyuan10/attention.py:368-369); the installer sets it
+
+    # -- call path (hunyuan10/attention.py:460-575) ---------------------------------------------
+    def get_qkv(self, attn, hidden_states):
+        return attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states)
+
+    def get_transpose_qkv(self, attn, query, key, value):
+        return tuple(t.unflatten(2, (attn.heads, -1)).transpose(1, 2).contiguous() for t in (query, key, value))
+
+    def get_qk_norm(self, attn, query, key):
+        if getattr(attn, "norm_q", None) is not None:
+            query = attn.norm_q(query)
+        if getattr(attn, "norm_k", None) is not None:
+            key = attn.norm_k(key)
+        return query, key
+
+    @staticmethod
+    def apply_rotary_emb(x, freqs_cis):
+        """Interleaved-pair rotation with real tables (cos, sin) [S, D], as diffusers' apply_rotary_emb
+        with use_real=True, use_real_unbind_dim=-1, which the reference calls (hunyuan10/attention.py:300-323)."""
+        cos, sin = freqs_cis
+        cos, sin = cos[None, None].to(x.device), sin[None, None].to(x.device)
+        x_real, x_imag = x.reshape(*x.shape[:-1], -1, 2).unbind(-1)
+        x_rot = torch.stack([-x_imag, x_real], dim=-1).flatten(3)
+        return (x.float() * cos + x_rot.float() * sin).to(x.dtype)
+
+    def get_rotary_emb(self, attn, query, key, image_rotary_emb, encoder_hidden_states):
+        if image_rotary_emb is None:
+            return query, key
+        if getattr(attn, "add_q_proj", None) is None and encoder_hidden_states is not None:
+            # single-stream block: text tokens are the tail of the sequence and are not rotated
+            txt = encoder_hidden_states.shape[1]
+            query = torch.cat([self.apply_rotary_emb(query[:, :, :-txt], image_rotary_emb), query[:, :, -txt:]], dim=2)
+            key = torch.cat([self.apply_rotary_emb(key[:, :, :-txt], image_rotary_emb), key[:, :, -txt:]], dim=2)
+        else:
+            query = self.apply_rotary_emb(query, image_rotary_emb)
+            key = self.apply_rotary_emb(key, image_rotary_emb)
+        return query, key
+
+    def get_encoder_condition_and_concat(self, attn, query, key, value, encoder_hidden_states):
+        if getattr(attn, "add_q_proj", None) is not None and encoder_hidden_states is not None:
+            eq, ek, ev = (proj(encoder_hidden_states).unflatten(2, (attn.heads, -1)).transpose(1, 2)
+                          for proj in (attn.add_q_proj, attn.add_k_proj, attn.add_v_proj))
+            if getattr(attn, "norm_added_q", None) is not None:
+                eq = attn.norm_added_q(eq)
+            if getattr(attn, "norm_added_k", None) is not None:
+                ek = attn.norm_added_k(ek)
+            query = torch.cat([query, eq], dim=2)
+            key = torch.cat([key, ek], dim=2)
+            value = torch.cat([value, ev], dim=2)
+        return query, key, value
+
+    @staticmethod
+    def get_cu_max_seqlen(attention_mask, device):
+        valid = attention_mask.sum()
+        cu = torch.stack([torch.zeros_like(valid), valid, torch.full_like(valid, attention_mask.numel())]).to(
+            device=device, dtype=torch.int32)
+        return cu, cu.clone(), attention_mask.numel(), attention_mask.numel()
+
+    def get_o(self, attn, hidden_states, encoder_hidden_states):
+        if encoder_hidden_states is not None:
+            txt = encoder_hidden_states.shape[1]
+            hidden_states, encoder_hidden_states = hidden_states[:, :-txt], hidden_states[:, -txt:]
+            if getattr(attn, "to_out", None) is not None:
+                hidden_states = attn.to_out[1](attn.to_out[0](hidden_states))
+            if getattr(attn, "to_add_out", None) is not None:
+                encoder_hidden_states = attn.to_add_out(encoder_hidden_states)
+        return hidden_states, encoder_hidden_states
+
+    def __call__(self, attn, hidden_states, encoder_hidden_states=None, attention_mask=None, image_rotary_emb=None,
+                 timestep=None):
+        """Returns (hidden_states, encoder_hidden_states) like the reference (hunyuan10/attention.py:536-575)."""
+        if getattr(attn, "add_q_proj", None) is None and encoder_hidden_states is not None:
+            hidden_states = torch.cat([hidden_states, encoder_hidden_states], dim=1)
+        query, key, value = self.get_qkv(attn, hidden_states)
+        query, key, value = self.get_transpose_qkv(attn, query, key, value)
+        query, key = self.get_qk_norm(attn, query, key)
+        query, key = self.get_rotary_emb(attn, query, key, image_rotary_emb, encoder_hidden_states)
+        query, key, value = self.get_encoder_condition_and_concat(attn, query, key, value, encoder_hidden_states)
+        cu_max_seqlens = None if attention_mask is None else self.get_cu_max_seqlen(attention_mask, query.device)
+        hidden_states = self.attention_core_logic(query, key, value, timestep, self.layer_idx, cu_max_seqlens)
+        hidden_states = hidden_states.transpose(1, 2).flatten(2, 3).to(query.dtype)
+        return self.get_o(attn, hidden_states, encoder_hidden_states)
 
     def attention_core_logic(self, query, key, value, timestep, layer_idx=None, cu_max_seqlens=None):
         """query/key/value [1, H, S, 128] -> [1, H, S, 128] (hunyuan10/attention.py:1031-1110)."""
         cfg, H, S, D = query.size()
         assert cfg == 1, "Batch size must be 1 for kmeans block sparse attention"
+        assert 0 <= self.prompt_length <= self.context_length, "prompt_length must lie in [0, context_length]"
         assert S == self.context_length + self.num_frame * self.frame_size, (
             f"Query Shape: {S} is not equivalent to {self.context_length} + {self.num_frame} * {self.frame_size}")
         self.current_inference_step = getattr(self, "_step_from_callback", None)
@@ -230,8 +384,9 @@ class Hunyuan_SAPAttn_Processor2_0(_SAPBase):
             n_video = self.num_frame * self.frame_size
             if self.zero_step_kmeans_init:
                 self.kmeans_clustering(query[:, :, :n_video].contiguous(), key[:, :, :n_video].contiguous())
-            # dense: prompt and video attend each other, the unused prompt only itself
-            valid = n_video + self.prompt_length
+            # dense (the reference's flashinfer_varlen_func, :1113-1185): two diagonal blocks, the
+            # tokens the attention mask keeps (video + prompt) and the unused prompt
+            valid = n_video + self.prompt_length if cu_max_seqlens is None else int(cu_max_seqlens[0][1])
             out = torch.empty_like(query)
             out[:, :, :valid] = self.flash_attention(query[:, :, :valid], key[:, :, :valid], value[:, :, :valid])
             if valid < S:

@@ -5,6 +5,8 @@ default: a directory `reference` beside this repository):
 
     python tests/golden/make_golden.py            # all fixtures (about 4 minutes)
     python tests/golden/make_golden.py layer_tiny_bf16   # just that one
+    python tests/golden/make_golden.py processor_wan     # the processor fixtures: each in a process
+    python tests/golden/make_golden.py processor_hunyuan # of its own (they configure class attributes)
 
 The reference's hot path is Triton + torch.  Its Triton kernels are executed on
 CPU tensors by the Triton interpreter (TRITON_INTERPRET=1); the wrappers'
@@ -42,6 +44,12 @@ checksum = synth.tensor_checksum
 
 def f32(t):
     return t.float().numpy()
+
+
+def bf16_bits(t):
+    """The bit patterns of a bf16 tensor as int16 (numpy has no bf16); golden_util.from_bf16_bits undoes it."""
+    assert t.dtype == torch.bfloat16
+    return t.contiguous().view(torch.int16).numpy()
 
 
 def layer_case(name, cfg, iters, density, rows_kept=8, max_ratio=None):
@@ -221,11 +229,182 @@ def producer_case(name, S, H, seed, eps=1e-6):
     print(name, "written")
 
 
+PROC_ROWS_KEPT = 8          # the processor fixtures keep every 8th output row
+
+
+def _diffusers_stand_ins():
+    """The reference's processor modules import a handful of names from diffusers, which is not
+    installed here.  None of them is executed on the routes the fixtures take; empty stand-ins let
+    the modules import.  `torch.compile` is the identity while they import (they compile
+    flex_attention at import time)."""
+    import types
+
+    def mod(mname, **attrs):
+        m = types.ModuleType(mname)
+        m.__dict__.update(attrs)
+        sys.modules.setdefault(mname, m)
+
+    att = type("Attention", (torch.nn.Module,), {})
+    for name in ("diffusers", "diffusers.models", "diffusers.models.transformers", "diffusers.pipelines",
+                 "diffusers.pipelines.hunyuan_video"):
+        mod(name)
+    mod("diffusers.models.attention_processor", Attention=att)
+    mod("diffusers.models.attention", Attention=att)
+    mod("diffusers.models.embeddings", apply_rotary_emb=None)
+    mod("diffusers.models.normalization", RMSNorm=type("RMSNorm", (torch.nn.Module,), {}))
+    mod("diffusers.models.transformers.transformer_wan", _get_added_kv_projections=None, dispatch_attention_fn=None)
+    mod("diffusers.pipelines.hunyuan_video.pipeline_hunyuan_video", DEFAULT_PROMPT_TEMPLATE={})
+
+
+def _import_reference_processors():
+    _diffusers_stand_ins()
+    real_compile = torch.compile
+    torch.compile = lambda f=None, **kw: f
+    try:
+        import svoo.models.wan.attention as ref_wan
+        import svoo.models.hunyuan10.attention as ref_hun
+    finally:
+        torch.compile = real_compile
+    return ref_wan, ref_hun
+
+
+def _fp32_attention_shim():
+    """The Triton interpreter cannot run tl.dot on bf16 operands and the reference's block-sparse
+    attention kernel does not up-cast before its dots: it is given the same values as fp32 and
+    its result is cast back (the one deviation of layer_case above)."""
+    orig = ref_cc.dynamic_block_sparse_fwd_triton
+
+    def shim(q, k, v, *rest, **kw):
+        return orig(q.float(), k.float(), v.float(), *rest, **kw).to(q.dtype)
+
+    return shim
+
+
+def processor_case_wan():
+    """The unmodified WanAttn_SAPAttn_Processor.__call__ -> attention_core_logic, configured by
+    class attributes the way the installer does it, over four denoising steps of one layer: a
+    dense warm-up step, the first clustering, a step that reuses the cached clustering, and a
+    re-clustering with kmeans_iter_step iterations; the per-head density comes from a CSV with a
+    hole (step 3 falls back to the scalar ratio).  SVG_SPARSE_ATTN_BACKEND=triton selects the
+    reference's Triton attention backend (FlashInfer has no CPU path)."""
+    from tests import golden_util as gu
+    os.environ["SVG_SPARSE_ATTN_BACKEND"] = "triton"
+    ref_wan, _ = _import_reference_processors()
+    ref_wan.ENABLE_FAST_KERNEL = False                    # norms through the block's own norm modules
+    ref_cc.dynamic_block_sparse_fwd_triton = _fp32_attention_shim()
+    P = gu.WAN_PROC
+    H = P["heads"]
+    T, Hh, W = P["grid"]
+    N = T * Hh * W
+    csv_path = os.path.join(HERE, "processor_wan_density.csv")
+    gu.write_density_csv(csv_path, H, [2, 3, 7], hole=(3, 1))
+    cls = ref_wan.WanAttn_SAPAttn_Processor
+    gu.configure_wan_processor(cls, RefLookup(csv_path))
+    cls.measure_attention_sparsity = False
+    maps = []
+    real_map = ref_wan.identify_dynamic_map
+
+    def recording_map(*a, **kw):
+        m = real_map(*a, **kw)
+        maps.append((m.clone(), a[5] if len(a) > 5 else kw.get("min_kc_ratio")))
+        return m
+
+    ref_wan.identify_dynamic_map = recording_map
+    attn = gu.make_attn(31, H)
+    cos, sin = gu.rotary_tables(32, N)
+    proc = cls(0)
+    out = {}
+    for i, (step, tval) in enumerate(P["steps"]):
+        hidden = gu.wan_step_hidden(step)
+        proc._step_from_callback = step
+        torch.manual_seed(100 + step)
+        n_maps = len(maps)
+        t0 = time.time()
+        with torch.no_grad():
+            y = proc(attn, hidden, rotary_emb=(cos, sin), timestep=torch.tensor([tval]))
+        torch.manual_seed(100 + step)                     # the draws co_cluster_tokens made, if it ran
+        out[f"q_init_{step}"] = torch.randint(0, N, (H, P["num_q"])).numpy().astype(np.int32)
+        out[f"k_init_{step}"] = torch.randint(0, N, (H, P["num_k"])).numpy().astype(np.int32)
+        out[f"out_{step}"] = bf16_bits(y[0, ::PROC_ROWS_KEPT])
+        out[f"hidden_checksum_{step}"] = checksum(hidden)
+        c = getattr(proc, "_cached_clustering_results", None)
+        if len(maps) > n_maps:
+            m, ratio = maps[-1]
+            out[f"map_bits_{step}"] = np.packbits(m.numpy())
+            out[f"map_shape_{step}"] = np.array(m.shape)
+            out[f"ratio_{step}"] = np.array(ratio if isinstance(ratio, list) else [ratio], dtype=np.float64)
+            out[f"qlabels_{step}"] = c["qlabels"].numpy().astype(np.int16)
+            out[f"klabels_{step}"] = c["klabels"].numpy().astype(np.int16)
+            out[f"qcentroids_{step}"] = bf16_bits(c["qcentroids"])
+            out[f"kcentroids_{step}"] = bf16_bits(c["kcentroids"])
+            out[f"ksizes_{step}"] = c["kcluster_sizes"].numpy().astype(np.int32)
+            out[f"qsizes_{step}"] = c["qcluster_sizes"].numpy().astype(np.int32)
+        print(f"processor_wan step {step}: {time.time() - t0:.1f}s, sparse={len(maps) > n_maps}")
+    np.savez_compressed(os.path.join(HERE, "processor_wan.npz"), **out)
+
+
+def processor_case_hunyuan():
+    """The unmodified Hunyuan_SAPAttn_Processor2_0.__call__ -> attention_core_logic on a
+    single-stream block (text tokens appended after the video tokens), prompt_length <
+    context_length so that the unused-prompt block is not empty.  Two substitutions, both needed
+    because this route otherwise ends in FlashInfer CUDA code: the module's
+    dynamic_block_sparse_fwd_flashinfer name is bound to the reference's own Triton backend
+    (same arguments and semantics), and no rotary table is passed (diffusers' apply_rotary_emb
+    is not installed)."""
+    from tests import golden_util as gu
+    _, ref_hun = _import_reference_processors()
+    ref_hun.ENABLE_FAST_KERNEL = False
+    triton_attn = _fp32_attention_shim()
+    ref_hun.dynamic_block_sparse_fwd_flashinfer = lambda q, k, v, m, rs, cs, is_cpu=False: triton_attn(q, k, v, m, rs, cs)
+    P = gu.HUN_PROC
+    H = P["heads"]
+    T, Hh, W = P["grid"]
+    N = T * Hh * W
+    cls = ref_hun.Hunyuan_SAPAttn_Processor2_0
+    gu.configure_hunyuan_processor(cls)
+    cls.measure_attention_sparsity = False
+    maps = []
+    real_map = ref_hun.identify_dynamic_map
+
+    def recording_map(*a, **kw):
+        m = real_map(*a, **kw)
+        maps.append(m.clone())
+        return m
+
+    ref_hun.identify_dynamic_map = recording_map
+    attn = gu.make_attn(41, H, joint=True)
+    hidden, enc, mask = gu.hunyuan_inputs()
+    proc = cls(0)
+    step, tval = P["steps"][0]
+    proc._step_from_callback = step
+    torch.manual_seed(100 + step)
+    t0 = time.time()
+    with torch.no_grad():
+        y, y_enc = proc(attn, hidden, encoder_hidden_states=enc, attention_mask=mask, image_rotary_emb=None,
+                        timestep=torch.tensor([tval]))
+    torch.manual_seed(100 + step)
+    out = dict(q_init=torch.randint(0, N, (H, P["num_q"])).numpy().astype(np.int32),
+               k_init=torch.randint(0, N, (H, P["num_k"])).numpy().astype(np.int32))
+    c = proc._cached_clustering_results
+    m = maps[-1]
+    out.update(out=bf16_bits(y[0, ::PROC_ROWS_KEPT]), out_enc=bf16_bits(y_enc[0]), input_checksum=checksum(hidden, enc),
+               map_bits=np.packbits(m.numpy()), map_shape=np.array(m.shape),
+               qlabels=c["qlabels"].numpy().astype(np.int16), klabels=c["klabels"].numpy().astype(np.int16),
+               qcentroids=bf16_bits(c["qcentroids"]), kcentroids=bf16_bits(c["kcentroids"]),
+               qsizes=c["qcluster_sizes"].numpy().astype(np.int32), ksizes=c["kcluster_sizes"].numpy().astype(np.int32))
+    np.savez_compressed(os.path.join(HERE, "processor_hunyuan.npz"), **out)
+    print(f"processor_hunyuan: {time.time() - t0:.1f}s")
+
+
 def main():
     import dataclasses
     only = sys.argv[1:]
     tiny = synth.LayerConfig("tiny-fp32", 90, 2, (4, 16, 16), torch.float32, 8, 16, 3, (0.25, 0.25), 1, False)
     if only:
+        if "processor_wan" in only:
+            processor_case_wan()
+        if "processor_hunyuan" in only:
+            processor_case_hunyuan()
         if "producer" in only:
             producer_case("producer_h6", 96, 6, 21)
             producer_case("producer_h4", 80, 4, 22)

@@ -25,7 +25,19 @@ def load(name):
     return np.load(os.path.join(GOLDEN, name + ".npz"))
 
 
-def unpack_map(z):
+def from_bf16_bits(a):
+    """int16 bit patterns (as stored by the fixture generator) -> bf16 tensor."""
+    return torch.from_numpy(np.ascontiguousarray(a)).view(torch.bfloat16)
+
+
+def unpack_map(z, suffix=""):
+    if suffix:
+        shape = tuple(int(x) for x in z["map_shape" + suffix])
+        return np.unpackbits(z["map_bits" + suffix])[: int(np.prod(shape))].reshape(shape).astype(bool)
+    return _unpack_map(z)
+
+
+def _unpack_map(z):
     shape = tuple(int(x) for x in z["map_shape"])
     return np.unpackbits(z["map_bits"])[: int(np.prod(shape))].reshape(shape).astype(bool)
 
@@ -75,3 +87,182 @@ def same_up_to_ties(got, ref, prob):
     a = np.sort(np.where(got, prob, -1.0), -1)
     b = np.sort(np.where(ref, prob, -1.0), -1)
     return bool((a == b).all())
+
+
+# ----------------------------------------------------------------------------------------------
+# Processor fixtures: the inputs are rebuilt from seeds by the generator and by the tests alike.
+# ----------------------------------------------------------------------------------------------
+class RMSNormModule(torch.nn.Module):
+    """Weight-only RMS norm over the last dimension (what a DiT block passes as attn.norm_q)."""
+
+    def __init__(self, dim, eps, weight):
+        super().__init__()
+        self.weight = torch.nn.Parameter(weight)
+        self.eps = eps
+
+    def forward(self, x):
+        xf = x.float()
+        y = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + self.eps)
+        return (y * self.weight.float()).to(x.dtype)
+
+
+def smooth_hidden(seed, grid, dim, extra_rows=0, noise=0.35):
+    """[1, N(+extra), dim] bf16 activations with low-frequency structure over the latent grid."""
+    import math
+    T, Hh, W = grid
+    g = torch.Generator("cpu").manual_seed(seed)
+    t, h, w = torch.meshgrid(torch.arange(T), torch.arange(Hh), torch.arange(W), indexing="ij")
+    coords = torch.stack([t.reshape(-1) / T, h.reshape(-1) / Hh, w.reshape(-1) / W], -1).float()
+    freqs = torch.randint(0, 3, (12, 3), generator=g).float()
+    freqs[freqs.sum(-1) == 0, 0] = 1
+    feat = torch.cos(2 * math.pi * coords @ freqs.T + torch.rand(12, generator=g) * 2 * math.pi)
+    x = feat @ (torch.randn(12, dim, generator=g) / 3) + noise * torch.randn(coords.shape[0], dim, generator=g)
+    if extra_rows:
+        x = torch.cat([x, torch.randn(extra_rows, dim, generator=g)], 0)
+    return x[None].bfloat16()
+
+
+def make_attn(seed, heads, joint=False, bias=True):
+    """A stand-in for a DiT block's attention module: q/k/v/out projections and QK norms, seeded.
+    joint=False: Wan layout (norms over all heads*128 columns); joint=True: HunyuanVideo
+    single-stream layout (norms over the 128 columns of a head, no added projections)."""
+    dim = heads * 128
+    g = torch.Generator("cpu").manual_seed(seed)
+    attn = torch.nn.Module()
+    for nm in ("to_q", "to_k", "to_v", "to_o"):
+        lin = torch.nn.Linear(dim, dim, bias=bias)
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(dim, dim, generator=g) / dim ** 0.5)
+            if bias:
+                lin.bias.copy_(torch.randn(dim, generator=g) * 0.05)
+        setattr(attn, nm, lin.bfloat16())
+    ndim = 128 if joint else dim
+    attn.norm_q = RMSNormModule(ndim, 1e-6, (1.0 + 0.2 * torch.randn(ndim, generator=g)).bfloat16())
+    attn.norm_k = RMSNormModule(ndim, 1e-6, (1.0 + 0.2 * torch.randn(ndim, generator=g)).bfloat16())
+    attn.heads = heads
+    attn.add_k_proj = None
+    attn.add_q_proj = None
+    attn.to_out = torch.nn.ModuleList([attn.to_o, torch.nn.Identity()])
+    del attn.to_o
+    return attn
+
+
+def rotary_tables(seed, S):
+    """(cos, sin) [1, S, 1, 128] fp32 in the layout a Wan rotary module hands to the processor."""
+    g = torch.Generator("cpu").manual_seed(seed)
+    ang = torch.rand(S, 64, generator=g) * 6.2831853
+    cos = torch.cos(ang).repeat_interleave(2, dim=-1)[None, :, None, :].contiguous()
+    sin = torch.sin(ang).repeat_interleave(2, dim=-1)[None, :, None, :].contiguous()
+    return cos, sin
+
+
+WAN_PROC = dict(heads=4, grid=(3, 16, 20), num_q=12, num_k=40, iter_init=2, iter_step=1, top_p=0.9, min_kc_ratio=0.15,
+                first_times_fp=900.0, start_reuse_step=2, reuse_interval=5, dyn_min=0.05, dyn_max=0.4,
+                # (1-based step from the pipeline callback, scheduler timestep): dense, cluster, reuse, re-cluster
+                steps=[(1, 950.0), (2, 800.0), (3, 700.0), (7, 300.0)])
+PROC_ROWS_KEPT = 8          # the processor fixtures keep every 8th output row
+HUN_PROC = dict(heads=3, grid=(2, 16, 20), num_q=10, num_k=32, iter_init=2, top_p=0.9, min_kc_ratio=0.2,
+                context_length=64, prompt_length=40, first_times_fp=900.0, steps=[(1, 500.0)])
+
+
+def write_density_csv(path, heads, steps, layer=0, seed=5, hole=None):
+    """A Step,Layer,Head,Sparsity table; `hole` = (step, head) that is left out."""
+    import csv
+    g = torch.Generator("cpu").manual_seed(seed)
+    with open(path, "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["Step", "Layer", "Head", "Sparsity"])
+        for s in steps:
+            for h in range(heads):
+                v = float(torch.rand(1, generator=g)) * 0.5
+                if hole is not None and (s, h) == hole:
+                    continue
+                w.writerow([s, layer, h, f"{v:.6f}"])
+
+
+def configure_wan_processor(cls, lookup):
+    """Class attributes exactly as the reference's installer assigns them
+    (svoo/models/wan/inference.py:267-328) for the WAN_PROC case."""
+    P = WAN_PROC
+    T, Hh, W = P["grid"]
+    cls.first_layers_fp = 0
+    cls.first_times_fp = P["first_times_fp"]
+    cls.context_length = 0
+    cls.num_frame = T
+    cls.frame_size = Hh * W
+    cls.num_q_centroids = P["num_q"]
+    cls.num_k_centroids = P["num_k"]
+    cls.top_p_kmeans = P["top_p"]
+    cls.min_kc_ratio = P["min_kc_ratio"]
+    cls.num_layers = 1
+    cls.kmeans_iter_init = P["iter_init"]
+    cls.kmeans_iter_step = P["iter_step"]
+    cls.zero_step_kmeans_init = False
+    cls.use_svoo = True
+    cls.start_reuse_step = P["start_reuse_step"]
+    cls.reuse_interval = P["reuse_interval"]
+    cls.sparsity_lookup = lookup
+    cls.use_dynamic_min_kc_ratio = True
+    cls.dynamic_min_kc_ratio_min = P["dyn_min"]
+    cls.dynamic_min_kc_ratio_max = P["dyn_max"]
+
+
+def configure_hunyuan_processor(cls):
+    """Class attributes as svoo/models/hunyuan10/inference.py assigns them, for the HUN_PROC case."""
+    P = HUN_PROC
+    T, Hh, W = P["grid"]
+    cls.first_layers_fp = 0
+    cls.first_times_fp = P["first_times_fp"]
+    cls.context_length = P["context_length"]
+    cls.prompt_length = P["prompt_length"]
+    cls.num_frame = T
+    cls.frame_size = Hh * W
+    cls.num_q_centroids = P["num_q"]
+    cls.num_k_centroids = P["num_k"]
+    cls.top_p_kmeans = P["top_p"]
+    cls.min_kc_ratio = P["min_kc_ratio"]
+    cls.kmeans_iter_init = P["iter_init"]
+    cls.kmeans_iter_step = P["iter_init"]
+    cls.zero_step_kmeans_init = False
+    cls.use_svoo = True
+    cls.start_reuse_step = None
+    cls.reuse_interval = 1
+    cls.use_dynamic_min_kc_ratio = False
+    cls.sparsity_lookup = None
+
+
+def wan_step_hidden(step):
+    """Activations of denoising step `step`: one smooth field, a little step-dependent noise."""
+    P = WAN_PROC
+    base = smooth_hidden(300, P["grid"], P["heads"] * 128).float()
+    g = torch.Generator("cpu").manual_seed(300 + step)
+    return (base + 0.08 * torch.randn(base.shape, generator=g)).bfloat16()
+
+
+def hunyuan_inputs():
+    """(hidden [1,N,dim], encoder [1,ctx,dim], attention mask [1, N+ctx] bool) of the HUN_PROC case."""
+    P = HUN_PROC
+    T, Hh, W = P["grid"]
+    n = T * Hh * W
+    x = smooth_hidden(400, P["grid"], P["heads"] * 128, extra_rows=P["context_length"])
+    mask = torch.zeros(1, n + P["context_length"], dtype=torch.bool)
+    mask[:, :n + P["prompt_length"]] = True
+    return x[:, :n].contiguous(), x[:, n:].contiguous(), mask
+
+
+def comparable_tokens(qlabels, ref_qlabels, video_map, ref_video_map):
+    """bool [N]: tokens that, in every head, carry the reference's query label and whose query
+    cluster keeps exactly the reference's key clusters.  The reference's torch.sort is unstable, so
+    equal-probability clusters at the cut may be swapped in its map; output rows of the affected
+    query clusters are compared nowhere, all other rows everywhere.  qlabels [H,N], maps [H,QC,KC]."""
+    ql = torch.as_tensor(np.asarray(qlabels).astype(np.int64))
+    rl = torch.as_tensor(np.asarray(ref_qlabels).astype(np.int64))
+    same_row = torch.as_tensor((np.asarray(video_map) == np.asarray(ref_video_map)).all(-1))
+    return ((ql == rl) & torch.gather(same_row, 1, ql)).all(0)
+
+
+def processor_map_ties_ok(qc, kc, qs, ks, p, ratio, got_video_map, ref_video_map):
+    """The two video maps keep clusters of equal probabilities in every row."""
+    from oracle import svoo_oracle as O
+    _, prob = O.identify_dynamic_map(qc[None], kc[None], qs[None], ks[None], p, ratio, return_probs=True)
+    return same_up_to_ties(np.asarray(got_video_map), np.asarray(ref_video_map), prob.numpy()[0])

@@ -1,0 +1,80 @@
+"""The processors' dataflow restated with plain torch + the CPU oracle (test infrastructure):
+what the reference's WanAttn_SAPAttn_Processor / Hunyuan_SAPAttn_Processor2_0 compute for the
+fixture cases of tests/golden_util.py, step by step, from the recorded initial indices."""
+import os
+
+import torch
+import torch.nn.functional as F
+
+from oracle import svoo_oracle as O
+from svoo_b200.sparsity import SparsityLookup, min_kc_ratio_for_heads
+from tests import golden_util as gu
+
+
+def wan_qkv(attn, hidden, cos, sin):
+    """q, k, v [1,H,S,128] as the Wan __call__ hands them to attention_core_logic when the norms run
+    through the block's own modules (svoo/models/wan/attention.py:169-195)."""
+    H = attn.heads
+    q, k, v = attn.to_q(hidden), attn.to_k(hidden), attn.to_v(hidden)
+    q, k = attn.norm_q(q), attn.norm_k(k)
+    q, k, v = (t.unflatten(2, (H, -1)) for t in (q, k, v))
+    q, k = O.rotary_interleaved(q, cos, sin), O.rotary_interleaved(k, cos, sin)
+    return tuple(t.transpose(1, 2).contiguous() for t in (q, k, v))
+
+
+def wan_steps(z):
+    """Runs the four steps of the WAN_PROC case through the oracle.  Yields
+    (step, sparse?, out [S, dim] bf16, aux dict or None)."""
+    P = gu.WAN_PROC
+    H = P["heads"]
+    T, Hh, W = P["grid"]
+    N = T * Hh * W
+    lookup = SparsityLookup(os.path.join(gu.GOLDEN, "processor_wan_density.csv"))
+    attn = gu.make_attn(31, H)
+    cos, sin = gu.rotary_tables(32, N)
+    cached, inited = None, False
+    with torch.no_grad():
+        for step, tval in P["steps"]:
+            hidden = gu.wan_step_hidden(step)
+            q, k, v = wan_qkv(attn, hidden, cos, sin)
+            if tval > P["first_times_fp"]:
+                o = F.scaled_dot_product_attention(q, k, v)
+                aux = None
+            else:
+                recluster = True
+                if step >= P["start_reuse_step"]:
+                    recluster = (step - P["start_reuse_step"]) % P["reuse_interval"] == 0
+                if recluster or cached is None:
+                    iters = P["iter_step"] if inited else P["iter_init"]
+                    qi = torch.from_numpy(z[f"q_init_{step}"]).long()
+                    ki = torch.from_numpy(z[f"k_init_{step}"]).long()
+                    cached = O.co_cluster_tokens(q[0], k[0], qi, ki, iters)
+                    inited = True
+                ratio = min_kc_ratio_for_heads(lookup, True, step, 0, H, P["min_kc_ratio"], P["dyn_min"], P["dyn_max"])
+                o, aux = O.attention_given_clustering(q, k, v, cached, P["top_p"], ratio)
+                aux["ratio"] = ratio
+            y = attn.to_out[0](o.transpose(1, 2).flatten(2, 3))
+            yield step, aux is not None, y[0], aux
+
+
+def hunyuan_qkv(attn, hidden, enc):
+    """q, k, v [1,H,S,128] of a single-stream block without rotary tables
+    (svoo/models/hunyuan10/attention.py:545-561)."""
+    x = torch.cat([hidden, enc], dim=1)
+    q, k, v = (t.unflatten(2, (attn.heads, -1)).transpose(1, 2).contiguous() for t in (attn.to_q(x), attn.to_k(x), attn.to_v(x)))
+    return attn.norm_q(q), attn.norm_k(k), v
+
+
+def hunyuan_step(z):
+    """The HUN_PROC case through the oracle: (out [N, dim], out_enc [ctx, dim], aux)."""
+    P = gu.HUN_PROC
+    attn = gu.make_attn(41, P["heads"], joint=True)
+    hidden, enc, mask = gu.hunyuan_inputs()
+    with torch.no_grad():
+        q, k, v = hunyuan_qkv(attn, hidden, enc)
+        qi, ki = torch.from_numpy(z["q_init"]).long(), torch.from_numpy(z["k_init"]).long()
+        o, aux = O.sparse_attention_layer(q, k, v, qi, ki, P["num_q"], P["num_k"], P["iter_init"], P["top_p"],
+                                          float(P["min_kc_ratio"]), 0, P["context_length"], P["prompt_length"])
+        y = o.transpose(1, 2).flatten(2, 3)
+        ctx = P["context_length"]
+        return attn.to_out[0](y[:, :-ctx])[0], y[0, -ctx:], aux

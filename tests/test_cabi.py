@@ -34,7 +34,7 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 
 
 def test_version_and_error_strings(lib):
-    assert lib.LIB.svoo_b200_version() == 100
+    assert lib.LIB.svoo_b200_version() == lib.VERSION
     assert lib.LIB.svoo_b200_error_string(0) == b"ok"
     assert b"128" in lib.LIB.svoo_b200_error_string(-3)
     with pytest.raises(ValueError):
@@ -51,6 +51,8 @@ def test_workspace_bytes(lib):
     assert lib.LIB.svoo_b200_workspace_bytes(40, 75600, 500, 100, ctypes.byref(out)) == 0
     assert out.value == big                                   # symmetric in (QC, KC)
     assert lib.LIB.svoo_b200_workspace_bytes(40, 75600, 100, 2000, ctypes.byref(out)) == -6
+    # the shipped HunyuanVideo setting: 256 / 1024 clusters plus the two text blocks
+    assert lib.LIB.svoo_b200_workspace_bytes(24, 118800 + 256, 258, 1026, ctypes.byref(out)) == 0
     assert lib.LIB.svoo_b200_workspace_bytes(0, 75600, 100, 500, ctypes.byref(out)) == -2
     assert lib.LIB.svoo_b200_workspace_bytes(1, 10, 1, 1, None) == -1
 
@@ -65,7 +67,21 @@ def test_host_side_argument_checks(lib):
     assert L.svoo_b200_permute(p + 2, p, 1, 4, 128, 4, 4, p, None) == -5
     assert L.svoo_b200_permute(p, p, 1, 4, 128, 2, 4, p, None) == -2
     assert L.svoo_b200_sort_labels(p, 1, 4, 4, p, p, p, 16, None) == -4
-    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 2, 2000, 0.1, p, None, p, 1 << 30, None) == -6
+    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 2, 2000, 0.1, p, None, None, p, 1 << 30, None) == -6
+    # the attention side takes the clusters plus two text blocks, the clustering does not
+    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 258, 1026, 0.1, p, None, None, p, 16, None) == -4
+    assert L.svoo_b200_sparse_attn(p, p, p, p, p, p, 1, 4, 128, 258, 1027, 0.1, p, None, None, p, 1 << 30, None) == -6
+    assert L.svoo_b200_cocluster(p, p, p, p, 1, 4, 128, 2, 1025, 1, p, p, p, p, p, p, p, p, p, p, p, 1 << 30, None) == -6
+    assert L.svoo_b200_cocluster(p, p, p, None, 1, 4, 128, 2, 2, 1, p, p, p, p, p, p, p, p, p, p, p, 1 << 30, None) == -1
+    # BH * N must fit a 32-bit row index
+    assert L.svoo_b200_permute(p, p, 200, 1 << 24, 128, 1 << 24, 1 << 24, p, None) == -2
+    assert L.svoo_b200_sort_labels_static(p, 200, 1 << 24, 4, p, p, None) == -2
+    assert L.svoo_b200_euclid_assign(p, p, 1, 4, 128, 2000, p, p, 1 << 30, None) == -6
+    assert L.svoo_b200_append_text_blocks(p, p, p, p, p, 1, 4, 2, 2, 4, 5, p, p, p, p, p, None) == -2
+    out = ctypes.c_int64(0)
+    assert L.svoo_b200_layer_scratch_bytes(2, 1000, 8, 16, 64, ctypes.byref(out)) == 0 and out.value > 3 * 2 * 1000 * 256
+    assert L.svoo_b200_layer_scratch_bytes(2, 1000, 8, 16, 1000, ctypes.byref(out)) == -2
+    assert L.svoo_b200_layer(p, p, p, p, p, 2, 1000, 128, 8, 16, 1, 0.9, p, p, 0.1, 64, 65, p, p, 1 << 40, p, 1 << 40, None) == -2
     assert L.svoo_b200_cocluster(p, p, p, p, 1, 4, 128, 2, 2, 0, p, p, p, p, p, p, p, p, p, p, p, 1 << 30, None) == -2
 
 
@@ -118,4 +134,4 @@ def test_header_is_plain_c_and_links(tmp_path):
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0, run.stderr
     version, rc, nbytes = run.stdout.split()
-    assert int(version) == 100 and int(rc) == 0 and int(nbytes) > 0
+    assert int(version) == 101 and int(rc) == 0 and int(nbytes) > 0

@@ -195,13 +195,8 @@ def test_cocluster_teacher_forced_larger(dev):
         ql = ops.cocluster_assign(qd, kc.to(dev), qc.to(dev))
         assert (ql.cpu().long() == ql_ref).float().mean() >= LABEL_AGREE
         qc, _ = O.centroid_update(q[0], ql_ref, qc)
-    # whole run: reported, and bounded loosely
+    # whole run (its agreement with the oracle is judged in test_whole_run_agreement_against_fp32_drift)
     full = ops.cocluster(qd, kd, qi.to(dev), ki.to(dev), cfg.iters)
-    ref = O.co_cluster_tokens(q[0], k[0], qi, ki, cfg.iters)
-    agree_q = (full.qlabels.cpu().long() == ref[0]).float().mean().item()
-    agree_k = (full.klabels.cpu().long() == ref[3]).float().mean().item()
-    print(f"cfg1 x2 heads, {cfg.iters} iterations: label agreement q={agree_q:.4f} k={agree_k:.4f}")
-    assert agree_q > 0.95 and agree_k > 0.95
     # permutation outputs are consistent with the labels
     idx_ref, off_ref = O.sort_labels(full.qlabels.cpu().long(), cfg.num_q)
     assert torch.equal(full.q_sorted_idx.cpu(), idx_ref) and torch.equal(full.q_offsets.cpu(), off_ref)
@@ -616,3 +611,214 @@ def test_argument_errors(dev):
                       torch.zeros(1, 4, dtype=torch.int64, device=dev), 0)         # no iterations
     with pytest.raises(ValueError):
         ops.permute(x.cpu(), torch.zeros(1, 10, dtype=torch.int32))                 # no CPU path
+
+
+# ----------------------------------------------------------------------------------------
+# whole-run label agreement at scale: measured against the drift of two correct fp32 implementations
+# ----------------------------------------------------------------------------------------
+def _masked_rows(q, k, v, ql, kl, dmap, rows, h):
+    """fp32 attention of the sampled query rows of head h over the key tokens their cluster keeps."""
+    keep = dmap[h][ql[h, rows]][:, kl[h]]                       # [rows, N] bool
+    sc = (q[h, rows].float() @ k[h].float().T) * 128 ** -0.5
+    sc = sc.masked_fill(~keep, float("-inf"))
+    return torch.softmax(sc, -1) @ v[h].float()
+
+
+@pytest.mark.parametrize("cfg_name", ["cfg1", "cfg2"])
+def test_whole_run_agreement_against_fp32_drift(dev, cfg_name, record_property):
+    """Whole k-means runs at Wan scale (2 heads).  A handful of near-tie flips per step move the
+    bf16 centroids, so any two correct implementations drift apart over the iterations; the bar is
+    therefore the drift between the oracle and a second fp32 evaluation order of the same algorithm
+    (oracle.co_cluster_tokens_one_gemm): the CUDA run must agree with the oracle at least as well,
+    within half a point, its clustering must be as good (objective within 0.5 %), and the layer
+    built on it must approximate dense attention as well as the oracle's layer does."""
+    ops, cc, _, layer = _mods()
+    cfg = dataclasses.replace(synth.CONFIGS[cfg_name], heads=2)
+    q, k, v = synth.make_qkv(cfg)
+    qi, ki = synth.init_indices(cfg)
+    dens = synth.head_densities(synth.CONFIGS[cfg_name])[:2]
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out, st = layer.sparse_attention_layer(qd, kd, vd, num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k,
+                                           kmeans_iters=cfg.iters, top_p=cfg.top_p, min_kc_ratio=dens, max_kc_ratio=dens,
+                                           init_indices=(qi, ki), return_state=True)
+    c = st.clustering
+    ref = O.co_cluster_tokens(q[0], k[0], qi, ki, cfg.iters)
+    var = O.co_cluster_tokens_one_gemm(q[0], k[0], qi, ki, cfg.iters)
+    ql, kl = c.qlabels.cpu().long(), c.klabels.cpu().long()
+    agree = {"cuda_q": (ql == ref[0]).float().mean().item(), "cuda_k": (kl == ref[3]).float().mean().item(),
+             "variant_q": (var[0] == ref[0]).float().mean().item(), "variant_k": (var[3] == ref[3]).float().mean().item()}
+    # objective of each clustering (queries over the key centroids, keys over the query centroids)
+    obj = {"cuda": O.clustering_objective(q[0], c.kcentroids.cpu(), c.qcentroids.cpu(), ql) +
+           O.clustering_objective(k[0], c.qcentroids.cpu(), c.kcentroids.cpu(), kl),
+           "oracle": O.clustering_objective(q[0], ref[4], ref[1], ref[0]) + O.clustering_objective(k[0], ref[1], ref[4], ref[3])}
+    # sparse-vs-dense error on sampled query rows
+    g = torch.Generator("cpu").manual_seed(5)
+    rows = torch.randperm(cfg.n_video, generator=g)[:256]
+    m_ref = O.identify_dynamic_map(ref[1][None], ref[4][None], ref[2][None], ref[5][None], cfg.top_p, dens, dens)[0]
+    m_cuda = st.block_map.cpu().bool()
+    err = {}
+    for h in range(2):
+        dense = torch.softmax((q[0, h, rows].float() @ k[0, h].float().T) * 128 ** -0.5, -1) @ v[0, h].float()
+        sp_ref = _masked_rows(q[0], k[0], v[0], ref[0], ref[3], m_ref, rows, h)
+        sp_cuda = _masked_rows(q[0], k[0], v[0], ql, kl, m_cuda, rows, h)
+        got = out[0, h, rows].cpu().float()
+        assert (got - sp_cuda).abs().max() <= ATTN_ATOL            # the kernel computes what its own map says
+        err[f"oracle_h{h}"] = (sp_ref - dense).abs().mean().item()
+        err[f"cuda_h{h}"] = (got - dense).abs().mean().item()
+    line = f"{cfg_name} x 2 heads, {cfg.iters} iterations: agreement {agree}, objective {obj}, mean |sparse - dense| {err}"
+    print(line)
+    record_property("whole_run", line)
+    os.makedirs(os.path.join(os.path.dirname(os.path.dirname(__file__)), "gpurun_out"), exist_ok=True)
+    with open(os.path.join(os.path.dirname(os.path.dirname(__file__)), "gpurun_out", f"whole_run_{cfg_name}.txt"), "w") as f:
+        f.write(line + "\n")
+    assert agree["cuda_q"] >= agree["variant_q"] - 0.005 and agree["cuda_k"] >= agree["variant_k"] - 0.005
+    assert abs(obj["cuda"] - obj["oracle"]) <= 0.005 * abs(obj["oracle"])
+    for h in range(2):
+        assert err[f"cuda_h{h}"] <= 1.1 * err[f"oracle_h{h}"] + 2e-3
+
+
+def test_cfg0_against_reference_fp32_run(dev):
+    """BASELINE config 0 is an fp32 config; this implementation computes in bf16.  Its result is
+    compared here with the reference's recorded fp32 labels directly: the agreement equals that of
+    the oracle run on the same bf16-rounded inputs (the difference is the input rounding, amplified
+    over 10 k-means iterations, not the kernels), and the clustering is as good."""
+    ops, cc, _, _ = _mods()
+    cfg = gu.LAYER_CASES["layer_cfg0"]
+    z = gu.load("layer_cfg0")
+    q, k, v = synth.make_qkv(cfg)
+    qi, ki = synth.init_indices(cfg)
+    iters = int(z["iters"][0])
+    ql, qc, qs, kl, kc, ks = cc.co_cluster_tokens(q[0].to(dev), k[0].to(dev), cfg.num_q, cfg.num_k, iters, init_indices=(qi, ki))
+    assert qc.dtype == torch.float32                          # results come back in the caller's dtype
+    rb = O.co_cluster_tokens(q[0].bfloat16(), k[0].bfloat16(), qi, ki, iters)
+    got_q, got_k = (ql.cpu().numpy() == z["qlabels"]).mean(), (kl.cpu().numpy() == z["klabels"]).mean()
+    or_q, or_k = (rb[0].numpy() == z["qlabels"]).mean(), (rb[3].numpy() == z["klabels"]).mean()
+    print(f"cfg0 labels against the reference's fp32 run: cuda q={got_q:.4f} k={got_k:.4f}; oracle on bf16 inputs q={or_q:.4f} k={or_k:.4f}")
+    assert abs(got_q - or_q) <= 0.01 and abs(got_k - or_k) <= 0.01
+    ref_l = (torch.from_numpy(z["qlabels"].astype(np.int64)), torch.from_numpy(z["klabels"].astype(np.int64)))
+    ref_c = (torch.from_numpy(z["qcentroids"]), torch.from_numpy(z["kcentroids"]))
+    obj_ref = O.clustering_objective(q[0], ref_c[1], ref_c[0], ref_l[0]) + O.clustering_objective(k[0], ref_c[0], ref_c[1], ref_l[1])
+    obj_got = O.clustering_objective(q[0], kc.cpu(), qc.cpu(), ql.cpu()) + O.clustering_objective(k[0], qc.cpu(), kc.cpu(), kl.cpu())
+    assert abs(obj_got - obj_ref) <= 0.01 * abs(obj_ref)
+
+
+# ----------------------------------------------------------------------------------------
+# rows next to the path: Euclidean assignment, log-sum-exp output, warm start, text blocks
+# ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("N,K", [(300, 8), (4096, 128), (10000, 100), (10000, 500), (3000, 1024)])
+def test_euclid_assign_matches_oracle(dev, N, K):
+    ops = _mods()[0]
+    cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=2, grid=(1, 1, N), rope=False)
+    q, _, _ = synth.make_qkv(cfg)
+    g = torch.Generator("cpu").manual_seed(N + K)
+    cent = torch.gather(q[0], 1, torch.randint(0, N, (2, K), generator=g)[..., None].expand(-1, -1, 128))
+    cent = (cent.float() + 0.05 * torch.randn(cent.shape, generator=g)).bfloat16()
+    ref = O.euclid_assign(q[0], cent)
+    got = ops.euclid_assign(q[0].to(dev), cent.to(dev))
+    assert ops.cluster_status(dev, 2, N, K, K) == 0
+    assert int(got.min()) >= 0 and int(got.max()) < K
+    assert (got.cpu().long() == ref).float().mean().item() >= LABEL_AGREE
+
+
+def test_batch_kmeans_euclid_api(dev):
+    """batch_kmeans_Euclid: the reference's loop and return values (labels int64, centroids, sizes
+    int32, iterations run); with tol = 0 it runs max_iters iterations."""
+    _, cc, _, _ = _mods()
+    cfg = dataclasses.replace(gu.TINY_BF16, cfg_id=95)
+    q, _, _ = synth.make_qkv(cfg)
+    init = synth.init_indices(cfg)[0]
+    lab, cent, sizes, n_it = cc.batch_kmeans_Euclid(q[0].to(dev), cfg.num_q, max_iters=3, tol=0.0, init_indices=init)
+    c0 = torch.gather(q[0], 1, init[..., None].expand(-1, -1, 128))
+    rl, rc, rs, r_it = O.batch_kmeans_euclid(q[0], c0, 3, tol=0.0)
+    assert n_it == r_it == 3 and lab.dtype == torch.int64 and sizes.dtype == torch.int32
+    assert (lab.cpu() == rl).float().mean() >= LABEL_AGREE
+    assert torch.equal(sizes.cpu().long().sum(-1), torch.full((cfg.heads,), cfg.n_video))
+    lab2 = cc.euclid_assign_triton(q[0].to(dev), cent)
+    assert lab2.dtype == torch.int64 and lab2.shape == lab.shape
+
+
+def test_attention_log_sum_exp_output(dev):
+    """lse = log2 of the softmax denominator of every row (what FlashInfer returns with
+    return_lse=True), -inf for rows without keys; the output itself is unchanged."""
+    ops = _mods()[0]
+    g = torch.Generator("cpu").manual_seed(17)
+    q_sizes, k_sizes = [300, 129, 0, 271], [128, 200, 0, 372]
+    S, H = sum(q_sizes), 2
+    q, k, v = (torch.randn(H, S, 128, generator=g).bfloat16() for _ in range(3))
+    m = torch.tensor([[1, 0, 1, 1], [0, 1, 0, 0], [1, 1, 1, 1], [0, 0, 1, 0]], dtype=torch.uint8).expand(H, 4, 4).contiguous()
+    q_off = torch.tensor([0] + list(np.cumsum(q_sizes)), dtype=torch.int32).expand(H, -1).contiguous()
+    k_off = torch.tensor([0] + list(np.cumsum(k_sizes)), dtype=torch.int32).expand(H, -1).contiguous()
+    idx = torch.stack([torch.randperm(S, generator=g) for _ in range(H)]).to(torch.int32)
+    args = (q.to(dev), k.to(dev), v.to(dev), m.to(dev), q_off.to(dev), k_off.to(dev))
+    plain = ops.sparse_attn(*args, out_row_idx=idx.to(dev))
+    out, lse = ops.sparse_attn(*args, out_row_idx=idx.to(dev), return_lse=True)
+    assert torch.equal(out, plain) and lse.dtype == torch.float32 and lse.shape == (H, S)
+    want = torch.full((H, S), float("-inf"))
+    for h in range(H):
+        for i in range(4):
+            a, b = int(q_off[h, i]), int(q_off[h, i + 1])
+            sel = [torch.arange(int(k_off[h, j]), int(k_off[h, j + 1])) for j in range(4) if m[h, i, j]]
+            sel = torch.cat(sel) if sel else torch.zeros(0, dtype=torch.long)
+            if a == b or sel.numel() == 0:
+                continue
+            sc = (q[h, a:b].float() @ k[h, sel].float().T) * 128 ** -0.5
+            want[h, idx[h, a:b].long()] = torch.logsumexp(sc, -1) / np.log(2.0)
+    got = lse.cpu()
+    assert torch.equal(torch.isinf(got), torch.isinf(want))
+    fin = torch.isfinite(want)
+    assert (got[fin] - want[fin]).abs().max() <= 2e-3
+
+
+def test_warm_started_clustering(dev):
+    """svoo_b200_cocluster without initial indices continues from the centroids it is given: one
+    iteration from the oracle's centroids gives the oracle's next labels, and the given tensors are
+    not modified."""
+    ops, cc, _, _ = _mods()
+    cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=2, grid=(7, 30, 52))
+    q, k, _ = synth.make_qkv(cfg)
+    qi, ki = synth.init_indices(cfg)
+    ref = O.co_cluster_tokens(q[0], k[0], qi, ki, 2)
+    qc0, kc0 = ref[1].to(dev), ref[4].to(dev)
+    keep = (qc0.clone(), kc0.clone())
+    c = cc.co_cluster(q[0].to(dev), k[0].to(dev), cfg.num_q, cfg.num_k, 1, init_centroids=(qc0, kc0))
+    assert torch.equal(qc0, keep[0]) and torch.equal(kc0, keep[1])
+    kl_ref = _oracle_assign(k[0], ref[1], ref[4])
+    kc1, _ = O.centroid_update(k[0], kl_ref, ref[4])
+    ql_ref = _oracle_assign(q[0], kc1, ref[1])
+    assert (c.klabels.cpu().long() == kl_ref).float().mean() >= LABEL_AGREE
+    assert (c.qlabels.cpu().long() == ql_ref).float().mean() >= LABEL_AGREE - 0.002     # through the updated key centroids
+    with pytest.raises(ValueError):
+        ops.cocluster(q[0].to(dev), k[0].to(dev), qi.to(dev), None, 1)
+
+
+def test_append_text_blocks_bit_exact(dev):
+    ops = _mods()[0]
+    g = torch.Generator("cpu").manual_seed(23)
+    H, QC, KC, N, text, prompt = 3, 5, 9, 700, 64, 40
+    m = torch.rand(1, H, QC, KC, generator=g) < 0.4
+    lab_q, lab_k = random_labels(H, N, QC, 1), random_labels(H, N, KC, 2)
+    qi, qo = O.sort_labels(lab_q, QC)
+    ki, ko = O.sort_labels(lab_k, KC)
+    qs, ks = (qo[:, 1:] - qo[:, :-1])[None], (ko[:, 1:] - ko[:, :-1])[None]
+    m2, qs2, ks2, idx2 = O.hunyuan_text_blocks(m, qs, ks, qi, N, text, prompt)
+    got = ops.append_text_blocks(m[0].to(dev).view(torch.uint8), qo.to(dev), ko.to(dev), qi.to(dev), ki.to(dev), text, prompt)
+    gm, gqo, gko, gqi, gki = (t.cpu() for t in got)
+    assert torch.equal(gm.bool(), m2[0]) and torch.equal(gqi, idx2.to(torch.int32))
+    assert torch.equal(gqo[:, 1:] - gqo[:, :-1], qs2[0]) and torch.equal(gko[:, 1:] - gko[:, :-1], ks2[0])
+    assert torch.equal(gki[:, :N], ki) and torch.equal(gki[:, N:], torch.arange(N, N + text, dtype=torch.int32).expand(H, -1))
+
+
+def test_single_call_layer_with_text_equals_staged_layer(dev):
+    """svoo_b200_layer with text tokens (one C call) against the stage-by-stage layer."""
+    ops, cc, _, layer = _mods()
+    cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=2, grid=(5, 30, 52), text_tokens=256, cfg_id=96)
+    q, k, v = (t.to(dev) for t in synth.make_qkv(cfg))
+    qi, ki = (t.to(dev) for t in synth.init_indices(cfg))
+    dens = [0.1, 0.2]
+    want = layer.sparse_attention_layer(q, k, v, num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k,
+                                        kmeans_iters=2, top_p=cfg.top_p, min_kc_ratio=dens, max_kc_ratio=dens,
+                                        init_indices=(qi, ki), context_length=256, prompt_length=180)
+    preserve, cap = cc.keep_limits(cfg.num_k, cfg.heads, dens, dens)
+    got = ops.layer(q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), qi, ki, 2, cfg.top_p, preserve, cap,
+                    text=256, prompt=180)
+    assert torch.equal(got, want[0])

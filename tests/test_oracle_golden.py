@@ -23,6 +23,15 @@ def test_map_matches_reference(name):
     assert gu.same_up_to_ties(got.numpy(), ref, prob.numpy())
     if not z["is_bf16"][0]:
         assert (got.numpy() == ref).all()
+    # rows in which the oracle (ties -> lower cluster index) and the reference run that made the fixture
+    # (ties -> whatever its sort did) keep a different member of a tie group
+    differing = int((got.numpy() != ref).any(-1).sum())
+    assert differing == ROWS_DIFFERING_BY_TIE_CHOICE[name], differing
+
+
+# per fixture: map rows (of rows in total) that differ from the reference by the choice inside a tie group
+ROWS_DIFFERING_BY_TIE_CHOICE = {"map_bf16_budget": 44, "map_bf16_topp_floor": 100, "map_bf16_scalar": 20, "map_fp32_topp": 0,
+                                "map_fp32_cap_scalar": 0, "map_bf16_big": 181, "map_all_ones": 0}
 
 
 @pytest.fixture(scope="module", params=list(gu.LAYER_CASES))
@@ -130,3 +139,61 @@ def test_producer_matches_reference_processor(name):
         assert ((near - trunc).abs() <= ulp).all()
     got = O.qk_prep(torch.from_numpy(z["xv"]).bfloat16(), None, 0.0, None, None, H)
     assert torch.equal(got.float(), torch.from_numpy(z["v"]))
+
+
+# ----------------------------------------------------------------------------------------------
+# processors: the oracle's restatement of their dataflow against the reference's recorded steps
+# ----------------------------------------------------------------------------------------------
+def _check_rows(y, want, ok_tokens, min_ok, atol=2e-2):
+    """y [S, dim] against the kept reference rows on the comparable tokens."""
+    ok = ok_tokens[::gu.PROC_ROWS_KEPT]
+    assert ok.float().mean() >= min_ok
+    d = (y[::gu.PROC_ROWS_KEPT].float() - want.float()).abs().amax(-1)
+    assert d[ok].max() <= atol
+
+
+def test_wan_processor_steps_match_reference():
+    from tests import processor_oracle as PO
+    z = gu.load("processor_wan")
+    for step, _ in gu.WAN_PROC["steps"]:
+        assert synth.tensor_checksum(gu.wan_step_hidden(step))[0] == z[f"hidden_checksum_{step}"][0], "RNG drift"
+    seen = []
+    for step, sparse, y, aux in PO.wan_steps(z):
+        want = gu.from_bf16_bits(z[f"out_{step}"])
+        seen.append((step, sparse))
+        if not sparse:
+            assert (y[::gu.PROC_ROWS_KEPT].float() - want.float()).abs().max() <= 2e-2
+            continue
+        assert (aux["qlabels"].numpy() == z[f"qlabels_{step}"]).mean() >= 0.999
+        assert (aux["klabels"].numpy() == z[f"klabels_{step}"]).mean() >= 0.999
+        got_ratio = aux["ratio"] if isinstance(aux["ratio"], list) else [aux["ratio"]]
+        np.testing.assert_allclose(got_ratio, z[f"ratio_{step}"], rtol=0, atol=1e-12)
+        ref_map = gu.unpack_map(z, f"_{step}")[0]
+        assert gu.processor_map_ties_ok(aux["qcentroids"], aux["kcentroids"], aux["qsizes"], aux["ksizes"],
+                                        gu.WAN_PROC["top_p"], aux["ratio"], aux["map"][0].numpy(), ref_map)
+        ok = gu.comparable_tokens(aux["qlabels"], z[f"qlabels_{step}"], aux["map"][0].numpy(), ref_map)
+        _check_rows(y, want, ok, 0.8)
+    assert seen == [(1, False), (2, True), (3, True), (7, True)]
+    # step 3 reuses the clustering of step 2 (no new labels in the reference's cache), and its density
+    # row has a hole, so it falls back to the scalar ratio
+    assert (z["qlabels_3"] == z["qlabels_2"]).all() and len(z["ratio_3"]) == 1 and len(z["ratio_2"]) == 4
+    assert not (z["qlabels_7"] == z["qlabels_2"]).all()
+
+
+def test_hunyuan_processor_step_matches_reference():
+    from tests import processor_oracle as PO
+    z = gu.load("processor_hunyuan")
+    hidden, enc, _ = gu.hunyuan_inputs()
+    assert synth.tensor_checksum(hidden, enc)[0] == z["input_checksum"][0], "RNG drift"
+    y, y_enc, aux = PO.hunyuan_step(z)
+    assert (aux["qlabels"].numpy() == z["qlabels"]).mean() >= 0.999
+    assert (aux["klabels"].numpy() == z["klabels"]).mean() >= 0.999
+    ref_map = gu.unpack_map(z)[0]
+    assert gu.processor_map_ties_ok(aux["qcentroids"], aux["kcentroids"], aux["qsizes"], aux["ksizes"],
+                                    gu.HUN_PROC["top_p"], float(gu.HUN_PROC["min_kc_ratio"]), aux["map_video"][0].numpy(),
+                                    ref_map)
+    ok = gu.comparable_tokens(aux["qlabels"], z["qlabels"], aux["map_video"][0].numpy(), ref_map)
+    _check_rows(y, gu.from_bf16_bits(z["out"]), ok, 0.8)
+    # the text rows: the prompt attends all video and prompt keys, the unused prompt only itself;
+    # neither depends on which tied cluster the map kept
+    assert (y_enc.float() - gu.from_bf16_bits(z["out_enc"]).float()).abs().max() <= 2e-2
