@@ -91,13 +91,27 @@ def profile_norm(x: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
     return torch.sqrt((dot * dot).sum(-1) + 1e-8)
 
 
-def cocluster_assign(x, c, pc, norms) -> torch.Tensor:
+def round_tf32(t: torch.Tensor) -> torch.Tensor:
+    """fp32 -> TF32 (10 mantissa bits, round to nearest, ties away from zero) -> fp32: what a
+    tensor-core dot with allow_tf32=True does to its fp32 operands on a GPU."""
+    bits = t.float().contiguous().view(torch.int32)
+    return ((bits + 0x1000) & -0x2000).view(torch.float32)
+
+
+def cocluster_assign(x, c, pc, norms, tf32: bool = False) -> torch.Tensor:
     """label = first argmin_j 2 - 2*<(x·c^T)/norm, pc_j> (co_clustering.py:2203-2252).
 
     x [B,N,D], c [B,K,D], pc [B,J,K] fp32, norms [B,N] -> int64 [B,N].
+    tf32=True rounds the operands of the second product to TF32, as the reference's kernel does on a
+    GPU (tl.dot(..., allow_tf32=True), :2242; the first product's operands are bf16 values, which
+    TF32 holds exactly).  The fixtures were made by the Triton interpreter, which multiplies in
+    fp32, so the default is the fp32 evaluation.
     """
     prof = torch.matmul(x.float(), c.float().transpose(-1, -2)) / norms[..., None]
-    dist = 2.0 - 2.0 * torch.matmul(prof, pc.float().transpose(-1, -2))
+    pcf = pc.float()
+    if tf32:
+        prof, pcf = round_tf32(prof), round_tf32(pcf)
+    dist = 2.0 - 2.0 * torch.matmul(prof, pcf.transpose(-1, -2))
     # torch.argmin returns the first minimal index on CPU, which is the rule the
     # reference's running (strict <) update across J tiles produces.
     return torch.argmin(dist, dim=-1)
@@ -118,21 +132,21 @@ def centroid_update(x, labels, old_centroids) -> Tuple[torch.Tensor, torch.Tenso
     return means.to(x.dtype), counts.to(torch.int32)
 
 
-def co_cluster_tokens(q, k, q_init_idx, k_init_idx, max_iters: int):
+def co_cluster_tokens(q, k, q_init_idx, k_init_idx, max_iters: int, tf32: bool = False):
     """Restates co_cluster_tokens (co_clustering.py:2402-2451) with the random
     initial token indices passed in (the reference draws q indices, then k
     indices, with torch.randint).  Returns the reference's tuple order:
-    (qlabels, qcentroids, qsizes, klabels, kcentroids, ksizes)."""
+    (qlabels, qcentroids, qsizes, klabels, kcentroids, ksizes).  tf32: see cocluster_assign."""
     B, N, D = q.shape
     qc = torch.gather(q, 1, q_init_idx[..., None].expand(-1, -1, D))
     kc = torch.gather(k, 1, k_init_idx[..., None].expand(-1, -1, D))
     ql = kl = qs = ks = None
     for _ in range(max_iters):
         pk = l2norm_rows(torch.matmul(kc, qc.transpose(-1, -2)))
-        kl = cocluster_assign(k, qc, pk, profile_norm(k, qc))
+        kl = cocluster_assign(k, qc, pk, profile_norm(k, qc), tf32)
         kc, ks = centroid_update(k, kl, kc)
         pq = l2norm_rows(torch.matmul(qc, kc.transpose(-1, -2)))
-        ql = cocluster_assign(q, kc, pq, profile_norm(q, kc))
+        ql = cocluster_assign(q, kc, pq, profile_norm(q, kc), tf32)
         qc, qs = centroid_update(q, ql, qc)
     return ql, qc, qs, kl, kc, ks
 

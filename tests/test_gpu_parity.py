@@ -626,32 +626,57 @@ def _masked_rows(q, k, v, ql, kl, dmap, rows, h):
 
 @pytest.mark.parametrize("cfg_name", ["cfg1", "cfg2"])
 def test_whole_run_agreement_against_fp32_drift(dev, cfg_name, record_property):
-    """Whole k-means runs at Wan scale (2 heads).  A handful of near-tie flips per step move the
-    bf16 centroids, so any two correct implementations drift apart over the iterations; the bar is
-    therefore the drift between the oracle and a second fp32 evaluation order of the same algorithm
-    (oracle.co_cluster_tokens_one_gemm): the CUDA run must agree with the oracle at least as well,
-    within half a point, its clustering must be as good (objective within 0.5 %), and the layer
-    built on it must approximate dense attention as well as the oracle's layer does."""
+    """Whole k-means runs at Wan scale (2 heads).  One or two near-tie tokens per 150,000 flip in
+    a step, the bf16 centroids move, and over the iterations any two correct implementations
+    drift apart.  So: (1) every step, started from the oracle's own centroids, must reproduce the
+    oracle's labels to 99.99 % (the north-star bar is 99.9 %); (2) the whole run must agree with
+    the fp32 oracle at least as well as the reference's own GPU arithmetic would -- its kernel
+    multiplies with TF32 operands (oracle tf32=True) -- and within a point of a second fp32
+    evaluation order (oracle.co_cluster_tokens_one_gemm); (3) the clustering must be as good
+    (objective within 0.5 %); (4) the layer built on it must approximate dense attention as well
+    as the oracle's layer does."""
     ops, cc, _, layer = _mods()
     cfg = dataclasses.replace(synth.CONFIGS[cfg_name], heads=2)
     q, k, v = synth.make_qkv(cfg)
     qi, ki = synth.init_indices(cfg)
     dens = synth.head_densities(synth.CONFIGS[cfg_name])[:2]
     qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    # (1) teacher-forced steps
+    qc = torch.gather(q[0], 1, qi[..., None].expand(-1, -1, 128))
+    kc = torch.gather(k[0], 1, ki[..., None].expand(-1, -1, 128))
+    step_agree = []
+    for it in range(cfg.iters):
+        kl_ref = _oracle_assign(k[0], qc, kc)
+        kl = ops.cocluster_assign(kd[0], qc.to(dev), kc.to(dev))
+        kc, _ = O.centroid_update(k[0], kl_ref, kc)
+        ql_ref = _oracle_assign(q[0], kc, qc)
+        ql = ops.cocluster_assign(qd[0], kc.to(dev), qc.to(dev))
+        qc, _ = O.centroid_update(q[0], ql_ref, qc)
+        step_agree.append(min((kl.cpu().long() == kl_ref).float().mean().item(), (ql.cpu().long() == ql_ref).float().mean().item()))
+    assert min(step_agree) >= 0.9999, step_agree
+    ref = (ql_ref, qc, None, kl_ref, kc, None)                # the teacher-forced chain IS the oracle's run
+    # (2) whole run
     out, st = layer.sparse_attention_layer(qd, kd, vd, num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k,
                                            kmeans_iters=cfg.iters, top_p=cfg.top_p, min_kc_ratio=dens, max_kc_ratio=dens,
                                            init_indices=(qi, ki), return_state=True)
     c = st.clustering
+    near_ties = ops.near_tie_count(dev, 2, cfg.n_video, cfg.num_q, cfg.num_k) / (2.0 * cfg.n_video)
     ref = O.co_cluster_tokens(q[0], k[0], qi, ki, cfg.iters)
+    assert torch.equal(ref[0], ql_ref) and torch.equal(ref[3], kl_ref)
     var = O.co_cluster_tokens_one_gemm(q[0], k[0], qi, ki, cfg.iters)
+    tf32 = O.co_cluster_tokens(q[0], k[0], qi, ki, cfg.iters, tf32=True)
     ql, kl = c.qlabels.cpu().long(), c.klabels.cpu().long()
-    agree = {"cuda_q": (ql == ref[0]).float().mean().item(), "cuda_k": (kl == ref[3]).float().mean().item(),
-             "variant_q": (var[0] == ref[0]).float().mean().item(), "variant_k": (var[3] == ref[3]).float().mean().item()}
-    # objective of each clustering (queries over the key centroids, keys over the query centroids)
+
+    def frac(a, b):
+        return (a == b).float().mean().item()
+
+    agree = {"cuda_q": frac(ql, ref[0]), "cuda_k": frac(kl, ref[3]), "one_gemm_q": frac(var[0], ref[0]),
+             "one_gemm_k": frac(var[3], ref[3]), "tf32_q": frac(tf32[0], ref[0]), "tf32_k": frac(tf32[3], ref[3])}
+    # (3) objective of each clustering (queries over the key centroids, keys over the query centroids)
     obj = {"cuda": O.clustering_objective(q[0], c.kcentroids.cpu(), c.qcentroids.cpu(), ql) +
            O.clustering_objective(k[0], c.qcentroids.cpu(), c.kcentroids.cpu(), kl),
            "oracle": O.clustering_objective(q[0], ref[4], ref[1], ref[0]) + O.clustering_objective(k[0], ref[1], ref[4], ref[3])}
-    # sparse-vs-dense error on sampled query rows
+    # (4) sparse-vs-dense error on sampled query rows
     g = torch.Generator("cpu").manual_seed(5)
     rows = torch.randperm(cfg.n_video, generator=g)[:256]
     m_ref = O.identify_dynamic_map(ref[1][None], ref[4][None], ref[2][None], ref[5][None], cfg.top_p, dens, dens)[0]
@@ -665,13 +690,17 @@ def test_whole_run_agreement_against_fp32_drift(dev, cfg_name, record_property):
         assert (got - sp_cuda).abs().max() <= ATTN_ATOL            # the kernel computes what its own map says
         err[f"oracle_h{h}"] = (sp_ref - dense).abs().mean().item()
         err[f"cuda_h{h}"] = (got - dense).abs().mean().item()
-    line = f"{cfg_name} x 2 heads, {cfg.iters} iterations: agreement {agree}, objective {obj}, mean |sparse - dense| {err}"
+    line = (f"{cfg_name} x 2 heads, {cfg.iters} iterations: per-step agreement (teacher-forced) min {min(step_agree):.6f}; "
+            f"whole-run agreement with the fp32 oracle {agree}; objective {obj}; mean |sparse - dense| {err}; "
+            f"tokens re-scored in fp32 in the last assignment {near_ties:.5f}")
     print(line)
     record_property("whole_run", line)
-    os.makedirs(os.path.join(os.path.dirname(os.path.dirname(__file__)), "gpurun_out"), exist_ok=True)
-    with open(os.path.join(os.path.dirname(os.path.dirname(__file__)), "gpurun_out", f"whole_run_{cfg_name}.txt"), "w") as f:
+    out_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, f"whole_run_{cfg_name}.txt"), "w") as f:
         f.write(line + "\n")
-    assert agree["cuda_q"] >= agree["variant_q"] - 0.005 and agree["cuda_k"] >= agree["variant_k"] - 0.005
+    assert agree["cuda_q"] >= agree["tf32_q"] and agree["cuda_k"] >= agree["tf32_k"]
+    assert agree["cuda_q"] >= agree["one_gemm_q"] - 0.01 and agree["cuda_k"] >= agree["one_gemm_k"] - 0.01
     assert abs(obj["cuda"] - obj["oracle"]) <= 0.005 * abs(obj["oracle"])
     for h in range(2):
         assert err[f"cuda_h{h}"] <= 1.1 * err[f"oracle_h{h}"] + 2e-3
