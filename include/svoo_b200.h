@@ -184,9 +184,7 @@ int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, cons
  * the tensor-core kernels report into.  Word 0 is cleared by svoo_b200_sparse_attn and
  * becomes non-zero if a CTA of the attention kernel gave up on one of its bounded barrier
  * waits (its output rows are then not written); word 1 is the same for the assignment
- * kernel of svoo_b200_cocluster / svoo_b200_cocluster_assign.  Word 2 counts the tokens of the
- * last assignment step whose two best scores were within rounding error of each other and
- * were therefore decided by an exact fp32 re-scoring (instrumentation).  No counterpart in the
+ * kernel of svoo_b200_cocluster / svoo_b200_cocluster_assign.  No counterpart in the
  * reference. */
 int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* offset_out);
 

@@ -4,10 +4,9 @@
 
 namespace svoo {
 cudaError_t launch_gather_rows(const void*, const int32_t*, void*, int64_t, int64_t, int64_t, cudaStream_t);
-cudaError_t launch_prologue(const void*, const void*, void*, void*, float*, int32_t*, int64_t, int64_t, int64_t,
-                            cudaStream_t);
-cudaError_t launch_assign_tc(const void*, const void*, const void*, const float*, int32_t*, int2*, int32_t*, int32_t*,
-                             int32_t*, int64_t, int64_t, int64_t, int32_t*, cudaStream_t);
+cudaError_t launch_prologue(const void*, const void*, void*, void*, int64_t, int64_t, int64_t, cudaStream_t);
+cudaError_t launch_assign_tc(const void*, const void*, const void*, int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t,
+                             int32_t*, cudaStream_t);
 cudaError_t launch_sort_labels(const int32_t*, int64_t, int64_t, int64_t, int32_t*, int32_t*, int32_t*, int32_t*,
                                cudaStream_t, bool);
 cudaError_t launch_centroid_update(const void*, const int32_t*, const int32_t*, const void*, void*, int32_t*, float*,
@@ -115,13 +114,11 @@ int svoo_b200_cocluster_assign(const void* x, const void* form_centroids, const 
   if (workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   SVOO_CUDA(launch_prologue(own_centroids, form_centroids, ws_at<void>(workspace, w.w_hi),
-                            ws_at<void>(workspace, w.w_lo), ws_at<float>(workspace, w.w_f32),
-                            ws_at<int32_t>(workspace, w.status) + 2, BH, J, K, st));
+                            ws_at<void>(workspace, w.w_lo), BH, J, K, st));
   SVOO_CUDA(cudaMemsetAsync(ws_at<int32_t>(workspace, w.status) + 1, 0, 4, st));
-  SVOO_CUDA(launch_assign_tc(x, ws_at<void>(workspace, w.w_hi), ws_at<void>(workspace, w.w_lo),
-                             ws_at<float>(workspace, w.w_f32), labels, ws_at<int2>(workspace, w.assign_partial),
-                             ws_at<int32_t>(workspace, w.status) + 1, ws_at<int32_t>(workspace, w.amb_list),
-                             ws_at<int32_t>(workspace, w.status) + 2, BH, N, J, nullptr, st));
+  SVOO_CUDA(launch_assign_tc(x, ws_at<void>(workspace, w.w_hi), ws_at<void>(workspace, w.w_lo), labels,
+                             ws_at<int2>(workspace, w.assign_partial), ws_at<int32_t>(workspace, w.status) + 1, BH, N, J, nullptr,
+                             st));
   return SVOO_OK;
 }
 
@@ -192,9 +189,6 @@ int svoo_b200_cocluster(const void* q, const void* k, const int32_t* q_init_idx,
   float* partial = ws_at<float>(workspace, w.partial);
   int2* apart = ws_at<int2>(workspace, w.assign_partial);
   int32_t* status = ws_at<int32_t>(workspace, w.status) + 1;       // word 1: assignment kernel
-  float* w_f32 = ws_at<float>(workspace, w.w_f32);
-  int32_t* amb = ws_at<int32_t>(workspace, w.amb_list);
-  int32_t* namb = ws_at<int32_t>(workspace, w.status) + 2;
 
   SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));
   if (q_init_idx) {
@@ -203,13 +197,13 @@ int svoo_b200_cocluster(const void* q, const void* k, const int32_t* q_init_idx,
   }
   for (int it = 0; it < iters; ++it) {
     // keys: profile over the query centroids
-    SVOO_CUDA(launch_prologue(kcentroids, qcentroids, w_hi, w_lo, w_f32, namb, BH, KC, QC, st));
-    SVOO_CUDA(launch_assign_tc(k, w_hi, w_lo, w_f32, klabels, apart, status, amb, namb, BH, N, KC, hist, st));
+    SVOO_CUDA(launch_prologue(kcentroids, qcentroids, w_hi, w_lo, BH, KC, QC, st));
+    SVOO_CUDA(launch_assign_tc(k, w_hi, w_lo, klabels, apart, status, BH, N, KC, hist, st));
     SVOO_CUDA(launch_sort_labels(klabels, BH, N, KC, k_sorted_idx, k_offsets, nullptr, hist, st, true));
     SVOO_CUDA(launch_centroid_update(k, k_sorted_idx, k_offsets, kcentroids, kcentroids, ksizes, partial, BH, N, KC, st));
     // queries: profile over the just-updated key centroids
-    SVOO_CUDA(launch_prologue(qcentroids, kcentroids, w_hi, w_lo, w_f32, namb, BH, QC, KC, st));
-    SVOO_CUDA(launch_assign_tc(q, w_hi, w_lo, w_f32, qlabels, apart, status, amb, namb, BH, N, QC, hist, st));
+    SVOO_CUDA(launch_prologue(qcentroids, kcentroids, w_hi, w_lo, BH, QC, KC, st));
+    SVOO_CUDA(launch_assign_tc(q, w_hi, w_lo, qlabels, apart, status, BH, N, QC, hist, st));
     SVOO_CUDA(launch_sort_labels(qlabels, BH, N, QC, q_sorted_idx, q_offsets, nullptr, hist, st, true));
     SVOO_CUDA(launch_centroid_update(q, q_sorted_idx, q_offsets, qcentroids, qcentroids, qsizes, partial, BH, N, QC, st));
   }

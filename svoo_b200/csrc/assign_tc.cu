@@ -53,19 +53,16 @@ __device__ __forceinline__ AsgJob asg_job(int64_t g, int n_jb, int n_xt) {
   return j;
 }
 
-// Running first-argmax over 32 accumulator columns starting at column c0, together with the
-// second-largest value seen (its index is not needed: a token whose two best scores are within
-// rounding error of each other is re-scored exactly later).  With kBias the per-column bias
-// (shared memory, indexed like the columns) is added to the score first.
+// Running first-argmax over 32 accumulator columns starting at column c0; with kBias the
+// per-column bias (shared memory, indexed like the columns) is added to the score first.
 template <bool kBias>
 __device__ __forceinline__ void argmax32(const uint32_t (&r)[32], int c0, int jlim, const float* bias, float& best,
-                                         int& best_c, float& second) {
+                                         int& best_c) {
   if (c0 + 32 <= jlim) {
 #pragma unroll
     for (int c = 0; c < 32; ++c) {
       float val = __uint_as_float(r[c]);
       if (kBias) val += bias[c0 + c];
-      second = fmaxf(second, fminf(val, best));
       if (val > best) { best = val; best_c = c0 + c; }
     }
   } else {
@@ -73,24 +70,10 @@ __device__ __forceinline__ void argmax32(const uint32_t (&r)[32], int c0, int jl
     for (int c = 0; c < 32; ++c) {
       float val = __uint_as_float(r[c]);
       if (kBias) val += bias[c0 + c];
-      if (c0 + c >= jlim) val = -INFINITY;
-      second = fmaxf(second, fminf(val, best));
-      if (val > best) { best = val; best_c = c0 + c; }
+      if (c0 + c < jlim && val > best) { best = val; best_c = c0 + c; }
     }
   }
 }
-
-// A partial result of one column group: x = bits of the best score, y = its column in the low 16
-// bits and, in the high 16 bits, the bf16 bits (rounded down) of the distance to the second-best
-// score of the group.
-__device__ __forceinline__ int2 pack_partial(float best, int j, float second) {
-  const float margin = best - second;                                  // >= 0, +inf when there is no second
-  return make_int2(__float_as_int(best), j | (int)((__float_as_uint(margin) >> 16) << 16));
-}
-__device__ __forceinline__ float partial_margin(int2 r) { return __uint_as_float((uint32_t)r.y & 0xffff0000u); }
-// Scores are sums of products of bf16 tokens with W = hi + lo (16 mantissa bits): two candidates
-// closer than this are not told apart reliably and are decided by the fp32 re-scoring.
-__device__ __forceinline__ bool near_tie(float best, float margin) { return margin < fabsf(best) * (1.0f / 4096.0f); }
 
 // kEuclid = false: scores x . (W_hi + W_lo), W rows of head bh at [bh * w_head_rows, +J).
 // kEuclid = true:  nearest centroid in Euclidean distance, argmax_j x . c_j + bias[bh, j] with
@@ -224,17 +207,17 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
       tc_fence_after();
       const uint32_t acc = tmem + lane_addr + b * 256 + half * HC;
       const int jlim = J - job.jb * JB - half * HC;            // valid columns of this half (may be <= 0)
-      float best = -INFINITY, second = -INFINITY;
+      float best = -INFINITY;
       int best_c = 0;
       tmem_ld32_nowait(acc, ra);
       tmem_wait_ld();
 #pragma unroll
       for (int ch = 0; ch < HC / 32; ch += 2) {
         tmem_ld32_nowait(acc + (ch + 1) * 32, rb);
-        argmax32<kEuclid>(ra, ch * 32, jlim, bias_s, best, best_c, second);
+        argmax32<kEuclid>(ra, ch * 32, jlim, bias_s, best, best_c);
         tmem_wait_ld();
         if (ch + 2 < HC / 32) tmem_ld32_nowait(acc + (ch + 2) * 32, ra);
-        argmax32<kEuclid>(rb, (ch + 1) * 32, jlim, bias_s, best, best_c, second);
+        argmax32<kEuclid>(rb, (ch + 1) * 32, jlim, bias_s, best, best_c);
         tmem_wait_ld();
       }
       tc_fence_before();
@@ -242,7 +225,7 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
       const int n = job.t * kAsgXT + r_local;
       if (n < N)
         partial[((int64_t)(job.jb * 2 + half) * BH + job.bh) * N + n] =
-            pack_partial(best, job.jb * JB + half * HC + best_c, second);
+            make_int2(__float_as_int(best), job.jb * JB + half * HC + best_c);
     }
   }
   tc_fence_before();
@@ -254,35 +237,17 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
   }
 }
 
-// Best (score, j) pair of token i over the column groups (the lower group wins ties) and whether the
-// runner-up is within rounding error of it.
-__device__ __forceinline__ int reduce_partials(const int2* __restrict__ partial, int64_t i, int64_t BHN, int groups,
-                                               bool& tie) {
-  int2 b = partial[i];
-  float margin = partial_margin(b);
-  for (int g = 1; g < groups; ++g) {
-    const int2 c = partial[(int64_t)g * BHN + i];
-    const float bv = __int_as_float(b.x), cv = __int_as_float(c.x);
-    if (cv > bv) {
-      margin = fminf(partial_margin(c), cv - bv);
-      b = c;
-    } else {
-      margin = fminf(margin, bv - cv);
-    }
-  }
-  tie = near_tie(__int_as_float(b.x), margin);
-  return b.y & 0xffff;
-}
-
-// labels[bh, n] = j of the best pair; near ties are appended to amb_list (if given) for re-scoring.
+// labels[bh, n] = j of the best (score, j) pair over the column groups; the lower group wins ties.
 __global__ void __launch_bounds__(256) assign_reduce_kernel(const int2* __restrict__ partial, int32_t* __restrict__ labels,
-                                                            int64_t BHN, int groups, int32_t* __restrict__ amb_list,
-                                                            int32_t* __restrict__ amb_count) {
+                                                            int64_t BHN, int groups) {
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= BHN) return;
-  bool tie;
-  labels[i] = reduce_partials(partial, i, BHN, groups, tie);
-  if (tie && amb_list) amb_list[atomicAdd(amb_count, 1)] = (int32_t)i;
+  int2 b = partial[i];
+  for (int g = 1; g < groups; ++g) {
+    const int2 c = partial[(int64_t)g * BHN + i];
+    if (__int_as_float(c.x) > __int_as_float(b.x)) b = c;
+  }
+  labels[i] = b.y;
 }
 
 // The same reduction fused with the first pass of the label sort: one CTA per (2048-token chunk,
@@ -290,8 +255,7 @@ __global__ void __launch_bounds__(256) assign_reduce_kernel(const int2* __restri
 __global__ void __launch_bounds__(256) assign_reduce_hist_kernel(const int2* __restrict__ partial,
                                                                  int32_t* __restrict__ labels,
                                                                  int32_t* __restrict__ chunk_hist, int BH, int N, int K,
-                                                                 int groups, int nchunks, int32_t* __restrict__ amb_list,
-                                                                 int32_t* __restrict__ amb_count) {
+                                                                 int groups, int nchunks) {
   __shared__ int hist[SVOO_MAX_CLUSTERS];
   const int bh = blockIdx.y, chunk = blockIdx.x;
   for (int k = threadIdx.x; k < K; k += 256) hist[k] = 0;
@@ -302,87 +266,18 @@ __global__ void __launch_bounds__(256) assign_reduce_hist_kernel(const int2* __r
     const int n = base + t;
     if (n < N) {
       const int64_t i = (int64_t)bh * N + n;
-      bool tie;
-      const int j = reduce_partials(partial, i, BHN, groups, tie);
-      labels[i] = j;
-      if (j >= 0 && j < K) atomicAdd(&hist[j], 1);
-      if (tie && amb_list) amb_list[atomicAdd(amb_count, 1)] = (int32_t)i;
+      int2 b = partial[i];
+      for (int g = 1; g < groups; ++g) {
+        const int2 c = partial[(int64_t)g * BHN + i];
+        if (__int_as_float(c.x) > __int_as_float(b.x)) b = c;
+      }
+      labels[i] = b.y;
+      if (b.y >= 0 && b.y < K) atomicAdd(&hist[b.y], 1);
     }
   }
   __syncthreads();
   int32_t* out = chunk_hist + ((int64_t)bh * nchunks + chunk) * K;
   for (int k = threadIdx.x; k < K; k += 256) out[k] = hist[k];
-}
-
-// Exact decision for the listed tokens: label = first argmax_j of the fp32 dot products x . W_j with
-// the unsplit W.  One warp per token; lane l holds dims 4l..4l+3 of x and reads the same dims of
-// every W row (one coalesced 512-byte row per step); 32 rows are accumulated side by side and
-// reduced with one butterfly.  If the label changes, the chunk histograms of the sort follow.
-// The list order depends on scheduling, the result does not.
-constexpr int kRescoreWarps = 8;
-__global__ void __launch_bounds__(kRescoreWarps * 32) assign_rescore_kernel(
-    const int32_t* __restrict__ amb_list, const int32_t* __restrict__ amb_count, const bf16* __restrict__ x,
-    const float* __restrict__ w_f32, int32_t* __restrict__ labels, int32_t* __restrict__ chunk_hist, int N, int J, int Jpad,
-    int nchunks) {
-  const int lane = threadIdx.x % 32;
-  const int warp = blockIdx.x * kRescoreWarps + threadIdx.x / 32, nwarps = gridDim.x * kRescoreWarps;
-  const int count = *amb_count;
-  for (int e = warp; e < count; e += nwarps) {
-    const int i = amb_list[e];
-    const int bh = i / N, n = i - bh * N;
-    const uint2 xr = *reinterpret_cast<const uint2*>(x + (int64_t)i * kHeadDim + 4 * lane);
-    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xr);
-    const float x0 = __low2float(xh[0]), x1 = __high2float(xh[0]), x2 = __low2float(xh[1]), x3 = __high2float(xh[1]);
-    const float4* wb = reinterpret_cast<const float4*>(w_f32 + (int64_t)bh * Jpad * kHeadDim) + lane;
-    float best = -INFINITY;
-    int best_j = 0;
-    for (int j0 = 0; j0 < J; j0 += 32) {
-      float p[32];
-#pragma unroll
-      for (int u = 0; u < 32; ++u) {
-        const int j = min(j0 + u, J - 1);
-        const float4 w = __ldg(wb + (int64_t)j * 32);
-        p[u] = fmaf(x0, w.x, fmaf(x1, w.y, fmaf(x2, w.z, x3 * w.w)));
-      }
-      // butterfly: after step s the 32 >> (s + 1) values a lane still holds are sums over 2^(s+1) lanes
-#pragma unroll
-      for (int s = 0; s < 5; ++s) {
-        const int half = 16 >> s, bit = 1 << s;
-#pragma unroll
-        for (int u = 0; u < half; ++u) {
-          const bool up = (lane & bit) != 0;
-          const float send = up ? p[u] : p[u + half];
-          const float keep = up ? p[u + half] : p[u];
-          p[u] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
-        }
-      }
-      // lane l now holds the score of row j0 + bit-reversal-free index: row = j0 + rev(l)
-      int row = 0;
-#pragma unroll
-      for (int s = 0; s < 5; ++s) row |= ((lane >> s) & 1) << (4 - s);
-      float val = (j0 + row < J) ? p[0] : -INFINITY;
-      int jj = j0 + row;
-      // first argmax over the 32 rows of this batch
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, val, o);
-        const int oj = __shfl_xor_sync(0xffffffffu, jj, o);
-        if (ov > val || (ov == val && oj < jj)) { val = ov; jj = oj; }
-      }
-      if (val > best) { best = val; best_j = jj; }
-    }
-    if (lane == 0) {
-      const int old = labels[i];
-      if (old != best_j) {
-        labels[i] = best_j;
-        if (chunk_hist) {
-          int32_t* h = chunk_hist + ((int64_t)bh * nchunks + n / kSortChunk) * J;
-          atomicSub(h + old, 1);
-          atomicAdd(h + best_j, 1);
-        }
-      }
-    }
-  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -437,41 +332,29 @@ static cudaError_t launch_assign_tc_jb(const void* x, const void* w_hi, const vo
   return cudaGetLastError();
 }
 
-// amb_list / amb_count == nullptr: no near-tie list (scores that are exact need none).
 static cudaError_t launch_assign_reduce(const int2* partial, int32_t* labels, int64_t BH, int64_t N, int64_t J, int jb,
-                                        int32_t* chunk_hist, int32_t* amb_list, int32_t* amb_count, cudaStream_t st) {
+                                        int32_t* chunk_hist, cudaStream_t st) {
   const int groups = 2 * (int)ceil_div64(J, jb);
   if (chunk_hist) {
     const int nchunks = sort_chunks(N);
-    tc::assign_reduce_hist_kernel<<<dim3((unsigned)nchunks, (unsigned)BH), 256, 0, st>>>(
-        partial, labels, chunk_hist, (int)BH, (int)N, (int)J, groups, nchunks, amb_list, amb_count);
+    tc::assign_reduce_hist_kernel<<<dim3((unsigned)nchunks, (unsigned)BH), 256, 0, st>>>(partial, labels, chunk_hist, (int)BH,
+                                                                                       (int)N, (int)J, groups, nchunks);
   } else {
-    tc::assign_reduce_kernel<<<(unsigned)ceil_div64(BH * N, 256), 256, 0, st>>>(partial, labels, BH * N, groups, amb_list,
-                                                                                amb_count);
+    tc::assign_reduce_kernel<<<(unsigned)ceil_div64(BH * N, 256), 256, 0, st>>>(partial, labels, BH * N, groups);
   }
   count_launches(2);
   return cudaGetLastError();
 }
 
 // chunk_hist != nullptr: also write the per-chunk label histograms of the sort (its first pass).
-// amb_count must be zero when the reduction starts (the prologue kernel clears it).
-cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, const float* w_f32, int32_t* labels,
-                             int2* partial, int32_t* status, int32_t* amb_list, int32_t* amb_count, int64_t BH, int64_t N,
-                             int64_t J, int32_t* chunk_hist, cudaStream_t st) {
+cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, int32_t* labels, int2* partial,
+                             int32_t* status, int64_t BH, int64_t N, int64_t J, int32_t* chunk_hist, cudaStream_t st) {
   const int Jpad = pad_clusters(J);
   const int jb = J <= 128 ? 128 : 256;
   cudaError_t e = jb == 128 ? launch_assign_tc_jb<128, false>(x, w_hi, w_lo, nullptr, partial, status, BH, N, J, Jpad, st)
                             : launch_assign_tc_jb<256, false>(x, w_hi, w_lo, nullptr, partial, status, BH, N, J, Jpad, st);
   if (e != cudaSuccess) return e;
-  e = launch_assign_reduce(partial, labels, BH, N, J, jb, chunk_hist, amb_list, amb_count, st);
-  if (e != cudaSuccess) return e;
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  tc::assign_rescore_kernel<<<(unsigned)(sms * 2), tc::kRescoreWarps * 32, 0, st>>>(
-      amb_list, amb_count, (const bf16*)x, w_f32, labels, chunk_hist, (int)N, (int)J, Jpad, sort_chunks(N));
-  count_launches(1);
-  return cudaGetLastError();
+  return launch_assign_reduce(partial, labels, BH, N, J, jb, chunk_hist, st);
 }
 
 // bias[bh, j] = -sum_d bf16(c_d * c_d) / 2: the centroid term of the squared distance with the
@@ -505,7 +388,7 @@ cudaError_t launch_euclid_assign_tc(const void* x, const void* centroids, float*
       ? launch_assign_tc_jb<128, true>(x, centroids, centroids, bias, partial, status, BH, N, K, (int)K, st)
       : launch_assign_tc_jb<256, true>(x, centroids, centroids, bias, partial, status, BH, N, K, (int)K, st);
   if (e != cudaSuccess) return e;
-  return launch_assign_reduce(partial, labels, BH, N, K, jb, chunk_hist, nullptr, nullptr, st);
+  return launch_assign_reduce(partial, labels, BH, N, K, jb, chunk_hist, st);
 }
 
 }  // namespace svoo

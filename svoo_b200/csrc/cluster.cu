@@ -53,11 +53,10 @@ inline size_t pro_smem_bytes(int K) {
 
 __global__ void __launch_bounds__(256) profile_prologue_kernel(
     const bf16* __restrict__ own, const bf16* __restrict__ form, bf16* __restrict__ w_hi,
-    bf16* __restrict__ w_lo, float* __restrict__ w_f32, int32_t* __restrict__ amb_count, int J, int K, int Jpad) {
+    bf16* __restrict__ w_lo, int J, int K, int Jpad) {
   extern __shared__ __align__(128) unsigned char pro_sm[];
   const int bh = blockIdx.y, j0 = blockIdx.x * kProR;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (blockIdx.x == 0 && bh == 0 && tid == 0) *amb_count = 0;     // the assignment that follows starts an empty list
   if (j0 >= J) {                                        // padding rows of W: zeros
     const int d = tid & 127, rg = tid >> 7;
     for (int r = rg * 8; r < rg * 8 + 8; ++r)
@@ -200,7 +199,6 @@ __global__ void __launch_bounds__(256) profile_prologue_kernel(
         hv.x = h0; hv.y = h1; lv.x = l0; lv.y = l1;
         *reinterpret_cast<__nv_bfloat162*>(w_hi + o) = hv;
         *reinterpret_cast<__nv_bfloat162*>(w_lo + o) = lv;
-        *reinterpret_cast<float2*>(w_f32 + o) = make_float2(v0, v1);
       }
     }
 }
@@ -449,16 +447,15 @@ cudaError_t launch_gather_rows(const void* x, const int32_t* idx, void* out, int
   return cudaGetLastError();
 }
 
-// Rows j >= J of w_f32 are never read (the re-scoring loops over j < J) and are left unwritten.
-cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void* w_lo, float* w_f32, int32_t* amb_count,
-                            int64_t BH, int64_t J, int64_t K, cudaStream_t st) {
+cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void* w_lo, int64_t BH, int64_t J,
+                            int64_t K, cudaStream_t st) {
   const int Jpad = pad_clusters(J);
   const size_t smem = pro_smem_bytes((int)K);
   cudaError_t e = cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)(Jpad / kProR), (unsigned)BH);
-  profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo, w_f32,
-                                                   amb_count, (int)J, (int)K, Jpad);
+  profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo,
+                                                   (int)J, (int)K, Jpad);
   count_launches(1);
   return cudaGetLastError();
 }

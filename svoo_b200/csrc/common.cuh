@@ -30,10 +30,8 @@ struct Workspace {
   int64_t partial;       // float [BH, Kmax, slabs, 128] centroid partial sums
   int64_t w_hi;          // bf16  [BH, Jpad, 128]
   int64_t w_lo;          // bf16  [BH, Jpad, 128]
-  int64_t w_f32;         // float [BH, Jpad, 128]: W before the split, for re-scoring near ties
-  int64_t amb_list;      // int32 [BH * N]: tokens whose two best scores are within rounding of each other
   int64_t assign_partial;  // int2 [Jpad/128, BH, N]: best (score bits, j) per column group
-  int64_t status;        // int32 [4]: words 0, 1 != 0 after a kernel gave up on a bounded wait; word 2 = entries of amb_list
+  int64_t status;        // int32 [4]: word 0 != 0 after a kernel gave up on a bounded wait
   int64_t runs;          // int2  [BH, QC, max_runs]: (first_row, virtual_begin) + sentinel (0, total)
   int64_t nruns;         // int32 [BH, QC]
   int64_t qtiles;        // int4  [BH, max_qtiles]
@@ -55,8 +53,6 @@ __host__ inline Workspace workspace_layout(int64_t BH, int64_t N, int64_t QC, in
   w.partial = take(BH * Kmax * kCentroidSlabs * kHeadDim * 4);
   w.w_hi = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
   w.w_lo = take(BH * (int64_t)pad_clusters(Kmax) * kRowBytes);
-  w.w_f32 = take(BH * (int64_t)pad_clusters(Kmax) * kHeadDim * 4);
-  w.amb_list = take(BH * N * 4);
   w.assign_partial = take((int64_t)(pad_clusters(Kmax) / 128) * BH * N * 8);   // two column groups per 256 rows
   w.status = take(16);
   // sized symmetrically in (QC, KC) so that one workspace serves either side

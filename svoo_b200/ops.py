@@ -309,16 +309,6 @@ def cluster_status(device: torch.device, BH: int, N: int, QC: int, KC: int) -> i
     return int(ws[off.value + 4:off.value + 8].view(torch.int32).item())
 
 
-def near_tie_count(device: torch.device, BH: int, N: int, QC: int, KC: int) -> int:
-    """Tokens that the last assignment step of the last cocluster / cocluster_assign call with these
-    sizes re-scored in fp32 because their two best scores were within rounding error (status word 2;
-    synchronises)."""
-    off = ctypes.c_int64(0)
-    check(LIB.svoo_b200_status_offset(BH, N, QC, KC, ctypes.byref(off)), "status_offset")
-    ws = workspace(device, BH, N, QC, KC)
-    return int(ws[off.value + 8:off.value + 12].view(torch.int32).item())
-
-
 def qk_prep(x: torch.Tensor, heads: int, weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
             cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The producer of the path's inputs in one pass: x [S, H*128] bf16 (a projection output) ->
