@@ -424,17 +424,193 @@ def layer_roofline_ms(cfg, heads, rho, n_tokens, peaks):
     return (tensor + (bytes_cent + bytes_perm) / (peaks["hbm_gbs"] * 1e9)) * 1e3
 
 
+# ------------------------------------------------------------------------------------------
+# cfg4: one denoising step of a Wan2.1-1.3B-shaped DiT with the sparse processor in every block
+# ------------------------------------------------------------------------------------------
+DIT_DENSITY = (0.05, 0.30)
+DIT_CLUSTERS = dict(num_q_centroids=100, num_k_centroids=500, top_p_kmeans=0.9, min_kc_ratio=0.05, kmeans_iter_init=5,
+                    kmeans_iter_step=5)
+
+
+def dit_inputs(cfg, seed=11):
+    g = torch.Generator("cpu").manual_seed(seed)
+    latents = torch.randn(1, cfg.in_channels, *cfg.latent, generator=g)
+    text = torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).bfloat16()
+    return latents.bfloat16(), text
+
+
+def run_dit_arm(args):
+    """--config cfg4: K denoising steps (one transformer forward each) of a random-init DiT with
+    Wan2.1-1.3B's shape (30 blocks, dim 1536, 12 heads, FFN 8960, cross attention to 512 x 4096 text
+    tokens) at 480p / 81 frames (32,760 tokens).  Self-attention of every block runs through
+    WanAttn_SAPAttn_Processor: 100 / 500 clusters, 5 iterations, top-p 0.9 with the per-(step,
+    layer, head) floor read through SparsityLookup from a seeded U[0.05, 0.30] CSV; the step index
+    is set before every step as the pipeline callback does.  N > 1: sequence parallel, the
+    self-attention re-shards to heads through peer stores."""
+    import tempfile
+    import torch.distributed as dist
+    from svoo_b200 import _lib, parallel, wan_dit
+    from svoo_b200.sparsity import SparsityLookup
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = wan_dit.WanDiTConfig(num_layers=args.dit_layers)
+    S, H = cfg.tokens, cfg.heads
+    if S % world:
+        raise SystemExit(f"{S} tokens do not split evenly over {world} ranks")
+    model = wan_dit.WanDiT(cfg).init_weights(seed=1).to(device=dev, dtype=torch.bfloat16).eval()
+    steps_total = args.warmup + args.steps
+    csv_path = os.path.join(tempfile.mkdtemp(), "density.csv")
+    wan_dit.write_density_table(csv_path, steps_total, cfg.num_layers, H, *DIT_DENSITY, seed=1004)
+    lookup = SparsityLookup(csv_path)
+    base = wan_dit.SequenceParallelWanProcessor if world > 1 else wan_dit.WanAttn_SAPAttn_Processor
+    proc_cls = type("BenchProcessor", (base,), {"_seen_timesteps": set()})
+    if world > 1:
+        parts = parallel.head_partition(H, world)
+        proc_cls.exchange = parallel.PeerExchange(parts, S, dev)
+        model.seq_shard = (rank, world)
+    procs = wan_dit.install_processors(model, proc_cls, cfg.grid, sparsity_lookup=lookup,
+                                       dynamic_min_kc_ratio_min=DIT_DENSITY[0], dynamic_min_kc_ratio_max=DIT_DENSITY[1],
+                                       **DIT_CLUSTERS)
+    latents_h, text_h = dit_inputs(cfg)
+    latents_h, text_h = latents_h.pin_memory(), text_h.pin_memory()
+    latents, text = latents_h.to(dev), text_h.to(dev)
+    attn_events = []
+
+    def pre(_m, _a, _k):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        attn_events.append([e, None])
+
+    def post(_m, _a, _k, _out):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        attn_events[-1][1] = e
+
+    for blk in model.blocks:
+        blk.attn1.register_forward_pre_hook(pre, with_kwargs=True)
+        blk.attn1.register_forward_hook(post, with_kwargs=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run_steps(first, count, e2e=False):
+        out = None
+        for s in range(first, first + count):
+            wan_dit.set_attention_step(model, s + 1)
+            t = torch.tensor([1000.0 - 20.0 * s], device=dev)
+            with torch.no_grad():
+                if e2e:
+                    lat = latents_h.to(dev, non_blocking=True)
+                    out = model(lat, t, text_h.to(dev, non_blocking=True))
+                    out_h.copy_(out, non_blocking=True)
+                else:
+                    out = model(latents, t, text)
+        return out
+
+    with torch.no_grad():
+        out_h = torch.empty_like(model(latents, torch.tensor([1000.0], device=dev), text), device="cpu").pin_memory()
+    for p in procs:                                         # that probe call clustered once: start the schedule afresh
+        p.centroids_init, p._cached_clustering_results = False, None
+    with ClockSampler(local) as clocks:
+        run_steps(0, args.warmup)
+        barrier()
+        attn_events.clear()
+        launches0 = _lib.LIB.svoo_b200_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run_steps(args.warmup, args.steps)
+        e1.record()
+        barrier()
+    launches = _lib.LIB.svoo_b200_launch_count() - launches0
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps, sum(a.elapsed_time(b) for a, b in attn_events) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    step_ms, attn_ms = ms.tolist()
+    for p in procs:
+        p.check_status()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run_steps(args.warmup, args.steps, e2e=True)
+    e1.record()
+    barrier()
+    e2e_ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        line = {
+            "metric": "dit_denoising_step_ms", "value": step_ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "wan1.3b-dit-480p", "blocks": cfg.num_layers, "dim": cfg.dim, "heads": H, "tokens": S,
+                       "q_clusters": 100, "k_clusters": 500, "kmeans_iters": 5, "density_floor_table": list(DIT_DENSITY),
+                       "parallelism": "one GPU" if world == 1 else f"sequence parallel x{world}, heads re-sharded by peer stores",
+                       "l2": "activations of one block (100 MB per tensor) and 2.6 GB of weights exceed the L2; no flush"},
+            "sparse_attention_ms_per_step": attn_ms, "sparse_attention_share": attn_ms / step_ms,
+            "e2e": {"value": float(e2e_ms.item()), "unit": "ms", "ms_per_step": float(e2e_ms.item()),
+                    "h2d_bytes_per_step": latents_h.numel() * 2 + text_h.numel() * 2, "d2h_bytes_per_step": out_h.numel() * 2},
+            "gpu_launches": int(launches), "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_dit_reference_arm(args):
+    """--impl reference --config cfg4: one block of the DiT per step on the host cores, its
+    self-attention through the CPU restatement of the reference's processor."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from oracle.wan_processor import OracleWanProcessor
+    from svoo_b200 import wan_dit
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = wan_dit.WanDiTConfig(num_layers=1)
+    model = wan_dit.WanDiT(cfg).init_weights(seed=1).to(dtype=torch.bfloat16).eval()
+    cls = type("CpuProcessor", (OracleWanProcessor,), {})
+    wan_dit.install_processors(model, cls, cfg.grid, **DIT_CLUSTERS)
+    latents, text = dit_inputs(cfg)
+    times = []
+    for s in range(args.warmup + args.steps):
+        wan_dit.set_attention_step(model, s + 1)
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            model(latents, torch.tensor([1000.0 - 20.0 * s]), text)
+        times.append(time.perf_counter() - t0)
+    ms = sum(times[args.warmup:]) / args.steps * 1e3 * 30
+    sample = "1 of 30 blocks per step (time x 30), full 32,760 tokens"
+    line = {"impl": "reference", "metric": "dit_denoising_step_ms", "value": ms, "unit": "ms", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "wan1.3b-dit-480p", "sample": sample},
+            "cpu_baseline": {"value": ms, "unit": "ms", "cores": os.cpu_count() or 1, "kind": "port", "sample": sample},
+            "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="svoo_b200", choices=["svoo_b200", "reference"])
-    ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS) + ["cfg4"])
+    ap.add_argument("--dit-layers", type=int, default=30, help="blocks of the cfg4 DiT (debugging)")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-group", type=int, default=4, help="heads per copy/compute group of the host-buffer path")
     args = ap.parse_args()
+    if args.config == "cfg4":
+        return run_dit_reference_arm(args) if args.impl == "reference" else run_dit_arm(args)
     cfg = synth.CONFIGS[args.config]
     if args.heads:
         cfg = dataclasses.replace(cfg, heads=args.heads)

@@ -216,19 +216,21 @@ int svoo_b200_append_text_blocks(const uint8_t* map, const int32_t* q_offsets, c
  * array, mapped into this process (CUDA IPC / symmetric memory).  The caller orders the
  * launches against the other ranks: a stream-ordered collective after the call before a
  * destination is read, and before a destination is overwritten again.
- *   - world in [1,16], H in [1,128], H % world == 0, n_loc >= 1.
+ *   - world in [1,16], H in [world,128], n_loc >= 1.  A rank owns at most hr = ceil(H / world)
+ *     heads (12 heads on 8 ranks: four ranks own two, four own one); every receive array has
+ *     room for hr heads.
  *
  * svoo_b200_push_heads: x = this rank's [n_loc, H, 128]; row (r, h) is stored into rank
- *   owner[h] at [slot[h], rank * n_loc + r, :] of its [H/world, N, 128] array.
- *   owner/slot: HOST int32 [H]; every (owner, slot) pair must be distinct, slot < H/world.
- * svoo_b200_push_seq: y = this rank's [H/world, N, 128]; row (i, n) is stored into rank
+ *   owner[h] at [slot[h], rank * n_loc + r, :] of its [hr, N, 128] array.
+ *   owner/slot: HOST int32 [H]; every (owner, slot) pair must be distinct, slot < hr.
+ * svoo_b200_push_seq: y = this rank's [heads_local, N, 128]; row (i, n) is stored into rank
  *   n / n_loc at [n % n_loc, my_heads[i], :] of its [n_loc, H, 128] array.
- *   my_heads: HOST int32 [H/world], distinct, in [0, H). */
+ *   my_heads: HOST int32 [heads_local], distinct, in [0, H); 1 <= heads_local <= hr. */
 /* svoo_b200_sparse_attn with the head -> sequence re-shard fused into its store: output row
  * n of local head i (after out_row_idx, if given) is written by the attention kernel straight
  * into rank n / n_loc at [n % n_loc, my_heads[i], :] of that rank's [n_loc, H, 128] array
- * (peer_dst as for svoo_b200_push_seq).  BH must equal H / world and S must equal
- * world * n_loc.  The caller fences as after svoo_b200_push_seq.  No counterpart in the
+ * (peer_dst as for svoo_b200_push_seq).  BH is this rank's head count (1 <= BH <= ceil(H / world))
+ * and S must equal world * n_loc.  The caller fences as after svoo_b200_push_seq.  No counterpart in the
  * reference. */
 int svoo_b200_sparse_attn_push(const void* q, const void* k, const void* v, const uint8_t* map,
                                const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
@@ -237,8 +239,8 @@ int svoo_b200_sparse_attn_push(const void* q, const void* k, const void* v, cons
                                int64_t workspace_bytes, void* stream);
 int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* owner, const int32_t* slot,
                          int32_t world, int32_t rank, int64_t n_loc, int64_t H, int64_t D, void* stream);
-int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int32_t world, int64_t n_loc,
-                       int64_t H, int64_t D, void* stream);
+int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int64_t heads_local, int32_t world,
+                       int64_t n_loc, int64_t H, int64_t D, void* stream);
 
 /* The whole layer in one call, for hosts that bind only one entry point: co-clustering
  * (svoo_b200_cocluster), cluster-block map (svoo_b200_block_map; top_p >= 1 gives the all-ones
@@ -274,7 +276,7 @@ int svoo_b200_qk_prep(const void* x, const float* weight, float eps, const float
                       int64_t H, int64_t D, void* out, void* stream);
 /* The same for a sequence-parallel caller: x is this rank's [n_loc, H*D] rows (cos, sin
  * [n_loc, D]) and every head's row is stored straight into the rank that owns the head, at
- * [slot[h], rank * n_loc + r, :] of its [H/world, N, D] array -- svoo_b200_push_heads fused
+ * [slot[h], rank * n_loc + r, :] of its [ceil(H/world), N, D] array -- svoo_b200_push_heads fused
  * into the producer (peer_dst, owner, slot as there).  No counterpart in the reference. */
 int svoo_b200_qk_prep_push(const void* x, const float* weight, float eps, const float* cos, const float* sin,
                            void* const* peer_dst, const int32_t* owner, const int32_t* slot, int32_t world, int32_t rank,

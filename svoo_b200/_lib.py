@@ -62,7 +62,7 @@ SIGNATURES = {
     "svoo_b200_peer_barrier": (c_int, [c_void_p, c_int32, c_int32, c_int32, ctypes.c_uint32, c_void_p, c_void_p]),
     "svoo_b200_push_heads": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int64, c_int64,
                                      c_void_p]),
-    "svoo_b200_push_seq": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p]),
+    "svoo_b200_push_seq": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int64, c_int64, c_void_p]),
 }
 
 

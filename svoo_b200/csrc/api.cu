@@ -256,7 +256,7 @@ namespace {
 int check_exchange(void* const* peer_dst, int32_t world, int64_t n_loc, int64_t H, int64_t D) {
   if (!peer_dst) return SVOO_ERR_NULL;
   if (D != kHeadDim) return SVOO_ERR_HEAD_DIM;
-  if (world < 1 || world > 16 || H < 1 || H > 128 || H % world != 0 || n_loc < 1 || n_loc * world > (int64_t)1 << 30)
+  if (world < 1 || world > 16 || H < world || H > 128 || n_loc < 1 || n_loc * world > (int64_t)1 << 30)
     return SVOO_ERR_SHAPE;
   for (int p = 0; p < world; ++p) {
     if (!peer_dst[p]) return SVOO_ERR_NULL;
@@ -316,7 +316,7 @@ int svoo_b200_sparse_attn_push(const void* q, const void* k, const void* v, cons
                                int64_t workspace_bytes, void* stream) {
   if (!my_heads) return SVOO_ERR_NULL;
   SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
-  if (BH != H / world || S != n_loc * world) return SVOO_ERR_SHAPE;
+  if (BH < 1 || BH > ceil_div64(H, world) || S != n_loc * world) return SVOO_ERR_SHAPE;
   bool seen[128] = {};
   for (int64_t i = 0; i < BH; ++i) {
     if (my_heads[i] < 0 || my_heads[i] >= H || seen[my_heads[i]]) return SVOO_ERR_SHAPE;
@@ -349,7 +349,7 @@ int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* ow
   SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
   if (rank < 0 || rank >= world) return SVOO_ERR_SHAPE;
   if (!aligned16(x)) return SVOO_ERR_ALIGN;
-  const int64_t hr = H / world;
+  const int64_t hr = ceil_div64(H, world);
   bool seen[16 * 128] = {};
   for (int64_t h = 0; h < H; ++h) {
     if (owner[h] < 0 || owner[h] >= world || slot[h] < 0 || slot[h] >= hr) return SVOO_ERR_SHAPE;
@@ -361,12 +361,13 @@ int svoo_b200_push_heads(const void* x, void* const* peer_dst, const int32_t* ow
   return SVOO_OK;
 }
 
-int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int32_t world, int64_t n_loc,
-                       int64_t H, int64_t D, void* stream) {
+int svoo_b200_push_seq(const void* y, void* const* peer_dst, const int32_t* my_heads, int64_t heads_local, int32_t world,
+                       int64_t n_loc, int64_t H, int64_t D, void* stream) {
   if (!y || !my_heads) return SVOO_ERR_NULL;
   SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
   if (!aligned16(y)) return SVOO_ERR_ALIGN;
-  const int64_t hr = H / world;
+  const int64_t hr = heads_local;
+  if (hr < 1 || hr > ceil_div64(H, world)) return SVOO_ERR_SHAPE;
   bool seen[128] = {};
   for (int64_t i = 0; i < hr; ++i) {
     if (my_heads[i] < 0 || my_heads[i] >= H || seen[my_heads[i]]) return SVOO_ERR_SHAPE;
@@ -415,7 +416,7 @@ int svoo_b200_qk_prep_push(const void* x, const float* weight, float eps, const 
   if (!owner || !slot) return SVOO_ERR_NULL;
   SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
   if (rank < 0 || rank >= world) return SVOO_ERR_SHAPE;
-  const int64_t hr = H / world;
+  const int64_t hr = ceil_div64(H, world);
   bool seen[16 * 128] = {};
   for (int64_t h = 0; h < H; ++h) {
     if (owner[h] < 0 || owner[h] >= world || slot[h] < 0 || slot[h] >= hr) return SVOO_ERR_SHAPE;

@@ -87,6 +87,8 @@ def cocluster(q: torch.Tensor, k: torch.Tensor, q_init_idx: Optional[torch.Tenso
         qcent, kcent = qc0.clone(), kc0.clone()
         qi_ptr = ki_ptr = 0
     else:
+        if q_init_idx is None or k_init_idx is None:
+            raise ValueError("cocluster needs both initial index tensors, or init_centroids")
         _need_cuda(q_init_idx, k_init_idx)
         QC, KC = q_init_idx.shape[-1], k_init_idx.shape[-1]
         qi = q_init_idx.to(torch.int32).contiguous()

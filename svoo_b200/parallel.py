@@ -138,15 +138,18 @@ class PeerExchange:
         self.rank = dist.get_rank(self.group)
         self.parts = parts
         self.H = sum(len(p) for p in parts)
-        self.hr = len(parts[self.rank])
-        if any(len(p) != self.hr for p in parts) or n_tokens % self.world:
-            raise ValueError("heads and tokens must split evenly over the ranks")
+        self.hr = len(parts[self.rank])                      # heads of this rank
+        self.hr_max = -(-self.H // self.world)               # room in every receive array
+        if n_tokens % self.world:
+            raise ValueError("tokens must split evenly over the ranks")
+        if min(len(p) for p in parts) < 1 or max(len(p) for p in parts) > self.hr_max:
+            raise ValueError("every rank needs between 1 and ceil(H / world) heads")
         self.N, self.n_loc, self.D = n_tokens, n_tokens // self.world, head_dim
-        self.heads_in = symm_mem.empty((3, self.hr, self.N, head_dim), dtype=torch.bfloat16, device=device)
+        self.heads_in = symm_mem.empty((3, self.hr_max, self.N, head_dim), dtype=torch.bfloat16, device=device)
         self.seq_out = symm_mem.empty((self.n_loc, self.H, head_dim), dtype=torch.bfloat16, device=device)
         h_in = symm_mem.rendezvous(self.heads_in, self.group)
         h_out = symm_mem.rendezvous(self.seq_out, self.group)
-        per = self.hr * self.N * head_dim * 2
+        per = self.hr_max * self.N * head_dim * 2
         self._in_ptrs = [(ctypes.c_void_p * self.world)(*[int(p) + t * per for p in h_in.buffer_ptrs]) for t in range(3)]
         self._out_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in h_out.buffer_ptrs])
         owner, slot = exchange_tables(parts)
@@ -216,7 +219,7 @@ class PeerExchange:
                 self.fence(1)
                 self.value_ready = torch.cuda.Event()
                 self.value_ready.record(self._side)
-        return self.heads_in[0], self.heads_in[1], self.heads_in[2]
+        return self.heads_in[0, :self.hr], self.heads_in[1, :self.hr], self.heads_in[2, :self.hr]
 
     def producer_to_heads(self, xq, xk, xv, norm_q, norm_k, cos, sin):
         """to_heads fused with the producer: xq, xk, xv are this rank's [N/P, H*128] projection
@@ -252,7 +255,7 @@ class PeerExchange:
             self.value_ready = torch.cuda.Event()
             self.value_ready.record(self._side)
         del keep
-        return self.heads_in[0], self.heads_in[1], self.heads_in[2]
+        return self.heads_in[0, :self.hr], self.heads_in[1, :self.hr], self.heads_in[2, :self.hr]
 
     @property
     def peer_out(self):
@@ -271,8 +274,8 @@ class PeerExchange:
         if tuple(y.shape) != (self.hr, self.N, self.D) or y.dtype != torch.bfloat16 or not y.is_contiguous():
             raise ValueError("head-sharded result must be contiguous bf16 [H_r, N, 128]")
         stream = torch.cuda.current_stream(y.device).cuda_stream
-        _lib.check(_lib.LIB.svoo_b200_push_seq(y.data_ptr(), self._out_ptrs, self._mine, self.world, self.n_loc, self.H,
-                                               self.D, stream), "push_seq")
+        _lib.check(_lib.LIB.svoo_b200_push_seq(y.data_ptr(), self._out_ptrs, self._mine, self.hr, self.world, self.n_loc,
+                                               self.H, self.D, stream), "push_seq")
         self.fence()
         return self.seq_out
 

@@ -7,7 +7,7 @@ import torch
 import torch.nn.functional as F
 
 from oracle import svoo_oracle as O
-from svoo_b200.sparsity import SparsityLookup, min_kc_ratio_for_heads
+from svoo_b200.sparsity import SparsityLookup
 from tests import golden_util as gu
 
 
@@ -23,38 +23,28 @@ def wan_qkv(attn, hidden, cos, sin):
 
 
 def wan_steps(z):
-    """Runs the four steps of the WAN_PROC case through the oracle.  Yields
+    """Runs the four steps of the WAN_PROC case through the oracle's processor
+    (oracle/wan_processor.py), replaying the recorded initial indices.  Yields
     (step, sparse?, out [S, dim] bf16, aux dict or None)."""
+    from oracle.wan_processor import OracleWanProcessor
     P = gu.WAN_PROC
     H = P["heads"]
     T, Hh, W = P["grid"]
     N = T * Hh * W
-    lookup = SparsityLookup(os.path.join(gu.GOLDEN, "processor_wan_density.csv"))
+    cls = type("OracleWanProcessorCase", (OracleWanProcessor,), {})
+    gu.configure_wan_processor(cls, SparsityLookup(os.path.join(gu.GOLDEN, "processor_wan_density.csv")))
     attn = gu.make_attn(31, H)
     cos, sin = gu.rotary_tables(32, N)
-    cached, inited = None, False
+    proc = cls(0)
     with torch.no_grad():
         for step, tval in P["steps"]:
             hidden = gu.wan_step_hidden(step)
-            q, k, v = wan_qkv(attn, hidden, cos, sin)
-            if tval > P["first_times_fp"]:
-                o = F.scaled_dot_product_attention(q, k, v)
-                aux = None
-            else:
-                recluster = True
-                if step >= P["start_reuse_step"]:
-                    recluster = (step - P["start_reuse_step"]) % P["reuse_interval"] == 0
-                if recluster or cached is None:
-                    iters = P["iter_step"] if inited else P["iter_init"]
-                    qi = torch.from_numpy(z[f"q_init_{step}"]).long()
-                    ki = torch.from_numpy(z[f"k_init_{step}"]).long()
-                    cached = O.co_cluster_tokens(q[0], k[0], qi, ki, iters)
-                    inited = True
-                ratio = min_kc_ratio_for_heads(lookup, True, step, 0, H, P["min_kc_ratio"], P["dyn_min"], P["dyn_max"])
-                o, aux = O.attention_given_clustering(q, k, v, cached, P["top_p"], ratio)
-                aux["ratio"] = ratio
-            y = attn.to_out[0](o.transpose(1, 2).flatten(2, 3))
-            yield step, aux is not None, y[0], aux
+            proc._step_from_callback = step
+            qi = torch.from_numpy(z[f"q_init_{step}"]).long()
+            ki = torch.from_numpy(z[f"k_init_{step}"]).long()
+            proc.draw_init_indices = lambda BH, n, qi=qi, ki=ki: (qi, ki)
+            y = proc(attn, hidden, rotary_emb=(cos, sin), timestep=torch.tensor([tval]))
+            yield step, proc.last_aux is not None, y[0], proc.last_aux
 
 
 def hunyuan_qkv(attn, hidden, enc):

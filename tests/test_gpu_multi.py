@@ -86,3 +86,95 @@ def test_peer_exchange_and_sharded_layer_two_gpus(tmp_path):
                          env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("OK") == 2
+
+
+CHILD_MORE = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["SVOO_ROOT"])
+from svoo_b200 import layer, parallel, processor, synth, wan_dit
+import dataclasses
+rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(local); dev = torch.device("cuda", local)
+dist.init_process_group("nccl", device_id=dev)
+
+def sharded_equals_single(cfg, parts, **extra):
+    H, N = cfg.heads, cfg.n_tokens
+    n_loc = N // world
+    dens = synth.head_densities(cfg)
+    q, k, v = (t.to(dev) for t in synth.make_qkv(cfg))
+    shard = lambda t: t[0, :, rank * n_loc:(rank + 1) * n_loc].transpose(0, 1).contiguous()
+    qi, ki = (t.to(dev) for t in synth.init_indices(cfg))
+    kw = dict(num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k, kmeans_iters=2, top_p=cfg.top_p, **extra)
+    x = parallel.PeerExchange(parts, N, dev)
+    out = parallel.sparse_attention_layer_sharded(shard(q), shard(k), shard(v), parts, densities=dens, init_indices=(qi, ki),
+                                                  exchange=x, **kw)
+    ref = layer.sparse_attention_layer(q, k, v, min_kc_ratio=dens, max_kc_ratio=dens, init_indices=(qi, ki), **kw)
+    assert torch.equal(out, shard(ref)) and x.status() == 0
+
+# 1. uneven head split: 3 heads on 2 ranks (the 12-heads-on-8-GPUs case in small)
+cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=3, grid=(7, 30, 52))
+parts = parallel.head_partition(3, world, synth.head_densities(cfg))
+assert sorted(len(p) for p in parts) == [1, 2]
+sharded_equals_single(cfg, parts)
+# 2. text tokens after the video tokens (joint attention): the sequence, text included, is split evenly
+cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=2, grid=(7, 30, 52), text_tokens=256, cfg_id=97)
+sharded_equals_single(cfg, parallel.head_partition(2, world), context_length=256, prompt_length=200)
+
+# 3. sequence-parallel DiT step against the one-GPU model (same weights, same initial indices)
+dcfg = wan_dit.WanDiTConfig(num_layers=2, dim=512, heads=4, ffn_dim=1024, text_dim=64, text_len=16, latent=(4, 32, 40))
+S = dcfg.tokens
+kw = dict(num_q_centroids=12, num_k_centroids=40, top_p_kmeans=0.9, min_kc_ratio=0.2, kmeans_iter_init=2, kmeans_iter_step=1)
+g = torch.Generator("cpu").manual_seed(0)
+lat = torch.randn(1, 16, *dcfg.latent, generator=g).bfloat16().to(dev)
+text = torch.randn(1, 16, 64, generator=g).bfloat16().to(dev)
+idx = [(torch.randint(0, S, (4, 12), generator=g), torch.randint(0, S, (4, 40), generator=g)) for _ in range(2)]
+def build(cls, shard):
+    m = wan_dit.WanDiT(dcfg).init_weights(1).to(device=dev, dtype=torch.bfloat16).eval()
+    procs = wan_dit.install_processors(m, cls, dcfg.grid, **kw)
+    m.seq_shard = shard
+    return m, procs
+single, p1 = build(type("P1", (processor.WanAttn_SAPAttn_Processor,), {}), None)
+sp_cls = type("P2", (wan_dit.SequenceParallelWanProcessor,), {})
+parts = parallel.head_partition(4, world)
+sp_cls.exchange = parallel.PeerExchange(parts, S, dev)
+sp, p2 = build(sp_cls, (rank, world))
+for l in range(2):
+    qi, ki = idx[l]
+    p1[l].draw_init_indices = lambda BH, n, d, qi=qi, ki=ki: (qi.to(d), ki.to(d))
+    mine = parts[rank]
+    p2[l].draw_init_indices = lambda BH, n, d, qi=qi, ki=ki, mine=mine: (qi[mine].to(d), ki[mine].to(d))
+for step in (1, 2):
+    wan_dit.set_attention_step(single, step); wan_dit.set_attention_step(sp, step)
+    t = torch.tensor([800.0 - 100 * step], device=dev)
+    with torch.no_grad():
+        want = single(lat, t, text)
+        got = sp(lat, t, text)                                # [1, S/P, C*patch]
+    T, Hh, W = dcfg.grid
+    rows = want.reshape(1, 16, T, 1, Hh, 2, W, 2).permute(0, 2, 4, 6, 3, 5, 7, 1).reshape(1, S, -1)
+    n_loc = S // world
+    mine_rows = rows[:, rank * n_loc:(rank + 1) * n_loc].float().flatten()
+    a = got.float().flatten()
+    cos = float(a @ mine_rows / (a.norm() * mine_rows.norm()))
+    assert cos >= 0.999, cos
+    for l in range(2):
+        p2[l].check_status()
+        full = p1[l]._cached_clustering_results.qlabels[parts[rank]]
+        assert (p2[l]._cached_clustering_results.qlabels == full).float().mean() >= 0.98
+assert sp_cls.exchange.status() == 0
+torch.cuda.synchronize(); dist.barrier(); dist.destroy_process_group()
+print("OK", rank)
+'''
+
+
+@pytest.mark.gpu
+def test_uneven_heads_text_tokens_and_sequence_parallel_dit_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "child_more.py"
+    script.write_text(CHILD_MORE)
+    env = dict(os.environ, SVOO_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
+                         env=env, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count("OK") == 2
