@@ -428,7 +428,11 @@ def layer_roofline_ms(cfg, heads, rho, n_tokens, peaks):
 # cfg4: one denoising step of a Wan2.1-1.3B-shaped DiT with the sparse processor in every block
 # ------------------------------------------------------------------------------------------
 DIT_DENSITY = (0.05, 0.30)
-DIT_CLUSTERS = dict(num_q_centroids=100, num_k_centroids=500, top_p_kmeans=0.9, min_kc_ratio=0.05, kmeans_iter_init=5,
+# top_p_kmeans = 0 makes the per-head floor the whole selection (the first sorted cluster plus the
+# floor, svoo/co_clustering.py:585-596): every query cluster keeps exactly max(1, int(d_h * 500)) key
+# clusters, i.e. the table's density is the budget, as in configs 1-3.  (With top-p 0.9 the nearly
+# uniform attention of a random-weight model would keep ~90 % of the clusters.)
+DIT_CLUSTERS = dict(num_q_centroids=100, num_k_centroids=500, top_p_kmeans=0.0, min_kc_ratio=0.05, kmeans_iter_init=5,
                     kmeans_iter_step=5)
 
 

@@ -100,7 +100,7 @@ class WanBlock(nn.Module):
         self.attn2 = Attention(d, cfg.heads, cfg.eps)
         self.norm3 = nn.LayerNorm(d, cfg.eps, elementwise_affine=False)
         self.ffn = nn.Sequential(nn.Linear(d, cfg.ffn_dim), nn.GELU(approximate="tanh"), nn.Linear(cfg.ffn_dim, d))
-        self.scale_shift_table = nn.Parameter(torch.randn(1, 6, d) / d ** 0.5)
+        self.scale_shift_table = nn.Parameter(torch.zeros(1, 6, d))
 
     @staticmethod
     def _ln(norm: nn.LayerNorm, x):
@@ -149,14 +149,16 @@ class WanDiT(nn.Module):
         self.blocks = nn.ModuleList([WanBlock(cfg) for _ in range(cfg.num_layers)])
         self.norm_out = nn.LayerNorm(d, cfg.eps, elementwise_affine=False)
         self.proj_out = nn.Linear(d, cfg.out_channels * math.prod(cfg.patch))
-        self.scale_shift_table = nn.Parameter(torch.randn(1, 2, d) / d ** 0.5)
+        self.scale_shift_table = nn.Parameter(torch.zeros(1, 2, d))
         self.seq_shard: Optional[Tuple[int, int]] = None      # (rank, world): this process holds tokens [rank*S/P, (rank+1)*S/P)
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0, std: float = 0.02) -> "WanDiT":
         g = torch.Generator("cpu").manual_seed(seed)
         for name, p in self.named_parameters():
-            if p.dim() >= 2 and "scale_shift_table" not in name:
+            if "scale_shift_table" in name:
+                p.copy_(torch.randn(p.shape, generator=g) / p.shape[-1] ** 0.5)
+            elif p.dim() >= 2:
                 p.copy_(torch.randn(p.shape, generator=g) * std)
             elif name.endswith("bias"):
                 p.zero_()

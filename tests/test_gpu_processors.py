@@ -106,26 +106,30 @@ def test_wan_processor_against_reference_steps(dev, fused_producer):
         c = proc._cached_clustering_results
         labels_seen[step] = c.qlabels
         ql, kl = c.qlabels.cpu().numpy(), c.klabels.cpu().numpy()
-        if step != 3:                                          # a clustering step: the oracle on the same q, k
-            iters = P["iter_init"] if step == 2 else P["iter_step"]
-            rl = _oracle_labels_on(seen, qi, ki, iters)
-            assert (ql == rl[0].numpy()).mean() >= 0.999 and (kl == rl[3].numpy()).mean() >= 0.999
-        # against the reference's recorded labels (its projections ran on the CPU)
-        assert (ql == z[f"qlabels_{step}"]).mean() >= 0.95
-        assert (kl == z[f"klabels_{step}"]).mean() >= 0.95
-        ref_map = gu.unpack_map(z, f"_{step}")[0]
         ratio = [float(r) for r in z[f"ratio_{step}"]]
         ratio = ratio if len(ratio) > 1 else ratio[0]
+        # strict: the oracle on the q, k, v this call produced (a clustering step clusters them, the
+        # reuse step keeps the oracle's clustering of step 2)
+        if step != 3:
+            iters = P["iter_init"] if step == 2 else P["iter_step"]
+            oracle_clustering = _oracle_labels_on(seen, qi, ki, iters)
+        rl = oracle_clustering
+        assert (ql == rl[0].numpy()).mean() >= 0.999 and (kl == rl[3].numpy()).mean() >= 0.999
         got_map = proc.last_block_map.cpu().numpy().astype(bool)
-        # bit-exact against the oracle on the processor's own centroids, up to ties against the reference
         m_or = O.identify_dynamic_map(c.qcentroids.cpu()[None], c.kcentroids.cpu()[None], c.qsizes.cpu()[None],
                                       c.ksizes.cpu()[None], P["top_p"], ratio)
-        assert (got_map == m_or[0].numpy()).all()
-        if (ql == z[f"qlabels_{step}"]).all() and (kl == z[f"klabels_{step}"]).all():
-            assert gu.processor_map_ties_ok(c.qcentroids.cpu(), c.kcentroids.cpu(), c.qsizes.cpu(), c.ksizes.cpu(),
-                                            P["top_p"], ratio, got_map, ref_map)
-        ok = gu.comparable_tokens(ql, z[f"qlabels_{step}"], got_map, ref_map)
-        _check_rows(y[0], want, ok, 0.5)
+        assert (got_map == m_or[0].numpy()).all()                # bit-exact on the processor's own centroids
+        o_ref, aux = O.attention_given_clustering(seen["q"], seen["k"], seen["v"], rl, P["top_p"], ratio)
+        with torch.no_grad():
+            y_ref = attn.to_out[0](o_ref.transpose(1, 2).flatten(2, 3).to(dev))
+        ok = gu.comparable_tokens(ql, rl[0].numpy(), got_map, aux["map"][0].numpy())
+        assert ok.float().mean() >= 0.9
+        assert (y[0].float() - y_ref[0].float()).abs().amax(-1).cpu()[ok].max() <= ATOL
+        # loose: the reference's recorded step.  Its projections ran on the CPU; a few bf16 roundings
+        # differ, some labels of this 960-token clustering with them, and then centroids and maps
+        assert (ql == z[f"qlabels_{step}"]).mean() >= 0.9 and (kl == z[f"klabels_{step}"]).mean() >= 0.9
+        a, b = y[0, ::gu.PROC_ROWS_KEPT].float().cpu().flatten(), want.float().flatten()
+        assert float(a @ b / (a.norm() * b.norm())) >= 0.98
     # the reuse step launched no clustering kernel: the same label tensor, and only the producer (3 when
     # fused), the map (1), the gathers (3) and the attention (3) ran
     assert labels_seen[3] is labels_seen[2] and labels_seen[7] is not labels_seen[2]
@@ -171,21 +175,30 @@ def test_hunyuan_processor_against_reference_step(dev):
     ql, kl = c.qlabels.cpu().numpy(), c.klabels.cpu().numpy()
     rl = _oracle_labels_on(seen, qi, ki, P["iter_init"], n_video=ql.shape[1])
     assert (ql == rl[0].numpy()).mean() >= 0.999 and (kl == rl[3].numpy()).mean() >= 0.999
-    assert (ql == z["qlabels"]).mean() >= 0.95 and (kl == z["klabels"]).mean() >= 0.95
     full = proc.last_block_map.cpu().numpy().astype(bool)
     QC, KC = P["num_q"], P["num_k"]
     assert full.shape == (P["heads"], QC + 2, KC + 2)
-    ref_map = gu.unpack_map(z)[0]
-    # the text blocks follow the reference's rule
-    m2, _, _, _ = O.hunyuan_text_blocks(torch.from_numpy(full[None, :, :QC, :KC]), c.qsizes.cpu()[None], c.ksizes.cpu()[None],
-                                        c.q_sorted_idx.cpu(), ql.shape[1], P["context_length"], P["prompt_length"])
-    assert (m2[0].numpy() == full).all()
-    if (ql == z["qlabels"]).all() and (kl == z["klabels"]).all():
-        assert gu.processor_map_ties_ok(c.qcentroids.cpu(), c.kcentroids.cpu(), c.qsizes.cpu(), c.ksizes.cpu(), P["top_p"],
-                                        float(P["min_kc_ratio"]), full[:, :QC, :KC], ref_map)
-    ok = gu.comparable_tokens(ql, z["qlabels"], full[:, :QC, :KC], ref_map)
-    _check_rows(y[0], gu.from_bf16_bits(z["out"]), ok, 0.5)
-    assert (y_enc[0].float().cpu() - gu.from_bf16_bits(z["out_enc"]).float()).abs().max() <= ATOL
+    # strict: the oracle's joint attention on the q, k, v this call produced
+    o_ref, aux = O.attention_given_clustering(seen["q"], seen["k"], seen["v"], rl, P["top_p"], float(P["min_kc_ratio"]), 0,
+                                              P["context_length"], P["prompt_length"])
+    m_own = O.identify_dynamic_map(c.qcentroids.cpu()[None], c.kcentroids.cpu()[None], c.qsizes.cpu()[None],
+                                   c.ksizes.cpu()[None], P["top_p"], float(P["min_kc_ratio"]))
+    m2, _, _, _ = O.hunyuan_text_blocks(m_own, c.qsizes.cpu()[None], c.ksizes.cpu()[None], c.q_sorted_idx.cpu(), ql.shape[1],
+                                        P["context_length"], P["prompt_length"])
+    assert (m2[0].numpy() == full).all()                         # bit-exact, text blocks by the reference's rule
+    ctx = P["context_length"]
+    y_all = o_ref.transpose(1, 2).flatten(2, 3).to(dev)
+    with torch.no_grad():
+        y_ref, y_enc_ref = attn.to_out[0](y_all[:, :-ctx]), y_all[:, -ctx:]
+    ok = gu.comparable_tokens(ql, rl[0].numpy(), full[:, :QC, :KC], aux["map_video"][0].numpy())
+    assert ok.float().mean() >= 0.9
+    assert (y[0].float() - y_ref[0].float()).abs().amax(-1).cpu()[ok].max() <= ATOL
+    assert (y_enc[0].float() - y_enc_ref[0].float()).abs().max() <= ATOL
+    # loose: the reference's recorded step (its projections ran on the CPU)
+    assert (ql == z["qlabels"]).mean() >= 0.9 and (kl == z["klabels"]).mean() >= 0.9
+    a, b = y[0, ::gu.PROC_ROWS_KEPT].float().cpu().flatten(), gu.from_bf16_bits(z["out"]).float().flatten()
+    assert float(a @ b / (a.norm() * b.norm())) >= 0.98
+    assert (y_enc[0].float().cpu() - gu.from_bf16_bits(z["out_enc"]).float()).abs().max() <= 2 * ATOL
 
 
 def test_hunyuan_dense_branch_and_rotary(dev):
@@ -285,13 +298,21 @@ def test_euclidean_mode_processor(dev):
 
 
 def test_dit_step_two_blocks_against_cpu_oracle(dev):
-    """A reduced DiT with the Wan block structure (2 blocks, 4 heads, 960 tokens): the GPU model with
-    WanAttn_SAPAttn_Processor in every block against the same weights on the CPU with the oracle's
-    processor, over two denoising steps (the second one reuses the clustering), density floors read
-    from a CSV through SparsityLookup, step index set as the pipeline callback does."""
+    """A reduced DiT with the Wan block structure (2 blocks, 4 heads, 960 tokens) over two denoising
+    steps (the second one reuses the clustering), density floors read from a CSV through
+    SparsityLookup, step index set as the pipeline callback does.  Two copies of the model with the
+    same weights run on the GPU: one with WanAttn_SAPAttn_Processor in every block, one with the
+    oracle's processor, whose sparse branch is computed on the CPU from the very q, k, v the block
+    produced (so that everything outside the path is identical in both)."""
     from oracle.wan_processor import OracleWanProcessor
     from svoo_b200 import processor, wan_dit
     from svoo_b200.sparsity import SparsityLookup
+
+    class OracleOnHost(OracleWanProcessor):
+        def attention_core_logic(self, query, key, value, timestep):
+            out = super().attention_core_logic(query.cpu(), key.cpu(), value.cpu(), timestep.cpu())
+            return out.to(query.device)
+
     cfg = wan_dit.WanDiTConfig(num_layers=2, dim=512, heads=4, ffn_dim=1024, text_dim=64, text_len=16, latent=(3, 32, 40))
     N = cfg.tokens
     path = os.path.join(os.environ.get("TMPDIR", "/tmp"), "svoo_b200_dit_density.csv")
@@ -299,37 +320,51 @@ def test_dit_step_two_blocks_against_cpu_oracle(dev):
     kw = dict(num_q_centroids=12, num_k_centroids=40, top_p_kmeans=0.9, min_kc_ratio=0.2, kmeans_iter_init=2,
               kmeans_iter_step=1, sparsity_lookup=SparsityLookup(path), dynamic_min_kc_ratio_min=0.05,
               dynamic_min_kc_ratio_max=0.4, start_reuse_step=1, reuse_interval=2)
-    cpu = wan_dit.WanDiT(cfg).init_weights(1).to(torch.bfloat16).eval()
+    ref_model = wan_dit.WanDiT(cfg).init_weights(1).to(device=dev, dtype=torch.bfloat16).eval()
     gpu = wan_dit.WanDiT(cfg).init_weights(1).to(device=dev, dtype=torch.bfloat16).eval()
-    cpu_procs = wan_dit.install_processors(cpu, type("OracleCase", (OracleWanProcessor,), {}), cfg.grid, **kw)
-    gpu_procs = wan_dit.install_processors(gpu, _fresh(processor.WanAttn_SAPAttn_Processor), cfg.grid, **kw)
-    for l, (pc, pg) in enumerate(zip(cpu_procs, gpu_procs)):
+    ref_procs = wan_dit.install_processors(ref_model, type("OracleCase", (OracleOnHost,), {}), cfg.grid, **kw)
+    plain_cls = _fresh(processor.WanAttn_SAPAttn_Processor)
+    plain_cls._fused_producer_applies = staticmethod(lambda *a: False)   # q, k, v bit-identical to the oracle model's
+    gpu_procs = wan_dit.install_processors(gpu, plain_cls, cfg.grid, **kw)
+    fused = wan_dit.WanDiT(cfg).init_weights(1).to(device=dev, dtype=torch.bfloat16).eval()
+    fused_procs = wan_dit.install_processors(fused, _fresh(processor.WanAttn_SAPAttn_Processor), cfg.grid, **kw)
+    for l, pf in enumerate(fused_procs):
+        g = torch.Generator("cpu").manual_seed(50 + l)
+        qi, ki = torch.randint(0, N, (cfg.heads, 12), generator=g), torch.randint(0, N, (cfg.heads, 40), generator=g)
+        pf.draw_init_indices = lambda BH, n, d, qi=qi, ki=ki: (qi.to(d), ki.to(d))
+    for l, (pc, pg) in enumerate(zip(ref_procs, gpu_procs)):
         g = torch.Generator("cpu").manual_seed(50 + l)
         qi, ki = torch.randint(0, N, (cfg.heads, 12), generator=g), torch.randint(0, N, (cfg.heads, 40), generator=g)
         pc.draw_init_indices = lambda BH, n, qi=qi, ki=ki: (qi, ki)
         pg.draw_init_indices = lambda BH, n, d, qi=qi, ki=ki: (qi.to(d), ki.to(d))
     g = torch.Generator("cpu").manual_seed(0)
-    lat = torch.randn(1, 16, *cfg.latent, generator=g).bfloat16()
-    text = torch.randn(1, 16, 64, generator=g).bfloat16()
+    lat = torch.randn(1, 16, *cfg.latent, generator=g).bfloat16().to(dev)
+    text = torch.randn(1, 16, 64, generator=g).bfloat16().to(dev)
     for step in (1, 2):
-        wan_dit.set_attention_step(cpu, step)
-        wan_dit.set_attention_step(gpu, step)
-        n0 = _launches()
+        for m in (ref_model, gpu, fused):
+            wan_dit.set_attention_step(m, step)
+        t = torch.tensor([900.0 - 100 * step], device=dev)
         with torch.no_grad():
-            want = cpu(lat, torch.tensor([900.0 - 100 * step]), text)
-            got = gpu(lat.to(dev), torch.tensor([900.0 - 100 * step], device=dev), text.to(dev))
+            want = ref_model(lat, t, text)
+            got = gpu(lat, t, text)
+            torch.cuda.synchronize()
+            n0 = _launches()
+            got_fused = fused(lat, t, text)
         torch.cuda.synchronize()
         launched = _launches() - n0
         for p in gpu_procs:
             p.check_status()
         assert got.shape == want.shape == lat.shape
-        a, b = got.float().cpu().flatten(), want.float().flatten()
-        assert float(a @ b / (a.norm() * b.norm())) >= 0.995
-        assert ((a - b).abs() <= 0.05 + 0.05 * b.abs()).float().mean() >= 0.97
-        for pc, pg in zip(cpu_procs, gpu_procs):
+        for l, (pc, pg) in enumerate(zip(ref_procs, gpu_procs)):
             assert pg.current_inference_step == step
             ql = pg._cached_clustering_results.qlabels.cpu().long()
-            assert (ql == pc.cached[0]).float().mean() >= 0.9       # the projections upstream ran on different hardware
+            assert (ql == pc.cached[0]).float().mean() >= (0.999 if l == 0 else 0.8)    # block 1 sees block 0's output rounding; random-weight activations have no cluster structure
+        a, b = got.float().cpu().flatten(), want.float().cpu().flatten()
+        assert float(a @ b / (a.norm() * b.norm())) >= 0.999
+        # the model with the fused producer (one-ulp differences in q, k; labels of random-weight
+        # activations, which have no cluster structure, move with them)
+        a = got_fused.float().cpu().flatten()
+        assert float(a @ b / (a.norm() * b.norm())) >= 0.98
         if step == 2:
             # reuse step: per block the fused producer (3), the map, three gathers and the attention (3)
             assert launched == cfg.num_layers * 10
