@@ -113,10 +113,12 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  pdl_trigger();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();                                             // W (and the centroids before it) come from the previous kernels
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -240,6 +242,8 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
 // labels[bh, n] = j of the best (score, j) pair over the column groups; the lower group wins ties.
 __global__ void __launch_bounds__(256) assign_reduce_kernel(const int2* __restrict__ partial, int32_t* __restrict__ labels,
                                                             int64_t BHN, int groups) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= BHN) return;
   int2 b = partial[i];
@@ -257,9 +261,11 @@ __global__ void __launch_bounds__(256) assign_reduce_hist_kernel(const int2* __r
                                                                  int32_t* __restrict__ chunk_hist, int BH, int N, int K,
                                                                  int groups, int nchunks) {
   __shared__ int hist[SVOO_MAX_CLUSTERS];
+  pdl_trigger();
   const int bh = blockIdx.y, chunk = blockIdx.x;
   for (int k = threadIdx.x; k < K; k += 256) hist[k] = 0;
   __syncthreads();
+  pdl_wait();
   const int64_t BHN = (int64_t)BH * N;
   const int base = chunk * kSortChunk;
   for (int t = threadIdx.x; t < kSortChunk; t += 256) {
@@ -327,9 +333,8 @@ static cudaError_t launch_assign_tc_jb(const void* x, const void* w_hi, const vo
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t total = BH * ceil_div64(J, JB) * ceil_div64(N, tc::kAsgXT);
   const unsigned grid = (unsigned)(total < sms ? total : sms);
-  tc::assign_tc_kernel<JB, kEuclid><<<grid, tc::kAsgThreads, C::kSmemBytes, st>>>(mx, mh, ml, partial, (int)BH, (int)N, (int)J,
-                                                                                 w_head_rows, bias, status);
-  return cudaGetLastError();
+  return launch_pdl(tc::assign_tc_kernel<JB, kEuclid>, dim3(grid), dim3(tc::kAsgThreads), (size_t)C::kSmemBytes, st, mx, mh, ml,
+                    partial, (int)BH, (int)N, (int)J, w_head_rows, bias, status);
 }
 
 static cudaError_t launch_assign_reduce(const int2* partial, int32_t* labels, int64_t BH, int64_t N, int64_t J, int jb,
@@ -337,13 +342,13 @@ static cudaError_t launch_assign_reduce(const int2* partial, int32_t* labels, in
   const int groups = 2 * (int)ceil_div64(J, jb);
   if (chunk_hist) {
     const int nchunks = sort_chunks(N);
-    tc::assign_reduce_hist_kernel<<<dim3((unsigned)nchunks, (unsigned)BH), 256, 0, st>>>(partial, labels, chunk_hist, (int)BH,
-                                                                                       (int)N, (int)J, groups, nchunks);
-  } else {
-    tc::assign_reduce_kernel<<<(unsigned)ceil_div64(BH * N, 256), 256, 0, st>>>(partial, labels, BH * N, groups);
+    count_launches(2);
+    return launch_pdl(tc::assign_reduce_hist_kernel, dim3((unsigned)nchunks, (unsigned)BH), dim3(256), 0, st,
+                      (const int2*)partial, labels, chunk_hist, (int)BH, (int)N, (int)J, groups, nchunks);
   }
   count_launches(2);
-  return cudaGetLastError();
+  return launch_pdl(tc::assign_reduce_kernel, dim3((unsigned)ceil_div64(BH * N, 256)), dim3(256), 0, st, (const int2*)partial,
+                    labels, BH * N, groups);
 }
 
 // chunk_hist != nullptr: also write the per-chunk label histograms of the sort (its first pass).
@@ -360,6 +365,8 @@ cudaError_t launch_assign_tc(const void* x, const void* w_hi, const void* w_lo, 
 // bias[bh, j] = -sum_d bf16(c_d * c_d) / 2: the centroid term of the squared distance with the
 // products rounded to the input type before the fp32 sum (svoo/co_clustering.py:389-390).
 __global__ void __launch_bounds__(256) euclid_bias_kernel(const bf16* __restrict__ c, float* __restrict__ bias, int64_t rows) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t row = (int64_t)blockIdx.x * 16 + threadIdx.x / 16;
   const int lane = threadIdx.x % 16;
   if (row >= rows) return;
@@ -381,7 +388,9 @@ __global__ void __launch_bounds__(256) euclid_bias_kernel(const bf16* __restrict
 // the centroids themselves as the stationary operand and -|c_j|^2 / 2 added in the epilogue.
 cudaError_t launch_euclid_assign_tc(const void* x, const void* centroids, float* bias, int32_t* labels, int2* partial,
                                     int32_t* status, int64_t BH, int64_t N, int64_t K, int32_t* chunk_hist, cudaStream_t st) {
-  euclid_bias_kernel<<<(unsigned)ceil_div64(BH * K, 16), 256, 0, st>>>((const bf16*)centroids, bias, BH * K);
+  cudaError_t eb = launch_pdl(euclid_bias_kernel, dim3((unsigned)ceil_div64(BH * K, 16)), dim3(256), 0, st,
+                              (const bf16*)centroids, bias, BH * K);
+  if (eb != cudaSuccess) return eb;
   count_launches(1);
   const int jb = K <= 128 ? 128 : 256;
   cudaError_t e = jb == 128

@@ -19,6 +19,8 @@ namespace svoo {
 // ---------------------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int32_t* __restrict__ idx,
                                    bf16* __restrict__ out, int N, int K) {
+  pdl_trigger();
+  pdl_wait();
   const int bh = blockIdx.y;
   const int c = blockIdx.x * (blockDim.x / 16) + threadIdx.x / 16;
   if (c >= K) return;
@@ -55,6 +57,8 @@ __global__ void __launch_bounds__(256) profile_prologue_kernel(
     const bf16* __restrict__ own, const bf16* __restrict__ form, bf16* __restrict__ w_hi,
     bf16* __restrict__ w_lo, int J, int K, int Jpad) {
   extern __shared__ __align__(128) unsigned char pro_sm[];
+  pdl_trigger();
+  pdl_wait();                                           // the centroids come from the previous kernel
   const int bh = blockIdx.y, j0 = blockIdx.x * kProR;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (j0 >= J) {                                        // padding rows of W: zeros
@@ -209,9 +213,11 @@ __global__ void __launch_bounds__(256) profile_prologue_kernel(
 __global__ void __launch_bounds__(256) label_hist_kernel(const int32_t* __restrict__ labels,
                                                          int32_t* __restrict__ chunk_hist, int N, int K, int nchunks) {
   __shared__ int hist[SVOO_MAX_CLUSTERS];
+  pdl_trigger();
   const int bh = blockIdx.y, chunk = blockIdx.x;
   for (int k = threadIdx.x; k < K; k += 256) hist[k] = 0;
   __syncthreads();
+  pdl_wait();
   const int base = chunk * kSortChunk;
   for (int i = threadIdx.x; i < kSortChunk; i += 256) {
     const int n = base + i;
@@ -229,6 +235,8 @@ __global__ void __launch_bounds__(256) label_hist_kernel(const int32_t* __restri
 __global__ void __launch_bounds__(1024) label_scan_kernel(int32_t* __restrict__ chunk_hist, int32_t* __restrict__ offsets,
                                                           int32_t* __restrict__ sizes, int K, int nchunks) {
   __shared__ int warp_tot[32];
+  pdl_trigger();
+  pdl_wait();
   const int bh = blockIdx.x, k = threadIdx.x, lane = k % 32, warp = k / 32;
   int total = 0;
   if (k < K) {
@@ -273,10 +281,12 @@ __global__ void __launch_bounds__(256) label_scatter_kernel(const int32_t* __res
                                                             const int32_t* __restrict__ offsets,
                                                             int32_t* __restrict__ sorted_idx, int N, int K, int nchunks) {
   extern __shared__ int wh[];          // [8][K] per-warp histogram, then per-warp running position
+  pdl_trigger();
   const int bh = blockIdx.y, chunk = blockIdx.x;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   for (int i = tid; i < 8 * K; i += 256) wh[i] = 0;
   __syncthreads();
+  pdl_wait();
   const int wbase = chunk * kSortChunk + warp * (kSortChunk / 8);
   const int32_t* lb = labels + (int64_t)bh * N;
   int mine[8];
@@ -339,6 +349,8 @@ __global__ void __launch_bounds__(256) centroid_partial_kernel(const bf16* __res
                                                                const int32_t* __restrict__ offsets,
                                                                float* __restrict__ partial, int N, int K, int nslabs) {
   __shared__ float red[16][kHeadDim + 4];
+  pdl_trigger();
+  pdl_wait();
   const int c = blockIdx.x, z = blockIdx.y, bh = blockIdx.z;
   const int begin = offsets[(int64_t)bh * (K + 1) + c], end = offsets[(int64_t)bh * (K + 1) + c + 1];
   int s0, s1;
@@ -387,6 +399,8 @@ __global__ void __launch_bounds__(128) centroid_finalize_kernel(const float* __r
                                                                 const int32_t* __restrict__ offsets,
                                                                 const bf16* __restrict__ old_c, bf16* __restrict__ new_c,
                                                                 int32_t* __restrict__ sizes, int K, int nslabs) {
+  pdl_trigger();
+  pdl_wait();
   const int c = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
   const int begin = offsets[(int64_t)bh * (K + 1) + c], end = offsets[(int64_t)bh * (K + 1) + c + 1];
   const int cnt = end - begin;
@@ -442,9 +456,8 @@ __global__ void __launch_bounds__(1024) offsets_from_sizes_kernel(const int32_t*
 cudaError_t launch_gather_rows(const void* x, const int32_t* idx, void* out, int64_t BH, int64_t N, int64_t K,
                                cudaStream_t st) {
   dim3 grid((unsigned)ceil_div64(K, 16), (unsigned)BH);
-  gather_rows_kernel<<<grid, 256, 0, st>>>((const bf16*)x, idx, (bf16*)out, (int)N, (int)K);
   count_launches(1);
-  return cudaGetLastError();
+  return launch_pdl(gather_rows_kernel, grid, dim3(256), 0, st, (const bf16*)x, idx, (bf16*)out, (int)N, (int)K);
 }
 
 cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void* w_lo, int64_t BH, int64_t J,
@@ -454,10 +467,9 @@ cudaError_t launch_prologue(const void* own, const void* form, void* w_hi, void*
   cudaError_t e = cudaFuncSetAttribute(profile_prologue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
   if (e != cudaSuccess) return e;
   dim3 grid((unsigned)(Jpad / kProR), (unsigned)BH);
-  profile_prologue_kernel<<<grid, 256, smem, st>>>((const bf16*)own, (const bf16*)form, (bf16*)w_hi, (bf16*)w_lo,
-                                                   (int)J, (int)K, Jpad);
   count_launches(1);
-  return cudaGetLastError();
+  return launch_pdl(profile_prologue_kernel, grid, dim3(256), smem, st, (const bf16*)own, (const bf16*)form, (bf16*)w_hi,
+                    (bf16*)w_lo, (int)J, (int)K, Jpad);
 }
 
 // hist_done: chunk_hist already holds the per-chunk label histograms (written by the assignment's
@@ -467,11 +479,14 @@ cudaError_t launch_sort_labels(const int32_t* labels, int64_t BH, int64_t N, int
   const int nchunks = sort_chunks(N);
   // label_scatter_kernel uses 8 * K * 4 <= 32 KB of dynamic shared memory: inside the default limit
   dim3 grid((unsigned)nchunks, (unsigned)BH);
-  if (!hist_done) label_hist_kernel<<<grid, 256, 0, st>>>(labels, chunk_hist, (int)N, (int)K, nchunks);
-  label_scan_kernel<<<(unsigned)BH, 1024, 0, st>>>(chunk_hist, offsets, sizes, (int)K, nchunks);
-  label_scatter_kernel<<<grid, 256, 8 * K * 4, st>>>(labels, chunk_hist, offsets, sorted_idx, (int)N, (int)K, nchunks);
+  cudaError_t e = cudaSuccess;
+  if (!hist_done) e = launch_pdl(label_hist_kernel, grid, dim3(256), 0, st, labels, chunk_hist, (int)N, (int)K, nchunks);
+  if (e != cudaSuccess) return e;
+  e = launch_pdl(label_scan_kernel, dim3((unsigned)BH), dim3(1024), 0, st, chunk_hist, offsets, sizes, (int)K, nchunks);
+  if (e != cudaSuccess) return e;
   count_launches(hist_done ? 2 : 3);
-  return cudaGetLastError();
+  return launch_pdl(label_scatter_kernel, grid, dim3(256), (size_t)(8 * K * 4), st, labels, (const int32_t*)chunk_hist,
+                    (const int32_t*)offsets, sorted_idx, (int)N, (int)K, nchunks);
 }
 
 cudaError_t launch_centroid_update(const void* x, const int32_t* sorted_idx, const int32_t* offsets,
@@ -483,11 +498,13 @@ cudaError_t launch_centroid_update(const void* x, const int32_t* sorted_idx, con
   int nslabs = (int)ceil_div64(4 * ceil_div64(N, K), kSlabMin);
   nslabs = nslabs < 1 ? 1 : (nslabs > kCentroidSlabs ? kCentroidSlabs : nslabs);
   dim3 grid((unsigned)K, (unsigned)nslabs, (unsigned)BH);
-  centroid_partial_kernel<<<grid, 256, 0, st>>>((const bf16*)x, sorted_idx, offsets, partial, (int)N, (int)K, nslabs);
+  cudaError_t e = launch_pdl(centroid_partial_kernel, grid, dim3(256), 0, st, (const bf16*)x, sorted_idx, offsets, partial,
+                             (int)N, (int)K, nslabs);
+  if (e != cudaSuccess) return e;
   dim3 grid2((unsigned)K, (unsigned)BH);
-  centroid_finalize_kernel<<<grid2, 128, 0, st>>>(partial, offsets, (const bf16*)old_c, (bf16*)new_c, sizes, (int)K, nslabs);
   count_launches(2);
-  return cudaGetLastError();
+  return launch_pdl(centroid_finalize_kernel, grid2, dim3(128), 0, st, (const float*)partial, offsets, (const bf16*)old_c,
+                    (bf16*)new_c, sizes, (int)K, nslabs);
 }
 
 cudaError_t launch_offsets_from_sizes(const int32_t* sizes, int32_t* offsets, int64_t BH, int64_t K, cudaStream_t st) {

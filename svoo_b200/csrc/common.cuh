@@ -69,6 +69,33 @@ int64_t& launch_counter();
 inline void count_launches(int n) { __atomic_fetch_add(&launch_counter(), (int64_t)n, __ATOMIC_RELAXED); }
 
 // ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  The clustering is a chain of short kernels (ten phases of
+// seven launches); launched this way, a kernel's CTAs are scheduled and run their set-up while
+// the previous kernel drains, and block in pdl_wait() until that kernel has completed and its
+// writes are visible.  Every kernel launched with launch_pdl() calls pdl_wait() before its first
+// access to memory that an earlier kernel of the stream wrote, and pdl_trigger() at its start
+// (the next kernel's CTAs may then be scheduled as soon as every CTA of this one has started).
+// Outside such a launch both are no-ops.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ---------------------------------------------------------------------------------------
 // Small device utilities
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
