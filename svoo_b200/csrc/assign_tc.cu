@@ -87,6 +87,11 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
   using C = AsgCfg<JB>;
   constexpr int NS = C::kXStages;
   constexpr uint32_t kIdesc = idesc_bf16(128, JB, false);
+  // At most 128 clusters: W_hi and W_lo are stacked as ONE 256-row operand (per 64-column half: the
+  // 128 hi rows, then the 128 lo rows), so that one M128 x N256 MMA per k-step computes both
+  // products, into accumulator columns j and j + 128, which the epilogue adds.
+  constexpr bool kStack = JB == 128 && !kEuclid;
+  constexpr uint32_t kIdescStack = idesc_bf16(128, 256, false);
   extern __shared__ unsigned char smem_raw[];
   const int n_jb = (J + JB - 1) / JB, n_xt = (N + kAsgXT - 1) / kAsgXT;
   const int64_t total = (int64_t)BH * n_jb * n_xt;
@@ -132,8 +137,13 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
           mbar_expect_tx(bar(C::W_FULL), (kEuclid ? 1 : 2) * C::kWBytes);
           const int y = job.bh * w_head_rows + job.jb * JB;
           for (int h = 0; h < 2; ++h) {
-            tma_load_2d(whi_s + h * C::kWHalf, &tm_hi, h * 64, y, bar(C::W_FULL));
-            if (!kEuclid) tma_load_2d(wlo_s + h * C::kWHalf, &tm_lo, h * 64, y, bar(C::W_FULL));
+            if (kStack) {
+              tma_load_2d(whi_s + h * 2 * C::kWHalf, &tm_hi, h * 64, y, bar(C::W_FULL));
+              tma_load_2d(whi_s + h * 2 * C::kWHalf + C::kWHalf, &tm_lo, h * 64, y, bar(C::W_FULL));
+            } else {
+              tma_load_2d(whi_s + h * C::kWHalf, &tm_hi, h * 64, y, bar(C::W_FULL));
+              if (!kEuclid) tma_load_2d(wlo_s + h * C::kWHalf, &tm_lo, h * 64, y, bar(C::W_FULL));
+            }
           }
           prev_block = block;
           ++wq;
@@ -165,9 +175,13 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t a = smem_desc_sw128(x_s + s * kAsgXBytes + (ks >> 2) * kAsgXHalf + (ks & 3) * 32, 16, 1024);
-          const uint32_t woff = (ks >> 2) * C::kWHalf + (ks & 3) * 32;
-          umma_ss(d, a, smem_desc_sw128(whi_s + woff, 16, 1024), kIdesc, ks > 0);
-          if (!kEuclid) umma_ss(d, a, smem_desc_sw128(wlo_s + woff, 16, 1024), kIdesc, 1);
+          if (kStack) {
+            umma_ss(d, a, smem_desc_sw128(whi_s + (ks >> 2) * 2 * C::kWHalf + (ks & 3) * 32, 16, 1024), kIdescStack, ks > 0);
+          } else {
+            const uint32_t woff = (ks >> 2) * C::kWHalf + (ks & 3) * 32;
+            umma_ss(d, a, smem_desc_sw128(whi_s + woff, 16, 1024), kIdesc, ks > 0);
+            if (!kEuclid) umma_ss(d, a, smem_desc_sw128(wlo_s + woff, 16, 1024), kIdesc, 1);
+          }
         }
         tc_commit(bar(C::X_EMPTY + s));
         tc_commit(bar(C::ACC_FULL + b));
@@ -211,6 +225,17 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
       const int jlim = J - job.jb * JB - half * HC;            // valid columns of this half (may be <= 0)
       float best = -INFINITY;
       int best_c = 0;
+      if (kStack) {
+#pragma unroll
+        for (int ch = 0; ch < HC / 32; ++ch) {
+          tmem_ld32_nowait(acc + ch * 32, ra);
+          tmem_ld32_nowait(acc + 128 + ch * 32, rb);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ra[c] = __float_as_uint(__uint_as_float(ra[c]) + __uint_as_float(rb[c]));
+          argmax32<false>(ra, ch * 32, jlim, bias_s, best, best_c);
+        }
+      } else {
       tmem_ld32_nowait(acc, ra);
       tmem_wait_ld();
 #pragma unroll
@@ -221,6 +246,7 @@ __global__ void __launch_bounds__(kAsgThreads, 1) assign_tc_kernel(
         if (ch + 2 < HC / 32) tmem_ld32_nowait(acc + (ch + 2) * 32, ra);
         argmax32<kEuclid>(rb, (ch + 1) * 32, jlim, bias_s, best, best_c);
         tmem_wait_ld();
+      }
       }
       tc_fence_before();
       mbar_arrive(bar(C::ACC_EMPTY + b));
