@@ -249,15 +249,12 @@ def run_gpu_arm(args, cfg):
         return out
 
     if world > 1:
-        dev_in = [torch.empty_like(t, device=dev) for t in host_in]
+        # host shards in, host shard out: the copies of one call overlap the compute of its neighbours
+        pipe = parallel.HostShardPipeline(xchg, dev)
+        qi_dev, ki_dev = qi_all.to(dev), ki_all.to(dev)
 
         def step_e2e():
-            for d_t, h_t in zip(dev_in[:2], host_in[:2]):
-                d_t.copy_(h_t, non_blocking=True)
-            q, k, v = (t[None] for t in xchg.to_heads(*dev_in, v_host=host_in[2]))    # V is copied behind the clustering
-            out = layer.sparse_attention_layer(q, k, v, min_kc_ratio=d_mine, max_kc_ratio=d_mine, init_indices=(qi, ki),
-                                               value_ready=xchg.value_ready, peer_out=xchg.peer_out, **kw)
-            host_out.copy_(xchg.seq_result(), non_blocking=True)
+            pipe(*host_in, host_out, parts, densities=dens, init_indices=(qi_dev, ki_dev), **kw)
     else:
         # host buffers in, host buffer out: copies of one head group overlap the compute of another
         pipe = layer.HostLayerPipeline(dev, H, N, heads_per_group=args.e2e_group)
@@ -270,7 +267,9 @@ def run_gpu_arm(args, cfg):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, with_timers=False):
+    def timed(fn, steps, with_timers=False, finish=None):
+        """`finish` runs after the last step and before the closing event: it makes the timing
+        stream wait for work that the steps left on other streams (the last device-to-host copy)."""
         timers = []
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -280,6 +279,8 @@ def run_gpu_arm(args, cfg):
             fn(t) if with_timers else fn()
             if t is not None:
                 timers.append(t)
+        if finish is not None:
+            finish()
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -296,7 +297,7 @@ def run_gpu_arm(args, cfg):
     launches = _lib.LIB.svoo_b200_launch_count() - launches0
     for _ in range(min(args.warmup, 2)):
         step_e2e()
-    e2e_ms, _ = timed(step_e2e, args.steps)
+    e2e_ms, _ = timed(step_e2e, args.steps, finish=lambda: torch.cuda.current_stream().wait_stream(pipe.copy_out))
 
     producer = measure_producer(cfg, dev, peaks_hbm=measured_peaks()[0]["hbm_gbs"]) if world == 1 else None
 
@@ -409,7 +410,7 @@ def measure_producer(cfg, dev, peaks_hbm, reps=5):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one sparse_attn launch per head of 75,600
 # tokens, from an ncu capture of a 4-head launch (profiles/sparse_attn_tc_kernel_wan14b_4heads.md).
-ATTN_DRAM_TRAFFIC_BYTES_PER_HEAD = 280.7e6 / 4
+ATTN_DRAM_TRAFFIC_BYTES_PER_HEAD = 281.6e6 / 4
 
 
 def layer_roofline_ms(cfg, heads, rho, n_tokens, peaks):

@@ -107,7 +107,10 @@ class HostLayerPipeline:
     """The layer for callers whose Q, K, V live in (pinned) host memory: heads are processed in
     groups, and the host-to-device copy of group g+1 and the device-to-host copy of group g-1
     run on their own streams while group g computes (heads are independent, so nothing else
-    changes).  Buffers are allocated once and reused by every call."""
+    changes).  Buffers are allocated once and reused by every call; the buffer hand-over events
+    persist across calls, so the copies of a call also overlap the tail of the previous one.
+    A call returns when its work is enqueued: `wait()` (or a device synchronize) before `out_host`
+    is read or the input tensors are overwritten."""
 
     def __init__(self, device: torch.device, heads: int, tokens: int, heads_per_group: int = 5):
         self.device = device
@@ -117,6 +120,14 @@ class HostLayerPipeline:
         shape = (1, self.group, tokens, 128)
         self.bufs = [[torch.empty(shape, dtype=torch.bfloat16, device=device) for _ in range(3)] for _ in range(2)]
         self.outs = [torch.empty(shape, dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.in_free = [None, None]         # event: compute finished reading input buffer set b
+        self.out_free = [None, None]        # event: device-to-host copy of output buffer b finished
+        self.n_groups = 0                   # groups processed so far (buffer parity runs on across calls)
+
+    def wait(self) -> None:
+        """Blocks the host until every copy and kernel of the calls so far has finished."""
+        self.copy_out.synchronize()
+        torch.cuda.current_stream(self.device).synchronize()
 
     def __call__(self, q_host, k_host, v_host, out_host, *, min_kc_ratio, max_kc_ratio, init_indices, **layer_kw):
         """q/k/v_host, out_host: [1, H, S, 128] bf16 pinned host tensors; per-head ratio lists and
@@ -124,25 +135,20 @@ class HostLayerPipeline:
         H = q_host.shape[1]
         compute = torch.cuda.current_stream(self.device)
         groups = [(h0, min(h0 + self.group, H)) for h0 in range(0, H, self.group)]
-        in_free = [None, None]          # event: compute finished reading input buffer set b
-        out_free = [None, None]         # event: device-to-host copy of output buffer b finished
         qi, ki = init_indices
-        start = torch.cuda.Event()
-        start.record(compute)
-        self.copy_in.wait_event(start)
-        self.copy_out.wait_event(start)
-        for g, (h0, h1) in enumerate(groups):
-            b, n = g % 2, h1 - h0
+        for h0, h1 in groups:
+            b, n = self.n_groups % 2, h1 - h0
+            self.n_groups += 1
             with torch.cuda.stream(self.copy_in):
-                if in_free[b] is not None:
-                    self.copy_in.wait_event(in_free[b])
+                if self.in_free[b] is not None:
+                    self.copy_in.wait_event(self.in_free[b])
                 for dst, src in zip(self.bufs[b], (q_host, k_host, v_host)):
                     dst[:, :n].copy_(src[:, h0:h1], non_blocking=True)
                 loaded = torch.cuda.Event()
                 loaded.record(self.copy_in)
             compute.wait_event(loaded)
-            if out_free[b] is not None:
-                compute.wait_event(out_free[b])
+            if self.out_free[b] is not None:
+                compute.wait_event(self.out_free[b])
             qd, kd, vd = (t[:, :n] for t in self.bufs[b])
             out = sparse_attention_layer(qd, kd, vd, min_kc_ratio=list(min_kc_ratio[h0:h1]),
                                          max_kc_ratio=list(max_kc_ratio[h0:h1]),
@@ -150,12 +156,11 @@ class HostLayerPipeline:
             self.outs[b][:, :n].copy_(out)
             done = torch.cuda.Event()
             done.record(compute)
-            in_free[b] = done
+            self.in_free[b] = done
             with torch.cuda.stream(self.copy_out):
                 self.copy_out.wait_event(done)
                 out_host[:, h0:h1].copy_(self.outs[b][:, :n], non_blocking=True)
                 stored = torch.cuda.Event()
                 stored.record(self.copy_out)
-            out_free[b] = stored
-        compute.wait_stream(self.copy_out)
+            self.out_free[b] = stored
         return out_host

@@ -306,3 +306,62 @@ def sparse_attention_layer_sharded(q_seq, k_seq, v_seq, parts, *, densities, ini
     if exchange is not None:
         return exchange.seq_result() if fused_store else exchange.to_seq(out[0])
     return head_to_seq_shard(out[0], parts, group)
+
+
+class HostShardPipeline:
+    """The sharded layer for a sequence-parallel caller whose activations live in (pinned) host
+    memory: this rank's [N/P, H, 128] shards of q, k, v come from the host and the [N/P, H, 128]
+    result shard goes back.  Device buffers are double: the host-to-device copies of call i+1 and
+    the device-to-host copy of call i-1 run on their own streams while call i computes.  A call
+    returns when its work is enqueued: `wait()` before `out_host` is read or the inputs are
+    overwritten."""
+
+    def __init__(self, exchange: PeerExchange, device):
+        self.x = exchange
+        self.device = device
+        shape = (exchange.n_loc, exchange.H, exchange.D)
+        self.bufs = [[torch.empty(shape, dtype=torch.bfloat16, device=device) for _ in range(3)] for _ in range(2)]
+        self.outs = [torch.empty(shape, dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.copy_in = torch.cuda.Stream(device)
+        self.copy_out = torch.cuda.Stream(device)
+        self.in_free = [None, None]
+        self.out_free = [None, None]
+        self.calls = 0
+
+    def wait(self) -> None:
+        self.copy_out.synchronize()
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def __call__(self, q_host, k_host, v_host, out_host, parts, *, densities, init_indices, **layer_kw):
+        from .layer import sparse_attention_layer
+        x = self.x
+        b = self.calls % 2
+        self.calls += 1
+        compute = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self.copy_in):
+            if self.in_free[b] is not None:
+                self.copy_in.wait_event(self.in_free[b])
+            for dst, src in zip(self.bufs[b], (q_host, k_host, v_host)):
+                dst.copy_(src, non_blocking=True)
+            loaded = torch.cuda.Event()
+            loaded.record(self.copy_in)
+        compute.wait_event(loaded)
+        if self.out_free[b] is not None:
+            compute.wait_event(self.out_free[b])
+        q, k, v = x.to_heads(*self.bufs[b])
+        mine = parts[x.rank]
+        qi, ki = init_indices
+        d = [densities[h] for h in mine]
+        sparse_attention_layer(q[None], k[None], v[None], min_kc_ratio=d, max_kc_ratio=d, init_indices=(qi[mine], ki[mine]),
+                               value_ready=x.value_ready, peer_out=x.peer_out, **layer_kw)
+        self.outs[b].copy_(x.seq_result())
+        done = torch.cuda.Event()
+        done.record(compute)
+        self.in_free[b] = done
+        with torch.cuda.stream(self.copy_out):
+            self.copy_out.wait_event(done)
+            out_host.copy_(self.outs[b], non_blocking=True)
+            stored = torch.cuda.Event()
+            stored.record(self.copy_out)
+        self.out_free[b] = stored
+        return out_host
