@@ -4,22 +4,10 @@ fixture cases of tests/golden_util.py, step by step, from the recorded initial i
 import os
 
 import torch
-import torch.nn.functional as F
 
 from oracle import svoo_oracle as O
 from svoo_b200.sparsity import SparsityLookup
 from tests import golden_util as gu
-
-
-def wan_qkv(attn, hidden, cos, sin):
-    """q, k, v [1,H,S,128] as the Wan __call__ hands them to attention_core_logic when the norms run
-    through the block's own modules (svoo/models/wan/attention.py:169-195)."""
-    H = attn.heads
-    q, k, v = attn.to_q(hidden), attn.to_k(hidden), attn.to_v(hidden)
-    q, k = attn.norm_q(q), attn.norm_k(k)
-    q, k, v = (t.unflatten(2, (H, -1)) for t in (q, k, v))
-    q, k = O.rotary_interleaved(q, cos, sin), O.rotary_interleaved(k, cos, sin)
-    return tuple(t.transpose(1, 2).contiguous() for t in (q, k, v))
 
 
 def wan_steps(z):

@@ -594,6 +594,57 @@ def test_full_size_properties(dev):
         assert (outp[h, a:b].float() - ref).abs().max() <= ATTN_ATOL
 
 
+def test_full_size_joint_attention_properties(dev):
+    """BASELINE config 3 at full length, two heads: 118,800 video tokens (33 x 45 x 80) + 256 text
+    tokens, 128 / 640 clusters, through the single-call C entry point with text blocks."""
+    ops, cc, _, layer = _mods()
+    cfg = dataclasses.replace(synth.CONFIGS["cfg3"], heads=2)
+    q, k, v = (t.to(dev) for t in synth.make_qkv(cfg))
+    qi, ki = synth.init_indices(cfg)
+    dens = synth.head_densities(synth.CONFIGS["cfg3"])[:2]
+    N, T, S = cfg.n_video, cfg.text_tokens, cfg.n_tokens
+    prompt = 200                                             # 56 unused text tokens: the last block is not empty
+    out, st = layer.sparse_attention_layer(q, k, v, num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k,
+                                           kmeans_iters=cfg.iters, top_p=cfg.top_p, min_kc_ratio=dens, max_kc_ratio=dens,
+                                           init_indices=(qi, ki), context_length=T, prompt_length=prompt, return_state=True)
+    assert ops.attention_status(dev, 2, S, cfg.num_q + 2, cfg.num_k + 2) == 0
+    assert ops.cluster_status(dev, 2, N, cfg.num_q, cfg.num_k) == 0
+    c = st.clustering
+    assert int(c.qsizes.sum()) == 2 * N and int(c.ksizes.sum()) == 2 * N
+    assert torch.equal(torch.sort(c.q_sorted_idx.long(), -1).values, torch.arange(N, device=dev).expand(2, N))
+    m = st.block_map.cpu().bool()
+    assert m.shape == (2, cfg.num_q + 2, cfg.num_k + 2)
+    for h in range(2):                                        # budget-exact video rows, text rules
+        assert (m[h, :cfg.num_q, :cfg.num_k].sum(-1) == max(1, int(float(np.float32(dens[h])) * cfg.num_k))).all()
+    assert m[:, cfg.num_q, :cfg.num_k + 1].all() and not m[:, cfg.num_q, cfg.num_k + 1].any()
+    assert m[:, :cfg.num_q + 1, cfg.num_k].all() and not m[:, cfg.num_q + 1, :cfg.num_k + 1].any()
+    assert torch.isfinite(out.float()).all()
+    # the same through the one-call C entry point
+    preserve, cap = cc.keep_limits(cfg.num_k, 2, dens, dens)
+    one = ops.layer(q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), qi.to(dev), ki.to(dev), cfg.iters, cfg.top_p,
+                    preserve, cap, text=T, prompt=prompt)
+    assert torch.equal(one, out[0])
+    qf, kf, vf = q[0].float().cpu(), k[0].float().cpu(), v[0].float().cpu()
+    for h in range(2):
+        # prompt rows attend every video and prompt key: exact dense softmax (fp32 on the host)
+        valid = N + prompt
+        dense = torch.softmax(qf[h, N:valid] @ kf[h, :valid].T * 128 ** -0.5, -1) @ vf[h, :valid]
+        assert (out[0, h, N:valid].float().cpu() - dense).abs().max() <= ATTN_ATOL
+        # unused prompt rows attend only themselves
+        own = torch.softmax(qf[h, valid:] @ kf[h, valid:].T * 128 ** -0.5, -1) @ vf[h, valid:]
+        assert (out[0, h, valid:].float().cpu() - own).abs().max() <= ATTN_ATOL
+    # sampled video query clusters: their selected key clusters plus the prompt block
+    kl, ql = c.klabels.cpu().long(), c.qlabels.cpu().long()
+    for h, i in ((0, 0), (1, 77), (1, 127)):
+        rows = (ql[h] == i).nonzero().flatten()[:300]
+        if rows.numel() == 0:
+            continue
+        keep = m[h, i, :cfg.num_k][kl[h]]
+        keys = torch.cat([keep.nonzero().flatten(), torch.arange(N, N + prompt)])
+        ref = torch.softmax(qf[h, rows] @ kf[h, keys].T * 128 ** -0.5, -1) @ vf[h, keys]
+        assert (out[0, h, rows].float().cpu() - ref).abs().max() <= ATTN_ATOL
+
+
 # ----------------------------------------------------------------------------------------
 # error behaviour through the C ABI
 # ----------------------------------------------------------------------------------------

@@ -111,3 +111,38 @@ def test_head_partition_properties():
     d = synth.head_densities(synth.CONFIGS["cfg2"])
     loads = [sum(d[h] for h in p) for p in head_partition(40, 8, d)]
     assert max(loads) / (sum(loads) / 8) < 1.01
+
+
+def test_exchange_tables_uneven_split():
+    """12 heads on 8 ranks (the Wan-1.3B head count on a full node): four ranks own two heads, four
+    own one; every receive array has ceil(12 / 8) = 2 head slots, and the kernels' row arithmetic
+    (replayed in numpy) still puts every row where the head-shard layout wants it, both ways."""
+    import numpy as np
+    from svoo_b200.parallel import exchange_tables, head_partition
+    world, H, n_loc, D = 8, 12, 3, 2
+    N = world * n_loc
+    rng = np.random.default_rng(1)
+    parts = head_partition(H, world, list(rng.uniform(0.05, 0.3, H)))
+    assert sorted(len(p) for p in parts) == [1, 1, 1, 1, 2, 2, 2, 2]
+    owner, slot = exchange_tables(parts)
+    hr = -(-H // world)
+    assert len(set(zip(owner, slot))) == H and max(slot) < hr
+    full = rng.standard_normal((H, N, D)).astype(np.float32)
+    recv = [np.full((hr, N, D), np.nan, np.float32) for _ in range(world)]
+    for rank in range(world):
+        x = full[:, rank * n_loc:(rank + 1) * n_loc].transpose(1, 0, 2).reshape(n_loc * H, D)
+        for t in range(n_loc * H):
+            r, h = divmod(t, H)
+            recv[owner[h]].reshape(hr * N, D)[slot[h] * N + rank * n_loc + r] = x[t]
+    seq = [np.full((n_loc * H, D), np.nan, np.float32) for _ in range(world)]
+    for rank in range(world):
+        mine = parts[rank]
+        assert np.array_equal(recv[rank][:len(mine)], full[mine])
+        y = recv[rank][:len(mine)].reshape(len(mine) * N, D)
+        for t in range(len(mine) * N):
+            i, n = divmod(t, N)
+            p = n // n_loc
+            seq[p][(n - p * n_loc) * H + mine[i]] = y[t]
+    for rank in range(world):
+        want = full[:, rank * n_loc:(rank + 1) * n_loc].transpose(1, 0, 2).reshape(n_loc * H, D)
+        assert np.array_equal(seq[rank], want)
