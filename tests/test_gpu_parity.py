@@ -744,10 +744,11 @@ def test_whole_run_agreement_against_fp32_drift(dev, cfg_name, record_property):
             f"whole-run agreement with the fp32 oracle {agree}; objective {obj}; mean |sparse - dense| {err}")
     print(line)
     record_property("whole_run", line)
-    out_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    os.makedirs(out_dir, exist_ok=True)
-    with open(os.path.join(out_dir, f"whole_run_{cfg_name}.txt"), "w") as f:
-        f.write(line + "\n")
+    out_dir = os.environ.get("SVOO_TEST_REPORT_DIR")          # optional: keep the figures as a text file
+    if out_dir:
+        os.makedirs(out_dir, exist_ok=True)
+        with open(os.path.join(out_dir, f"whole_run_{cfg_name}.txt"), "w") as f:
+            f.write(line + "\n")
     assert agree["cuda_q"] >= agree["tf32_q"] and agree["cuda_k"] >= agree["tf32_k"]
     assert agree["cuda_q"] >= agree["one_gemm_q"] - 0.01 and agree["cuda_k"] >= agree["one_gemm_k"] - 0.01
     assert abs(obj["cuda"] - obj["oracle"]) <= 0.005 * abs(obj["oracle"])
