@@ -362,20 +362,25 @@ __global__ void __launch_bounds__(256) centroid_partial_kernel(const bf16* __res
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  for (int s = s0 + grp; s < s1; s += 64) {
-    uint4 v[4];
+  // a thread adds rows s0 + grp + 16 k, k = 0, 1, 2, ... in that order; eight gathers are in flight
+  for (int s = s0 + grp; s < s1; s += 128) {
+    int row[8];
+    uint4 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const int ss = s + u * 16;
-      if (ss < s1) {
-        const int row = idx[ss];
-        v[u] = __ldg(reinterpret_cast<const uint4*>(xb + (int64_t)row * kHeadDim) + lane);
+      row[u] = ss < s1 ? idx[ss] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (row[u] >= 0) {
+        v[u] = __ldg(reinterpret_cast<const uint4*>(xb + (int64_t)row[u] * kHeadDim) + lane);
       } else {
         v[u] = make_uint4(0, 0, 0, 0);
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -395,13 +400,16 @@ __global__ void __launch_bounds__(256) centroid_partial_kernel(const bf16* __res
   }
 }
 
-__global__ void __launch_bounds__(128) centroid_finalize_kernel(const float* __restrict__ partial,
-                                                                const int32_t* __restrict__ offsets,
-                                                                const bf16* __restrict__ old_c, bf16* __restrict__ new_c,
-                                                                int32_t* __restrict__ sizes, int K, int nslabs) {
+// Four clusters per CTA (one per group of 128 threads): a CTA per cluster would be 20,000 CTAs of
+// a few hundred bytes of work each at 40 heads x 500 clusters.
+constexpr int kFinalizePerCta = 4;
+__global__ void __launch_bounds__(128 * kFinalizePerCta) centroid_finalize_kernel(
+    const float* __restrict__ partial, const int32_t* __restrict__ offsets, const bf16* __restrict__ old_c,
+    bf16* __restrict__ new_c, int32_t* __restrict__ sizes, int K, int nslabs) {
   pdl_trigger();
   pdl_wait();
-  const int c = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
+  const int c = blockIdx.x * kFinalizePerCta + threadIdx.x / 128, bh = blockIdx.y, d = threadIdx.x % 128;
+  if (c >= K) return;
   const int begin = offsets[(int64_t)bh * (K + 1) + c], end = offsets[(int64_t)bh * (K + 1) + c + 1];
   const int cnt = end - begin;
   const int64_t o = ((int64_t)bh * K + c) * kHeadDim + d;
@@ -501,9 +509,9 @@ cudaError_t launch_centroid_update(const void* x, const int32_t* sorted_idx, con
   cudaError_t e = launch_pdl(centroid_partial_kernel, grid, dim3(256), 0, st, (const bf16*)x, sorted_idx, offsets, partial,
                              (int)N, (int)K, nslabs);
   if (e != cudaSuccess) return e;
-  dim3 grid2((unsigned)K, (unsigned)BH);
+  dim3 grid2((unsigned)ceil_div64(K, kFinalizePerCta), (unsigned)BH);
   count_launches(2);
-  return launch_pdl(centroid_finalize_kernel, grid2, dim3(128), 0, st, (const float*)partial, offsets, (const bf16*)old_c,
+  return launch_pdl(centroid_finalize_kernel, grid2, dim3(128 * kFinalizePerCta), 0, st, (const float*)partial, offsets, (const bf16*)old_c,
                     (bf16*)new_c, sizes, (int)K, nslabs);
 }
 
