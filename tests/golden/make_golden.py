@@ -229,6 +229,25 @@ def producer_case(name, S, H, seed, eps=1e-6):
     print(name, "written")
 
 
+def euclid_case(name="euclid_fp32"):
+    """batch_kmeans_Euclid and euclid_assign_triton (svoo/co_clustering.py:335-541) on one small fp32
+    problem (the interpreter cannot run the kernel's tl.dot on bf16 operands): 3 iterations from
+    given initial centroids with tol = 0, so that the loop runs to max_iters."""
+    from tests import golden_util as gu
+    cfg = gu.EUCLID_CASE
+    q, _, _ = synth.make_qkv(cfg)
+    x = q[0]
+    init = synth.init_indices(cfg)[0]
+    c0 = torch.gather(x, 1, init[..., None].expand(-1, -1, 128))
+    labels, cent, sizes, n_it = ref_cc.batch_kmeans_Euclid(x, cfg.num_q, max_iters=3, tol=0.0, init_centroids=c0.clone())
+    x_sq = (x ** 2).sum(-1)
+    one = ref_cc.euclid_assign_triton(x, c0, x_sq)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), input_checksum=checksum(x), labels=labels.numpy().astype(np.int16),
+                        centroids=f32(cent), sizes=sizes.numpy().astype(np.int32), iters=np.array([n_it]),
+                        labels_first_assign=one.numpy().astype(np.int16))
+    print(name, "written:", n_it, "iterations")
+
+
 PROC_ROWS_KEPT = 8          # the processor fixtures keep every 8th output row
 
 
@@ -401,6 +420,8 @@ def main():
     only = sys.argv[1:]
     tiny = synth.LayerConfig("tiny-fp32", 90, 2, (4, 16, 16), torch.float32, 8, 16, 3, (0.25, 0.25), 1, False)
     if only:
+        if "euclid" in only:
+            euclid_case()
         if "processor_wan" in only:
             processor_case_wan()
         if "processor_hunyuan" in only:

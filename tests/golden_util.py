@@ -17,6 +17,7 @@ LAYER_CASES = {
     "layer_tiny_bf16": TINY_BF16,
     "layer_cfg0": synth.CONFIGS["cfg0"],
 }
+EUCLID_CASE = dataclasses.replace(TINY_FP32, name="euclid-fp32", cfg_id=98, num_q=24, grid=(4, 16, 24))
 MAP_CASES = ["map_bf16_budget", "map_bf16_topp_floor", "map_bf16_scalar", "map_fp32_topp",
              "map_fp32_cap_scalar", "map_bf16_big", "map_all_ones"]
 

@@ -197,3 +197,21 @@ def test_hunyuan_processor_step_matches_reference():
     # the text rows: the prompt attends all video and prompt keys, the unused prompt only itself;
     # neither depends on which tied cluster the map kept
     assert (y_enc.float() - gu.from_bf16_bits(z["out_enc"]).float()).abs().max() <= 2e-2
+
+
+def test_euclidean_kmeans_matches_reference():
+    """batch_kmeans_Euclid / euclid_assign_triton of the reference (svoo/co_clustering.py:335-541) on one
+    fp32 problem: first assignment, labels after three iterations, centroids and sizes."""
+    z = gu.load("euclid_fp32")
+    cfg = gu.EUCLID_CASE
+    q, _, _ = synth.make_qkv(cfg)
+    x = q[0]
+    init = synth.init_indices(cfg)[0]
+    c0 = torch.gather(x, 1, init[..., None].expand(-1, -1, x.shape[-1]))
+    first = O.euclid_assign(x, c0)
+    assert (first.numpy() == z["labels_first_assign"]).mean() >= 0.9995
+    labels, cent, sizes, n_it = O.batch_kmeans_euclid(x, c0, 3, tol=0.0)
+    assert n_it == int(z["iters"][0]) == 3
+    assert (labels.numpy() == z["labels"]).mean() >= 0.999
+    np.testing.assert_allclose(cent.float().numpy(), z["centroids"], atol=2e-3)
+    assert np.abs(sizes.numpy() - z["sizes"]).max() <= 2
