@@ -248,6 +248,77 @@ def euclid_case(name="euclid_fp32"):
     print(name, "written:", n_it, "iterations")
 
 
+def ear_case(name, cfg, settings):
+    """The error-aware routing variant (svoo/co_clustering.py:1314-2050) on one small problem:
+    value centroids (the Wan processor's _compute_value_centroids), error_estimation_triton,
+    identify_dynamic_map_estimated for each (top_p, gamma, min_kc_ratio) of `settings`, and the
+    centroid-compensation kernel _fused_qc_kernel_opt.  That kernel's wrapper obtains the token part
+    (o, log2-sum-exp) from FlashInfer's CUDA code; here the token part is the exact masked softmax
+    (oracle.ear_oracle.token_attention_with_lse), the kernel itself runs as written.
+    For a bf16 case the interpreter cannot run tl.dot on bf16 operands: error_estimation_triton is
+    given fp32 copies of its tensor arguments (the torch part of the selection sees bf16)."""
+    from oracle import ear_oracle as E
+    ref_wan, _ = _import_reference_processors()
+    t0 = time.time()
+    q, k, v = synth.make_qkv(cfg)
+    H, N, D = cfg.heads, cfg.n_video, 128
+    torch.manual_seed(7)
+    ql, qc, qs, kl, kc, ks = ref_cc.co_cluster_tokens(q[0], k[0], cfg.num_q, cfg.num_k, max_iters=2)
+    qp, q_sorted = ref_pm.permute_tensor_by_labels_triton(q, ql, dim=2)
+    kp, k_sorted = ref_pm.permute_tensor_by_labels_triton(k, kl, dim=2)
+    vp, _ = ref_pm.permute_tensor_by_labels_triton(v, kl, dim=2, sorted_indices=k_sorted)
+    vc = ref_wan.WanAttn_SAPAttn_Processor._compute_value_centroids(v[0], kl, ks, cfg.num_k)
+    qc4, kc4, vc4 = (t.view(1, H, -1, D) for t in (qc, kc, vc))
+    qs3, ks3 = qs.view(1, H, -1), ks.view(1, H, -1)
+    lowp = cfg.dtype == torch.bfloat16
+    orig_est = ref_cc.error_estimation_triton
+    if lowp:
+        def est32(qcen, kcen, vcen, pk, pv, a, b, c_logits, *rest, **kw):
+            return orig_est(qcen.float(), kcen.float(), vcen.float(), pk.float(), pv.float(), a, b, c_logits.float(), *rest, **kw)
+        ref_cc.error_estimation_triton = est32
+    store = dict(input_checksum=checksum(q, k, v), qlabels=ql.numpy().astype(np.int16), klabels=kl.numpy().astype(np.int16),
+                 qcentroids=f32(qc), kcentroids=f32(kc), vcentroids=f32(vc), qsizes=qs.numpy(), ksizes=ks.numpy(),
+                 settings=np.array([[s[0], s[1]] for s in settings], dtype=np.float64),
+                 ratios=np.array([np.resize(np.asarray(s[2], dtype=np.float64), H) for s in settings]),
+                 ratio_is_list=np.array([isinstance(s[2], list) for s in settings]))
+    try:
+        for n, (top_p, gamma, ratio) in enumerate(settings):
+            clog = torch.einsum("bhqd,bhkd->bhqk", qc4, kc4) * (D ** -0.5)
+            sc = ref_cc.error_estimation_triton(qc4, kc4, vc4, kp, vp, qs3, ks3, clog, gamma, 1e-8)
+            m = ref_cc.identify_dynamic_map_estimated(qp, kp, vp, qs3, ks3, qc4, kc4, vc4, top_p, gamma=gamma, min_kc_ratio=ratio)
+            store[f"scores_{n}"] = sc[0].numpy().astype(np.float32)
+            store[f"map_bits_{n}"] = np.packbits(m[0].numpy())
+            store["map_shape"] = np.array(m[0].shape)
+            store[f"c_logits_{n}"] = f32(clog[0])
+    finally:
+        ref_cc.error_estimation_triton = orig_est
+    # centroid compensation on the last map (fp32 copies for a bf16 case: tl.dot again)
+    up = (lambda t: t.float()) if lowp else (lambda t: t)
+    o_tok, lse2 = E.token_attention_with_lse(qp[0], kp[0], vp[0], m[0], qs, ks)
+    o_flash = o_tok.to(q.dtype)                     # FlashInfer returns the tensors' dtype
+    qf, o_in = up(qp[0]).contiguous(), up(o_flash).contiguous()
+    kcf, vcf = up(kc).contiguous(), up(vc).contiguous()
+    indptr = torch.zeros(1, H, cfg.num_q + 1, dtype=torch.int32)
+    indptr[..., 1:] = torch.cumsum(qs3, -1)
+    o_fin = torch.empty_like(qf)
+    lse_fin = torch.empty(H, N, dtype=torch.float32)
+    ref_cc._fused_qc_kernel_opt[(cfg.num_q, H)](
+        Q=qf, K_centroids=kcf, V_centroids=vcf, block_mask_map=m, block_col_sz=ks3, O_flash=o_in, LSE_flash=lse2,
+        QC_INDPTR=indptr, LSE_final=lse_fin, Out=o_fin,
+        stride_qh=qf.stride(0), stride_qs=qf.stride(1), stride_qd=qf.stride(2),
+        stride_ch=kcf.stride(0), stride_cn=kcf.stride(1), stride_cd=kcf.stride(2),
+        stride_mb=m.stride(0), stride_mh=m.stride(1), stride_mq=m.stride(2), stride_mk=m.stride(3),
+        stride_szb=ks3.stride(0), stride_szh=ks3.stride(1), stride_szn=ks3.stride(2),
+        stride_ipb=indptr.stride(0), stride_iph=indptr.stride(1), stride_ipn=indptr.stride(2),
+        sm_scale=D ** -0.5, B=1, H=H, S=N, D=D, KC_NUM=cfg.num_k, BLOCK_M=128, BLOCK_N=64)
+    out = ref_pm.apply_inverse_permutation_triton(o_fin[None], q_sorted, dim=2)[0]
+    lse_orig = torch.empty_like(lse_fin)
+    lse_orig.scatter_(1, q_sorted.reshape(H, N).long(), lse_fin)
+    store.update(out_rows=f32(out[:, ::8]), lse_rows=lse_orig[:, ::8].numpy(), rows_kept=np.array([8]))
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **store)
+    print(f"{name}: {time.time() - t0:.1f}s  map density {m.float().mean():.3f}")
+
+
 PROC_ROWS_KEPT = 8          # the processor fixtures keep every 8th output row
 
 
@@ -422,6 +493,10 @@ def main():
     if only:
         if "euclid" in only:
             euclid_case()
+        if "ear" in only:
+            from tests import golden_util as gu
+            for nm, (cfg, settings) in gu.EAR_CASES.items():
+                ear_case(nm, cfg, settings)
         if "processor_wan" in only:
             processor_case_wan()
         if "processor_hunyuan" in only:

@@ -18,6 +18,13 @@ LAYER_CASES = {
     "layer_cfg0": synth.CONFIGS["cfg0"],
 }
 EUCLID_CASE = dataclasses.replace(TINY_FP32, name="euclid-fp32", cfg_id=98, num_q=24, grid=(4, 16, 24))
+# name -> (config, [(top_p, gamma, min_kc_ratio), ...]); the compensation is recorded for the last setting
+EAR_CASES = {
+    "ear_fp32": (dataclasses.replace(TINY_FP32, name="ear-fp32", cfg_id=97, num_q=12, num_k=40, grid=(4, 16, 24)),
+                 [(0.9, 1.0, 0.0), (0.7, 0.5, 0.1), (0.8, 1.0, [0.05, 0.2]), (0.4, 1.0, 0.05)]),
+    "ear_bf16": (dataclasses.replace(TINY_BF16, name="ear-bf16", cfg_id=96, num_q=12, num_k=40, grid=(4, 16, 24)),
+                 [(0.9, 1.0, 0.0), (0.8, 1.0, [0.05, 0.2]), (0.4, 1.0, [0.1, 0.05])]),
+}
 MAP_CASES = ["map_bf16_budget", "map_bf16_topp_floor", "map_bf16_scalar", "map_fp32_topp",
              "map_fp32_cap_scalar", "map_bf16_big", "map_all_ones"]
 
@@ -88,6 +95,43 @@ def same_up_to_ties(got, ref, prob):
     a = np.sort(np.where(got, prob, -1.0), -1)
     b = np.sort(np.where(ref, prob, -1.0), -1)
     return bool((a == b).all())
+
+
+def unpack_ear_map(z, n):
+    shape = tuple(int(x) for x in z["map_shape"])
+    return np.unpackbits(z[f"map_bits_{n}"])[: int(np.prod(shape))].reshape(shape).astype(bool)
+
+
+def ear_inputs(cfg, z, q, k, v):
+    """Tensors of an EAR fixture: the recorded labels / centroids of the reference run, the stable
+    permutation of the seeded q, k, v by those labels (the reference's own order inside a cluster may
+    differ; nothing that is compared depends on it)."""
+    from oracle import svoo_oracle as O
+    dt = cfg.dtype
+    ql, kl = (torch.from_numpy(z[n].astype(np.int64)) for n in ("qlabels", "klabels"))
+    qc, kc, vc = (torch.from_numpy(z[n]).to(dt) for n in ("qcentroids", "kcentroids", "vcentroids"))
+    qs, ks = torch.from_numpy(z["qsizes"]), torch.from_numpy(z["ksizes"])
+    q_idx, q_off = O.sort_labels(ql, cfg.num_q)
+    k_idx, k_off = O.sort_labels(kl, cfg.num_k)
+    return dict(ql=ql, kl=kl, qc=qc, kc=kc, vc=vc, qs=qs, ks=ks, q_idx=q_idx, k_idx=k_idx, q_off=q_off, k_off=k_off,
+                q=q[0], k=k[0], v=v[0], qp=O.permute(q[0], q_idx), kp=O.permute(k[0], k_idx), vp=O.permute(v[0], k_idx))
+
+
+def ear_row_has_boundary_tie(prob, preserve, budget_kept, scores, got, ref):
+    """Why two selections of one map row may differ although both follow the rule: the reference sorts
+    with an unstable sort, so among clusters of equal budget probability it may put a different one
+    inside the guaranteed set or inside the budget (which changes the budget by their areas), and among
+    candidates of equal score a different one before the cut.  True when the row has such a tie: at the
+    guaranteed boundary, at a boundary of the kept budget positions, or between a candidate kept by one
+    side only and one kept by the other."""
+    sp = np.sort(prob)[::-1]
+    if 0 < preserve < len(sp) and sp[preserve - 1] == sp[preserve]:
+        return True
+    edges = np.nonzero(budget_kept[:-1] != budget_kept[1:])[0]        # sorted positions where keep flips
+    if any(sp[e] == sp[e + 1] for e in edges):
+        return True
+    only_got, only_ref = scores[got & ~ref], scores[ref & ~got]
+    return bool(len(only_got) and len(only_ref) and np.isin(only_got, only_ref).any())
 
 
 # ----------------------------------------------------------------------------------------------

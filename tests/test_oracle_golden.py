@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import ear_oracle as E
 from oracle import svoo_oracle as O
 from svoo_b200 import synth
 from tests import golden_util as gu
@@ -215,3 +216,76 @@ def test_euclidean_kmeans_matches_reference():
     assert (labels.numpy() == z["labels"]).mean() >= 0.999
     np.testing.assert_allclose(cent.float().numpy(), z["centroids"], atol=2e-3)
     assert np.abs(sizes.numpy() - z["sizes"]).max() <= 2
+
+
+# ----------------------------------------------------------------------------------------------
+# error-aware routing (EAR): value centroids, block scores, budgeted selection, centroid compensation
+# ----------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module", params=list(gu.EAR_CASES))
+def ear(request):
+    name = request.param
+    cfg, settings = gu.EAR_CASES[name]
+    z = gu.load(name)
+    q, k, v = synth.make_qkv(cfg)
+    assert synth.tensor_checksum(q, k, v)[0] == z["input_checksum"][0], "RNG drift: regenerate fixtures"
+    return name, cfg, settings, z, gu.ear_inputs(cfg, z, q, k, v)
+
+
+def test_ear_value_centroids(ear):
+    name, cfg, settings, z, t = ear
+    got = E.value_centroids(t["v"], t["kl"], t["ks"], cfg.num_k)
+    # the reference sums in the tokens' dtype: exact agreement only in fp32
+    tol = 1e-5 if cfg.dtype == torch.float32 else 3e-2
+    np.testing.assert_allclose(got.float().numpy(), z["vcentroids"], atol=tol)
+
+
+def test_ear_block_scores(ear):
+    name, cfg, settings, z, t = ear
+    for n, (top_p, gamma, ratio) in enumerate(settings):
+        clog = E.centroid_logits(t["qc"], t["kc"])
+        np.testing.assert_allclose(clog, z[f"c_logits_{n}"], atol=0 if cfg.dtype == torch.bfloat16 else 1e-5,
+                                   rtol=0 if cfg.dtype == torch.bfloat16 else 1e-5)
+        vn, cvd, vc_sq = E.value_stats(t["vp"], t["vc"], t["k_off"])
+        sc = E.error_scores(t["qc"], t["kp"], t["k_off"], t["qs"], t["ks"], clog, vn, cvd, vc_sq, gamma)
+        # bf16 case: the reference kernel was fed fp32 copies, so its products were not rounded to bf16
+        np.testing.assert_allclose(sc.numpy(), z[f"scores_{n}"], atol=2e-3 if cfg.dtype == torch.float32 else 2e-2)
+
+
+def test_ear_selection_matches_reference(ear):
+    """Given the reference's own block scores, the selection is the reference's up to the order
+    inside groups of equal budget probability or equal score (torch.sort there is unstable)."""
+    name, cfg, settings, z, t = ear
+    for n, (top_p, gamma, ratio) in enumerate(settings):
+        ref = gu.unpack_ear_map(z, n)
+        clog = E.centroid_logits(t["qc"], t["kc"])
+        got, aux = E.select_blocks(clog, z[f"scores_{n}"], t["qs"], t["ks"], top_p, ratio, cfg.dtype == torch.bfloat16, True)
+        got = got.numpy()
+        rows_equal = (got == ref).all(-1)
+        assert rows_equal.mean() >= (0.95 if cfg.dtype == torch.float32 else 0.6), (name, n, rows_equal.mean())
+        # a differing row has a tie where the order of equal keys decides
+        for h, i in zip(*np.nonzero(~rows_equal)):
+            assert gu.ear_row_has_boundary_tie(aux["prob"][h, i], aux["preserve"][h], aux["budget_kept"][h, i],
+                                               z[f"scores_{n}"][h, i], got[h, i], ref[h, i]), (name, n, h, i)
+
+
+def test_ear_map_from_own_scores(ear):
+    """Whole identify_dynamic_map_estimated from the oracle's own scores: entries may move where two
+    candidates' scores differ by less than the estimate's own tolerance."""
+    name, cfg, settings, z, t = ear
+    for n, (top_p, gamma, ratio) in enumerate(settings):
+        ref = gu.unpack_ear_map(z, n)
+        got = E.identify_dynamic_map_estimated(t["kp"], t["vp"], t["qs"], t["ks"], t["qc"], t["kc"], t["vc"], top_p, gamma, ratio)
+        assert (got.numpy() == ref).mean() >= 0.97, (name, n, (got.numpy() == ref).mean())
+
+
+def test_ear_compensated_attention(ear):
+    name, cfg, settings, z, t = ear
+    ref_map = torch.from_numpy(gu.unpack_ear_map(z, len(settings) - 1))
+    out_p, lse_p = E.compensated_attention(t["qp"], t["kp"], t["vp"], t["kc"], t["vc"], ref_map, t["qs"], t["ks"])
+    out = O.inverse_permute(out_p, t["q_idx"])
+    lse = torch.empty_like(lse_p)
+    lse.scatter_(1, t["q_idx"].long(), lse_p)
+    step = int(z["rows_kept"][0])
+    tol = 2e-5 if cfg.dtype == torch.float32 else 2e-2
+    np.testing.assert_allclose(out[:, ::step].float().numpy(), z["out_rows"], atol=tol)
+    np.testing.assert_allclose(lse[:, ::step].numpy(), z["lse_rows"], atol=1e-4 if cfg.dtype == torch.float32 else 2e-2)
