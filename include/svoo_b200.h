@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define SVOO_B200_VERSION 101
+#define SVOO_B200_VERSION 102
 
 enum {
   SVOO_OK = 0,
@@ -179,6 +179,62 @@ int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, cons
                                int64_t BH, int64_t S, int64_t D, int64_t QC, int64_t KC, float sm_scale,
                                void* out, const int32_t* out_row_idx,
                                void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Error-aware routing ("EAR"): the reference's alternative block selection and forward of the
+ * Wan processor (svoo/models/wan/attention.py:1047-1076, 1184-1196).  All tensors bf16 and in
+ * cluster order; QC, KC <= SVOO_MAX_CLUSTERS.  The four calls share one scratch buffer of
+ * svoo_b200_ear_workspace_bytes() bytes, which carries the value statistics from the first call to
+ * the second (same stream).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Scratch size of the EAR calls; *status_offset_out (optional) = byte offset of the int32 status
+ * word that svoo_b200_sparse_attn_ear clears and its kernel sets when a bounded wait expires. */
+int svoo_b200_ear_workspace_bytes(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* bytes_out,
+                                  int64_t* status_offset_out);
+
+/* Replaces _compute_value_centroids (svoo/models/wan/attention.py:594-610) and
+ * _precompute_v_stats_kernel (svoo/co_clustering.py:1314-1395).  v_perm [BH,N,128] in key-cluster
+ * order, k_offsets [BH,KC+1].  vcentroids_out [BH,KC,128]: mean value row of every key cluster
+ * (fp32 sums, rounded once; zero for an empty cluster).  The per-token |v|^2 and v.vc and the
+ * per-cluster |vc|^2 stay in the scratch buffer. */
+int svoo_b200_ear_value_centroids(const void* v_perm, const int32_t* k_offsets, int64_t BH, int64_t N, int64_t D,
+                                  int64_t QC, int64_t KC, void* vcentroids_out, void* ear_workspace,
+                                  int64_t ear_workspace_bytes, void* stream);
+
+/* Replaces the centroid-logit einsum of identify_dynamic_map_estimated (svoo/co_clustering.py:1724)
+ * and error_estimation_triton / _error_estimation_kernel (:1398-1689).  After
+ * svoo_b200_ear_value_centroids on the same scratch buffer.  c_logits_out, scores_out: fp32
+ * [BH,QC,KC]; c_logits = bf16(bf16(qc.kc) D^-0.5); scores = log(max(err,1e-8)) - gamma
+ * log(max(|Q_i||K_j|,1e-8)) with err the squared error of replacing the cluster's keys by its
+ * centroid. */
+int svoo_b200_ear_block_scores(const void* qcentroids, const void* kcentroids, const void* k_perm,
+                               const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t N, int64_t D,
+                               int64_t QC, int64_t KC, float gamma, float* c_logits_out, float* scores_out,
+                               void* ear_workspace, int64_t ear_workspace_bytes, void* stream);
+
+/* Replaces the selection of identify_dynamic_map_estimated (svoo/co_clustering.py:1738-1798):
+ * budget from the size-weighted centroid softmax and top_p, `preserve_host[h]` guaranteed clusters
+ * (max(1, int(ratio*KC)) there, 0 for ratio <= 0), `budget_preserve_host[h]` = max(1, int(ratio*KC*2)),
+ * then the highest-score candidates that fit the remaining budget.  Host arrays of BH ints.
+ * map_out uint8 [BH,QC,KC].  Bit-reproducible from its inputs (fixed-order fp32 arithmetic, ties by
+ * lower cluster index; the reference's torch.sort is unstable). */
+int svoo_b200_ear_select_blocks(const float* c_logits, const float* scores, const int32_t* q_offsets,
+                                const int32_t* k_offsets, int64_t BH, int64_t QC, int64_t KC, float top_p,
+                                const int32_t* preserve_host, const int32_t* budget_preserve_host, uint8_t* map_out,
+                                void* stream);
+
+/* Replaces dynamic_block_sparse_prune_fwd_flashinfer + _fused_qc_kernel_opt
+ * (svoo/co_clustering.py:1800-2050) in one pass: a query of cluster i attends the key tokens of the
+ * clusters map[i] selects and, for every other cluster j, one virtual key (key centroid j, value
+ * centroid j, logit bias log(|K_j| + 1e-6)); the softmax runs over the union, which is what the
+ * reference's merge of FlashInfer's (output, log-sum-exp) with the centroid part computes.
+ * k_ext, v_ext: [BH*S + BH*KC, 128] -- the cluster-ordered rows of all heads, then the centroid rows
+ * of all heads.  out, out_row_idx, lse as in svoo_b200_sparse_attn. */
+int svoo_b200_sparse_attn_ear(const void* q, const void* k_ext, const void* v_ext, const uint8_t* map,
+                              const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
+                              int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx, float* lse,
+                              void* ear_workspace, int64_t ear_workspace_bytes, void* stream);
 
 /* Byte offset, inside a workspace of these sizes, of a 4-word int32 status block that
  * the tensor-core kernels report into.  Word 0 is cleared by svoo_b200_sparse_attn and

@@ -47,6 +47,16 @@ SIGNATURES = {
                                            c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
                                            c_void_p]),
     "svoo_b200_status_offset": (c_int, [c_int64, c_int64, c_int64, c_int64, _I64P]),
+    "svoo_b200_ear_workspace_bytes": (c_int, [c_int64, c_int64, c_int64, c_int64, _I64P, _I64P]),
+    "svoo_b200_ear_value_centroids": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p,
+                                              c_void_p, c_int64, c_void_p]),
+    "svoo_b200_ear_block_scores": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                           c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "svoo_b200_ear_select_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float,
+                                            _I32P, _I32P, c_void_p, c_void_p]),
+    "svoo_b200_sparse_attn_ear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                          c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_int64, c_void_p]),
     "svoo_b200_offsets_from_sizes": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "svoo_b200_sparse_attn_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_int32, c_int64,
@@ -66,7 +76,7 @@ SIGNATURES = {
 }
 
 
-VERSION = 101          # SVOO_B200_VERSION of include/svoo_b200.h this binding was written for
+VERSION = 102          # SVOO_B200_VERSION of include/svoo_b200.h this binding was written for
 
 
 class SvooB200Error(RuntimeError):

@@ -19,7 +19,18 @@ cudaError_t launch_build_runs(const uint8_t*, const int32_t*, int2*, int32_t*, i
 cudaError_t launch_build_qtiles(const int32_t*, int4*, int32_t*, int64_t, int64_t, int64_t, int, cudaStream_t);
 cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, void*, const int32_t*, const int4*,
                                   const int32_t*, const int2*, const int32_t*, int32_t*, int64_t, int64_t, int64_t,
-                                  int64_t, float, void* const*, const int32_t*, int, int64_t, int, float*, cudaStream_t);
+                                  int64_t, float, void* const*, const int32_t*, int, int64_t, int, float*, cudaStream_t,
+                                  const int32_t* ear_ltok = nullptr, const int32_t* ear_k_offsets = nullptr,
+                                  int ear_max_runs = 0);
+cudaError_t launch_ear_value_stats(const void*, const int32_t*, void*, float*, float*, float*, int64_t, int64_t, int64_t,
+                                   cudaStream_t);
+cudaError_t launch_ear_scores(const void*, const void*, const void*, const int32_t*, const int32_t*, const float*,
+                              const float*, const float*, float*, float*, int64_t, int64_t, int64_t, int64_t, float,
+                              cudaStream_t);
+cudaError_t launch_ear_select(const float*, const float*, const int32_t*, const int32_t*, uint8_t*, int64_t, int64_t, int64_t,
+                              float, const int32_t*, const int32_t*, cudaStream_t);
+cudaError_t launch_ear_build_runs(const uint8_t*, const int32_t*, int2*, int32_t*, int32_t*, int64_t, int64_t, int64_t,
+                                  int64_t, int, cudaStream_t);
 cudaError_t launch_euclid_assign_tc(const void*, const void*, float*, int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t,
                                     int32_t*, cudaStream_t);
 cudaError_t launch_append_text_blocks(const uint8_t*, const int32_t*, const int32_t*, const int32_t*, const int32_t*,
@@ -332,6 +343,117 @@ int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, cons
                                void* workspace, int64_t workspace_bytes, void* stream) {
   return sparse_attn_impl(false, q, k, v, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, out, out_row_idx,
                           workspace, workspace_bytes, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Error-aware routing (EAR)
+// ---------------------------------------------------------------------------------------
+namespace {
+struct EarWorkspace {
+  int64_t vnorm, cvd, vcsq, runs, nruns, ltok, qtiles, nqtiles, status, total;
+};
+inline int ear_max_runs(int64_t KC) { return (int)(KC + 6); }
+inline EarWorkspace ear_layout(int64_t BH, int64_t N, int64_t QC, int64_t KC) {
+  EarWorkspace w;
+  int64_t o = 0;
+  auto take = [&](int64_t bytes) { int64_t at = o; o += align_up(bytes, 256); return at; };
+  w.vnorm = take(BH * N * 4);
+  w.cvd = take(BH * N * 4);
+  w.vcsq = take(BH * KC * 4);
+  w.runs = take(BH * QC * (int64_t)ear_max_runs(KC) * 8);
+  w.nruns = take(BH * QC * 4);
+  w.ltok = take(BH * QC * 4);
+  w.qtiles = take(BH * (int64_t)max_qtiles(N, QC) * 16);
+  w.nqtiles = take(BH * 4);
+  w.status = take(16);
+  w.total = o;
+  return w;
+}
+int check_ear(int64_t BH, int64_t N, int64_t D, int64_t QC, int64_t KC) {
+  SVOO_TRY(check_tokens(BH, N, D));
+  if (QC < 1 || KC < 1 || QC > SVOO_MAX_CLUSTERS || KC > SVOO_MAX_CLUSTERS) return SVOO_ERR_CLUSTERS;
+  return SVOO_OK;
+}
+}  // namespace
+
+int svoo_b200_ear_workspace_bytes(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* bytes_out,
+                                  int64_t* status_offset_out) {
+  if (!bytes_out) return SVOO_ERR_NULL;
+  SVOO_TRY(check_ear(BH, N, kHeadDim, QC, KC));
+  const EarWorkspace w = ear_layout(BH, N, QC, KC);
+  *bytes_out = w.total;
+  if (status_offset_out) *status_offset_out = w.status;
+  return SVOO_OK;
+}
+
+int svoo_b200_ear_value_centroids(const void* v_perm, const int32_t* k_offsets, int64_t BH, int64_t N, int64_t D,
+                                  int64_t QC, int64_t KC, void* vcentroids_out, void* ear_workspace,
+                                  int64_t ear_workspace_bytes, void* stream) {
+  if (!v_perm || !k_offsets || !vcentroids_out || !ear_workspace) return SVOO_ERR_NULL;
+  SVOO_TRY(check_ear(BH, N, D, QC, KC));
+  if (!aligned16(v_perm) || !aligned16(vcentroids_out) || !aligned16(ear_workspace)) return SVOO_ERR_ALIGN;
+  const EarWorkspace w = ear_layout(BH, N, QC, KC);
+  if (ear_workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  SVOO_CUDA(launch_ear_value_stats(v_perm, k_offsets, vcentroids_out, ws_at<float>(ear_workspace, w.vnorm),
+                                   ws_at<float>(ear_workspace, w.cvd), ws_at<float>(ear_workspace, w.vcsq), BH, N, KC,
+                                   (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_ear_block_scores(const void* qcentroids, const void* kcentroids, const void* k_perm, const int32_t* q_offsets,
+                               const int32_t* k_offsets, int64_t BH, int64_t N, int64_t D, int64_t QC, int64_t KC,
+                               float gamma, float* c_logits_out, float* scores_out, void* ear_workspace,
+                               int64_t ear_workspace_bytes, void* stream) {
+  if (!qcentroids || !kcentroids || !k_perm || !q_offsets || !k_offsets || !c_logits_out || !scores_out || !ear_workspace)
+    return SVOO_ERR_NULL;
+  SVOO_TRY(check_ear(BH, N, D, QC, KC));
+  if (!aligned16(qcentroids) || !aligned16(kcentroids) || !aligned16(k_perm) || !aligned16(ear_workspace)) return SVOO_ERR_ALIGN;
+  const EarWorkspace w = ear_layout(BH, N, QC, KC);
+  if (ear_workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  SVOO_CUDA(launch_ear_scores(qcentroids, kcentroids, k_perm, q_offsets, k_offsets, ws_at<float>(ear_workspace, w.vnorm),
+                              ws_at<float>(ear_workspace, w.cvd), ws_at<float>(ear_workspace, w.vcsq), c_logits_out, scores_out,
+                              BH, N, QC, KC, gamma, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_ear_select_blocks(const float* c_logits, const float* scores, const int32_t* q_offsets, const int32_t* k_offsets,
+                                int64_t BH, int64_t QC, int64_t KC, float top_p, const int32_t* preserve_host,
+                                const int32_t* budget_preserve_host, uint8_t* map_out, void* stream) {
+  if (!c_logits || !scores || !q_offsets || !k_offsets || !preserve_host || !budget_preserve_host || !map_out)
+    return SVOO_ERR_NULL;
+  if (BH < 1 || BH > SVOO_MAX_HEADS) return SVOO_ERR_SHAPE;
+  if (QC < 1 || KC < 1 || QC > SVOO_MAX_CLUSTERS || KC > SVOO_MAX_CLUSTERS) return SVOO_ERR_CLUSTERS;
+  for (int64_t h = 0; h < BH; ++h)
+    if (preserve_host[h] < 0 || budget_preserve_host[h] < 0) return SVOO_ERR_SHAPE;
+  SVOO_CUDA(launch_ear_select(c_logits, scores, q_offsets, k_offsets, map_out, BH, QC, KC, top_p, preserve_host,
+                              budget_preserve_host, (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_sparse_attn_ear(const void* q, const void* k_ext, const void* v_ext, const uint8_t* map,
+                              const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
+                              int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx, float* lse,
+                              void* ear_workspace, int64_t ear_workspace_bytes, void* stream) {
+  if (!q || !k_ext || !v_ext || !map || !q_offsets || !k_offsets || !out || !ear_workspace) return SVOO_ERR_NULL;
+  SVOO_TRY(check_ear(BH, S, D, QC, KC));
+  if ((BH * S + BH * KC) > 2147483647LL) return SVOO_ERR_SHAPE;
+  if (!aligned16(q) || !aligned16(k_ext) || !aligned16(v_ext) || !aligned16(out) || !aligned16(ear_workspace))
+    return SVOO_ERR_ALIGN;
+  const EarWorkspace w = ear_layout(BH, S, QC, KC);
+  if (ear_workspace_bytes < w.total) return SVOO_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  int2* runs = ws_at<int2>(ear_workspace, w.runs);
+  int32_t* nruns = ws_at<int32_t>(ear_workspace, w.nruns);
+  int32_t* ltok = ws_at<int32_t>(ear_workspace, w.ltok);
+  int4* qtiles = ws_at<int4>(ear_workspace, w.qtiles);
+  int32_t* nqtiles = ws_at<int32_t>(ear_workspace, w.nqtiles);
+  int32_t* status = ws_at<int32_t>(ear_workspace, w.status);
+  SVOO_CUDA(launch_ear_build_runs(map, k_offsets, runs, nruns, ltok, BH, S, QC, KC, ear_max_runs(KC), st));
+  SVOO_CUDA(launch_build_qtiles(q_offsets, qtiles, nqtiles, BH, S, QC, 256, st));
+  SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));
+  SVOO_CUDA(launch_sparse_attn_tc(q, k_ext, v_ext, out, out_row_idx, qtiles, nqtiles, runs, nruns, status, BH, S, QC, KC,
+                                  sm_scale, nullptr, nullptr, 0, 0, 0, lse, st, ltok, k_offsets, ear_max_runs(KC)));
+  return SVOO_OK;
 }
 
 int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* offset_out) {

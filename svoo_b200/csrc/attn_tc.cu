@@ -36,9 +36,18 @@ constexpr int kBN = 128;                 // key rows per step
 constexpr int kTile = 128 * kRowBytes;   // 32 KB: one [128 x 128] bf16 tile = two 16 KB boxes
 constexpr int kBox = 128 * 128;          // 16 KB: 128 rows x 64 columns
 constexpr int kSmemTiles = 6 * kTile;    // Q0 Q1 | K0 K1 | V0 V1
-constexpr int kMaxRunsSmem = SVOO_MAX_ATTN_CLUSTERS / 2 + 2;
-constexpr int kRunTableBytes = (kMaxRunsSmem * 8 + 255) / 256 * 256;
-constexpr int kSmemBytes = kSmemTiles + 256 + kRunTableBytes + 1024;   // + barriers, run table, slack
+// Run table in shared memory.  Plain mode: runs of selected clusters alternate with gaps, at most
+// KC / 2 + 1 of them.  EAR mode (one virtual key per pruned cluster appended, see ear.cu): token runs
+// and centroid runs together can reach KC + 1; its bias table holds one value per key of the tiles
+// that contain centroid keys.
+template <bool kEar>
+struct AttnSmem {
+  static constexpr int kMaxRuns = kEar ? SVOO_MAX_ATTN_CLUSTERS + 6 : SVOO_MAX_ATTN_CLUSTERS / 2 + 2;
+  static constexpr int kRunTableBytes = (kMaxRuns * 8 + 255) / 256 * 256;
+  static constexpr int kBiasFloats = kEar ? SVOO_MAX_ATTN_CLUSTERS + 128 + 6 : 0;
+  static constexpr int kBiasBytes = (kBiasFloats * 4 + 255) / 256 * 256;
+  static constexpr int kBytes = kSmemTiles + 256 + kRunTableBytes + kBiasBytes + 1024;   // + barriers, tables, slack
+};
 constexpr int kKWarp = 8, kVWarp = 9, kMmaWarp = 10;     // after the 8 softmax warps
 // 12 warps; 65536 / (12 * 32) leaves 168 registers per thread at launch.
 constexpr int kThreads = 12 * 32;       // warp 11 only completes the service warpgroup (register hand-over below)
@@ -156,11 +165,17 @@ __device__ __forceinline__ void tma_gather_tile(uint32_t dst, const CUtensorMap*
   }
 }
 
+// kEar: the key list of a query cluster ends with centroid rows (virtual keys of the pruned clusters,
+// read from the rows that follow the tokens of all heads in K and V); key position >= ltok carries the
+// additive bias log(|K_j| + 1e-6) of its cluster (svoo/co_clustering.py:1873-1876).
+template <bool kEar>
 __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     const __grid_constant__ AttnMaps maps, const __grid_constant__ OutPeers peers, bf16* __restrict__ out,
     const int32_t* __restrict__ out_row_idx, const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles,
     const int2* __restrict__ runs, const int32_t* __restrict__ nruns, int S, int QC, int max_tiles, int max_runs,
-    float scale_log2, int32_t* __restrict__ status, float* __restrict__ lse) {
+    float scale_log2, int32_t* __restrict__ status, float* __restrict__ lse, const int32_t* __restrict__ ltok,
+    const int32_t* __restrict__ k_offsets, int KC, int rows_total) {
+  constexpr int kMaxRunsSmem = AttnSmem<kEar>::kMaxRuns;
   extern __shared__ unsigned char smem_raw[];
   const int bh = blockIdx.y;
   if ((int)blockIdx.x >= nqtiles[bh]) return;
@@ -177,6 +192,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + kSmemTiles + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kSmemTiles + NUM_BARS * 8 + 8);
   int2* runs_s = reinterpret_cast<int2*>(gen_base + kSmemTiles + 256);
+  float* bias_s = reinterpret_cast<float*>(gen_base + kSmemTiles + 256 + AttnSmem<kEar>::kRunTableBytes);
   auto bar = [&](int i) { return bars + 8u * i; };
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -200,6 +216,30 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   const uint32_t tmem = *tmem_slot;
   const int L = runs_s[nr].y;                      // selected key rows in total
   const int T = (L + kBN - 1) / kBN;               // packed key tiles
+  // EAR: keys [l_tok, L) are centroid rows; bias_s[v - bias0] (bias0 = first key of the first tile that
+  // holds one) is their logit bias divided by the softmax scale, so that adding it to the raw score
+  // leaves the rest of the softmax unchanged; zero for the token keys of that tile.
+  int l_tok = L, bias0 = L;
+  if (kEar) {
+    l_tok = min(ltok[(int64_t)bh * QC + qi], L);
+    bias0 = l_tok / kBN * kBN;
+    const int cen0 = ((int)gridDim.y - bh) * S + bh * KC;          // first centroid row of this head, as in the run list
+    const int32_t* ko = k_offsets + (int64_t)bh * (KC + 1);
+    for (int v = bias0 + tid; v < L; v += kThreads) {
+      float b = 0.f;
+      if (v >= l_tok) {
+        int lo = 0, hi = nr - 1;                                     // last run whose first key is <= v
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (runs_s[mid].y <= v) lo = mid; else hi = mid - 1;
+        }
+        const int j = min(max(runs_s[lo].x - cen0 + (v - runs_s[lo].y), 0), KC - 1);
+        b = __log2f((float)(ko[j + 1] - ko[j]) + 1e-6f) / scale_log2;
+      }
+      bias_s[v - bias0] = b;
+    }
+    __syncthreads();
+  }
 
   // Registers move from the service warpgroup (TMA producers, MMA issuer, one idle warp) to the
   // two softmax warpgroups: 12 warps leave 168 registers per thread at launch; the softmax keeps
@@ -210,7 +250,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     // ---------------------------------------------------------------- TMA producers (K + Q, V)
     if (lane == 0 && T > 0) {
       const int is_v = warp == kVWarp;
-      const int rows_total = (int)gridDim.y * S;
       if (!is_v) {
         mbar_expect_tx(bar(Q_FULL), nq * kTile);
         for (int w = 0; w < nq; ++w)
@@ -356,6 +395,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(S_FREE + w));
+        if (kEar && (j + 1) * kBN > l_tok) {                      // a tile with centroid keys
+          const float* bj = bias_s + (j * kBN - bias0);
+#pragma unroll
+          for (int i = 0; i < 128; ++i) sc[i] = __float_as_uint(__uint_as_float(sc[i]) + bj[i]);
+        }
         if (valid < kBN) {                                        // last tile only: columns past the last key
 #pragma unroll
           for (int i = 0; i < 128; ++i)
@@ -484,7 +528,8 @@ cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, v
                                   const int4* qtiles, const int32_t* nqtiles, const int2* runs, const int32_t* nruns,
                                   int32_t* status, int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale,
                                   void* const* peer_dst, const int32_t* my_heads, int world, int64_t n_loc, int H,
-                                  float* lse, cudaStream_t st) {
+                                  float* lse, cudaStream_t st, const int32_t* ear_ltok, const int32_t* ear_k_offsets,
+                                  int ear_max_runs) {
   // a build whose register hand-over does not add up (the spill-check build) must never launch:
   // its softmax warps would wait for registers that nobody frees
   if (128 * tc::kRegsService + 256 * tc::kRegsSoftmax > 168 * tc::kThreads) return cudaErrorInvalidConfiguration;
@@ -495,18 +540,32 @@ cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, v
     peers.n_loc = (int)n_loc;
     peers.H = H;
   }
+  // EAR: K and V hold the centroid rows of all heads after the token rows of all heads
+  const bool ear = ear_ltok != nullptr;
+  const int64_t kv_rows = BH * S + (ear ? BH * KC : 0);
   alignas(64) tc::AttnMaps maps;
   bool ok = tc::make_row_tensor_map(&maps.q, q, BH * S, 128);
   for (int i = 0; i < tc::kBoxHeights && ok; ++i)
-    ok = tc::make_row_tensor_map(&maps.k[i], k, BH * S, 1 << i) && tc::make_row_tensor_map(&maps.v[i], v, BH * S, 1 << i);
+    ok = tc::make_row_tensor_map(&maps.k[i], k, kv_rows, 1 << i) && tc::make_row_tensor_map(&maps.v[i], v, kv_rows, 1 << i);
   if (!ok) return cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(tc::sparse_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       tc::kSmemBytes);
-  if (e != cudaSuccess) return e;
   dim3 grid((unsigned)max_qtiles(S, QC), (unsigned)BH);
-  tc::sparse_attn_tc_kernel<<<grid, tc::kThreads, tc::kSmemBytes, st>>>(
-      maps, peers, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), max_runs(KC),
-      sm_scale * 1.4426950408889634f, status, peer_dst ? nullptr : lse);
+  const float scale_log2 = sm_scale * 1.4426950408889634f;
+  cudaError_t e;
+  if (ear) {
+    e = cudaFuncSetAttribute(tc::sparse_attn_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             tc::AttnSmem<true>::kBytes);
+    if (e != cudaSuccess) return e;
+    tc::sparse_attn_tc_kernel<true><<<grid, tc::kThreads, tc::AttnSmem<true>::kBytes, st>>>(
+        maps, peers, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), ear_max_runs,
+        scale_log2, status, peer_dst ? nullptr : lse, ear_ltok, ear_k_offsets, (int)KC, (int)kv_rows);
+  } else {
+    e = cudaFuncSetAttribute(tc::sparse_attn_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             tc::AttnSmem<false>::kBytes);
+    if (e != cudaSuccess) return e;
+    tc::sparse_attn_tc_kernel<false><<<grid, tc::kThreads, tc::AttnSmem<false>::kBytes, st>>>(
+        maps, peers, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), max_runs(KC),
+        scale_log2, status, peer_dst ? nullptr : lse, nullptr, nullptr, (int)KC, (int)kv_rows);
+  }
   count_launches(1);
   return cudaGetLastError();
 }

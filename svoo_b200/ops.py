@@ -358,3 +358,112 @@ def layer(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_init_idx: torch.T
                               D ** -0.5 if sm_scale is None else float(sm_scale), int(text), int(prompt), out.data_ptr(),
                               scratch.data_ptr(), scratch.numel(), ws.data_ptr(), ws.numel(), _stream()), "layer")
     return out
+
+
+# ----------------------------------------------------------------------------------------------
+# Error-aware routing (EAR)
+# ----------------------------------------------------------------------------------------------
+_ear_workspaces = {}
+
+
+def ear_workspace(device: torch.device, BH: int, N: int, QC: int, KC: int) -> torch.Tensor:
+    """Cached scratch of the EAR calls (one per device and stream); it carries the value statistics
+    from ear_value_centroids to ear_block_scores."""
+    need, _ = _ear_sizes(BH, N, QC, KC)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    ws = _ear_workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        _ear_workspaces[key] = ws
+    return ws
+
+
+def _ear_sizes(BH, N, QC, KC):
+    need, status = ctypes.c_int64(0), ctypes.c_int64(0)
+    check(LIB.svoo_b200_ear_workspace_bytes(BH, N, QC, KC, ctypes.byref(need), ctypes.byref(status)), "ear_workspace_bytes")
+    return need.value, status.value
+
+
+def ear_value_centroids(v_perm: torch.Tensor, k_offsets: torch.Tensor, QC: int, out: Optional[torch.Tensor] = None):
+    """Mean value row of every key cluster, bf16 [BH, KC, 128] (written into `out` when given, e.g. the
+    centroid rows of an extended V tensor); the per-token statistics the block scores need stay in
+    the EAR scratch of this device and stream."""
+    _need_cuda(v_perm, k_offsets)
+    BH, N, D = _tokens(v_perm)
+    KC = k_offsets.shape[1] - 1
+    vc = torch.empty(BH, KC, HEAD_DIM, dtype=torch.bfloat16, device=v_perm.device) if out is None else out
+    ws = ear_workspace(v_perm.device, BH, N, QC, KC)
+    check(LIB.svoo_b200_ear_value_centroids(v_perm.data_ptr(), k_offsets.data_ptr(), BH, N, D, QC, KC, vc.data_ptr(),
+                                            ws.data_ptr(), ws.numel(), _stream()), "ear_value_centroids")
+    return vc
+
+
+def ear_block_scores(qcentroids: torch.Tensor, kcentroids: torch.Tensor, k_perm: torch.Tensor, q_offsets: torch.Tensor,
+                     k_offsets: torch.Tensor, gamma: float):
+    """(centroid logits, log-efficiency scores), fp32 [BH, QC, KC]; after ear_value_centroids on this
+    device and stream."""
+    _need_cuda(qcentroids, kcentroids, k_perm, q_offsets, k_offsets)
+    BH, N, D = _tokens(k_perm)
+    QC, KC = q_offsets.shape[1] - 1, k_offsets.shape[1] - 1
+    if qcentroids.dtype != torch.bfloat16 or kcentroids.dtype != torch.bfloat16:
+        raise ValueError("ear_block_scores needs bf16 centroids")
+    clog = torch.empty(BH, QC, KC, dtype=torch.float32, device=k_perm.device)
+    scores = torch.empty_like(clog)
+    ws = ear_workspace(k_perm.device, BH, N, QC, KC)
+    check(LIB.svoo_b200_ear_block_scores(qcentroids.contiguous().data_ptr(), kcentroids.contiguous().data_ptr(),
+                                         k_perm.data_ptr(), q_offsets.data_ptr(), k_offsets.data_ptr(), BH, N, D, QC, KC,
+                                         float(gamma), clog.data_ptr(), scores.data_ptr(), ws.data_ptr(), ws.numel(),
+                                         _stream()), "ear_block_scores")
+    return clog, scores
+
+
+def ear_select_blocks(c_logits: torch.Tensor, scores: torch.Tensor, q_offsets: torch.Tensor, k_offsets: torch.Tensor,
+                      top_p: float, preserve: Sequence[int], budget_preserve: Sequence[int]) -> torch.Tensor:
+    """uint8 [BH, QC, KC]; preserve / budget_preserve are per-head python ints (numbers of key clusters)."""
+    _need_cuda(c_logits, scores, q_offsets, k_offsets)
+    BH, QC, KC = c_logits.shape
+    if len(preserve) != BH or len(budget_preserve) != BH:
+        raise ValueError("preserve and budget_preserve need one entry per head")
+    if c_logits.dtype != torch.float32 or scores.dtype != torch.float32 or tuple(scores.shape) != (BH, QC, KC):
+        raise ValueError("c_logits and scores must be fp32 [BH, QC, KC]")
+    out = torch.empty(BH, QC, KC, dtype=torch.uint8, device=c_logits.device)
+    arr = ctypes.c_int32 * BH
+    check(LIB.svoo_b200_ear_select_blocks(c_logits.contiguous().data_ptr(), scores.contiguous().data_ptr(),
+                                          q_offsets.data_ptr(), k_offsets.data_ptr(), BH, QC, KC, float(top_p),
+                                          arr(*[int(v) for v in preserve]), arr(*[int(v) for v in budget_preserve]),
+                                          out.data_ptr(), _stream()), "ear_select_blocks")
+    return out
+
+
+def sparse_attn_ear(q: torch.Tensor, k_ext: torch.Tensor, v_ext: torch.Tensor, block_map_u8: torch.Tensor,
+                    q_offsets: torch.Tensor, k_offsets: torch.Tensor, sm_scale: Optional[float] = None,
+                    out_row_idx: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                    return_lse: bool = False):
+    """EAR forward: q [BH,S,128] in cluster order; k_ext, v_ext [BH*S + BH*KC, 128] = the cluster-ordered
+    rows of all heads followed by the key / value centroid rows of all heads.  Output, out_row_idx and
+    the log2-sum-exp as in sparse_attn."""
+    _need_cuda(q, k_ext, v_ext, block_map_u8, q_offsets, k_offsets)
+    BH, S, D = _tokens(q)
+    QC, KC = q_offsets.shape[1] - 1, k_offsets.shape[1] - 1
+    if tuple(block_map_u8.shape) != (BH, QC, KC) or block_map_u8.dtype not in (torch.uint8, torch.bool):
+        raise ValueError("block map must be uint8/bool [BH, QC, KC]")
+    for t in (k_ext, v_ext):
+        if tuple(t.shape) != (BH * S + BH * KC, HEAD_DIM) or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError("k_ext and v_ext must be contiguous bf16 [BH*S + BH*KC, 128]")
+    ws = ear_workspace(q.device, BH, S, QC, KC)
+    y = torch.empty_like(q) if out is None else out
+    lse = torch.empty(BH, S, dtype=torch.float32, device=q.device) if return_lse else None
+    check(LIB.svoo_b200_sparse_attn_ear(q.data_ptr(), k_ext.data_ptr(), v_ext.data_ptr(), block_map_u8.data_ptr(),
+                                        q_offsets.data_ptr(), k_offsets.data_ptr(), BH, S, D, QC, KC,
+                                        D ** -0.5 if sm_scale is None else float(sm_scale), y.data_ptr(),
+                                        0 if out_row_idx is None else out_row_idx.data_ptr(),
+                                        0 if lse is None else lse.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+          "sparse_attn_ear")
+    return (y, lse) if return_lse else y
+
+
+def ear_attention_status(device: torch.device, BH: int, S: int, QC: int, KC: int) -> int:
+    """Status word of the last sparse_attn_ear on this device and stream (0 = no bounded wait expired)."""
+    _, off = _ear_sizes(BH, S, QC, KC)
+    ws = ear_workspace(device, BH, S, QC, KC)
+    return int(ws[off:off + 4].view(torch.int32).item())

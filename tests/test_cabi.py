@@ -77,6 +77,15 @@ def test_host_side_argument_checks(lib):
     assert L.svoo_b200_permute(p, p, 200, 1 << 24, 128, 1 << 24, 1 << 24, p, None) == -2
     assert L.svoo_b200_sort_labels_static(p, 200, 1 << 24, 4, p, p, None) == -2
     assert L.svoo_b200_euclid_assign(p, p, 1, 4, 128, 2000, p, p, 1 << 30, None) == -6
+    # error-aware routing entries: argument checks run before any device work
+    assert L.svoo_b200_ear_workspace_bytes(2, 4096, 32, 128, None, None) == -1
+    assert L.svoo_b200_ear_value_centroids(None, p, 1, 64, 128, 4, 8, p, p, 1 << 30, None) == -1
+    assert L.svoo_b200_ear_value_centroids(p, p, 1, 64, 64, 4, 8, p, p, 1 << 30, None) == -3
+    assert L.svoo_b200_ear_block_scores(p, p, p, p, p, 1, 64, 128, 4, 2000, 1.0, p, p, p, 1 << 30, None) == -6
+    assert L.svoo_b200_ear_block_scores(p, p, p, p, p, 1, 64, 128, 4, 8, 1.0, p, p, p, 16, None) == -4
+    assert L.svoo_b200_ear_select_blocks(p, p, p, p, 1, 4, 8, 0.9, None, None, p, None) == -1
+    assert L.svoo_b200_sparse_attn_ear(p, p, p, p, p, p, 1, 64, 128, 4, 8, 0.1, None, None, None, p, 1 << 30, None) == -1
+    assert L.svoo_b200_sparse_attn_ear(p, p, p, p, p, p, 1, 64, 128, 4, 8, 0.1, p, None, None, p, 16, None) == -4
     assert L.svoo_b200_append_text_blocks(p, p, p, p, p, 1, 4, 2, 2, 4, 5, p, p, p, p, p, None) == -2
     out = ctypes.c_int64(0)
     assert L.svoo_b200_layer_scratch_bytes(2, 1000, 8, 16, 64, ctypes.byref(out)) == 0 and out.value > 3 * 2 * 1000 * 256
@@ -134,4 +143,4 @@ def test_header_is_plain_c_and_links(tmp_path):
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0, run.stderr
     version, rc, nbytes = run.stdout.split()
-    assert int(version) == 101 and int(rc) == 0 and int(nbytes) > 0
+    assert int(version) == 102 and int(rc) == 0 and int(nbytes) > 0

@@ -1,0 +1,175 @@
+"""The error-aware routing (EAR) kernels through the C ABI against the CPU oracle.  Needs a B200.
+
+Bars: centroid logits and the block selection bit-exact (from identical inputs); value centroids
+within one bf16 rounding; block scores <= 2e-2 (they are logs of sums whose order differs);
+attention max-abs-err <= 2e-2 and cosine >= 0.999 in bf16, log2-sum-exp <= 5e-3.
+"""
+import dataclasses
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ear_oracle as E
+from oracle import svoo_oracle as O
+from svoo_b200 import synth
+from tests import golden_util as gu
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda:0")
+
+
+def cosine(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a @ b) / (a.norm() * b.norm() + 1e-30))
+
+
+def clustered_case(dev, H, grid, num_q, num_k, seed, empty_k=()):
+    """Seeded bf16 q, k, v, one co-clustering on the GPU, everything permuted on the CPU by the
+    stable sort of those labels."""
+    from svoo_b200 import ops
+    cfg = synth.LayerConfig(f"ear-{seed}", seed, H, grid, torch.bfloat16, num_q, num_k, 2, (0.1, 0.3), 1, True)
+    q, k, v = synth.make_qkv(cfg)
+    qi, ki = synth.init_indices(cfg)
+    c = ops.cocluster(q[0].to(dev), k[0].to(dev), qi.to(dev), ki.to(dev), 2)
+    kl = c.klabels.cpu().long()
+    for e in empty_k:                                    # force empty key clusters
+        kl[kl == e] = (e + 1) % num_k
+    ql = c.qlabels.cpu().long()
+    q_idx, q_off = O.sort_labels(ql, num_q)
+    k_idx, k_off = O.sort_labels(kl, num_k)
+    qs, ks = q_off[:, 1:] - q_off[:, :-1], k_off[:, 1:] - k_off[:, :-1]
+    t = dict(cfg=cfg, q=q[0], k=k[0], v=v[0], ql=ql, kl=kl, q_idx=q_idx, k_idx=k_idx, q_off=q_off, k_off=k_off, qs=qs, ks=ks,
+             qc=c.qcentroids.cpu(), kc=c.kcentroids.cpu(), qp=O.permute(q[0], q_idx), kp=O.permute(k[0], k_idx),
+             vp=O.permute(v[0], k_idx))
+    return t
+
+
+def gpu_scores(dev, t, gamma):
+    from svoo_b200 import ops
+    QC = t["qc"].shape[1]
+    vc = ops.ear_value_centroids(t["vp"].to(dev), t["k_off"].int().to(dev), QC)
+    clog, sc = ops.ear_block_scores(t["qc"].to(dev), t["kc"].to(dev), t["kp"].to(dev), t["q_off"].int().to(dev),
+                                    t["k_off"].int().to(dev), gamma)
+    return vc, clog, sc
+
+
+@pytest.mark.parametrize("H,grid,num_q,num_k,empty", [(3, (4, 16, 32), 20, 70, (0, 5)), (2, (8, 32, 60), 100, 500, ()),
+                                                      (2, (3, 16, 20), 100, 500, ()), (1, (2, 16, 16), 5, 9, ())])
+def test_value_centroids_logits_scores(dev, H, grid, num_q, num_k, empty):
+    t = clustered_case(dev, H, grid, num_q, num_k, seed=31 + num_k, empty_k=empty)
+    vc, clog, sc = gpu_scores(dev, t, 1.0)
+    vc_ref = E.value_centroids(t["v"], t["kl"], t["ks"], num_k)
+    assert (vc.cpu().float() - vc_ref.float()).abs().max() <= 2e-2          # one bf16 rounding of a value <= 4
+    assert (vc.cpu() == vc_ref).float().mean() >= 0.99
+    clog_ref = E.centroid_logits(t["qc"], t["kc"])
+    assert np.array_equal(clog.cpu().numpy(), clog_ref)
+    vn, cvd, vc_sq = E.value_stats(t["vp"], vc.cpu(), t["k_off"])
+    sc_ref = E.error_scores(t["qc"], t["kp"], t["k_off"], t["qs"], t["ks"], clog_ref, vn, cvd, vc_sq, 1.0)
+    err = (sc.cpu() - sc_ref).abs()
+    assert torch.isfinite(sc).all()
+    # a cluster of one or two keys equals its centroid up to rounding: its error is a difference of
+    # nearly equal sums, i.e. rounding noise on both sides; the bound is for clusters of >= 8 keys
+    big = (t["ks"] >= 8)[:, None, :].expand_as(err)
+    if big.any():
+        assert err[big].max() <= 2e-2, float(err[big].max())
+        assert err[big].mean() <= 1e-3
+
+
+@pytest.mark.parametrize("H,grid,num_q,num_k,top_p,ratio", [
+    (3, (4, 16, 32), 20, 70, 0.9, 0.0), (3, (4, 16, 32), 20, 70, 0.6, 0.1), (3, (4, 16, 32), 20, 70, 0.8, [0.05, 0.0, 0.3]),
+    (2, (3, 16, 20), 100, 500, 0.9, [0.07, 0.2]), (1, (4, 16, 32), 64, 1024, 0.5, 0.05), (1, (2, 16, 16), 5, 9, 0.4, 0.2)])
+def test_selection_bit_exact(dev, H, grid, num_q, num_k, top_p, ratio):
+    """The CUDA selection from the CUDA scores equals the oracle's selection from the same scores."""
+    from svoo_b200 import ops
+    t = clustered_case(dev, H, grid, num_q, num_k, seed=77 + num_k, empty_k=(1,))
+    _, clog, sc = gpu_scores(dev, t, 1.0)
+    pres, bud = E.ratio_lengths(num_k, H, ratio)
+    got = ops.ear_select_blocks(clog, sc, t["q_off"].int().to(dev), t["k_off"].int().to(dev), top_p, pres, bud)
+    ref = E.select_blocks(clog.cpu().numpy(), sc.cpu().numpy(), t["qs"], t["ks"], top_p, ratio, True)
+    assert torch.equal(got.cpu().bool(), ref)
+    dens = float(ref.float().mean())
+    assert 0.0 < dens < 1.0 or top_p >= 0.9
+
+
+def _ext(dev, perm, cen):
+    """[BH*S + BH*KC, 128]: token rows of all heads, then centroid rows of all heads."""
+    return torch.cat([perm.reshape(-1, 128), cen.reshape(-1, 128)], 0).contiguous().to(dev)
+
+
+@pytest.mark.parametrize("H,grid,num_q,num_k,top_p,ratio,empty", [
+    (3, (4, 16, 32), 20, 70, 0.5, 0.05, (0, 5)), (2, (3, 16, 20), 100, 500, 0.6, [0.07, 0.2], ()),
+    (1, (2, 16, 16), 5, 9, 0.3, 0.0, ()), (2, (5, 16, 24), 7, 300, 0.4, 0.02, (3,))])
+def test_ear_attention_matches_oracle(dev, H, grid, num_q, num_k, top_p, ratio, empty):
+    from svoo_b200 import ops
+    t = clustered_case(dev, H, grid, num_q, num_k, seed=5 + num_k, empty_k=empty)
+    vc, clog, sc = gpu_scores(dev, t, 1.0)
+    pres, bud = E.ratio_lengths(num_k, H, ratio)
+    m = ops.ear_select_blocks(clog, sc, t["q_off"].int().to(dev), t["k_off"].int().to(dev), top_p, pres, bud)
+    S = t["qp"].shape[1]
+    k_ext, v_ext = _ext(dev, t["kp"], t["kc"]), _ext(dev, t["vp"], vc.cpu())
+    out, lse2 = ops.sparse_attn_ear(t["qp"].to(dev), k_ext, v_ext, m, t["q_off"].int().to(dev), t["k_off"].int().to(dev),
+                                    out_row_idx=t["q_idx"].int().to(dev), return_lse=True)
+    assert ops.ear_attention_status(dev, H, S, num_q, num_k) == 0
+    ref_p, lse_p = E.compensated_attention(t["qp"], t["kp"], t["vp"], t["kc"], vc.cpu(), m.cpu().bool(), t["qs"], t["ks"])
+    ref = O.inverse_permute(ref_p, t["q_idx"])
+    lse_ref = torch.empty_like(lse_p)
+    lse_ref.scatter_(1, t["q_idx"].long(), lse_p)
+    assert (out.cpu().float() - ref.float()).abs().max() <= 2e-2
+    assert cosine(out.cpu(), ref) >= 0.999
+    assert (lse2.cpu() - lse_ref / math.log(2.0)).abs().max() <= 5e-3
+    # and the compensation matters: without it the result is further from the oracle
+    plain = ops.sparse_attn(t["qp"].to(dev), t["kp"].to(dev), t["vp"].to(dev), m, t["q_off"].int().to(dev),
+                            t["k_off"].int().to(dev), out_row_idx=t["q_idx"].int().to(dev))
+    assert (plain.cpu().float() - ref.float()).abs().max() > (out.cpu().float() - ref.float()).abs().max()
+
+
+def test_ear_attention_full_map_equals_plain(dev):
+    """Every cluster selected: no centroid key, the EAR kernel gives the plain kernel's bits."""
+    from svoo_b200 import ops
+    t = clustered_case(dev, 2, (4, 16, 32), 12, 40, seed=3)
+    H, S = 2, t["qp"].shape[1]
+    m = torch.ones(H, 12, 40, dtype=torch.uint8, device=dev)
+    vc = E.value_centroids(t["v"], t["kl"], t["ks"], 40)
+    a = ops.sparse_attn_ear(t["qp"].to(dev), _ext(dev, t["kp"], t["kc"]), _ext(dev, t["vp"], vc), m,
+                            t["q_off"].int().to(dev), t["k_off"].int().to(dev))
+    b = ops.sparse_attn(t["qp"].to(dev), t["kp"].to(dev), t["vp"].to(dev), m, t["q_off"].int().to(dev), t["k_off"].int().to(dev))
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("name", list(gu.EAR_CASES))
+def test_reference_fixture(dev, name):
+    """The recorded run of the reference (labels, centroids, maps, compensated output).  The fp32 case
+    is computed in bf16 here, so its bounds are the loose ones."""
+    from svoo_b200 import ops
+    cfg, settings = gu.EAR_CASES[name]
+    z = gu.load(name)
+    q, k, v = synth.make_qkv(cfg)
+    t = gu.ear_inputs(cfg, z, q, k, v)
+    b16 = lambda x: x.to(torch.bfloat16)
+    H, QC, KC = cfg.heads, cfg.num_q, cfg.num_k
+    qo, ko = t["q_off"].int().to(dev), t["k_off"].int().to(dev)
+    vc = ops.ear_value_centroids(b16(t["vp"]).to(dev), ko, QC)
+    assert (vc.cpu().float() - torch.from_numpy(z["vcentroids"])).abs().max() <= 3e-2
+    for n, (top_p, gamma, ratio) in enumerate(settings):
+        clog, sc = ops.ear_block_scores(b16(t["qc"]).to(dev), b16(t["kc"]).to(dev), b16(t["kp"]).to(dev), qo, ko, gamma)
+        assert (sc.cpu() - torch.from_numpy(z[f"scores_{n}"])).abs().max() <= (3e-2 if cfg.dtype == torch.bfloat16 else 0.15)
+        pres, bud = E.ratio_lengths(KC, H, ratio)
+        m = ops.ear_select_blocks(clog, sc, qo, ko, top_p, pres, bud)
+        agree = float((m.cpu().bool().numpy() == gu.unpack_ear_map(z, n)).mean())
+        assert agree >= (0.97 if cfg.dtype == torch.bfloat16 else 0.9), (name, n, agree)
+    ref_map = torch.from_numpy(gu.unpack_ear_map(z, len(settings) - 1)).to(torch.uint8).to(dev)
+    k_ext = torch.cat([b16(t["kp"]).reshape(-1, 128), b16(t["kc"]).reshape(-1, 128)]).contiguous().to(dev)
+    v_ext = torch.cat([b16(t["vp"]).reshape(-1, 128), b16(t["vc"]).reshape(-1, 128)]).contiguous().to(dev)
+    out, lse2 = ops.sparse_attn_ear(b16(t["qp"]).to(dev), k_ext, v_ext, ref_map, qo, ko, out_row_idx=t["q_idx"].int().to(dev),
+                                    return_lse=True)
+    step = int(z["rows_kept"][0])
+    ref_rows = torch.from_numpy(z["out_rows"])
+    assert (out.cpu()[:, ::step].float() - ref_rows).abs().max() <= 3e-2
+    assert cosine(out.cpu()[:, ::step], ref_rows) >= 0.999
+    assert (lse2.cpu()[:, ::step] * math.log(2.0) - torch.from_numpy(z["lse_rows"])).abs().max() <= 3e-2
