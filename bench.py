@@ -131,9 +131,41 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------
 # CPU arm (the oracle port of the reference's algorithm, on the host cores)
 # ------------------------------------------------------------------------------------------
-def cpu_layer_sample(cfg, head: int):
+def centroid_key_flops(block_map, q_off):
+    """EAR: 4 * 128 flops per (query row, pruned key cluster) pair -- one virtual key each."""
+    qs = (q_off[:, 1:] - q_off[:, :-1]).double()
+    pruned = (block_map.shape[-1] - block_map.double().sum(-1))
+    return float((qs * pruned).sum()) * 4.0 * 128.0
+
+
+def cpu_ear_sample(cfg, head: int):
+    """One head of the workload through the CPU restatement of the reference's EAR path."""
+    from oracle import ear_oracle as E
+    from oracle import svoo_oracle as O
+    one = dataclasses.replace(cfg, heads=1)
+    q, k, v = synth.make_qkv(cfg, heads=[head])
+    qi, ki = synth.init_indices(cfg)
+    d = synth.head_densities(cfg)[head]
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    ql, qc, qs, kl, kc, ks = O.co_cluster_tokens(q[0], k[0], qi[head:head + 1], ki[head:head + 1], cfg.iters)
+    q_idx, q_off = O.sort_labels(ql, cfg.num_q)
+    k_idx, k_off = O.sort_labels(kl, cfg.num_k)
+    qp, kp, vp = O.permute(q[0], q_idx), O.permute(k[0], k_idx), O.permute(v[0], k_idx)
+    vc = E.value_centroids(v[0], kl, ks, cfg.num_k)
+    m = E.identify_dynamic_map_estimated(kp, vp, qs, ks, qc, kc, vc, cfg.top_p, 1.0, [d])
+    out_p, _ = E.compensated_attention(qp, kp, vp, kc, vc, m, qs, ks)
+    O.inverse_permute(out_p, q_idx)
+    dt = time.perf_counter() - t0
+    rho = O.realised_density(m[None], qs[None], ks[None])[0].tolist()
+    return dt, cluster_flops_reference(one, 1) + attention_flops(rho, cfg.n_tokens) + centroid_key_flops(m, q_off)
+
+
+def cpu_layer_sample(cfg, head: int, pattern: str = "svoo"):
     """One head of the workload through the CPU restatement of the reference path.
     Returns (seconds, reference-algorithm flops of that head)."""
+    if pattern == "ear":
+        return cpu_ear_sample(cfg, head)
     from oracle import svoo_oracle as O
     one = dataclasses.replace(cfg, heads=1)
     q, k, v = synth.make_qkv(cfg, heads=[head])
@@ -160,10 +192,10 @@ def run_reference_arm(args, cfg):
         return
     cores = os.cpu_count() or 1
     for _ in range(args.warmup):
-        cpu_layer_sample(cfg, 0)
+        cpu_layer_sample(cfg, 0, args.pattern)
     tot_t, tot_f = 0.0, 0.0
     for s in range(args.steps):
-        dt, fl = cpu_layer_sample(cfg, s % cfg.heads)
+        dt, fl = cpu_layer_sample(cfg, s % cfg.heads, args.pattern)
         tot_t += dt
         tot_f += fl
     val = tot_f / tot_t / 1e12
@@ -172,8 +204,8 @@ def run_reference_arm(args, cfg):
         "impl": "reference", "metric": "sparse_attn_layer_effective_tflops", "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot_t / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg.name, "heads": cfg.heads, "tokens": cfg.n_tokens, "q_clusters": cfg.num_q,
-                   "k_clusters": cfg.num_k, "kmeans_iters": cfg.iters, "sample": sample},
+        "config": {"workload": cfg.name + ("-ear" if args.pattern == "ear" else ""), "heads": cfg.heads, "tokens": cfg.n_tokens,
+                   "q_clusters": cfg.num_q, "k_clusters": cfg.num_k, "kmeans_iters": cfg.iters, "sample": sample},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -212,6 +244,11 @@ def run_gpu_arm(args, cfg):
     d_mine = [dens[h] for h in mine]
     kw = dict(num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k, kmeans_iters=cfg.iters, top_p=cfg.top_p,
               context_length=cfg.text_tokens)
+    ear = args.pattern == "ear"
+    if ear:
+        if world > 1 or cfg.text_tokens:
+            raise SystemExit("--pattern ear: video-only self attention on one GPU, as in the reference")
+        kw["ear_gamma"] = 1.0
 
     q_d, k_d, v_d = q_h.to(dev), k_h.to(dev), v_h.to(dev)
     if world > 1:
@@ -315,8 +352,9 @@ def run_gpu_arm(args, cfg):
 
     st = state["st"]
     rho = realised_density(st.block_map, st.q_offsets, st.k_offsets)
-    flops = torch.tensor([cluster_flops_reference(cfg, len(mine)) + attention_flops(rho, N),
-                          attention_flops(rho, N)], dtype=torch.float64, device=dev)
+    extra = centroid_key_flops(st.block_map, st.q_offsets) if ear else 0.0
+    flops = torch.tensor([cluster_flops_reference(cfg, len(mine)) + attention_flops(rho, N) + extra,
+                          attention_flops(rho, N) + extra], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(flops)
     flops_total, flops_attn_all = flops.tolist()
@@ -328,7 +366,7 @@ def run_gpu_arm(args, cfg):
             stage[name] = stage.get(name, 0.0) + ms / len(timers)
     peaks, peak_kind = measured_peaks()
     attn_ms = stage.get("attention", float("nan"))
-    attn_flops_rank = attention_flops(rho, N)
+    attn_flops_rank = attention_flops(rho, N) + extra
     achieved = attn_flops_rank / (attn_ms * 1e-3) / 1e12
     peak = peaks["bf16_tflops_sustained"]
 
@@ -339,8 +377,8 @@ def run_gpu_arm(args, cfg):
             "metric": "sparse_attn_layer_effective_tflops", "value": flops_total / (ms_per_step * 1e-3) / 1e12,
             "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg.name, "heads": H, "tokens": N, "q_clusters": cfg.num_q, "k_clusters": cfg.num_k,
-                       "kmeans_iters": cfg.iters, "density_budget": list(cfg.density),
+            "config": {"workload": cfg.name + ("-ear" if ear else ""), "heads": H, "tokens": N, "q_clusters": cfg.num_q,
+                       "k_clusters": cfg.num_k, "kmeans_iters": cfg.iters, "density_budget": list(cfg.density),
                        "realised_density_mean_rank0": sum(rho) / len(rho),
                        "parallelism": f"heads/{world}" + ("+peer-store re-shard" if world > 1 else ""),
                        "l2": f"inputs ({3 * len(mine) * N * D * 2 / 1e9:.2f} GB of Q,K,V on rank 0) are larger than the 126 MB L2; "
@@ -362,7 +400,7 @@ def run_gpu_arm(args, cfg):
             "clocks": clocks.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
-            dt, fl = cpu_layer_sample(cfg, 0)
+            dt, fl = cpu_layer_sample(cfg, 0, args.pattern)
             line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
                                     "kind": "port", "seconds": dt,
                                     "sample": f"head 0 of {H} of the {cfg.name} layer, full {cfg.n_video} tokens, once"}
@@ -611,6 +649,8 @@ def main():
     ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS) + ["cfg4"])
     ap.add_argument("--dit-layers", type=int, default=30, help="blocks of the cfg4 DiT (debugging)")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (debugging)")
+    ap.add_argument("--pattern", default="svoo", choices=["svoo", "ear"],
+                    help="ear: the error-aware routing variant of the layer (one GPU, video-only configs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-group", type=int, default=4, help="heads per copy/compute group of the host-buffer path")
     args = ap.parse_args()

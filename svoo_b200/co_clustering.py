@@ -193,3 +193,103 @@ def dynamic_block_sparse_fwd_flashinfer(q, k, v, block_mask_map, block_row_sz, b
 def dynamic_block_sparse_fwd_triton(q, k, v, dynamic_map, qc_size, kc_size):
     """Name and signature of the reference's alternative backend (svoo/co_clustering.py:1111)."""
     return dynamic_block_sparse_fwd(q, k, v, dynamic_map, qc_size, kc_size)
+
+
+# ----------------------------------------------------------------------------------------------
+# Error-aware routing (EAR): names and signatures of svoo/co_clustering.py:1570-2050
+# ----------------------------------------------------------------------------------------------
+def ear_limits(kc_num: int, H: int, min_kc_ratio: Ratio):
+    """Per-head (guaranteed, budget-preserved) numbers of key clusters of identify_dynamic_map_estimated:
+    max(1, int(r * KC)) and max(1, int(r * KC * 2)) for a positive ratio r, else 0, with the reference's
+    list / one-element / scalar dispatch (svoo/co_clustering.py:1748-1774)."""
+    vals = [0.0] * H
+    if isinstance(min_kc_ratio, torch.Tensor):
+        if min_kc_ratio.numel() == H:
+            vals = [float(v) for v in min_kc_ratio.to(dtype=torch.float32).flatten().tolist()]
+        elif min_kc_ratio.numel() == 1:
+            vals = [float(min_kc_ratio.item())] * H
+    elif isinstance(min_kc_ratio, (list, tuple)):
+        if len(min_kc_ratio) == H:
+            vals = [float(v) for v in torch.tensor(min_kc_ratio, dtype=torch.float32).tolist()]
+        elif len(min_kc_ratio) == 1:
+            vals = [float(min_kc_ratio[0])] * H
+    elif isinstance(min_kc_ratio, (int, float)):
+        vals = [float(min_kc_ratio)] * H
+    preserve = [min(kc_num, max(1, int(r * kc_num))) if r > 0 else 0 for r in vals]
+    budget = [min(kc_num, max(1, int(r * kc_num * 2))) if r > 0 else 0 for r in vals]
+    return preserve, budget
+
+
+def _offsets(sizes: torch.Tensor, device) -> torch.Tensor:
+    B, H, K = sizes.shape
+    return ops.offsets_from_sizes(sizes.reshape(B * H, K).to(device))
+
+
+def compute_value_centroids(v_perm: torch.Tensor, k_cluster_sizes: torch.Tensor) -> torch.Tensor:
+    """Mean value row of every key cluster from the cluster-ordered values [B,H,S,D]: what the Wan
+    processor's _compute_value_centroids (svoo/models/wan/attention.py:594-610) yields from the
+    unpermuted values and the labels.  Returns bf16 [B,H,KC,D]."""
+    B, H, S, D = v_perm.shape
+    KC = k_cluster_sizes.shape[-1]
+    vc = ops.ear_value_centroids(_as_bf16(v_perm).reshape(B * H, S, D).contiguous(), _offsets(k_cluster_sizes, v_perm.device), 1)
+    return vc.view(B, H, KC, D)
+
+
+def _ear_scores(query_centroids, key_centroids, permuted_K, permuted_V, qc_sz, kc_sz, gamma):
+    B, H, qc_num, D = query_centroids.shape
+    kc_num = key_centroids.shape[2]
+    S = permuted_K.shape[2]
+    dev = permuted_K.device
+    q_off, k_off = _offsets(qc_sz, dev), _offsets(kc_sz, dev)
+    ops.ear_value_centroids(_as_bf16(permuted_V).reshape(B * H, S, D).contiguous(), k_off, qc_num)
+    clog, sc = ops.ear_block_scores(_as_bf16(query_centroids).reshape(B * H, qc_num, D),
+                                    _as_bf16(key_centroids).reshape(B * H, kc_num, D),
+                                    _as_bf16(permuted_K).reshape(B * H, S, D).contiguous(), q_off, k_off, gamma)
+    return clog, sc, q_off, k_off
+
+
+def error_estimation_triton(query_centroids, key_centroids, value_centroids, permuted_K, permuted_V, qc_sz, kc_sz,
+                            c_logits=None, gamma: float = 1.0, eps: float = 1e-8, BLOCK_SIZE_Q: int = 64,
+                            BLOCK_SIZE_K: int = 32):
+    """Log-efficiency score of every (query cluster, key cluster) pair, fp32 [B,H,QC,KC]
+    (svoo/co_clustering.py:1570-1689).  The value centroids and the centroid logits are recomputed by the
+    kernels (as the key-cluster means of permuted_V and bf16(bf16(qc.kc) D^-0.5)); `value_centroids`,
+    `c_logits`, `eps` (1e-8) and the block sizes are accepted for signature compatibility."""
+    B, H, qc_num, _ = query_centroids.shape
+    _, sc, _, _ = _ear_scores(query_centroids, key_centroids, permuted_K, permuted_V, qc_sz, kc_sz, gamma)
+    return sc.view(B, H, qc_num, -1)
+
+
+def identify_dynamic_map_estimated(q_perm, k_perm, v_perm, qc_sz, kc_sz, qcentroids, kcentroids, vcentroids, top_p=0.9,
+                                   gamma=1.0, min_kc_ratio=0.0):
+    """Bool map [B,H,QC,KC] under the error-aware budget (svoo/co_clustering.py:1691-1798): per-block
+    error estimate, budget from the size-weighted centroid softmax and top_p, guaranteed minimum
+    coverage, then the highest-score blocks that fit.  No host synchronisation."""
+    B, H, qc_num, D = qcentroids.shape
+    kc_num = kcentroids.shape[2]
+    clog, sc, q_off, k_off = _ear_scores(qcentroids, kcentroids, k_perm, v_perm, qc_sz, kc_sz, gamma)
+    preserve, budget = ear_limits(kc_num, H, min_kc_ratio)
+    m = ops.ear_select_blocks(clog, sc, q_off, k_off, float(top_p), preserve * B, budget * B)
+    return m.view(B, H, qc_num, kc_num).view(torch.bool)
+
+
+def dynamic_block_sparse_prune_fwd_flashinfer(q, k, v, k_centroids, v_centroids, block_mask_map, block_row_sz, block_col_sz,
+                                              is_cpu: bool = True, out_row_idx=None):
+    """EAR forward over cluster-ordered q,k,v [B,H,S,D] (svoo/co_clustering.py:1924-2050): selected blocks
+    at token granularity, every other key cluster through its centroids.  One kernel pass; this wrapper
+    concatenates the token and centroid rows into the layout the kernel reads (the layer path writes
+    them there directly)."""
+    B, H, S, D = q.shape
+    qc_num, kc_num = block_row_sz.shape[-1], block_col_sz.shape[-1]
+    assert block_mask_map.shape == (B, H, qc_num, kc_num)
+    assert k_centroids.shape == (B, H, kc_num, D) and v_centroids.shape == (B, H, kc_num, D)
+    dev = q.device
+    q_off, k_off = _offsets(block_row_sz, dev), _offsets(block_col_sz, dev)
+    m = block_mask_map.to(dev).reshape(B * H, qc_num, kc_num).contiguous()
+    m = m.view(torch.uint8) if m.dtype == torch.bool else m.to(torch.uint8)
+    k_ext = torch.cat([_as_bf16(k).reshape(-1, D), _as_bf16(k_centroids).reshape(-1, D)])
+    v_ext = torch.cat([_as_bf16(v).reshape(-1, D), _as_bf16(v_centroids).reshape(-1, D)])
+    o = ops.sparse_attn_ear(_as_bf16(q).reshape(B * H, S, D).contiguous(), k_ext, v_ext, m, q_off, k_off,
+                            out_row_idx=None if out_row_idx is None else out_row_idx.reshape(B * H, S).contiguous())
+    return o.view(B, H, S, D).to(q.dtype)
+

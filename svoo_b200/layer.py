@@ -50,7 +50,8 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
                            init_indices=None, clustering: Optional[ops.Clustering] = None,
                            context_length: int = 0, prompt_length: Optional[int] = None,
                            return_state: bool = False, timer: Optional[StageTimer] = None,
-                           value_ready: Optional[torch.cuda.Event] = None, peer_out=None):
+                           value_ready: Optional[torch.cuda.Event] = None, peer_out=None,
+                           ear_gamma: Optional[float] = None):
     """query/key/value: [1, H, S, 128] bf16 CUDA, S = video tokens + context_length text
     tokens (text last, never clustered).  Returns [1, H, S, 128] in the original token order.
     `value_ready`: an event the launching stream waits for before it first reads `value`
@@ -73,6 +74,9 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
         c = cc.co_cluster(qv, kv, num_q_centroids, num_k_centroids, kmeans_iters, init_indices=init_indices)
         del qv, kv
     mark("cocluster")
+    if ear_gamma is not None:
+        return _ear_layer(q, k, v, c, top_p, min_kc_ratio, float(ear_gamma), context_length, peer_out, value_ready, mark,
+                          return_state)
     preserve, cap = cc.keep_limits(num_k_centroids, H, min_kc_ratio, max_kc_ratio)
     if top_p >= 1.0:
         m = torch.ones(H, num_q_centroids, num_k_centroids, dtype=torch.uint8, device=q.device)
@@ -100,6 +104,39 @@ def sparse_attention_layer(query: torch.Tensor, key: torch.Tensor, value: torch.
         out = out.unsqueeze(0)
     if return_state:
         return out, LayerState(c, m, q_off, k_off)
+    return out
+
+
+def _ear_layer(q, k, v, c, top_p, min_kc_ratio, gamma, context_length, peer_out, value_ready, mark, return_state):
+    """The error-aware routing variant after the clustering (svoo/models/wan/attention.py:1037-1076,
+    1184-1196): permute, value centroids, block scores, budgeted selection, attention with one virtual
+    key per pruned cluster.  K and V are permuted straight into the [H*S + H*KC, 128] tensors the
+    kernel reads (token rows of all heads, then centroid rows of all heads)."""
+    if context_length or peer_out is not None:
+        raise ValueError("the EAR variant covers video-only self attention on one GPU, as in the reference")
+    H, S, D = q.shape
+    QC, KC = c.qcentroids.shape[1], c.kcentroids.shape[1]
+    if value_ready is not None:
+        torch.cuda.current_stream(q.device).wait_event(value_ready)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    k_ext = torch.empty(H * S + H * KC, D, dtype=q.dtype, device=q.device)
+    v_ext = torch.empty_like(k_ext)
+    kp, vp = k_ext[:H * S].view(H, S, D), v_ext[:H * S].view(H, S, D)
+    qp = ops.permute(q, c.q_sorted_idx)
+    ops.permute(k, c.k_sorted_idx, out=kp)
+    ops.permute(v, c.k_sorted_idx, out=vp)
+    k_ext[H * S:].view(H, KC, D).copy_(c.kcentroids)
+    mark("permute")
+    ops.ear_value_centroids(vp, c.k_offsets, QC, out=v_ext[H * S:].view(H, KC, D))
+    clog, scores = ops.ear_block_scores(c.qcentroids, c.kcentroids, kp, c.q_offsets, c.k_offsets, gamma)
+    preserve, budget = cc.ear_limits(KC, H, min_kc_ratio)
+    m = ops.ear_select_blocks(clog, scores, c.q_offsets, c.k_offsets, top_p, preserve, budget)
+    mark("block_map")
+    out = ops.sparse_attn_ear(qp, k_ext, v_ext, m, c.q_offsets, c.k_offsets, D ** -0.5, out_row_idx=c.q_sorted_idx)
+    mark("attention")
+    out = out.unsqueeze(0)
+    if return_state:
+        return out, LayerState(c, m, c.q_offsets, c.k_offsets)
     return out
 
 

@@ -41,6 +41,10 @@ class _SAPBase:
     kmeans_iter_init = 0
     kmeans_iter_step = 0
     use_svoo = True
+    # error-aware routing (wan/attention.py:580-581): block selection by estimated error and centroid
+    # compensation of the pruned blocks
+    use_ear = False
+    ear_gamma = 1.0
     # reuse of a clustering across denoising steps
     start_reuse_step = None
     reuse_interval = 1
@@ -172,7 +176,7 @@ class _SAPBase:
                                             num_k_centroids=self.num_k_centroids, kmeans_iters=0,
                                             top_p=self.top_p_kmeans, min_kc_ratio=ratio, clustering=c,
                                             context_length=self.context_length, prompt_length=prompt_length,
-                                            return_state=True)
+                                            return_state=True, ear_gamma=self.ear_gamma if self.use_ear else None)
         self.last_block_map = state.block_map              # uint8 [H, QC(+2), KC(+2)] of the last sparse call
         return out
 
@@ -282,6 +286,12 @@ class WanAttn_SAPAttn_Processor(_SAPBase):
         else:
             out = self._sparse(query, key, value)
         return out.transpose(1, 2).flatten(2, 3)
+
+
+class WanAttn_EARAttn_Processor(WanAttn_SAPAttn_Processor):
+    """Wan processor variant with error-aware routing enabled (wan/attention.py:1219-1222)."""
+
+    use_ear = True
 
 
 class Hunyuan_SAPAttn_Processor2_0(_SAPBase):

@@ -173,3 +173,68 @@ def test_reference_fixture(dev, name):
     assert (out.cpu()[:, ::step].float() - ref_rows).abs().max() <= 3e-2
     assert cosine(out.cpu()[:, ::step], ref_rows) >= 0.999
     assert (lse2.cpu()[:, ::step] * math.log(2.0) - torch.from_numpy(z["lse_rows"])).abs().max() <= 3e-2
+
+
+def test_layer_ear_matches_oracle(dev):
+    """The whole EAR layer (clustering, permute, value centroids, scores, selection, attention): the
+    attention against the oracle on the layer's own clustering and map; the map against the map the
+    oracle derives from its own scores."""
+    from svoo_b200 import layer
+    cfg = synth.LayerConfig("ear-layer", 61, 3, (6, 16, 32), torch.bfloat16, 16, 96, 2, (0.05, 0.2), 1, True)
+    q, k, v = synth.make_qkv(cfg)
+    qi, ki = synth.init_indices(cfg)
+    ratios = synth.head_densities(cfg)
+    out, st = layer.sparse_attention_layer(q.to(dev), k.to(dev), v.to(dev), num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k,
+                                           kmeans_iters=2, top_p=0.6, min_kc_ratio=ratios, init_indices=(qi.to(dev), ki.to(dev)),
+                                           return_state=True, ear_gamma=1.0)
+    c = st.clustering
+    ql, kl = c.qlabels.cpu().long(), c.klabels.cpu().long()
+    q_idx, q_off = O.sort_labels(ql, cfg.num_q)
+    k_idx, k_off = O.sort_labels(kl, cfg.num_k)
+    assert torch.equal(q_idx.int(), c.q_sorted_idx.cpu()) and torch.equal(k_off.int(), c.k_offsets.cpu())
+    qs, ks = q_off[:, 1:] - q_off[:, :-1], k_off[:, 1:] - k_off[:, :-1]
+    qp, kp, vp = O.permute(q[0], q_idx), O.permute(k[0], k_idx), O.permute(v[0], k_idx)
+    qc, kc = c.qcentroids.cpu(), c.kcentroids.cpu()
+    vc = E.value_centroids(v[0], kl, ks, cfg.num_k)
+    m = st.block_map.cpu().bool()
+    ref_map = E.identify_dynamic_map_estimated(kp, vp, qs, ks, qc, kc, vc, 0.6, 1.0, ratios)
+    assert float((m == ref_map).float().mean()) >= 0.97
+    assert 0.05 < float(m.float().mean()) < 0.9
+    ref_p, _ = E.compensated_attention(qp, kp, vp, kc, vc, m, qs, ks)
+    ref = O.inverse_permute(ref_p, q_idx)
+    assert (out[0].cpu().float() - ref.float()).abs().max() <= 2e-2
+    assert cosine(out[0].cpu(), ref) >= 0.999
+
+
+def test_ear_processor(dev, tmp_path):
+    """WanAttn_EARAttn_Processor.attention_core_logic: the error-aware branch runs behind the same
+    call as the plain one, gives a different map and a result closer to dense attention at the same
+    budget (the point of the compensation)."""
+    from svoo_b200 import processor as P
+    Wp = gu.WAN_PROC
+    H, (T, Hh, W) = Wp["heads"], Wp["grid"]
+    N = T * Hh * W
+
+    def run(cls):
+        gu.configure_wan_processor(cls, None)
+        cls.use_dynamic_min_kc_ratio = False
+        cls.min_kc_ratio = 0.1
+        cls.top_p_kmeans = 0.5
+        cls.start_reuse_step = None
+        proc = cls(0)
+        proc._step_from_callback = 2
+        proc.draw_init_indices = lambda BH, n, device: tuple(i.to(device) for i in synth.init_indices(
+            synth.LayerConfig("p", 9, BH, (T, Hh, W), torch.bfloat16, Wp["num_q"], Wp["num_k"], 2, (0.1, 0.1), 1, True)))
+        return proc, proc.attention_core_logic(q, k, v, torch.tensor([500.0]))
+
+    cfg = synth.LayerConfig("ear-proc", 62, H, (T, Hh, W), torch.bfloat16, Wp["num_q"], Wp["num_k"], 2, (0.1, 0.1), 1, True)
+    q, k, v = (t.to(dev) for t in synth.make_qkv(cfg))
+    p_ear, y_ear = run(P.WanAttn_EARAttn_Processor)
+    p_sap, y_sap = run(P.WanAttn_SAPAttn_Processor)
+    assert p_ear.use_ear and not p_sap.use_ear
+    assert y_ear.shape == (1, N, H * 128) and torch.isfinite(y_ear.float()).all()
+    dense = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float()).transpose(1, 2).flatten(2, 3)
+    e_ear = float((y_ear.float() - dense).abs().mean())
+    e_sap = float((y_sap.float() - dense).abs().mean())
+    assert not torch.equal(p_ear.last_block_map, p_sap.last_block_map)
+    assert e_ear < e_sap, (e_ear, e_sap)
