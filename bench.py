@@ -378,7 +378,7 @@ def run_gpu_arm(args, cfg):
             "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg.name + ("-ear" if ear else ""), "heads": H, "tokens": N, "q_clusters": cfg.num_q,
-                       "k_clusters": cfg.num_k, "kmeans_iters": cfg.iters, "density_budget": list(cfg.density),
+                       "k_clusters": cfg.num_k, "kmeans_iters": cfg.iters, "top_p": cfg.top_p, "density_budget": list(cfg.density),
                        "realised_density_mean_rank0": sum(rho) / len(rho),
                        "parallelism": f"heads/{world}" + ("+peer-store re-shard" if world > 1 else ""),
                        "l2": f"inputs ({3 * len(mine) * N * D * 2 / 1e9:.2f} GB of Q,K,V on rank 0) are larger than the 126 MB L2; "
@@ -649,6 +649,7 @@ def main():
     ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS) + ["cfg4"])
     ap.add_argument("--dit-layers", type=int, default=30, help="blocks of the cfg4 DiT (debugging)")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (debugging)")
+    ap.add_argument("--top-p", type=float, default=None, help="override the config's top-p of the block selection")
     ap.add_argument("--pattern", default="svoo", choices=["svoo", "ear"],
                     help="ear: the error-aware routing variant of the layer (one GPU, video-only configs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -659,6 +660,8 @@ def main():
     cfg = synth.CONFIGS[args.config]
     if args.heads:
         cfg = dataclasses.replace(cfg, heads=args.heads)
+    if args.top_p is not None:
+        cfg = dataclasses.replace(cfg, top_p=args.top_p)
     if args.impl == "reference":
         run_reference_arm(args, cfg)
     else:
