@@ -228,7 +228,8 @@ int svoo_b200_ear_select_blocks(const float* c_logits, const float* scores, cons
  * (svoo/co_clustering.py:1800-2050) in one pass: a query of cluster i attends the key tokens of the
  * clusters map[i] selects and, for every other cluster j, one virtual key (key centroid j, value
  * centroid j, logit bias log(|K_j| + 1e-6)); the softmax runs over the union, which is what the
- * reference's merge of FlashInfer's (output, log-sum-exp) with the centroid part computes.
+ * reference's merge of FlashInfer's (output, log-sum-exp) with the centroid part computes.  (The
+ * kernel reads all KC centroid rows of the head and masks those of the selected clusters.)
  * k_ext, v_ext: [BH*S + BH*KC, 128] -- the cluster-ordered rows of all heads, then the centroid rows
  * of all heads.  out, out_row_idx, lse as in svoo_b200_sparse_attn. */
 int svoo_b200_sparse_attn_ear(const void* q, const void* k_ext, const void* v_ext, const uint8_t* map,

@@ -20,7 +20,7 @@ cudaError_t launch_build_qtiles(const int32_t*, int4*, int32_t*, int64_t, int64_
 cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, void*, const int32_t*, const int4*,
                                   const int32_t*, const int2*, const int32_t*, int32_t*, int64_t, int64_t, int64_t,
                                   int64_t, float, void* const*, const int32_t*, int, int64_t, int, float*, cudaStream_t,
-                                  const int32_t* ear_ltok = nullptr, const int32_t* ear_k_offsets = nullptr,
+                                  const uint8_t* ear_map = nullptr, const int32_t* ear_k_offsets = nullptr,
                                   int ear_max_runs = 0);
 cudaError_t launch_ear_value_stats(const void*, const int32_t*, void*, float*, float*, float*, int64_t, int64_t, int64_t,
                                    cudaStream_t);
@@ -29,8 +29,8 @@ cudaError_t launch_ear_scores(const void*, const void*, const void*, const int32
                               cudaStream_t);
 cudaError_t launch_ear_select(const float*, const float*, const int32_t*, const int32_t*, uint8_t*, int64_t, int64_t, int64_t,
                               float, const int32_t*, const int32_t*, cudaStream_t);
-cudaError_t launch_ear_build_runs(const uint8_t*, const int32_t*, int2*, int32_t*, int32_t*, int64_t, int64_t, int64_t,
-                                  int64_t, int, cudaStream_t);
+cudaError_t launch_ear_build_runs(const uint8_t*, const int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t, int64_t, int,
+                                  cudaStream_t);
 cudaError_t launch_euclid_assign_tc(const void*, const void*, float*, int32_t*, int2*, int32_t*, int64_t, int64_t, int64_t,
                                     int32_t*, cudaStream_t);
 cudaError_t launch_append_text_blocks(const uint8_t*, const int32_t*, const int32_t*, const int32_t*, const int32_t*,
@@ -350,9 +350,9 @@ int svoo_b200_sparse_attn_simt(const void* q, const void* k, const void* v, cons
 // ---------------------------------------------------------------------------------------
 namespace {
 struct EarWorkspace {
-  int64_t vnorm, cvd, vcsq, runs, nruns, ltok, qtiles, nqtiles, status, total;
+  int64_t vnorm, cvd, vcsq, runs, nruns, qtiles, nqtiles, status, total;
 };
-inline int ear_max_runs(int64_t KC) { return (int)(KC + 6); }
+inline int ear_max_runs(int64_t KC) { return (int)(KC / 2 + 4); }   // token runs + the centroid run + sentinel
 inline EarWorkspace ear_layout(int64_t BH, int64_t N, int64_t QC, int64_t KC) {
   EarWorkspace w;
   int64_t o = 0;
@@ -362,7 +362,6 @@ inline EarWorkspace ear_layout(int64_t BH, int64_t N, int64_t QC, int64_t KC) {
   w.vcsq = take(BH * KC * 4);
   w.runs = take(BH * QC * (int64_t)ear_max_runs(KC) * 8);
   w.nruns = take(BH * QC * 4);
-  w.ltok = take(BH * QC * 4);
   w.qtiles = take(BH * (int64_t)max_qtiles(N, QC) * 16);
   w.nqtiles = take(BH * 4);
   w.status = take(16);
@@ -444,15 +443,14 @@ int svoo_b200_sparse_attn_ear(const void* q, const void* k_ext, const void* v_ex
   cudaStream_t st = (cudaStream_t)stream;
   int2* runs = ws_at<int2>(ear_workspace, w.runs);
   int32_t* nruns = ws_at<int32_t>(ear_workspace, w.nruns);
-  int32_t* ltok = ws_at<int32_t>(ear_workspace, w.ltok);
   int4* qtiles = ws_at<int4>(ear_workspace, w.qtiles);
   int32_t* nqtiles = ws_at<int32_t>(ear_workspace, w.nqtiles);
   int32_t* status = ws_at<int32_t>(ear_workspace, w.status);
-  SVOO_CUDA(launch_ear_build_runs(map, k_offsets, runs, nruns, ltok, BH, S, QC, KC, ear_max_runs(KC), st));
+  SVOO_CUDA(launch_ear_build_runs(map, k_offsets, runs, nruns, BH, S, QC, KC, ear_max_runs(KC), st));
   SVOO_CUDA(launch_build_qtiles(q_offsets, qtiles, nqtiles, BH, S, QC, 256, st));
   SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));
   SVOO_CUDA(launch_sparse_attn_tc(q, k_ext, v_ext, out, out_row_idx, qtiles, nqtiles, runs, nruns, status, BH, S, QC, KC,
-                                  sm_scale, nullptr, nullptr, 0, 0, 0, lse, st, ltok, k_offsets, ear_max_runs(KC)));
+                                  sm_scale, nullptr, nullptr, 0, 0, 0, lse, st, map, k_offsets, ear_max_runs(KC)));
   return SVOO_OK;
 }
 

@@ -36,13 +36,12 @@ constexpr int kBN = 128;                 // key rows per step
 constexpr int kTile = 128 * kRowBytes;   // 32 KB: one [128 x 128] bf16 tile = two 16 KB boxes
 constexpr int kBox = 128 * 128;          // 16 KB: 128 rows x 64 columns
 constexpr int kSmemTiles = 6 * kTile;    // Q0 Q1 | K0 K1 | V0 V1
-// Run table in shared memory.  Plain mode: runs of selected clusters alternate with gaps, at most
-// KC / 2 + 1 of them.  EAR mode (one virtual key per pruned cluster appended, see ear.cu): token runs
-// and centroid runs together can reach KC + 1; its bias table holds one value per key of the tiles
-// that contain centroid keys.
+// Run table in shared memory: runs of selected clusters alternate with gaps, at most KC / 2 + 1 of
+// them.  EAR mode (see ear.cu) appends one run, the centroid rows of the head; its bias table holds
+// one value per key of the tiles that contain centroid keys.
 template <bool kEar>
 struct AttnSmem {
-  static constexpr int kMaxRuns = kEar ? SVOO_MAX_ATTN_CLUSTERS + 6 : SVOO_MAX_ATTN_CLUSTERS / 2 + 2;
+  static constexpr int kMaxRuns = SVOO_MAX_ATTN_CLUSTERS / 2 + (kEar ? 4 : 2);
   static constexpr int kRunTableBytes = (kMaxRuns * 8 + 255) / 256 * 256;
   static constexpr int kBiasFloats = kEar ? SVOO_MAX_ATTN_CLUSTERS + 128 + 6 : 0;
   static constexpr int kBiasBytes = (kBiasFloats * 4 + 255) / 256 * 256;
@@ -165,15 +164,16 @@ __device__ __forceinline__ void tma_gather_tile(uint32_t dst, const CUtensorMap*
   }
 }
 
-// kEar: the key list of a query cluster ends with centroid rows (virtual keys of the pruned clusters,
-// read from the rows that follow the tokens of all heads in K and V); key position >= ltok carries the
-// additive bias log(|K_j| + 1e-6) of its cluster (svoo/co_clustering.py:1873-1876).
+// kEar: the key list of a query cluster ends with the KC centroid rows of its head (read from the rows
+// that follow the tokens of all heads in K and V).  Centroid j is a virtual key standing for the whole
+// cluster j: it carries the additive bias log(|K_j| + 1e-6) (svoo/co_clustering.py:1873-1876) when the
+// cluster was pruned and -inf when its tokens are in the list themselves.
 template <bool kEar>
 __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     const __grid_constant__ AttnMaps maps, const __grid_constant__ OutPeers peers, bf16* __restrict__ out,
     const int32_t* __restrict__ out_row_idx, const int4* __restrict__ qtiles, const int32_t* __restrict__ nqtiles,
     const int2* __restrict__ runs, const int32_t* __restrict__ nruns, int S, int QC, int max_tiles, int max_runs,
-    float scale_log2, int32_t* __restrict__ status, float* __restrict__ lse, const int32_t* __restrict__ ltok,
+    float scale_log2, int32_t* __restrict__ status, float* __restrict__ lse, const uint8_t* __restrict__ map,
     const int32_t* __restrict__ k_offsets, int KC, int rows_total) {
   constexpr int kMaxRunsSmem = AttnSmem<kEar>::kMaxRuns;
   extern __shared__ unsigned char smem_raw[];
@@ -216,25 +216,21 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   const uint32_t tmem = *tmem_slot;
   const int L = runs_s[nr].y;                      // selected key rows in total
   const int T = (L + kBN - 1) / kBN;               // packed key tiles
-  // EAR: keys [l_tok, L) are centroid rows; bias_s[v - bias0] (bias0 = first key of the first tile that
-  // holds one) is their logit bias divided by the softmax scale, so that adding it to the raw score
-  // leaves the rest of the softmax unchanged; zero for the token keys of that tile.
+  // EAR: keys [l_tok, L) are the head's KC centroid rows (the last run); bias_s[v - bias0] (bias0 = first
+  // key of the first tile that holds one) is the logit bias of key v divided by the softmax scale, so
+  // that adding it to the raw score leaves the rest of the softmax unchanged: zero for the token keys
+  // of that tile, -inf for the centroid of a selected cluster.
   int l_tok = L, bias0 = L;
   if (kEar) {
-    l_tok = min(ltok[(int64_t)bh * QC + qi], L);
+    l_tok = nr > 0 ? runs_s[nr - 1].y : L;
     bias0 = l_tok / kBN * kBN;
-    const int cen0 = ((int)gridDim.y - bh) * S + bh * KC;          // first centroid row of this head, as in the run list
     const int32_t* ko = k_offsets + (int64_t)bh * (KC + 1);
+    const uint8_t* mrow = map + ((int64_t)bh * QC + qi) * KC;
     for (int v = bias0 + tid; v < L; v += kThreads) {
       float b = 0.f;
       if (v >= l_tok) {
-        int lo = 0, hi = nr - 1;                                     // last run whose first key is <= v
-        while (lo < hi) {
-          const int mid = (lo + hi + 1) >> 1;
-          if (runs_s[mid].y <= v) lo = mid; else hi = mid - 1;
-        }
-        const int j = min(max(runs_s[lo].x - cen0 + (v - runs_s[lo].y), 0), KC - 1);
-        b = __log2f((float)(ko[j + 1] - ko[j]) + 1e-6f) / scale_log2;
+        const int j = min(v - l_tok, KC - 1);
+        b = mrow[j] ? -INFINITY : __log2f((float)(ko[j + 1] - ko[j]) + 1e-6f) / scale_log2;
       }
       bias_s[v - bias0] = b;
     }
@@ -415,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         const float m_tile = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * scale_log2;   // the scale is positive
         bool pv_done = (j == 0);                                  // PV of the previous tile complete (O and P free)
         if (j == 0) {
-          m_used = m_tile;
+          m_used = kEar ? fmaxf(m_tile, -1e30f) : m_tile;           // EAR: a first tile of masked centroids only
         } else {
           // O is rescaled only when a row maximum grows by more than 2^8; the running sum keeps
           // the same stale maximum, so O / l stays exact
@@ -528,7 +524,7 @@ cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, v
                                   const int4* qtiles, const int32_t* nqtiles, const int2* runs, const int32_t* nruns,
                                   int32_t* status, int64_t BH, int64_t S, int64_t QC, int64_t KC, float sm_scale,
                                   void* const* peer_dst, const int32_t* my_heads, int world, int64_t n_loc, int H,
-                                  float* lse, cudaStream_t st, const int32_t* ear_ltok, const int32_t* ear_k_offsets,
+                                  float* lse, cudaStream_t st, const uint8_t* ear_map, const int32_t* ear_k_offsets,
                                   int ear_max_runs) {
   // a build whose register hand-over does not add up (the spill-check build) must never launch:
   // its softmax warps would wait for registers that nobody frees
@@ -541,7 +537,7 @@ cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, v
     peers.H = H;
   }
   // EAR: K and V hold the centroid rows of all heads after the token rows of all heads
-  const bool ear = ear_ltok != nullptr;
+  const bool ear = ear_map != nullptr;
   const int64_t kv_rows = BH * S + (ear ? BH * KC : 0);
   alignas(64) tc::AttnMaps maps;
   bool ok = tc::make_row_tensor_map(&maps.q, q, BH * S, 128);
@@ -557,7 +553,7 @@ cudaError_t launch_sparse_attn_tc(const void* q, const void* k, const void* v, v
     if (e != cudaSuccess) return e;
     tc::sparse_attn_tc_kernel<true><<<grid, tc::kThreads, tc::AttnSmem<true>::kBytes, st>>>(
         maps, peers, (bf16*)out, out_row_idx, qtiles, nqtiles, runs, nruns, (int)S, (int)QC, max_qtiles(S, QC), ear_max_runs,
-        scale_log2, status, peer_dst ? nullptr : lse, ear_ltok, ear_k_offsets, (int)KC, (int)kv_rows);
+        scale_log2, status, peer_dst ? nullptr : lse, ear_map, ear_k_offsets, (int)KC, (int)kv_rows);
   } else {
     e = cudaFuncSetAttribute(tc::sparse_attn_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              tc::AttnSmem<false>::kBytes);

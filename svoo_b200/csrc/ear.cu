@@ -1,7 +1,7 @@
 // Error-aware routing ("EAR") on top of the co-clustered layout: value centroids and per-token
 // value statistics, the estimated error of replacing a key cluster by its centroid for every
 // (query cluster, key cluster) pair, the budgeted block selection, and the key-row runs of the
-// attention kernel with one virtual key per pruned cluster.
+// attention kernel with the head's centroid rows appended as virtual keys.
 //
 // Reference: svoo/models/wan/attention.py:594-610 (value centroids), svoo/co_clustering.py:1314-1395
 // (value statistics), :1398-1565 (block error estimate), :1691-1798 (selection), :1800-1921
@@ -436,15 +436,14 @@ __global__ void __launch_bounds__(256) ear_select_kernel(const float* __restrict
 // ---------------------------------------------------------------------------------------------
 // Key-row runs of the attention kernel in EAR mode.  The K/V tensors the kernel reads are the
 // cluster-ordered rows of all heads followed by the centroid rows of all heads ([BH*S + BH*KC, 128]);
-// a query cluster's key list is the token runs of its selected clusters, then one centroid row for
-// every cluster it did not select (empty ones included, as in the reference's merge).  `ltok` gets
-// the number of token rows, after which the kernel adds the centroid bias.  One warp per (head,
-// query cluster); entries as in build_runs_kernel, rows relative to the head's first token row.
+// a query cluster's key list is the token runs of its selected clusters, then ONE run: the KC
+// centroid rows of its head (whole 128-row TMA boxes; the kernel masks the centroids of the selected
+// clusters, see the bias table there).  One warp per (head, query cluster); entries as in
+// build_runs_kernel, rows relative to the head's first token row.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) ear_build_runs_kernel(const uint8_t* __restrict__ map, const int32_t* __restrict__ k_off,
-                                                             int2* __restrict__ runs, int32_t* __restrict__ nruns,
-                                                             int32_t* __restrict__ ltok, int QC, int KC, int max_runs,
-                                                             int rows_total, int BH, int S) {
+                                                             int2* __restrict__ runs, int32_t* __restrict__ nruns, int QC,
+                                                             int KC, int max_runs, int rows_total, int BH, int S) {
   const int row = blockIdx.x * 8 + threadIdx.x / 32;
   if (row >= rows_total) return;
   const int lane = threadIdx.x % 32;
@@ -452,49 +451,39 @@ __global__ void __launch_bounds__(256) ear_build_runs_kernel(const uint8_t* __re
   const uint8_t* m = map + (int64_t)row * KC;
   const int32_t* off = k_off + (int64_t)bh * (KC + 1);
   int2* out = runs + (int64_t)row * max_runs;
-  const int cen0 = (BH - bh) * S + bh * KC;            // first centroid row of this head, relative to its token rows
+  bool carry = false;
   int n_start = 0, n_end = 0;
-  // pass 0: token runs of selected, non-empty clusters (.x = first row, .y = end row for now);
-  // pass 1: centroid runs of the clusters not selected
-  for (int pass = 0; pass < 2; ++pass) {
-    bool carry = false;
-    for (int base = 0; base <= KC; base += 32) {
-      const int j = base + lane;
-      int o0 = 0;
-      bool act = false;
-      if (j <= KC) o0 = pass == 0 ? off[j] : cen0 + j;
-      if (j < KC) act = pass == 0 ? (m[j] != 0 && off[j + 1] > o0) : (m[j] == 0);
-      const unsigned bal = __ballot_sync(0xffffffffu, act);
-      const bool prev = lane > 0 ? ((bal >> (lane - 1)) & 1u) : carry;
-      const bool is_start = act && !prev;
-      const bool is_end = (j <= KC) && !act && prev;
-      const unsigned sb = __ballot_sync(0xffffffffu, is_start);
-      const unsigned eb = __ballot_sync(0xffffffffu, is_end);
-      const unsigned lt = (1u << lane) - 1u;
-      if (is_start) { const int r = n_start + __popc(sb & lt); if (r < max_runs) out[r].x = o0; }
-      if (is_end) { const int r = n_end + __popc(eb & lt); if (r < max_runs) out[r].y = o0; }
-      n_start += __popc(sb);
-      n_end += __popc(eb);
-      carry = (bal >> 31) & 1u;
-    }
-    if (pass == 0 && lane == 0) ltok[row] = -n_start;  // number of token runs, turned into rows below
-    __syncwarp();
+  for (int base = 0; base <= KC; base += 32) {
+    const int j = base + lane;
+    int o0 = 0;
+    bool act = false;
+    if (j <= KC) o0 = off[j];
+    if (j < KC) act = m[j] != 0 && off[j + 1] > o0;
+    const unsigned bal = __ballot_sync(0xffffffffu, act);
+    const bool prev = lane > 0 ? ((bal >> (lane - 1)) & 1u) : carry;
+    const bool is_start = act && !prev;
+    const bool is_end = (j <= KC) && !act && prev;
+    const unsigned sb = __ballot_sync(0xffffffffu, is_start);
+    const unsigned eb = __ballot_sync(0xffffffffu, is_end);
+    const unsigned lt = (1u << lane) - 1u;
+    if (is_start) { const int r = n_start + __popc(sb & lt); if (r < max_runs) out[r].x = o0; }
+    if (is_end) { const int r = n_end + __popc(eb & lt); if (r < max_runs) out[r].y = o0; }
+    n_start += __popc(sb);
+    n_end += __popc(eb);
+    carry = (bal >> 31) & 1u;
   }
-  const int n = n_start < max_runs - 1 ? n_start : max_runs - 1;
+  const int n = n_start < max_runs - 2 ? n_start : max_runs - 2;
   __syncwarp();
   if (lane == 0) {
-    const int n_tok_runs = -ltok[row];
-    int vbeg = 0, tok_rows = 0;
+    int vbeg = 0;
     for (int r = 0; r < n; ++r) {
       const int2 se = out[r];
       out[r] = make_int2(se.x, vbeg);
       vbeg += se.y - se.x;
-      if (r + 1 == n_tok_runs) tok_rows = vbeg;
     }
-    if (n_tok_runs == 0) tok_rows = 0;
-    out[n] = make_int2(0, vbeg);
-    nruns[row] = n;
-    ltok[row] = tok_rows;
+    out[n] = make_int2((BH - bh) * S + bh * KC, vbeg);          // the head's centroid rows
+    out[n + 1] = make_int2(0, vbeg + KC);
+    nruns[row] = n + 1;
   }
 }
 
@@ -541,11 +530,11 @@ cudaError_t launch_ear_select(const float* c_logits, const float* scores, const 
   return cudaGetLastError();
 }
 
-cudaError_t launch_ear_build_runs(const uint8_t* map, const int32_t* k_off, int2* runs, int32_t* nruns, int32_t* ltok,
-                                  int64_t BH, int64_t S, int64_t QC, int64_t KC, int max_runs, cudaStream_t st) {
+cudaError_t launch_ear_build_runs(const uint8_t* map, const int32_t* k_off, int2* runs, int32_t* nruns, int64_t BH,
+                                  int64_t S, int64_t QC, int64_t KC, int max_runs, cudaStream_t st) {
   const int rows = (int)(BH * QC);
-  ear_build_runs_kernel<<<(rows + 7) / 8, 256, 0, st>>>(map, k_off, runs, nruns, ltok, (int)QC, (int)KC, max_runs, rows,
-                                                        (int)BH, (int)S);
+  ear_build_runs_kernel<<<(rows + 7) / 8, 256, 0, st>>>(map, k_off, runs, nruns, (int)QC, (int)KC, max_runs, rows, (int)BH,
+                                                        (int)S);
   count_launches(1);
   return cudaGetLastError();
 }

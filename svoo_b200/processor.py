@@ -92,7 +92,8 @@ class _SAPBase:
         if self._last_shape is None:
             return
         dev, H, S, n_video, qc_attn, kc_attn = self._last_shape
-        if ops.attention_status(dev, H, S, qc_attn, kc_attn) != 0:
+        attn_status = ops.ear_attention_status if self.use_ear else ops.attention_status
+        if attn_status(dev, H, S, qc_attn, kc_attn) != 0:
             raise RuntimeError(f"layer {self.layer_idx}: the attention kernel timed out on a barrier; output incomplete")
         if ops.cluster_status(dev, H, n_video, self.num_q_centroids, self.num_k_centroids) != 0:
             raise RuntimeError(f"layer {self.layer_idx}: the assignment kernel timed out on a barrier; labels incomplete")

@@ -232,9 +232,55 @@ def test_ear_processor(dev, tmp_path):
     p_ear, y_ear = run(P.WanAttn_EARAttn_Processor)
     p_sap, y_sap = run(P.WanAttn_SAPAttn_Processor)
     assert p_ear.use_ear and not p_sap.use_ear
+    p_ear.check_status()
+    p_sap.check_status()
     assert y_ear.shape == (1, N, H * 128) and torch.isfinite(y_ear.float()).all()
     dense = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float()).transpose(1, 2).flatten(2, 3)
     e_ear = float((y_ear.float() - dense).abs().mean())
     e_sap = float((y_sap.float() - dense).abs().mean())
     assert not torch.equal(p_ear.last_block_map, p_sap.last_block_map)
     assert e_ear < e_sap, (e_ear, e_sap)
+
+
+def test_full_size_ear_layer_properties(dev):
+    """Two heads of the Wan-14B 720p layer (75,600 tokens, 100 / 500 clusters) through the EAR layer:
+    the kernel's status word, the realised density, and three query clusters of head 0 recomputed by
+    the oracle's formula from the layer's own clustering and map."""
+    from svoo_b200 import layer, ops
+    cfg = dataclasses.replace(synth.CONFIGS["cfg2"], heads=2)
+    q, k, v = synth.make_qkv(cfg)
+    qi, ki = synth.init_indices(cfg)
+    ratios = [0.1, 0.2]
+    out, st = layer.sparse_attention_layer(q.to(dev), k.to(dev), v.to(dev), num_q_centroids=cfg.num_q, num_k_centroids=cfg.num_k,
+                                           kmeans_iters=cfg.iters, top_p=0.0, min_kc_ratio=ratios,
+                                           init_indices=(qi.to(dev), ki.to(dev)), return_state=True, ear_gamma=1.0)
+    assert ops.ear_attention_status(dev, 2, cfg.n_video, cfg.num_q, cfg.num_k) == 0
+    assert torch.isfinite(out.float()).all()
+    c = st.clustering
+    m = st.block_map.cpu().bool()
+    q_off, k_off = c.q_offsets.cpu().long(), c.k_offsets.cpu().long()
+    qs, ks = q_off[:, 1:] - q_off[:, :-1], k_off[:, 1:] - k_off[:, :-1]
+    rho = O.realised_density(m[None], qs[None], ks[None])[0]
+    assert 0.1 < float(rho.min()) and float(rho.max()) < 0.6, rho
+    # every query cluster keeps at least its guaranteed clusters
+    pres, _ = E.ratio_lengths(cfg.num_k, 2, ratios)
+    assert all(int(m[h].sum(-1).min()) >= pres[h] for h in range(2))
+    h = 0
+    k_idx, q_idx = c.k_sorted_idx[h].cpu().long(), c.q_sorted_idx[h].cpu().long()
+    kp, vp = k[0, h][k_idx].float(), v[0, h][k_idx].float()
+    kc = c.kcentroids[h].cpu().float()
+    vc = E.value_centroids(v[0, h:h + 1], c.klabels[h:h + 1].cpu().long(), ks[h:h + 1], cfg.num_k)[0].float()
+    bias = torch.log(ks[h].float() + 1e-6)
+    scale = 128 ** -0.5
+    for i in (0, 37, 99):
+        rows = q_idx[q_off[h, i]:q_off[h, i + 1]]
+        if len(rows) == 0:
+            continue
+        qi_rows = q[0, h][rows].float()
+        sel = torch.cat([torch.arange(k_off[h, j], k_off[h, j + 1]) for j in torch.nonzero(m[h, i]).flatten().tolist()])
+        rest = torch.nonzero(~m[h, i]).flatten()
+        sc = torch.cat([(qi_rows @ kp[sel].T) * scale, (qi_rows @ kc[rest].T) * scale + bias[rest][None, :]], 1)
+        ref = torch.softmax(sc, -1) @ torch.cat([vp[sel], vc[rest]], 0)
+        got = out[0, h].cpu()[rows].float()
+        assert (got - ref).abs().max() <= 2e-2, (i, float((got - ref).abs().max()))
+        assert cosine(got, ref) >= 0.999
