@@ -3,7 +3,8 @@
 // One CTA owns up to two 128-row query tiles of one query cluster.  The key rows that the
 // cluster's map row selects form a list of runs of the cluster-ordered K/V; the CTA walks
 // their concatenation 128 keys at a time, so key tiles are always full except the last one
-// (a tile is packed across run boundaries from several TMA boxes of power-of-two heights).
+// (a tile is packed across run boundaries from several TMA boxes of power-of-two heights).  A
+// query tile with at most 64 rows (the tail of a cluster) runs M = 64 MMAs.
 //
 //   warps 0-3   softmax of query tile 0: thread r owns row r (TMEM lane r).  The 128 scores of the
 //   warps 4-7   row are copied to registers and S is handed back at once; row max, exp2, row sum,
@@ -132,6 +133,11 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
 // Instruction descriptor: D fp32, A/B bf16, M = 128, N = 128; bit 16 = B is MN-major.
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
+// M = 64 forms for a query tile with at most 64 rows (the last tile of a cluster): half the rows of
+// every MMA.  Row i of such a tile lives in TMEM lane (i % 16) + 32 * (i / 16) -- sixteen rows per
+// warp quadrant -- for the accumulators S and O and for the A operand P alike, so the softmax thread
+// of that lane serves it and the other lanes of the quadrant idle.
+constexpr uint32_t kIdescM64 = (128u >> 4) << 24 ^ (64u >> 4) << 24;      // xor turns the M = 128 field into M = 64
 
 // Packed key tile j = virtual rows [128 j, 128 j + 128) of the concatenated runs.  Every run
 // segment inside it is contiguous in the cluster-ordered tensor and is fetched by TMA as
@@ -184,6 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
   const int nr = min(nruns[(int64_t)bh * QC + qi], kMaxRunsSmem - 1);
   const int2* rl = runs + ((int64_t)bh * QC + qi) * max_runs;
   const int nq = (row1 - row0 > kBM) ? 2 : 1;
+  const int rows_w[2] = {min(row1 - row0, kBM), max(row1 - row0 - kBM, 0)};      // rows of the CTA's query tiles
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_s = base, k_s = base + 2 * kTile, v_s = base + 4 * kTile;
@@ -276,13 +283,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       const uint32_t q_lo = ((q_s & 0x3FFFFu) >> 4) | (1u << 16);
       const uint32_t k_lo = ((k_s & 0x3FFFFu) >> 4) | (1u << 16);
       const uint32_t v_lo = ((v_s & 0x3FFFFu) >> 4) | ((uint32_t)(kBox >> 4) << 16);
+      const uint32_t m64x[2] = {rows_w[0] <= 64 ? kIdescM64 : 0u, rows_w[1] <= 64 ? kIdescM64 : 0u};
       auto issue_qk = [&](auto wc, auto sc) {
         constexpr int w = decltype(wc)::value, st = decltype(sc)::value;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t off = ((ks >> 2) * kBox + (ks & 3) * 32) >> 4;
-          umma_ss_lo(tmem + kColS, q_lo + ((w * kTile) >> 4) + off, k_lo + ((st * kTile) >> 4) + off, kDescHi, kIdescQK,
-                     ks > 0);
+          umma_ss_lo(tmem + kColS, q_lo + ((w * kTile) >> 4) + off, k_lo + ((st * kTile) >> 4) + off, kDescHi,
+                     kIdescQK ^ m64x[w], ks > 0);
         }
       };
       auto issue_pv = [&](auto wc, auto sc, bool accumulate) {
@@ -290,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           umma_ts_lo(tmem + kColO + w * 128, tmem + kColP + w * 64 + ks * 8, v_lo + ((st * kTile + ks * 2048) >> 4), kDescHi,
-                     kIdescPV, (accumulate || ks > 0) ? 1u : 0u);
+                     kIdescPV ^ m64x[w], (accumulate || ks > 0) ? 1u : 0u);
       };
       using I0 = std::integral_constant<int, 0>;
       using I1 = std::integral_constant<int, 1>;
@@ -369,7 +377,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
     const int w = warp >> 2;
     if (w < nq) {
       const int quad = warp & 3;
-      const int r_local = quad * 32 + lane;                       // row of the query tile == TMEM lane
+      const bool m64 = rows_w[w] <= 64;                           // M = 64 tile: sixteen rows per quadrant
+      const int r_local = m64 ? quad * 16 + (lane & 15) : quad * 32 + lane;   // row of the query tile served by this TMEM lane
+      const bool lane_has_row = !m64 || lane < 16;
       const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
       const uint32_t s_t = tmem + lane_addr + kColS;              // S, shared with the other query tile
       const uint32_t p_t = tmem + lane_addr + kColP + w * 64;     // P of this query tile (packed bf16)
@@ -415,7 +425,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
         } else {
           // O is rescaled only when a row maximum grows by more than 2^8; the running sum keeps
           // the same stale maximum, so O / l stays exact
-          const bool need = m_tile > m_used + kRescaleThreshold;
+          const bool need = lane_has_row && m_tile > m_used + kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P_FREE + w), (j - 1) & 1, abort_flag));
             if (!ok) break;
@@ -467,7 +477,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_attn_tc_kernel(
       uint32_t ra[32];
       // epilogue: O / l -> bf16 rows
       const int row = row0 + w * kBM + r_local;
-      const bool store = row < row1;
+      const bool store = lane_has_row && row < row1;
       int dst = row;
       if (store && out_row_idx) dst = out_row_idx[(int64_t)bh * S + row];
       dst = store ? min(max(dst, 0), S - 1) : 0;
