@@ -259,11 +259,14 @@ def install_processors(model: WanDiT, processor_cls, grid: Tuple[int, int, int],
                        num_k_centroids: int, top_p_kmeans: float, min_kc_ratio: float, kmeans_iter_init: int,
                        kmeans_iter_step: int, sparsity_lookup=None, dynamic_min_kc_ratio_min=None,
                        dynamic_min_kc_ratio_max=None, start_reuse_step=None, reuse_interval: int = 1,
-                       first_layers_fp: int = 0, first_times_fp: float = float("inf")) -> List:
+                       first_layers_fp: int = 0, first_times_fp: float = float("inf"), pattern: str = "SVOO",
+                       ear_gamma: float = 1.0) -> List:
     """Class attributes and per-block processors, the way the reference's installer sets them
-    (svoo/models/wan/inference.py:267-355).  Cross attention (attn2) gets a processor of the same
-    class: it is called without a timestep and takes the dense branch.  Returns the attn1 processors."""
+    (svoo/models/wan/inference.py:267-355); `pattern == "EAR"` switches the error-aware routing on
+    (`:281-282`).  Cross attention (attn2) gets a processor of the same class: it is called without a
+    timestep and takes the dense branch.  Returns the attn1 processors."""
     cls = processor_cls
+    cls.use_ear, cls.ear_gamma = pattern == "EAR", ear_gamma
     cls.first_layers_fp, cls.first_times_fp = first_layers_fp, first_times_fp
     cls.context_length, cls.num_frame, cls.frame_size = 0, grid[0], grid[1] * grid[2]
     cls.num_q_centroids, cls.num_k_centroids = num_q_centroids, num_k_centroids

@@ -284,3 +284,31 @@ def test_full_size_ear_layer_properties(dev):
         got = out[0, h].cpu()[rows].float()
         assert (got - ref).abs().max() <= 2e-2, (i, float((got - ref).abs().max()))
         assert cosine(got, ref) >= 0.999
+
+
+def test_dit_step_with_ear_pattern(dev):
+    """install_processors(pattern="EAR") on a reduced DiT (2 blocks, 4 heads, 3,840 tokens): one
+    denoising step runs through WanAttn_SAPAttn_Processor with error-aware routing switched on by the
+    installer, stays close to the same model with dense attention, and leaves both status words clear."""
+    from svoo_b200 import processor, wan_dit
+    cfg = wan_dit.WanDiTConfig(num_layers=2, dim=512, heads=4, ffn_dim=1024, text_dim=64, text_len=16, latent=(3, 32, 40))
+    kw = dict(num_q_centroids=12, num_k_centroids=40, top_p_kmeans=0.5, min_kc_ratio=0.15, kmeans_iter_init=2, kmeans_iter_step=1)
+    fresh = lambda: type("Case", (processor.WanAttn_SAPAttn_Processor,), {})
+    ear = wan_dit.WanDiT(cfg).init_weights(1).to(device=dev, dtype=torch.bfloat16).eval()
+    dense = wan_dit.WanDiT(cfg).init_weights(1).to(device=dev, dtype=torch.bfloat16).eval()
+    ear_procs = wan_dit.install_processors(ear, fresh(), cfg.grid, pattern="EAR", ear_gamma=1.0, **kw)
+    wan_dit.install_processors(dense, fresh(), cfg.grid, first_layers_fp=99, **kw)
+    assert all(p.use_ear for p in ear_procs) and not processor.WanAttn_SAPAttn_Processor.use_ear
+    g = torch.Generator("cpu").manual_seed(0)
+    lat = torch.randn(1, 16, *cfg.latent, generator=g).bfloat16().to(dev)
+    text = torch.randn(1, 16, 64, generator=g).bfloat16().to(dev)
+    t = torch.tensor([500.0], device=dev)
+    for m in (ear, dense):
+        wan_dit.set_attention_step(m, 1)
+    with torch.no_grad():
+        got, want = ear(lat, t, text), dense(lat, t, text)
+    for p in ear_procs:
+        p.check_status()
+        assert p.last_block_map is not None and 0.0 < float(p.last_block_map.float().mean()) < 1.0
+    assert got.shape == want.shape and torch.isfinite(got.float()).all()
+    assert cosine(got.cpu(), want.cpu()) >= 0.98
