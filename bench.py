@@ -448,7 +448,7 @@ def measure_producer(cfg, dev, peaks_hbm, reps=5):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one sparse_attn launch per head of 75,600
 # tokens, from an ncu capture of a 4-head launch (profiles/sparse_attn_tc_kernel_wan14b_4heads.md).
-ATTN_DRAM_TRAFFIC_BYTES_PER_HEAD = 281.6e6 / 4
+ATTN_DRAM_TRAFFIC_BYTES_PER_HEAD = 282.5e6 / 4
 
 
 def layer_roofline_ms(cfg, heads, rho, n_tokens, peaks):
