@@ -312,3 +312,43 @@ def test_dit_step_with_ear_pattern(dev):
         assert p.last_block_map is not None and 0.0 < float(p.last_block_map.float().mean()) < 1.0
     assert got.shape == want.shape and torch.isfinite(got.float()).all()
     assert cosine(got.cpu(), want.cpu()) >= 0.98
+
+
+@pytest.mark.parametrize("KC,rows_per_cluster", [(32, 128), (1024, 4), (9, 455)])
+def test_ear_attention_crafted_maps(dev, KC, rows_per_cluster):
+    """Hand-made layouts through the attention entry alone: key clusters of exactly 128 rows (the token
+    part ends on a tile boundary), 1024 clusters (the largest centroid run), a query cluster that selects
+    nothing (all keys are centroids), one that selects everything (all centroids masked), empty key
+    clusters inside and at the end."""
+    from svoo_b200 import ops
+    H, QC = 2, 4
+    N = KC * rows_per_cluster
+    g = torch.Generator("cpu").manual_seed(KC)
+    q, k, v = (torch.randn(H, N, 128, generator=g).mul(0.7).bfloat16() for _ in range(3))
+    ks = torch.full((H, KC), rows_per_cluster, dtype=torch.int64)
+    if KC >= 9:                                         # two empty clusters: their rows go to the neighbour
+        ks[:, 3] += ks[:, 4]
+        ks[:, 4] = 0
+        ks[:, KC - 2] += ks[:, KC - 1]
+        ks[:, KC - 1] = 0
+    qs = torch.tensor([[N // 2, 0, N // 4, N - N // 2 - N // 4]] * H, dtype=torch.int64)
+    off = lambda s: torch.cat([torch.zeros(H, 1, dtype=torch.int64), torch.cumsum(s, -1)], 1)
+    q_off, k_off = off(qs), off(ks)
+    kc = torch.stack([torch.stack([k[h, k_off[h, j]:k_off[h, j + 1]].float().mean(0) if ks[h, j] else torch.zeros(128)
+                                   for j in range(KC)]) for h in range(H)]).bfloat16()
+    vc = torch.stack([torch.stack([v[h, k_off[h, j]:k_off[h, j + 1]].float().mean(0) if ks[h, j] else torch.zeros(128)
+                                   for j in range(KC)]) for h in range(H)]).bfloat16()
+    m = torch.rand(H, QC, KC, generator=g) < 0.3
+    m[:, 0] = False
+    m[:, 2] = True
+    m[1, 3, :] = False
+    m[1, 3, 4 if KC >= 9 else 0] = True                 # head 1, cluster 3: only an empty cluster selected (or one cluster)
+    k_ext = torch.cat([k.reshape(-1, 128), kc.reshape(-1, 128)]).contiguous().to(dev)
+    v_ext = torch.cat([v.reshape(-1, 128), vc.reshape(-1, 128)]).contiguous().to(dev)
+    out, lse2 = ops.sparse_attn_ear(q.to(dev), k_ext, v_ext, m.to(torch.uint8).to(dev), q_off.int().to(dev), k_off.int().to(dev),
+                                    return_lse=True)
+    assert ops.ear_attention_status(dev, H, N, QC, KC) == 0
+    ref, lse = E.compensated_attention(q, k, v, kc, vc, m, qs, ks)
+    assert (out.cpu().float() - ref.float()).abs().max() <= 2e-2
+    assert cosine(out.cpu(), ref) >= 0.999
+    assert (lse2.cpu() - lse / math.log(2.0)).abs().max() <= 5e-3
