@@ -133,24 +133,30 @@ __global__ void __launch_bounds__(256) ear_centroid_logits_kernel(const bf16* __
 //     err_ij = sum_{t in K_j} | e^{a_it} v_t - e^{c_ij} vc_j |^2,   a_it = qc_i . k_t D^-0.5
 // expanded into sum e^{2a}|v|^2 - 2 e^c sum e^a (v.vc) + e^{2c} |vc|^2 |K_j| and evaluated relative to
 // a running maximum as the reference does; score = log(max(err, eps)) - gamma log(max(|Q_i||K_j|, eps)).
-// One CTA = 64 query centroids (16 per warp, their A fragments stay in registers) x a few key
-// clusters; the cluster's key rows go through shared memory 64 at a time and the logits come from
+// One CTA = 128 query centroids (16 per warp, their A fragments stay in registers) x four key
+// clusters; the clusters' key rows go through a three-deep cp.async ring 64 at a time (the next two
+// chunks, of this cluster or the following ones, are in flight while this one is used) and the logits come from
 // mma.sync m16n8k16 (bf16 in, fp32 out).
 // ---------------------------------------------------------------------------------------------
-constexpr int kEarQ = 64, kEarTok = 64, kEarStride = kHeadDim + 8, kEarClustersPerCta = 8;
+constexpr int kEarQ = 128, kEarTok = 64, kEarStride = kHeadDim + 8, kEarClustersPerCta = 4, kEarThreads = 256;
+constexpr int kEarStages = 3;
+constexpr int kEarSmemBytes = (kEarQ + kEarStages * kEarTok) * kEarStride * 2 + 2 * kEarStages * kEarTok * 4;
 
-__global__ void __launch_bounds__(128) ear_scores_kernel(const bf16* __restrict__ qc, const bf16* __restrict__ k_perm,
-                                                         const int32_t* __restrict__ k_off, const int32_t* __restrict__ q_off,
-                                                         const float* __restrict__ c_logits, const float* __restrict__ vnorm,
-                                                         const float* __restrict__ cvd, const float* __restrict__ vcsq,
-                                                         float* __restrict__ scores, int N, int QC, int KC, float scale,
-                                                         float gamma, float eps) {
-  __shared__ __align__(16) bf16 q_s[kEarQ * kEarStride];
-  __shared__ __align__(16) bf16 k_s[kEarTok * kEarStride];
-  __shared__ float vn_s[kEarTok], cv_s[kEarTok];
+__global__ void __launch_bounds__(kEarThreads) ear_scores_kernel(const bf16* __restrict__ qc, const bf16* __restrict__ k_perm,
+                                                                 const int32_t* __restrict__ k_off,
+                                                                 const int32_t* __restrict__ q_off,
+                                                                 const float* __restrict__ c_logits,
+                                                                 const float* __restrict__ vnorm, const float* __restrict__ cvd,
+                                                                 const float* __restrict__ vcsq, float* __restrict__ scores,
+                                                                 int N, int QC, int KC, float scale, float gamma, float eps) {
+  extern __shared__ __align__(16) unsigned char ear_sc_sm[];
+  bf16* q_s = reinterpret_cast<bf16*>(ear_sc_sm);                          // [128][136]
+  bf16* k_s = q_s + kEarQ * kEarStride;                                    // [3][64][136]: a three-deep ring
+  float* vn_s = reinterpret_cast<float*>(k_s + kEarStages * kEarTok * kEarStride);   // [3][64]
+  float* cv_s = vn_s + kEarStages * kEarTok;                               // [3][64]
   const int bh = blockIdx.z, qt = blockIdx.y, tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int g = lane / 4, tq = lane % 4;
-  for (int t = tid; t < kEarQ * 16; t += 128) {
+  for (int t = tid; t < kEarQ * 16; t += kEarThreads) {
     const int r = t / 16, c = t % 16, qi = qt * kEarQ + r;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (qi < QC) v = __ldg(reinterpret_cast<const uint4*>(qc + ((int64_t)bh * QC + qi) * kHeadDim) + c);
@@ -171,71 +177,120 @@ __global__ void __launch_bounds__(128) ear_scores_kernel(const bf16* __restrict_
   const int32_t* qo = q_off + (int64_t)bh * (QC + 1);
   const float qsz0 = qi0 < QC ? (float)(qo[qi0 + 1] - qo[qi0]) : 0.f;
   const float qsz1 = qi1 < QC ? (float)(qo[qi1 + 1] - qo[qi1]) : 0.f;
-  const int j_end = min((int)(blockIdx.x + 1) * kEarClustersPerCta, KC);
-  for (int j = blockIdx.x * kEarClustersPerCta; j < j_end; ++j) {
-    const int begin = off[j], n = off[j + 1] - begin;
-    const float c0 = qi0 < QC ? c_logits[((int64_t)bh * QC + qi0) * KC + j] : 0.f;
-    const float c1 = qi1 < QC ? c_logits[((int64_t)bh * QC + qi1) * KC + j] : 0.f;
+  const int j_begin = blockIdx.x * kEarClustersPerCta, j_end = min(j_begin + kEarClustersPerCta, KC);
+
+  // chunk (cluster jc, first token tc) -> buffer b: 64 key rows and their value statistics by cp.async
+  // (zero-filled past the cluster's end)
+  auto load_chunk = [&](int jc, int tc, int b) {
+    const int begin = off[jc], n = off[jc + 1] - begin;
+    const uint32_t dst = smem_u32(k_s + b * kEarTok * kEarStride);
+    for (int t = tid; t < kEarTok * 16; t += kEarThreads) {
+      const int r = t / 16, c = t % 16;
+      const bool ok = tc + r < n;
+      cp_async16(dst + (r * kEarStride + c * 8) * 2, k_perm + ((int64_t)bh * N + begin + (ok ? tc + r : 0)) * kHeadDim + c * 8, ok);
+    }
+    if (tid < 2 * kEarTok) {
+      const int r = tid % kEarTok;
+      const bool ok = tc + r < n;
+      const float* src = (tid < kEarTok ? vnorm : cvd) + (int64_t)bh * N + begin + (ok ? tc + r : 0);
+      const uint32_t d4 = smem_u32((tid < kEarTok ? vn_s : cv_s) + b * kEarTok + r);
+      const int sz = ok ? 4 : 0;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d4), "l"(src), "r"(sz));
+    }
+    cp_async_commit();
+  };
+  // the chunk after (jc, tc): the next one of the same cluster, else the first of the next non-empty one
+  auto next_chunk = [&](int& jc, int& tc) {
+    tc += kEarTok;
+    while (jc < j_end && tc >= off[jc + 1] - off[jc]) {
+      ++jc;
+      tc = 0;
+    }
+  };
+  // (pj, pt): the next chunk to load; chunks are consumed in the same order, two loads ahead
+  int pj = j_begin, pt = -kEarTok;
+  next_chunk(pj, pt);
+  int issued = 0, consumed = 0;
+  for (int k = 0; k < kEarStages - 1 && pj < j_end; ++k) {
+    load_chunk(pj, pt, issued % kEarStages);
+    ++issued;
+    next_chunk(pj, pt);
+  }
+  // the running maximum and every exponent are kept in base 2 (ex2.approx; the estimate feeds a ranking
+  // and tolerates its 2 ulp): a' = a log2(e), c' = c log2(e)
+  const float kLog2e = 1.4426950408889634f;
+  const float scale2 = scale * kLog2e;
+  const bool warp_has_rows = qt * kEarQ + warp * 16 < QC;
+  for (int j = j_begin; j < j_end; ++j) {
+    const int n = off[j + 1] - off[j];
+    const float c0 = qi0 < QC ? c_logits[((int64_t)bh * QC + qi0) * KC + j] * kLog2e : 0.f;
+    const float c1 = qi1 < QC ? c_logits[((int64_t)bh * QC + qi1) * KC + j] * kLog2e : 0.f;
     float run0 = c0, run1 = c1, sq0 = 0.f, sq1 = 0.f, cr0 = 0.f, cr1 = 0.f;
     for (int t0 = 0; t0 < n; t0 += kEarTok) {
+      // wait for this chunk; the barrier also says that everyone is done with the chunk before it, whose
+      // buffer the next load reuses
+      if (issued - consumed >= 2) cp_async_wait<1>(); else cp_async_wait<0>();
       __syncthreads();
-      for (int t = tid; t < kEarTok * 16; t += 128) {
-        const int r = t / 16, c = t % 16;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (t0 + r < n) v = __ldg(reinterpret_cast<const uint4*>(k_perm + ((int64_t)bh * N + begin + t0 + r) * kHeadDim) + c);
-        *reinterpret_cast<uint4*>(&k_s[r * kEarStride + c * 8]) = v;
+      if (pj < j_end) {
+        load_chunk(pj, pt, issued % kEarStages);
+        ++issued;
+        next_chunk(pj, pt);
       }
-      if (tid < kEarTok) {
-        const bool ok = t0 + tid < n;
-        vn_s[tid] = ok ? vnorm[(int64_t)bh * N + begin + t0 + tid] : 0.f;
-        cv_s[tid] = ok ? cvd[(int64_t)bh * N + begin + t0 + tid] : 0.f;
-      }
-      __syncthreads();
-      float s[8][4];
+      const int buf = consumed % kEarStages;
+      ++consumed;
+      if (warp_has_rows) {
+        const bf16* kb = k_s + buf * kEarTok * kEarStride;
+        const float* vn = vn_s + buf * kEarTok;
+        const float* cv = cv_s + buf * kEarTok;
+        float s[8][4];
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        for (int nt = 0; nt < 8; ++nt) {
+          s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const bf16* base = &k_s[(nt * 8 + g) * kEarStride + kk * 16 + 2 * tq];
-          mma_bf16(s[nt], a[kk], *reinterpret_cast<const uint32_t*>(base), *reinterpret_cast<const uint32_t*>(base + 8));
+          for (int kk = 0; kk < 8; ++kk) {
+            const bf16* base = &kb[(nt * 8 + g) * kEarStride + kk * 16 + 2 * tq];
+            mma_bf16(s[nt], a[kk], *reinterpret_cast<const uint32_t*>(base), *reinterpret_cast<const uint32_t*>(base + 8));
+          }
         }
-      }
-      float m0 = -INFINITY, m1 = -INFINITY;
+        float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const bool ok = t0 + nt * 8 + 2 * tq + e < n;
-          s[nt][e] = ok ? s[nt][e] * scale : -INFINITY;
-          s[nt][2 + e] = ok ? s[nt][2 + e] * scale : -INFINITY;
-          m0 = fmaxf(m0, s[nt][e]);
-          m1 = fmaxf(m1, s[nt][2 + e]);
+          for (int e = 0; e < 2; ++e) {
+            const bool ok = t0 + nt * 8 + 2 * tq + e < n;
+            s[nt][e] = ok ? s[nt][e] * scale2 : -INFINITY;
+            s[nt][2 + e] = ok ? s[nt][2 + e] * scale2 : -INFINITY;
+            m0 = fmaxf(m0, s[nt][e]);
+            m1 = fmaxf(m1, s[nt][2 + e]);
+          }
         }
-      }
-      m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
-      m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
-      m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
-      m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
-      const float new0 = fmaxf(run0, m0), new1 = fmaxf(run1, m1);
-      sq0 *= expf(2.0f * (run0 - new0));
-      cr0 *= expf(run0 - new0);
-      sq1 *= expf(2.0f * (run1 - new1));
-      cr1 *= expf(run1 - new1);
+        m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+        m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+        m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+        m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+        const float new0 = fmaxf(run0, m0), new1 = fmaxf(run1, m1);
+        const float r0 = exp2f(run0 - new0), r1 = exp2f(run1 - new1);
+        sq0 *= r0 * r0;
+        cr0 *= r0;
+        sq1 *= r1 * r1;
+        cr1 *= r1;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int c = nt * 8 + 2 * tq + e;
-          const float p0 = expf(s[nt][e] - new0), p1 = expf(s[nt][2 + e] - new1);       // exp(-inf) = 0 for the padding
-          sq0 += p0 * p0 * vn_s[c];
-          cr0 += p0 * cv_s[c];
-          sq1 += p1 * p1 * vn_s[c];
-          cr1 += p1 * cv_s[c];
+          for (int e = 0; e < 2; ++e) {
+            const int c = nt * 8 + 2 * tq + e;
+            float p0, p1;                                  // ex2(-inf) = 0 for the padding
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(s[nt][e] - new0));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(s[nt][2 + e] - new1));
+            sq0 += p0 * p0 * vn[c];
+            cr0 += p0 * cv[c];
+            sq1 += p1 * p1 * vn[c];
+            cr1 += p1 * cv[c];
+          }
         }
+        run0 = new0;
+        run1 = new1;
       }
-      run0 = new0;
-      run1 = new1;
     }
 #pragma unroll
     for (int o = 1; o <= 2; o <<= 1) {
@@ -245,18 +300,22 @@ __global__ void __launch_bounds__(128) ear_scores_kernel(const bf16* __restrict_
       cr1 += __shfl_xor_sync(0xffffffffu, cr1, o);
     }
     if (tq == 0) {
+      // err = (sq - 2 cp cr + cp^2 |vc|^2 n) 2^(2 run): its logarithm is taken piecewise so that a large
+      // running maximum cannot overflow the product (the reference multiplies and clamps; the two agree
+      // wherever that product is finite)
       const float vs = vcsq[(int64_t)bh * KC + j], nf = (float)n;
+      const float kLn2 = 0.6931471805599453f;
       if (qi0 < QC) {
-        const float cp = expf(c0 - run0);
-        float err = sq0 - 2.0f * cp * cr0 + cp * cp * vs * nf;
-        err = fmaxf(err * expf(2.0f * run0), eps);
-        scores[((int64_t)bh * QC + qi0) * KC + j] = logf(err) - gamma * logf(fmaxf(qsz0 * nf, eps));
+        const float cp = exp2f(c0 - run0);
+        const float err = sq0 - 2.0f * cp * cr0 + cp * cp * vs * nf;
+        const float le = err > 0.f ? logf(err) + 2.0f * run0 * kLn2 : -INFINITY;
+        scores[((int64_t)bh * QC + qi0) * KC + j] = fmaxf(le, logf(eps)) - gamma * logf(fmaxf(qsz0 * nf, eps));
       }
       if (qi1 < QC) {
-        const float cp = expf(c1 - run1);
-        float err = sq1 - 2.0f * cp * cr1 + cp * cp * vs * nf;
-        err = fmaxf(err * expf(2.0f * run1), eps);
-        scores[((int64_t)bh * QC + qi1) * KC + j] = logf(err) - gamma * logf(fmaxf(qsz1 * nf, eps));
+        const float cp = exp2f(c1 - run1);
+        const float err = sq1 - 2.0f * cp * cr1 + cp * cp * vs * nf;
+        const float le = err > 0.f ? logf(err) + 2.0f * run1 * kLn2 : -INFINITY;
+        scores[((int64_t)bh * QC + qi1) * KC + j] = fmaxf(le, logf(eps)) - gamma * logf(fmaxf(qsz1 * nf, eps));
       }
     }
   }
@@ -505,7 +564,9 @@ cudaError_t launch_ear_scores(const void* qc, const void* kc, const void* k_perm
   ear_centroid_logits_kernel<<<dim3((unsigned)ceil_div64(QC, 8), (unsigned)BH), 256, 0, st>>>(
       (const bf16*)qc, (const bf16*)kc, c_logits, (int)QC, (int)KC, scale);
   dim3 grid((unsigned)ceil_div64(KC, kEarClustersPerCta), (unsigned)ceil_div64(QC, kEarQ), (unsigned)BH);
-  ear_scores_kernel<<<grid, 128, 0, st>>>((const bf16*)qc, (const bf16*)k_perm, k_off, q_off, c_logits, vnorm, cvd, vcsq, scores,
+  cudaError_t e = cudaFuncSetAttribute(ear_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kEarSmemBytes);
+  if (e != cudaSuccess) return e;
+  ear_scores_kernel<<<grid, kEarThreads, kEarSmemBytes, st>>>((const bf16*)qc, (const bf16*)k_perm, k_off, q_off, c_logits, vnorm, cvd, vcsq, scores,
                                           (int)N, (int)QC, (int)KC, scale, gamma, 1e-8f);
   count_launches(2);
   return cudaGetLastError();
