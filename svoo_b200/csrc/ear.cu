@@ -451,15 +451,22 @@ __global__ void __launch_bounds__(256) ear_select_kernel(const float* __restrict
   }
   __syncwarp();
   const int preserve = lim.preserve[bh], bpres = lim.budget_preserve[bh];
+  // The sequential passes below run on lane 0 in the fixed order the CPU side uses; everything that is
+  // a gather or a scatter is done by the whole warp before or after them, so that a pass reads its
+  // operands in order from shared memory and carries only its fp32 sums.
+  for (int r = lane; r < KC; r += 32) {              // areas in budget order (vw is free: the probabilities live in kw)
+    const int j = 0xFFFF - (int)(kw[r] & 0xFFFFu);
+    vw[r] = area[j];
+    if (r < preserve) gflag[j] = 1;
+  }
+  __syncwarp();
   float remaining = 0.f;
   if (lane == 0) {
     const float p_b = bf16_round(top_p);
     float run = 0.f, budget = 0.f;
     bool keep = true;                                   // position 0 is always kept
     for (int r = 0; r < KC; ++r) {
-      const int j = 0xFFFF - (int)(kw[r] & 0xFFFFu);
-      if (keep || r < bpres) budget = __fadd_rn(budget, area[j]);
-      if (r < preserve) gflag[j] = 1;
+      if (keep || r < bpres) budget = __fadd_rn(budget, vw[r]);
       run = __fadd_rn(run, __uint_as_float(kw[r] & 0xFFFF0000u));
       keep = bf16_round(run) <= p_b;                    // decides position r + 1
     }
@@ -478,17 +485,21 @@ __global__ void __launch_bounds__(256) ear_select_kernel(const float* __restrict
     default: ear_sort_scores<32>(sc, gflag, kw, KC, KCpad, lane); break;
   }
   __syncwarp();
-  uint8_t* out = map + ((int64_t)bh * QC + i) * KC;
-  if (lane == 0) {
+  for (int r = lane; r < KC; r += 32) vw[r] = area[kw[r]];      // areas in candidate order
+  __syncwarp();
+  if (lane == 0) {                                    // position r is kept while (running sum - own area) < remaining
     float run = 0.f;
     for (int r = 0; r < KC; ++r) {
-      const int j = (int)kw[r];
-      const float aj = area[j];
+      const float aj = vw[r];
       run = __fadd_rn(run, aj);
-      if (__fsub_rn(run, aj) < remaining) gflag[j] |= 2;
+      if (__fsub_rn(run, aj) < remaining) kw[r] |= 0x80000000u;
     }
   }
   __syncwarp();
+  for (int r = lane; r < KC; r += 32)
+    if (kw[r] & 0x80000000u) gflag[kw[r] & 0xFFFFu] |= 2;     // distinct clusters: no two lanes write one byte
+  __syncwarp();
+  uint8_t* out = map + ((int64_t)bh * QC + i) * KC;
   for (int j = lane; j < KC; j += 32) out[j] = gflag[j] ? 1 : 0;
 }
 
