@@ -415,16 +415,21 @@ def measure_producer(cfg, dev, peaks_hbm, reps=5):
     """The step before the layer (RMS norm + rotary embedding + head transpose of the Q, K, V
     projections, one kernel launch per tensor), timed on its own: not part of `value`."""
     from svoo_b200 import ops
-    if cfg.text_tokens:
-        return None                                          # the Wan producer (norm over the whole projection row)
     H, S = cfg.heads, cfg.n_tokens
+    joint = cfg.text_tokens > 0                              # HunyuanVideo: per-head norm, text rows not rotated
+    rows = S - cfg.text_tokens
     g = torch.Generator("cpu").manual_seed(3)
     x = [torch.randn(S, H * D, generator=g, dtype=torch.float32).bfloat16().to(dev) for _ in range(3)]
-    w = [(1.0 + 0.1 * torch.randn(H * D, generator=g)).to(dev) for _ in range(2)]
-    ang = torch.rand(S, D // 2, generator=g) * 6.2831853
+    w = [(1.0 + 0.1 * torch.randn(D if joint else H * D, generator=g)).to(dev) for _ in range(2)]
+    ang = torch.rand(rows, D // 2, generator=g) * 6.2831853
     cos, sin = torch.cos(ang).repeat_interleave(2, -1).to(dev), torch.sin(ang).repeat_interleave(2, -1).to(dev)
 
     def run():
+        if joint:
+            ops.qk_prep_heads(x[0], H, w[0], 1e-6, cos, sin, rows)
+            ops.qk_prep_heads(x[1], H, w[1], 1e-6, cos, sin, rows)
+            ops.qk_prep_heads(x[2], H)
+            return
         ops.qk_prep(x[0], H, w[0], 1e-6, cos, sin)
         ops.qk_prep(x[1], H, w[1], 1e-6, cos, sin)
         ops.qk_prep(x[2], H)
@@ -439,9 +444,10 @@ def measure_producer(cfg, dev, peaks_hbm, reps=5):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / reps
-    nbytes = 3 * 2 * S * H * D * 2 + 2 * 2 * S * D * 4          # x read + y written per tensor; cos, sin for Q and K
+    nbytes = 3 * 2 * S * H * D * 2 + 2 * 2 * rows * D * 4       # x read + y written per tensor; cos, sin for Q and K
     gbs = nbytes / (ms * 1e-3) / 1e9
-    return {"what": "rmsnorm + rope + head transpose of the Q, K, V projections (3 launches)", "ms": ms,
+    what = ("per-head rmsnorm + text-last rope + head transpose" if joint else "rmsnorm + rope + head transpose")
+    return {"what": what + " of the Q, K, V projections (3 launches)", "ms": ms,
             "algorithmic_bytes": nbytes, "achieved": gbs, "peak": peaks_hbm, "unit": "GB/s", "frac": gbs / peaks_hbm,
             "bound": "hbm"}
 

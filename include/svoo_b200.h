@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define SVOO_B200_VERSION 102
+#define SVOO_B200_VERSION 103
 
 enum {
   SVOO_OK = 0,
@@ -331,6 +331,20 @@ int svoo_b200_layer(const void* q, const void* k, const void* v, const int32_t* 
  * With weight == NULL and cos == NULL it is the plain head transpose (V).  H <= 128. */
 int svoo_b200_qk_prep(const void* x, const float* weight, float eps, const float* cos, const float* sin, int64_t S,
                       int64_t H, int64_t D, void* out, void* stream);
+/* The per-head producer of HunyuanVideo's blocks, one pass: RMS norm over the D values of every
+ * (token, head) with weight [D] (fp32), y = bf16((x * rsqrt(mean(x^2) + eps)) * w)
+ * (rmsnorm_narrow_n_subwarp_reduction, svoo/kernels/include/norm/narrow_rms_norm.cuh:22-74, called from
+ * apply_qk_norm, svoo/models/hunyuan10/attention.py:262-270); interleaved-pair rotation of the first
+ * `rope_rows` tokens, out[i] = bf16(y[i] cos[i] + (i even ? -y[i+1] : y[i-1]) sin[i]) with cos, sin
+ * [rope_rows, D] fp32 (ApplyQKRotaryCosSinTXTLASTCacheInPlace, svoo/kernels/include/rope/rope_enc_txtlast.cuh:34-110:
+ * the text tokens at the end of the sequence are not rotated); head transpose
+ * (get_transpose_qkv, hunyuan10/attention.py:471-476).  x: [S, H*D] bf16; row s of head h is stored at
+ * out[h][out_row0 + s] of an [H, out_rows, D] array, so the video and the text tokens of a
+ * double-stream block (separate projections) can be placed in one sequence.  weight == NULL / cos ==
+ * NULL skip that part. */
+int svoo_b200_qk_prep_heads(const void* x, const float* weight, float eps, const float* cos, const float* sin, int64_t S,
+                            int64_t H, int64_t D, int64_t rope_rows, void* out, int64_t out_rows, int64_t out_row0,
+                            void* stream);
 /* The same for a sequence-parallel caller: x is this rank's [n_loc, H*D] rows (cos, sin
  * [n_loc, D]) and every head's row is stored straight into the rank that owns the head, at
  * [slot[h], rank * n_loc + r, :] of its [ceil(H/world), N, D] array -- svoo_b200_push_heads fused

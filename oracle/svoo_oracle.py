@@ -23,6 +23,9 @@ Reference locations restated here (paths inside the reference project):
   * producer of Q, K, V (RMS norm, rotary embedding, head transpose)
                                       svoo/kernels/triton/rmsnorm.py:9-46,
                                       svoo/models/wan/attention.py:112-131,177-195
+  * HunyuanVideo's producer (per-head RMS norm, text-last rotary embedding; restated from CUDA
+    source, not pinned)               svoo/kernels/include/norm/narrow_rms_norm.cuh:22-74,
+                                      svoo/kernels/include/rope/rope_enc.cuh:17-36
 """
 from __future__ import annotations
 
@@ -78,6 +81,27 @@ def qk_prep(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, cos: Op
 # --------------------------------------------------------------------------------------
 # co-clustering
 # --------------------------------------------------------------------------------------
+
+def qk_prep_heads(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                  sin: Optional[torch.Tensor], rope_rows: int, heads: int) -> torch.Tensor:
+    """HunyuanVideo's producer, [S, H*128] -> [H, S, 128], as the reference's own CUDA kernels compute it
+    (restated from their source; they cannot run without a GPU, so this function is not pinned by a
+    fixture): y = dtype((x * rsqrt(sum(x^2)/128 + eps)) * w) per (token, head)
+    (svoo/kernels/include/norm/narrow_rms_norm.cuh:22-74); for the first `rope_rows` tokens
+    out[i] = dtype(y[i] cos[i] + (i even ? -y[i+1] : y[i-1]) sin[i]) (svoo/kernels/include/rope/rope_enc.cuh:17-36,
+    rope_enc_txtlast.cuh:34-78); head transpose.  fp32 arithmetic."""
+    S = x.shape[0]
+    y = x.view(S, heads, 128).float()
+    if weight is not None:
+        rstd = torch.rsqrt((y * y).sum(-1, keepdim=True) / 128.0 + eps)
+        y = ((y * rstd) * weight.float()).to(x.dtype).float()
+    if cos is not None and rope_rows > 0:
+        c, sn = cos.float()[:rope_rows, None], sin.float()[:rope_rows, None]
+        v = y[:rope_rows]
+        rot = torch.stack([-v[..., 1::2], v[..., 0::2]], -1).flatten(-2)
+        y = torch.cat([(v * c + rot * sn).to(x.dtype).float(), y[rope_rows:]], 0)
+    return y.to(x.dtype).transpose(0, 1).contiguous()
+
 
 def l2norm_rows(x: torch.Tensor, eps: float = 1e-8) -> torch.Tensor:
     """x / sqrt(sum(x^2) + eps) along the last dim, fp32 out (l2norm.py:36-41)."""

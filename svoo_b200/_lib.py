@@ -47,6 +47,8 @@ SIGNATURES = {
                                            c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64,
                                            c_void_p]),
     "svoo_b200_status_offset": (c_int, [c_int64, c_int64, c_int64, c_int64, _I64P]),
+    "svoo_b200_qk_prep_heads": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                        c_void_p, c_int64, c_int64, c_void_p]),
     "svoo_b200_ear_workspace_bytes": (c_int, [c_int64, c_int64, c_int64, c_int64, _I64P, _I64P]),
     "svoo_b200_ear_value_centroids": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                               c_void_p, c_int64, c_void_p]),
@@ -76,7 +78,7 @@ SIGNATURES = {
 }
 
 
-VERSION = 102          # SVOO_B200_VERSION of include/svoo_b200.h this binding was written for
+VERSION = 103          # SVOO_B200_VERSION of include/svoo_b200.h this binding was written for
 
 
 class SvooB200Error(RuntimeError):

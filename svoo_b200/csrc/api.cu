@@ -45,6 +45,8 @@ cudaError_t launch_push_seq(const void*, void* const*, const int32_t*, int, int6
 cudaError_t launch_peer_barrier(void* const*, int, int, int, uint32_t, int32_t*, cudaStream_t);
 cudaError_t launch_qk_prep(const void*, const float*, float, const float*, const float*, int64_t, int, void*, void* const*,
                            const int32_t*, const int32_t*, int, int, cudaStream_t);
+cudaError_t launch_qk_prep_heads(const void*, const float*, float, const float*, const float*, int64_t, int, int64_t, void*,
+                                 int64_t, int64_t, cudaStream_t);
 }  // namespace svoo
 
 namespace svoo {
@@ -526,6 +528,19 @@ int svoo_b200_qk_prep(const void* x, const float* weight, float eps, const float
   if (!aligned16(out)) return SVOO_ERR_ALIGN;
   SVOO_CUDA(launch_qk_prep(x, weight, eps, cosv, sinv, S, (int)H, out, nullptr, nullptr, nullptr, 0, 0,
                            (cudaStream_t)stream));
+  return SVOO_OK;
+}
+
+int svoo_b200_qk_prep_heads(const void* x, const float* weight, float eps, const float* cosv, const float* sinv, int64_t S,
+                            int64_t H, int64_t D, int64_t rope_rows, void* out, int64_t out_rows, int64_t out_row0,
+                            void* stream) {
+  SVOO_TRY(check_prep(x, weight, cosv, sinv, S, H, D));
+  if (!out) return SVOO_ERR_NULL;
+  if (!aligned16(out)) return SVOO_ERR_ALIGN;
+  if (rope_rows < 0 || rope_rows > S || out_row0 < 0 || out_rows < out_row0 + S) return SVOO_ERR_SHAPE;
+  if (H * out_rows > 2147483647LL) return SVOO_ERR_SHAPE;
+  SVOO_CUDA(launch_qk_prep_heads(x, weight, eps, cosv, sinv, S, (int)H, rope_rows, out, out_rows, out_row0,
+                                 (cudaStream_t)stream));
   return SVOO_OK;
 }
 

@@ -282,4 +282,84 @@ cudaError_t launch_qk_prep(const void* x, const float* weight, float eps, const 
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Per-head variant (HunyuanVideo): RMS norm over the 128 values of every (token, head), rotary
+// embedding of the first `rope_rows` tokens only (the text tokens at the end of the sequence are not
+// rotated) and the head transpose, in one pass.  Arithmetic of the reference's own CUDA kernels:
+//   y = bf16((x * rsqrtf(sum(x^2) / 128 + eps)) * w)     rmsnorm_narrow_n_subwarp_reduction,
+//                                                         svoo/kernels/include/norm/narrow_rms_norm.cuh:22-74
+//   out[i] = bf16(y[i] cos[i] + (i even ? -y[i+1] : y[i-1]) sin[i])
+//                                                         vec_apply_llama_rope_cos_sin_interleave,
+//                                                         svoo/kernels/include/rope/rope_enc.cuh:17-36, called for
+//                                                         the rows before the text by rope_enc_txtlast.cuh:34-78
+// One half-warp per (token, head): 16 lanes x 8 values, the sum of squares per lane in element order,
+// then a butterfly over the 16 lanes, as there.  The rows of head h go to out[h][out_row0 + s] of an
+// [H, out_rows, 128] array, so a caller can place video and text tokens of separate projections in one
+// sequence.  HBM-bound: 2 * 256 bytes per (token, head).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) qk_prep_heads_kernel(const uint4* __restrict__ x, const float* __restrict__ weight,
+                                                            float eps, const float* __restrict__ cosv,
+                                                            const float* __restrict__ sinv, int64_t S, int H,
+                                                            int64_t rope_rows, uint4* __restrict__ out, int64_t out_rows,
+                                                            int64_t out_row0) {
+  const int64_t item = (int64_t)blockIdx.x * 16 + threadIdx.x / 16;
+  const int sub = threadIdx.x % 16;
+  const bool live = item < S * H;
+  const int64_t s = live ? item / H : 0;
+  const int h = live ? (int)(item % H) : 0;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (live) v = __ldg(x + item * 16 + sub);
+  const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v);
+  float y[8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    y[2 * e] = __low2float(hv[e]);
+    y[2 * e + 1] = __high2float(hv[e]);
+  }
+  if (weight) {
+    float sum = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum = fmaf(y[e], y[e], sum);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float rstd = rsqrtf(sum / (float)kHeadDim + eps);
+    const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + sub * 8));
+    const float4 w1 = __ldg(reinterpret_cast<const float4*>(weight + sub * 8 + 4));
+    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = bf16_round(__fmul_rn(__fmul_rn(y[e], rstd), w[e]));
+  }
+  if (cosv && live && s < rope_rows) {
+    const float* cb = cosv + s * kHeadDim + sub * 8;
+    const float* sb = sinv + s * kHeadDim + sub * 8;
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cb)), c1 = __ldg(reinterpret_cast<const float4*>(cb + 4));
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sb)), s1 = __ldg(reinterpret_cast<const float4*>(sb + 4));
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      o[e] = fmaf(-y[e + 1], sn[e], __fmul_rn(y[e], c[e]));
+      o[e + 1] = fmaf(y[e], sn[e + 1], __fmul_rn(y[e + 1], c[e + 1]));
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = o[e];
+  }
+  if (live) {
+    uint4 r;
+    __nv_bfloat162* hr = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) hr[e] = __floats2bfloat162_rn(y[2 * e], y[2 * e + 1]);
+    out[((int64_t)h * out_rows + out_row0 + s) * 16 + sub] = r;
+  }
+}
+
+cudaError_t launch_qk_prep_heads(const void* x, const float* weight, float eps, const float* cosv, const float* sinv, int64_t S,
+                                 int H, int64_t rope_rows, void* out, int64_t out_rows, int64_t out_row0, cudaStream_t st) {
+  qk_prep_heads_kernel<<<(unsigned)ceil_div64(S * H, 16), 256, 0, st>>>((const uint4*)x, weight, eps, cosv, sinv, S, H, rope_rows,
+                                                                      (uint4*)out, out_rows, out_row0);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
 }  // namespace svoo

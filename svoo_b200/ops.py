@@ -334,6 +334,38 @@ def qk_prep(x: torch.Tensor, heads: int, weight: Optional[torch.Tensor] = None, 
     return out
 
 
+def qk_prep_heads(x: torch.Tensor, heads: int, weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                  cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None, rope_rows: Optional[int] = None,
+                  out: Optional[torch.Tensor] = None, out_row0: int = 0) -> torch.Tensor:
+    """HunyuanVideo's producer in one pass: x [S, H*128] bf16 -> rows [out_row0, out_row0 + S) of
+    out [H, rows, 128] with the RMS norm over the 128 values of every (token, head) (weight [128]),
+    the interleaved-pair rotary embedding of the first `rope_rows` tokens (cos, sin [>= rope_rows, 128]) and
+    the head transpose.  weight / cos None skip that part."""
+    _need_cuda(x)
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.shape[1] != heads * 128:
+        raise ValueError("x must be contiguous bf16 [S, H*128]")
+    S = x.shape[0]
+    w = None if weight is None else weight.detach().to(device=x.device, dtype=torch.float32).contiguous()
+    if w is not None and w.numel() != 128:
+        raise ValueError("weight must have 128 entries")
+    rr = 0
+    c = s_ = None
+    if cos is not None:
+        rr = S if rope_rows is None else int(rope_rows)
+        c = cos.to(device=x.device, dtype=torch.float32).reshape(-1, 128).contiguous()
+        s_ = sin.to(device=x.device, dtype=torch.float32).reshape(-1, 128).contiguous()
+        if c.shape[0] < rr or s_.shape[0] < rr:
+            raise ValueError("cos / sin need at least rope_rows rows")
+    if out is None:
+        out = torch.empty(heads, out_row0 + S, 128, dtype=torch.bfloat16, device=x.device)
+    if out.dim() != 3 or out.shape[0] != heads or out.shape[2] != 128 or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be contiguous bf16 [H, rows, 128]")
+    check(LIB.svoo_b200_qk_prep_heads(x.data_ptr(), 0 if w is None else w.data_ptr(), float(eps),
+                                      0 if c is None else c.data_ptr(), 0 if s_ is None else s_.data_ptr(), S, heads, 128, rr,
+                                      out.data_ptr(), out.shape[1], int(out_row0), _stream()), "qk_prep_heads")
+    return out
+
+
 def layer(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_init_idx: torch.Tensor, k_init_idx: torch.Tensor,
           iters: int, top_p: float, preserve: Sequence[int], cap: Sequence[int],
           sm_scale: Optional[float] = None, text: int = 0, prompt: int = 0) -> torch.Tensor:

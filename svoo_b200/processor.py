@@ -358,6 +358,59 @@ class Hunyuan_SAPAttn_Processor2_0(_SAPBase):
             device=device, dtype=torch.int32)
         return cu, cu.clone(), attention_mask.numel(), attention_mask.numel()
 
+    @staticmethod
+    def _fused_producer_applies(attn, hidden_states, image_rotary_emb) -> bool:
+        """One-pass per-head norm + text-last rotary + head transpose (svoo_b200_qk_prep_heads): one bf16
+        CUDA sample, 128-wide heads, weight-only RMS norms over the head dimension, real (cos, sin) tables."""
+        if not (hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16 and hidden_states.shape[0] == 1):
+            return False
+        if hidden_states.shape[-1] != attn.heads * 128 or attn.heads > 128:
+            return False
+        for name in ("norm_q", "norm_k"):
+            n = getattr(attn, name, None)
+            if n is None or getattr(n, "weight", None) is None or getattr(n, "bias", None) is not None:
+                return False
+            if n.weight.numel() != 128 or not hasattr(n, "eps"):
+                return False
+        for name in ("norm_added_q", "norm_added_k"):
+            n = getattr(attn, name, None)
+            if n is not None and (getattr(n, "weight", None) is None or n.weight.numel() != 128
+                                  or getattr(n, "bias", None) is not None or not hasattr(n, "eps")):
+                return False
+        if image_rotary_emb is not None:
+            if not (isinstance(image_rotary_emb, (tuple, list)) and len(image_rotary_emb) == 2
+                    and all(torch.is_tensor(t) and t.shape[-1] == 128 for t in image_rotary_emb)):
+                return False
+        return True
+
+    def fused_producer(self, attn, hidden_states, encoder_hidden_states, image_rotary_emb):
+        """Replaces get_transpose_qkv + apply_qk_norm + apply_qk_rope_single / _double (+ the text
+        projections and the concatenation of a double-stream block) of the reference
+        (hunyuan10/attention.py:262-290, 460-534) for the case _fused_producer_applies accepts.
+        `hidden_states`: video tokens, followed by the text tokens in a single-stream block."""
+        H = attn.heads
+        cos, sin = (None, None) if image_rotary_emb is None else image_rotary_emb
+        query, key, value = self.get_qkv(attn, hidden_states)
+        S = hidden_states.shape[1]
+        txt = 0 if encoder_hidden_states is None else encoder_hidden_states.shape[1]
+        if getattr(attn, "add_q_proj", None) is None or encoder_hidden_states is None:
+            rope_rows = S - txt if getattr(attn, "add_q_proj", None) is None else S
+            q = ops.qk_prep_heads(query[0].contiguous(), H, attn.norm_q.weight, attn.norm_q.eps, cos, sin, rope_rows)
+            k = ops.qk_prep_heads(key[0].contiguous(), H, attn.norm_k.weight, attn.norm_k.eps, cos, sin, rope_rows)
+            v = ops.qk_prep_heads(value[0].contiguous(), H)
+            return q[None], k[None], v[None]
+        # double-stream block: the text tokens have their own projections and norms and follow the video tokens
+        outs = [torch.empty(H, S + txt, 128, dtype=hidden_states.dtype, device=hidden_states.device) for _ in range(3)]
+        nq, nk = getattr(attn, "norm_added_q", None), getattr(attn, "norm_added_k", None)
+        ops.qk_prep_heads(query[0].contiguous(), H, attn.norm_q.weight, attn.norm_q.eps, cos, sin, S, out=outs[0])
+        ops.qk_prep_heads(key[0].contiguous(), H, attn.norm_k.weight, attn.norm_k.eps, cos, sin, S, out=outs[1])
+        ops.qk_prep_heads(value[0].contiguous(), H, out=outs[2])
+        eq, ek, ev = (proj(encoder_hidden_states)[0].contiguous() for proj in (attn.add_q_proj, attn.add_k_proj, attn.add_v_proj))
+        ops.qk_prep_heads(eq, H, None if nq is None else nq.weight, 0.0 if nq is None else nq.eps, out=outs[0], out_row0=S)
+        ops.qk_prep_heads(ek, H, None if nk is None else nk.weight, 0.0 if nk is None else nk.eps, out=outs[1], out_row0=S)
+        ops.qk_prep_heads(ev, H, out=outs[2], out_row0=S)
+        return tuple(t[None] for t in outs)
+
     def get_o(self, attn, hidden_states, encoder_hidden_states):
         if encoder_hidden_states is not None:
             txt = encoder_hidden_states.shape[1]
@@ -373,11 +426,14 @@ class Hunyuan_SAPAttn_Processor2_0(_SAPBase):
         """Returns (hidden_states, encoder_hidden_states) like the reference (hunyuan10/attention.py:536-575)."""
         if getattr(attn, "add_q_proj", None) is None and encoder_hidden_states is not None:
             hidden_states = torch.cat([hidden_states, encoder_hidden_states], dim=1)
-        query, key, value = self.get_qkv(attn, hidden_states)
-        query, key, value = self.get_transpose_qkv(attn, query, key, value)
-        query, key = self.get_qk_norm(attn, query, key)
-        query, key = self.get_rotary_emb(attn, query, key, image_rotary_emb, encoder_hidden_states)
-        query, key, value = self.get_encoder_condition_and_concat(attn, query, key, value, encoder_hidden_states)
+        if self._fused_producer_applies(attn, hidden_states, image_rotary_emb):
+            query, key, value = self.fused_producer(attn, hidden_states, encoder_hidden_states, image_rotary_emb)
+        else:
+            query, key, value = self.get_qkv(attn, hidden_states)
+            query, key, value = self.get_transpose_qkv(attn, query, key, value)
+            query, key = self.get_qk_norm(attn, query, key)
+            query, key = self.get_rotary_emb(attn, query, key, image_rotary_emb, encoder_hidden_states)
+            query, key, value = self.get_encoder_condition_and_concat(attn, query, key, value, encoder_hidden_states)
         cu_max_seqlens = None if attention_mask is None else self.get_cu_max_seqlen(attention_mask, query.device)
         hidden_states = self.attention_core_logic(query, key, value, timestep, self.layer_idx, cu_max_seqlens)
         hidden_states = hidden_states.transpose(1, 2).flatten(2, 3).to(query.dtype)

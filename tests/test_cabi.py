@@ -77,6 +77,9 @@ def test_host_side_argument_checks(lib):
     assert L.svoo_b200_permute(p, p, 200, 1 << 24, 128, 1 << 24, 1 << 24, p, None) == -2
     assert L.svoo_b200_sort_labels_static(p, 200, 1 << 24, 4, p, p, None) == -2
     assert L.svoo_b200_euclid_assign(p, p, 1, 4, 128, 2000, p, p, 1 << 30, None) == -6
+    assert L.svoo_b200_qk_prep_heads(p, None, 1e-6, None, None, 64, 4, 128, 0, None, 64, 0, None) == -1
+    assert L.svoo_b200_qk_prep_heads(p, None, 1e-6, None, None, 64, 4, 128, 65, p, 64, 0, None) == -2
+    assert L.svoo_b200_qk_prep_heads(p, None, 1e-6, None, None, 64, 4, 128, 0, p, 64, 1, None) == -2
     # error-aware routing entries: argument checks run before any device work
     assert L.svoo_b200_ear_workspace_bytes(2, 4096, 32, 128, None, None) == -1
     assert L.svoo_b200_ear_value_centroids(None, p, 1, 64, 128, 4, 8, p, p, 1 << 30, None) == -1
@@ -143,4 +146,4 @@ def test_header_is_plain_c_and_links(tmp_path):
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0, run.stderr
     version, rc, nbytes = run.stdout.split()
-    assert int(version) == 102 and int(rc) == 0 and int(nbytes) > 0
+    assert int(version) == 103 and int(rc) == 0 and int(nbytes) > 0

@@ -463,6 +463,36 @@ def test_producer_full_width(dev, S, H):
     assert torch.equal(plain, x[0].unflatten(1, (H, 128)).transpose(0, 1))
 
 
+@pytest.mark.parametrize("S,H,txt", [(1000, 24, 256), (77, 3, 0), (17, 1, 5), (4096, 24, 64)])
+def test_per_head_producer(dev, S, H, txt):
+    """HunyuanVideo's producer (per-head RMS norm, rotary embedding of the tokens before the text, head
+    transpose) against the oracle's restatement of the reference's CUDA kernels; every part optional;
+    rows placed at an offset of a longer sequence."""
+    ops = _mods()[0]
+    g = torch.Generator("cpu").manual_seed(43 + S)
+    x = (torch.randn(S, H * 128, generator=g) * 1.7).bfloat16()
+    w = (1.0 + 0.3 * torch.randn(128, generator=g)).bfloat16()
+    ang = torch.rand(S - txt, 64, generator=g) * 6.2831853
+    cos, sin = torch.cos(ang).repeat_interleave(2, -1), torch.sin(ang).repeat_interleave(2, -1)
+    got = ops.qk_prep_heads(x.to(dev), H, w.to(dev), 1e-6, cos.to(dev), sin.to(dev), S - txt).cpu()
+    _ulp_close(got, O.qk_prep_heads(x, w, 1e-6, cos, sin, S - txt, H), 0.999)
+    norm_only = ops.qk_prep_heads(x.to(dev), H, w.to(dev), 1e-6).cpu()
+    _ulp_close(norm_only, O.qk_prep_heads(x, w, 1e-6, None, None, 0, H), 0.999)
+    if txt:                                            # the text rows are normed, not rotated
+        assert torch.equal(got[:, S - txt:], norm_only[:, S - txt:])
+    rope_only = ops.qk_prep_heads(x.to(dev), H, None, 0.0, cos.to(dev), sin.to(dev), S - txt).cpu()
+    _ulp_close(rope_only, O.qk_prep_heads(x, None, 0.0, cos, sin, S - txt, H), 0.999)
+    plain = ops.qk_prep_heads(x.to(dev), H).cpu()
+    assert torch.equal(plain, x.unflatten(1, (H, 128)).transpose(0, 1))
+    # two projections into one sequence: S rows, then 9 more
+    extra = (torch.randn(9, H * 128, generator=g)).bfloat16()
+    out = torch.full((H, S + 9, 128), 7.0, dtype=torch.bfloat16, device=dev)
+    ops.qk_prep_heads(x.to(dev), H, w.to(dev), 1e-6, cos.to(dev), sin.to(dev), S - txt, out=out)
+    ops.qk_prep_heads(extra.to(dev), H, w.to(dev), 1e-6, out=out, out_row0=S)
+    assert torch.equal(out[:, :S].cpu(), got)
+    _ulp_close(out[:, S:].cpu(), O.qk_prep_heads(extra, w, 1e-6, None, None, 0, H), 0.999)
+
+
 # ----------------------------------------------------------------------------------------
 # whole layer
 # ----------------------------------------------------------------------------------------

@@ -368,3 +368,53 @@ def test_dit_step_two_blocks_against_cpu_oracle(dev):
         if step == 2:
             # reuse step: per block the fused producer (3), the map, three gathers and the attention (3)
             assert launched == cfg.num_layers * 10
+
+
+@pytest.mark.parametrize("double_stream", [False, True])
+def test_hunyuan_fused_producer_equals_module_path(dev, double_stream):
+    """The one-pass producer (svoo_b200_qk_prep_heads) hands attention_core_logic the q, k, v that the
+    module-by-module path (to_q/k/v, head transpose, norm modules, rotary helper, text projections and
+    concatenation) produces: single-stream block (text at the end of the sequence, not rotated) and
+    double-stream block (text through add_*_proj and norm_added_*)."""
+    from svoo_b200 import processor
+    P = gu.HUN_PROC
+    hidden, enc, mask = (t.to(dev) for t in gu.hunyuan_inputs())
+    n = hidden.shape[1]
+    g = torch.Generator("cpu").manual_seed(2)
+    ang = torch.rand(n, 64, generator=g) * 6.2831853
+    rot = (torch.cos(ang).repeat_interleave(2, -1).to(dev), torch.sin(ang).repeat_interleave(2, -1).to(dev))
+    attn = gu.make_attn(41, P["heads"], joint=True)
+    if double_stream:
+        dim = P["heads"] * 128
+        for nm in ("add_q_proj", "add_k_proj", "add_v_proj", "to_add_out"):
+            lin = torch.nn.Linear(dim, dim)
+            with torch.no_grad():
+                lin.weight.copy_(torch.randn(dim, dim, generator=g) / dim ** 0.5)
+                lin.bias.copy_(torch.randn(dim, generator=g) * 0.05)
+            setattr(attn, nm, lin.bfloat16())
+        attn.norm_added_q = gu.RMSNormModule(128, 1e-6, (1.0 + 0.2 * torch.randn(128, generator=g)).bfloat16())
+        attn.norm_added_k = gu.RMSNormModule(128, 1e-6, (1.0 + 0.2 * torch.randn(128, generator=g)).bfloat16())
+    attn = attn.to(dev)
+    results = {}
+    for fused in (True, False):
+        cls = _fresh(processor.Hunyuan_SAPAttn_Processor2_0)
+        gu.configure_hunyuan_processor(cls)
+        cls.first_times_fp = 100.0                              # dense branch: the producer is what differs
+        if not fused:
+            cls._fused_producer_applies = staticmethod(lambda *a: False)
+        proc = cls(0)
+        seen = _record_core_inputs(proc)
+        n0 = _launches()
+        with torch.no_grad():
+            y, y_enc = proc(attn, hidden, encoder_hidden_states=enc, attention_mask=mask, image_rotary_emb=rot,
+                            timestep=torch.tensor([500.0], device=dev))
+        results[fused] = (seen, y.cpu(), y_enc.cpu(), _launches() - n0)
+    a, b = results[True], results[False]
+    assert a[3] == (6 if double_stream else 3) and b[3] == 0       # producer launches of the library
+    for t in ("q", "k", "v"):
+        x, r = a[0][t].float(), b[0][t].float()
+        assert x.shape == r.shape == (1, P["heads"], n + enc.shape[1], 128)
+        assert (x == r).float().mean() >= 0.99
+        assert (x - r).abs().max() <= 2.0 ** -5 * max(1.0, float(r.abs().max()))
+    assert torch.equal(a[0]["v"], b[0]["v"])
+    assert (a[1].float() - b[1].float()).abs().max() <= 3e-2 and (a[2].float() - b[2].float()).abs().max() <= 3e-2
