@@ -8,7 +8,8 @@ benchmark's CPU-baseline leg do.
 Parity status: PINNED.  Every function below is checked (tests/test_oracle_golden.py)
 against outputs of the reference's own functions, executed unmodified on CPU
 (Triton kernels under the Triton interpreter) by tests/golden/make_golden.py and
-committed as fixtures under tests/golden/.
+committed as fixtures under tests/golden/.  One exception, parity unpinned: qk_prep_heads
+restates two CUDA kernels of the reference, which cannot be executed without a GPU.
 
 Reference locations restated here (paths inside the reference project):
   * co_cluster_tokens                 svoo/co_clustering.py:2402-2451
