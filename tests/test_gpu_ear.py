@@ -352,3 +352,32 @@ def test_ear_attention_crafted_maps(dev, KC, rows_per_cluster):
     assert (out.cpu().float() - ref.float()).abs().max() <= 2e-2
     assert cosine(out.cpu(), ref) >= 0.999
     assert (lse2.cpu() - lse / math.log(2.0)).abs().max() <= 5e-3
+
+
+def test_reference_named_wrappers(dev):
+    """co_clustering.identify_dynamic_map_estimated, error_estimation_triton, compute_value_centroids and
+    dynamic_block_sparse_prune_fwd_flashinfer with the reference's signatures (4-D tensors, sizes
+    instead of offsets) give what the ops give."""
+    from svoo_b200 import co_clustering as cc
+    from svoo_b200 import ops
+    t = clustered_case(dev, 2, (4, 16, 32), 12, 40, seed=19)
+    H, QC, KC = 2, 12, 40
+    d4 = lambda x: x[None].to(dev)
+    qs4, ks4 = t["qs"][None].int().to(dev), t["ks"][None].int().to(dev)
+    vc4 = cc.compute_value_centroids(d4(t["vp"]), ks4)
+    vc, clog, sc = gpu_scores(dev, t, 0.7)
+    assert torch.equal(vc4[0], vc)
+    sc4 = cc.error_estimation_triton(d4(t["qc"]), d4(t["kc"]), vc4, d4(t["kp"]), d4(t["vp"]), qs4, ks4, None, 0.7)
+    assert sc4.shape == (1, H, QC, KC) and torch.equal(sc4[0], sc)
+    ratio = [0.1, 0.05]
+    m4 = cc.identify_dynamic_map_estimated(d4(t["qp"]), d4(t["kp"]), d4(t["vp"]), qs4, ks4, d4(t["qc"]), d4(t["kc"]), vc4,
+                                           top_p=0.5, gamma=0.7, min_kc_ratio=ratio)
+    pres, bud = cc.ear_limits(KC, H, ratio)
+    assert (pres, bud) == E.ratio_lengths(KC, H, ratio)
+    m = ops.ear_select_blocks(clog, sc, t["q_off"].int().to(dev), t["k_off"].int().to(dev), 0.5, pres, bud)
+    assert m4.dtype == torch.bool and torch.equal(m4[0].to(torch.uint8), m)
+    o4 = cc.dynamic_block_sparse_prune_fwd_flashinfer(d4(t["qp"]), d4(t["kp"]), d4(t["vp"]), d4(t["kc"]), vc4, m4, qs4, ks4,
+                                                      is_cpu=False)
+    k_ext, v_ext = _ext(dev, t["kp"], t["kc"]), _ext(dev, t["vp"], vc.cpu())
+    o = ops.sparse_attn_ear(t["qp"].to(dev), k_ext, v_ext, m, t["q_off"].int().to(dev), t["k_off"].int().to(dev))
+    assert o4.shape == (1, H, t["qp"].shape[1], 128) and torch.equal(o4[0], o)
