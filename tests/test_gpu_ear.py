@@ -60,7 +60,8 @@ def gpu_scores(dev, t, gamma):
 
 
 @pytest.mark.parametrize("H,grid,num_q,num_k,empty", [(3, (4, 16, 32), 20, 70, (0, 5)), (2, (8, 32, 60), 100, 500, ()),
-                                                      (2, (3, 16, 20), 100, 500, ()), (1, (2, 16, 16), 5, 9, ())])
+                                                      (2, (3, 16, 20), 100, 500, ()), (1, (2, 16, 16), 5, 9, ()),
+                                                      (1, (8, 32, 60), 256, 1024, (7,))])
 def test_value_centroids_logits_scores(dev, H, grid, num_q, num_k, empty):
     t = clustered_case(dev, H, grid, num_q, num_k, seed=31 + num_k, empty_k=empty)
     vc, clog, sc = gpu_scores(dev, t, 1.0)
@@ -104,7 +105,8 @@ def _ext(dev, perm, cen):
 
 @pytest.mark.parametrize("H,grid,num_q,num_k,top_p,ratio,empty", [
     (3, (4, 16, 32), 20, 70, 0.5, 0.05, (0, 5)), (2, (3, 16, 20), 100, 500, 0.6, [0.07, 0.2], ()),
-    (1, (2, 16, 16), 5, 9, 0.3, 0.0, ()), (2, (5, 16, 24), 7, 300, 0.4, 0.02, (3,))])
+    (1, (2, 16, 16), 5, 9, 0.3, 0.0, ()), (2, (5, 16, 24), 7, 300, 0.4, 0.02, (3,)),
+    (1, (8, 32, 60), 256, 1024, 0.3, 0.05, ())])
 def test_ear_attention_matches_oracle(dev, H, grid, num_q, num_k, top_p, ratio, empty):
     from svoo_b200 import ops
     t = clustered_case(dev, H, grid, num_q, num_k, seed=5 + num_k, empty_k=empty)
