@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define SVOO_B200_VERSION 103
+#define SVOO_B200_VERSION 104
 
 enum {
   SVOO_OK = 0,
@@ -236,6 +236,15 @@ int svoo_b200_sparse_attn_ear(const void* q, const void* k_ext, const void* v_ex
                               const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
                               int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx, float* lse,
                               void* ear_workspace, int64_t ear_workspace_bytes, void* stream);
+
+/* The same with the output rows stored straight into the ranks' sequence shards, as
+ * svoo_b200_sparse_attn_push does for the plain kernel (peer_dst, my_heads, world, n_loc, H as there).
+ * No counterpart in the reference (its EAR mode runs on one GPU). */
+int svoo_b200_sparse_attn_ear_push(const void* q, const void* k_ext, const void* v_ext, const uint8_t* map,
+                                   const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
+                                   int64_t QC, int64_t KC, float sm_scale, void* const* peer_dst, const int32_t* my_heads,
+                                   int32_t world, int64_t n_loc, int64_t H, const int32_t* out_row_idx, void* ear_workspace,
+                                   int64_t ear_workspace_bytes, void* stream);
 
 /* Byte offset, inside a workspace of these sizes, of a 4-word int32 status block that
  * the tensor-core kernels report into.  Word 0 is cleared by svoo_b200_sparse_attn and

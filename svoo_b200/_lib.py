@@ -56,6 +56,9 @@ SIGNATURES = {
                                            c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "svoo_b200_ear_select_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float,
                                             _I32P, _I32P, c_void_p, c_void_p]),
+    "svoo_b200_sparse_attn_ear_push": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                               c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_int32, c_int64,
+                                               c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
     "svoo_b200_sparse_attn_ear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                           c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_int64, c_void_p]),
@@ -78,7 +81,7 @@ SIGNATURES = {
 }
 
 
-VERSION = 103          # SVOO_B200_VERSION of include/svoo_b200.h this binding was written for
+VERSION = 104          # SVOO_B200_VERSION of include/svoo_b200.h this binding was written for
 
 
 class SvooB200Error(RuntimeError):

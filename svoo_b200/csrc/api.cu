@@ -431,11 +431,12 @@ int svoo_b200_ear_select_blocks(const float* c_logits, const float* scores, cons
   return SVOO_OK;
 }
 
-int svoo_b200_sparse_attn_ear(const void* q, const void* k_ext, const void* v_ext, const uint8_t* map,
-                              const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
-                              int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx, float* lse,
-                              void* ear_workspace, int64_t ear_workspace_bytes, void* stream) {
-  if (!q || !k_ext || !v_ext || !map || !q_offsets || !k_offsets || !out || !ear_workspace) return SVOO_ERR_NULL;
+static int sparse_attn_ear_impl(const void* q, const void* k_ext, const void* v_ext, const uint8_t* map,
+                                const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
+                                int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx, float* lse,
+                                void* ear_workspace, int64_t ear_workspace_bytes, void* stream, void* const* peer_dst,
+                                const int32_t* my_heads, int world, int64_t n_loc, int H) {
+  if (!q || !k_ext || !v_ext || !map || !q_offsets || !k_offsets || (!out && !peer_dst) || !ear_workspace) return SVOO_ERR_NULL;
   SVOO_TRY(check_ear(BH, S, D, QC, KC));
   if ((BH * S + BH * KC) > 2147483647LL) return SVOO_ERR_SHAPE;
   if (!aligned16(q) || !aligned16(k_ext) || !aligned16(v_ext) || !aligned16(out) || !aligned16(ear_workspace))
@@ -452,8 +453,33 @@ int svoo_b200_sparse_attn_ear(const void* q, const void* k_ext, const void* v_ex
   SVOO_CUDA(launch_build_qtiles(q_offsets, qtiles, nqtiles, BH, S, QC, 256, st));
   SVOO_CUDA(cudaMemsetAsync(status, 0, 4, st));
   SVOO_CUDA(launch_sparse_attn_tc(q, k_ext, v_ext, out, out_row_idx, qtiles, nqtiles, runs, nruns, status, BH, S, QC, KC,
-                                  sm_scale, nullptr, nullptr, 0, 0, 0, lse, st, map, k_offsets, ear_max_runs(KC)));
+                                  sm_scale, peer_dst, my_heads, world, n_loc, H, lse, st, map, k_offsets, ear_max_runs(KC)));
   return SVOO_OK;
+}
+
+int svoo_b200_sparse_attn_ear(const void* q, const void* k_ext, const void* v_ext, const uint8_t* map,
+                              const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
+                              int64_t QC, int64_t KC, float sm_scale, void* out, const int32_t* out_row_idx, float* lse,
+                              void* ear_workspace, int64_t ear_workspace_bytes, void* stream) {
+  return sparse_attn_ear_impl(q, k_ext, v_ext, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, out, out_row_idx, lse,
+                              ear_workspace, ear_workspace_bytes, stream, nullptr, nullptr, 0, 0, 0);
+}
+
+int svoo_b200_sparse_attn_ear_push(const void* q, const void* k_ext, const void* v_ext, const uint8_t* map,
+                                   const int32_t* q_offsets, const int32_t* k_offsets, int64_t BH, int64_t S, int64_t D,
+                                   int64_t QC, int64_t KC, float sm_scale, void* const* peer_dst, const int32_t* my_heads,
+                                   int32_t world, int64_t n_loc, int64_t H, const int32_t* out_row_idx, void* ear_workspace,
+                                   int64_t ear_workspace_bytes, void* stream) {
+  if (!my_heads) return SVOO_ERR_NULL;
+  SVOO_TRY(check_exchange(peer_dst, world, n_loc, H, D));
+  if (BH < 1 || BH > ceil_div64(H, world) || S != n_loc * world) return SVOO_ERR_SHAPE;
+  bool seen[128] = {};
+  for (int64_t i = 0; i < BH; ++i) {
+    if (my_heads[i] < 0 || my_heads[i] >= H || seen[my_heads[i]]) return SVOO_ERR_SHAPE;
+    seen[my_heads[i]] = true;
+  }
+  return sparse_attn_ear_impl(q, k_ext, v_ext, map, q_offsets, k_offsets, BH, S, D, QC, KC, sm_scale, nullptr, out_row_idx,
+                              nullptr, ear_workspace, ear_workspace_bytes, stream, peer_dst, my_heads, world, n_loc, (int)H);
 }
 
 int svoo_b200_status_offset(int64_t BH, int64_t N, int64_t QC, int64_t KC, int64_t* offset_out) {

@@ -112,8 +112,8 @@ def _ear_layer(q, k, v, c, top_p, min_kc_ratio, gamma, context_length, peer_out,
     1184-1196): permute, value centroids, block scores, budgeted selection, attention with one virtual
     key per pruned cluster.  K and V are permuted straight into the [H*S + H*KC, 128] tensors the
     kernel reads (token rows of all heads, then centroid rows of all heads)."""
-    if context_length or peer_out is not None:
-        raise ValueError("the EAR variant covers video-only self attention on one GPU, as in the reference")
+    if context_length:
+        raise ValueError("the EAR variant covers video-only self attention, as in the reference")
     H, S, D = q.shape
     QC, KC = c.qcentroids.shape[1], c.kcentroids.shape[1]
     if value_ready is not None:
@@ -132,9 +132,11 @@ def _ear_layer(q, k, v, c, top_p, min_kc_ratio, gamma, context_length, peer_out,
     preserve, budget = cc.ear_limits(KC, H, min_kc_ratio)
     m = ops.ear_select_blocks(clog, scores, c.q_offsets, c.k_offsets, top_p, preserve, budget)
     mark("block_map")
-    out = ops.sparse_attn_ear(qp, k_ext, v_ext, m, c.q_offsets, c.k_offsets, D ** -0.5, out_row_idx=c.q_sorted_idx)
+    out = ops.sparse_attn_ear(qp, k_ext, v_ext, m, c.q_offsets, c.k_offsets, D ** -0.5, out_row_idx=c.q_sorted_idx,
+                              peer_out=peer_out)
     mark("attention")
-    out = out.unsqueeze(0)
+    if out is not None:
+        out = out.unsqueeze(0)
     if return_state:
         return out, LayerState(c, m, c.q_offsets, c.k_offsets)
     return out

@@ -470,10 +470,10 @@ def ear_select_blocks(c_logits: torch.Tensor, scores: torch.Tensor, q_offsets: t
 def sparse_attn_ear(q: torch.Tensor, k_ext: torch.Tensor, v_ext: torch.Tensor, block_map_u8: torch.Tensor,
                     q_offsets: torch.Tensor, k_offsets: torch.Tensor, sm_scale: Optional[float] = None,
                     out_row_idx: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                    return_lse: bool = False):
+                    return_lse: bool = False, peer_out=None):
     """EAR forward: q [BH,S,128] in cluster order; k_ext, v_ext [BH*S + BH*KC, 128] = the cluster-ordered
-    rows of all heads followed by the key / value centroid rows of all heads.  Output, out_row_idx and
-    the log2-sum-exp as in sparse_attn."""
+    rows of all heads followed by the key / value centroid rows of all heads.  Output, out_row_idx, the
+    log2-sum-exp and peer_out as in sparse_attn."""
     _need_cuda(q, k_ext, v_ext, block_map_u8, q_offsets, k_offsets)
     BH, S, D = _tokens(q)
     QC, KC = q_offsets.shape[1] - 1, k_offsets.shape[1] - 1
@@ -483,6 +483,14 @@ def sparse_attn_ear(q: torch.Tensor, k_ext: torch.Tensor, v_ext: torch.Tensor, b
         if tuple(t.shape) != (BH * S + BH * KC, HEAD_DIM) or t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise ValueError("k_ext and v_ext must be contiguous bf16 [BH*S + BH*KC, 128]")
     ws = ear_workspace(q.device, BH, S, QC, KC)
+    if peer_out is not None:
+        ptrs, heads, world, n_loc, H = peer_out
+        check(LIB.svoo_b200_sparse_attn_ear_push(q.data_ptr(), k_ext.data_ptr(), v_ext.data_ptr(), block_map_u8.data_ptr(),
+                                                 q_offsets.data_ptr(), k_offsets.data_ptr(), BH, S, D, QC, KC,
+                                                 D ** -0.5 if sm_scale is None else float(sm_scale), ptrs, heads, world, n_loc,
+                                                 H, 0 if out_row_idx is None else out_row_idx.data_ptr(), ws.data_ptr(),
+                                                 ws.numel(), _stream()), "sparse_attn_ear_push")
+        return None
     y = torch.empty_like(q) if out is None else out
     lse = torch.empty(BH, S, dtype=torch.float32, device=q.device) if return_lse else None
     check(LIB.svoo_b200_sparse_attn_ear(q.data_ptr(), k_ext.data_ptr(), v_ext.data_ptr(), block_map_u8.data_ptr(),

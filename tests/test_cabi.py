@@ -146,4 +146,4 @@ def test_header_is_plain_c_and_links(tmp_path):
     run = subprocess.run([str(exe)], capture_output=True, text=True)
     assert run.returncode == 0, run.stderr
     version, rc, nbytes = run.stdout.split()
-    assert int(version) == 103 and int(rc) == 0 and int(nbytes) > 0
+    assert int(version) == 104 and int(rc) == 0 and int(nbytes) > 0

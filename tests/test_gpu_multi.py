@@ -119,6 +119,9 @@ sharded_equals_single(cfg, parts)
 # 2. text tokens after the video tokens (joint attention): the sequence, text included, is split evenly
 cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=2, grid=(7, 30, 52), text_tokens=256, cfg_id=97)
 sharded_equals_single(cfg, parallel.head_partition(2, world), context_length=256, prompt_length=200)
+# 2b. the error-aware routing variant through the peer-store re-shard (3 heads, uneven)
+cfg = dataclasses.replace(synth.CONFIGS["cfg1"], heads=3, grid=(7, 30, 52), top_p=0.3)
+sharded_equals_single(cfg, parallel.head_partition(3, world, synth.head_densities(cfg)), ear_gamma=1.0)
 
 # 3. sequence-parallel DiT step against the one-GPU model (same weights, same initial indices)
 dcfg = wan_dit.WanDiTConfig(num_layers=2, dim=512, heads=4, ffn_dim=1024, text_dim=64, text_len=16, latent=(4, 32, 40))
