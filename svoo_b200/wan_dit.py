@@ -239,7 +239,8 @@ class SequenceParallelWanProcessor(WanAttn_SAPAttn_Processor):
             ratio = [ratio[h] for h in x.parts[x.rank]]
         sparse_attention_layer(query, key, value, num_q_centroids=self.num_q_centroids, num_k_centroids=self.num_k_centroids,
                                kmeans_iters=0, top_p=self.top_p_kmeans, min_kc_ratio=ratio, clustering=c,
-                               value_ready=x.value_ready, peer_out=x.peer_out)
+                               value_ready=x.value_ready, peer_out=x.peer_out,
+                               ear_gamma=self.ear_gamma if self.use_ear else None)
         return x.seq_result()                                  # [S/P, H_all, 128]
 
     def attention_core_logic(self, query, key, value, timestep):
