@@ -383,3 +383,32 @@ def test_reference_named_wrappers(dev):
     k_ext, v_ext = _ext(dev, t["kp"], t["kc"]), _ext(dev, t["vp"], vc.cpu())
     o = ops.sparse_attn_ear(t["qp"].to(dev), k_ext, v_ext, m, t["q_off"].int().to(dev), t["k_off"].int().to(dev))
     assert o4.shape == (1, H, t["qp"].shape[1], 128) and torch.equal(o4[0], o)
+
+
+def test_ear_attention_first_tile_fully_masked(dev):
+    """128 empty key clusters that the map selects, no other cluster selected: the key list has no
+    token, its first tile holds 128 masked centroids (bias -inf), the second the 128 pruned ones."""
+    from svoo_b200 import ops
+    H, QC, KC, rows = 1, 2, 256, 16
+    N = 128 * rows
+    g = torch.Generator("cpu").manual_seed(5)
+    q, k, v = (torch.randn(H, N, 128, generator=g).mul(0.7).bfloat16() for _ in range(3))
+    ks = torch.cat([torch.zeros(H, 128, dtype=torch.int64), torch.full((H, 128), rows, dtype=torch.int64)], 1)
+    qs = torch.tensor([[N // 2, N // 2]] * H, dtype=torch.int64)
+    off = lambda s: torch.cat([torch.zeros(H, 1, dtype=torch.int64), torch.cumsum(s, -1)], 1)
+    q_off, k_off = off(qs), off(ks)
+    mean = lambda t, j: t[0, k_off[0, j]:k_off[0, j + 1]].float().mean(0) if ks[0, j] else torch.zeros(128)
+    kc = torch.stack([mean(k, j) for j in range(KC)])[None].bfloat16()
+    vc = torch.stack([mean(v, j) for j in range(KC)])[None].bfloat16()
+    m = torch.zeros(H, QC, KC, dtype=torch.bool)
+    m[:, 0, :128] = True                               # query cluster 0: the empty clusters only
+    m[:, 1, 100:140] = True                            # query cluster 1: some empty, some real ones
+    k_ext = torch.cat([k.reshape(-1, 128), kc.reshape(-1, 128)]).contiguous().to(dev)
+    v_ext = torch.cat([v.reshape(-1, 128), vc.reshape(-1, 128)]).contiguous().to(dev)
+    out, lse2 = ops.sparse_attn_ear(q.to(dev), k_ext, v_ext, m.to(torch.uint8).to(dev), q_off.int().to(dev), k_off.int().to(dev),
+                                    return_lse=True)
+    assert ops.ear_attention_status(dev, H, N, QC, KC) == 0
+    ref, lse = E.compensated_attention(q, k, v, kc, vc, m, qs, ks)
+    assert torch.isfinite(out.float()).all()
+    assert (out.cpu().float() - ref.float()).abs().max() <= 2e-2
+    assert (lse2.cpu() - lse / math.log(2.0)).abs().max() <= 5e-3
