@@ -129,11 +129,14 @@ def error_scores(qc, k_perm, k_off, q_sizes, k_sizes, c_logits, vn, cvd, vc_sq, 
 def ratio_lengths(KC: int, H: int, min_kc_ratio):
     """(preserve_len, budget_preserve_len) per head, 0 where the ratio is not positive
     (co_clustering.py:1748-1774)."""
-    mn, kind = O._ratio_list(min_kc_ratio, H)
-    if isinstance(min_kc_ratio, torch.Tensor) and min_kc_ratio.numel() == 1:
+    if isinstance(min_kc_ratio, torch.Tensor) and min_kc_ratio.numel() == 1 and H != 1:
         mn, kind = float(min_kc_ratio.item()), "scalar"
-    if isinstance(min_kc_ratio, (list, tuple)) and len(min_kc_ratio) == 1 and H != 1:
+    elif isinstance(min_kc_ratio, (list, tuple)) and len(min_kc_ratio) == 1 and H != 1:
         mn, kind = float(min_kc_ratio[0]), "scalar"
+    elif isinstance(min_kc_ratio, torch.Tensor):
+        mn, kind = O._ratio_list(min_kc_ratio.flatten(), H) if min_kc_ratio.numel() == H else (None, "none")
+    else:
+        mn, kind = O._ratio_list(min_kc_ratio, H)
     if kind == "scalar":
         mn = [mn] * H
     elif kind != "list":

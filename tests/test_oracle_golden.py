@@ -289,3 +289,44 @@ def test_ear_compensated_attention(ear):
     tol = 2e-5 if cfg.dtype == torch.float32 else 2e-2
     np.testing.assert_allclose(out[:, ::step].float().numpy(), z["out_rows"], atol=tol)
     np.testing.assert_allclose(lse[:, ::step].numpy(), z["lse_rows"], atol=1e-4 if cfg.dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("ratio", [0.0, 0.1, 0.05, 1.0, [0.05, 0.2, 0.0], [0.3], torch.tensor([0.07, 0.0, 0.5]),
+                                   torch.tensor(0.25), (0.01, 0.02, 0.9), None, [0.1, 0.2]])
+@pytest.mark.parametrize("KC", [9, 40, 500, 1024])
+def test_ear_limits_host_logic(ratio, KC):
+    """The product's per-head (guaranteed, budget-preserved) cluster counts against the reference's
+    rule, evaluated directly (svoo/co_clustering.py:1748-1774): per-head for H entries, one value for
+    all heads for a scalar / one-element list / one-element tensor, nothing otherwise; counts clamp
+    to KC as the reference's slices do."""
+    from svoo_b200 import co_clustering as cc
+    H = 3
+
+    def reference_rule():
+        per_head = scalar = None
+        r = ratio
+        if isinstance(r, torch.Tensor):
+            if r.numel() == H:
+                per_head = r.to(torch.float32).flatten()
+            elif r.numel() == 1:
+                scalar = float(r.item())
+        elif isinstance(r, (list, tuple)):
+            if len(r) == H:
+                per_head = torch.tensor(r, dtype=torch.float32)
+            elif len(r) == 1:
+                scalar = float(r[0])
+        elif isinstance(r, (int, float)):
+            scalar = float(r)
+        vals = [0.0] * H
+        if per_head is not None:
+            vals = [float(per_head[h].item()) for h in range(H)]
+        elif scalar is not None:
+            vals = [scalar] * H
+        pres = [min(KC, max(1, int(v * KC))) if v > 0 else 0 for v in vals]
+        bud = [min(KC, max(1, int(v * KC * 2))) if v > 0 else 0 for v in vals]
+        return pres, bud
+
+    assert cc.ear_limits(KC, H, ratio) == reference_rule()
+    if not (isinstance(ratio, (list, tuple)) and len(ratio) not in (1, H)) and ratio is not None:
+        pres, bud = E.ratio_lengths(KC, H, ratio)
+        assert ([min(KC, p) for p in pres], [min(KC, b) for b in bud]) == reference_rule()
